@@ -1,0 +1,116 @@
+"""Generate tests/golden/*.npz by running the REFERENCE's own numpy operator reference (tools/opref.py, unmodified) on
+a small seeded synthetic pack.
+
+    python tests/golden/make_golden.py --reference /path/to/reference/checkout
+
+The reference's tools import `exl3_codec` (and convert_trunk_enc also `encode`), lab modules the reference does not
+ship. A scratch IJAH_REF_DIR is built with convert/exl3_codec.py = this repository's oracle/exl3_codec.py and an
+`encode.py` whose encoder-only names raise if called; everything else that runs is the reference's code. The fixtures
+therefore pin the operator semantics (routing, Hadamard placement, scale order, SwiGLU, slot sum, shared expert,
+trunk decode) but not the codec's bit layout, which has no reference-side golden (see oracle/exl3_codec.py).
+
+The pack itself is not stored: tests regenerate it from the seed with ijah_b200.packgen and check the SHA-256 of its
+tensors against the one recorded here, so a drift of the random stream is reported, not silently compared.
+"""
+import argparse
+import hashlib
+import os
+import shutil
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+sys.path.insert(0, str(ROOT))
+from ijah_b200 import packgen  # noqa: E402
+
+SEED = 20261125
+DIMS = dict(hidden=256, inter=128, experts=32, k_expert=5, k_shared=6)
+TOPK = 4
+TRUNK = [dict(layer=0, hidden=256, q_out=512, kv_out=64, K=6), dict(layer=1, hidden=256, q_out=512, kv_out=64, K=8)]
+
+
+def small_pack_tensors():
+    rng = np.random.default_rng(SEED)
+    t = packgen.moe_layer(rng, layer=0, **DIMS)
+    for tr in TRUNK:
+        t.update(packgen.trunk_layer(rng, **tr))
+    return t
+
+
+def tensors_digest(t):
+    h = hashlib.sha256()
+    for name in sorted(t):
+        h.update(name.encode())
+        h.update(np.ascontiguousarray(t[name][1]).tobytes())
+    return h.hexdigest()
+
+
+def inputs():
+    rng = np.random.default_rng(SEED + 1)
+    return rng.standard_normal((4, DIMS["hidden"])).astype(np.float16).astype(np.float32)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    a = ap.parse_args()
+    tmp = Path(tempfile.mkdtemp(prefix="ijah_golden_"))
+    try:
+        (tmp / "ref/convert").mkdir(parents=True)
+        shutil.copy(ROOT / "oracle/exl3_codec.py", tmp / "ref/convert/exl3_codec.py")
+        (tmp / "ref/convert/encode.py").write_text(
+            "def _enc(*a, **k):\n    raise NotImplementedError('encoder-only name; not on the decode path')\n"
+            "block_ldl = block_rms = refit_scales = sample_scale_tiles = _enc\n")
+        tens = small_pack_tensors()
+        pack = packgen.write_pack(tmp / "pack", tens, {"num_experts_per_tok": TOPK}, shards=3, misalign=2)
+        os.environ["IJAH_REF_DIR"] = str(tmp / "ref")
+        os.environ["IJAH_PACK"] = str(pack)
+        sys.path.insert(0, str(Path(a.reference) / "tools"))
+        import opref as O  # the reference's module
+
+        P = O.PackNP()
+        x = inputs()
+        out = dict(seed=np.int64(SEED), digest=np.array(tensors_digest(tens)), x=x, topk=np.int64(TOPK))
+        pre = "language_model.model.layers.0.mlp"
+        Wg = P.tensor(pre + ".gate.weight")
+        logits, p, ids, w = O.moe_route(x, Wg, top_k=TOPK, bf=False)
+        out.update(logits=logits, probs=p, ids=ids.astype(np.int32), weights=w)
+        out["routed"] = O.moe_routed(x, ids, w, P, 0, bf=False)
+        sh = O.shared_expert(x, P, pre, bf=False)
+        for k, v in sh.items():
+            out[k] = np.asarray(v, np.float32)
+        out["block_out"] = (out["routed"] + sh["shared_scale"] * sh["shared_out"]).astype(np.float32)
+        # dense expert weights of two experts (all three projections), subsampled to keep the file small, + sums
+        for e in (int(ids[0, 0]), 31):
+            for proj in ("gate", "up", "down"):
+                W = P.expert(0, proj, e)
+                out[f"W_{proj}_{e}_sub"] = W[::7, ::5].copy()
+                out[f"W_{proj}_{e}_sum"] = np.float64(W.astype(np.float64).sum())
+                inner, suh, svh = P.expert_parts(0, proj, e)
+                out[f"inner_{proj}_{e}_sub"] = inner[::7, ::5].copy()
+        e = int(ids[0, 0])
+        inner, suh, svh = P.expert_parts(0, "gate", e)
+        io = O.exl3_inner_out(x[0], inner, suh)
+        out["gate_inner_out"] = io
+        out["gate_finish"] = O.exl3_finish(io, svh)
+        out["gate_expert_id"] = np.int64(e)
+        # trunk linears (convert_trunk_enc.decode through PackNP.linear): y = x @ W^T, W [out, in]
+        for tr in TRUNK:
+            for proj in ("q", "k", "v", "o"):
+                name = f"language_model.model.layers.{tr['layer']}.self_attn.{proj}_proj"
+                W = P.linear(name)
+                xin = x if W.shape[1] == DIMS["hidden"] else np.tile(x, (1, W.shape[1] // DIMS["hidden"]))
+                out[f"trunk_L{tr['layer']}_{proj}_y"] = O.linear(xin, W, bf=False)
+                out[f"trunk_L{tr['layer']}_{proj}_Wsub"] = W[::5, ::7].copy()
+        np.savez_compressed(HERE / "moe_small.npz", **out)
+        print("wrote", HERE / "moe_small.npz", {k: np.shape(v) for k, v in out.items()})
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+if __name__ == "__main__":
+    main()
