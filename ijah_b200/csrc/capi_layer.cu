@@ -1,0 +1,283 @@
+// C ABI, part 3: the layer object of the reference (models/flash_next/layer.h:226-268) restricted to its MoE block,
+// and the kernel-by-name entry points. Dims come from the pack's tensor shapes (the reference hard-codes 2560 / 640).
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/ijah_b200.h"
+#include "capi_internal.hpp"
+#include "moe_object.hpp"
+
+using namespace ijah;
+
+namespace ijah {
+constexpr int kHC = 4;  // hyper-connection streams (reference models/flash_next/layer.h:17-19)
+
+struct Layer {
+  std::shared_ptr<Pack> pack;  // keeps the mapping alive past ne_pack_close (reference core/capi.mm:105-110)
+  std::unique_ptr<Moe> moe;
+  int rows = 1, H = 0, I = 0, E = 0, k = 0;
+  float *mlp_in = nullptr, *mlp_out = nullptr, *h_mid = nullptr, *h_out = nullptr, *inj = nullptr;
+  std::vector<void *> owned;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  ~Layer() {
+    for (void *p : owned) cudaFree(p);
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+  }
+};
+
+static ne_exl3_weight single(Pack &p, const std::string &pre, int *K) {
+  const TensorInfo *t = nullptr;
+  ne_exl3_weight w{};
+  w.trellis_dev = p.device(pre + ".trellis", &t);
+  IJ_CHECK(t->ndim == 3 && t->dtype == NE_U16 && t->shape[2] % 16 == 0, "%s.trellis: want U16 [in/16][out/16][16K]", pre.c_str());
+  w.in = (int)t->shape[0] * 16; w.out = (int)t->shape[1] * 16; w.K = (int)t->shape[2] / 16;
+  if (K) *K = w.K;
+  const TensorInfo *s = nullptr;
+  w.suh_dev = p.device(pre + ".suh", &s);
+  IJ_CHECK(s->dtype == NE_F16 && (int64_t)(s->nbytes / 2) == w.in, "%s.suh: want F16 [%d]", pre.c_str(), w.in);
+  w.svh_dev = p.device(pre + ".svh", &s);
+  IJ_CHECK(s->dtype == NE_F16 && (int64_t)(s->nbytes / 2) == w.out, "%s.svh: want F16 [%d]", pre.c_str(), w.out);
+  return w;
+}
+
+static ne_exl3_stack stack(Pack &p, const std::string &pre, int E, int in, int out, int *K) {
+  const TensorInfo *t = nullptr;
+  ne_exl3_stack w{};
+  w.trellis_dev = p.device(pre + ".trellis", &t);
+  IJ_CHECK(t->ndim == 4 && t->dtype == NE_U16 && t->shape[0] == E && t->shape[1] * 16 == in && t->shape[2] * 16 == out && t->shape[3] % 16 == 0,
+           "%s.trellis: want U16 [%d][%d][%d][16K]", pre.c_str(), E, in / 16, out / 16);
+  const int k = (int)t->shape[3] / 16;
+  IJ_CHECK(*K == 0 || *K == k, "%s: K%d differs from the other projections (K%d)", pre.c_str(), k, *K);
+  *K = k;
+  const TensorInfo *s = nullptr;
+  w.suh_dev = p.device(pre + ".suh", &s);
+  IJ_CHECK(s->dtype == NE_F16 && (int64_t)(s->nbytes / 2) == (int64_t)E * in, "%s.suh: want F16 [%d][%d]", pre.c_str(), E, in);
+  w.svh_dev = p.device(pre + ".svh", &s);
+  IJ_CHECK(s->dtype == NE_F16 && (int64_t)(s->nbytes / 2) == (int64_t)E * out, "%s.svh: want F16 [%d][%d]", pre.c_str(), E, out);
+  return w;
+}
+
+static int config_top_k(const Pack &p) {
+  try {
+    const Json j = JsonParser(p.config.data(), p.config.size()).parse();
+    if (const Json *v = j.get("num_experts_per_tok")) return (int)v->as_int();
+    if (const Json *t = j.get("text_config"))
+      if (const Json *v = t->get("num_experts_per_tok")) return (int)v->as_int();
+  } catch (...) {
+  }
+  return 10;  // the reference's constant (kernels/fn_moe.metal:17)
+}
+
+static Layer *make_layer(ne_pack *cp, int layer, int rows) {
+  auto pk = pack_from_c(cp);
+  IJ_CHECK(pk != nullptr, "null pack");
+  IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
+  auto L = std::make_unique<Layer>();
+  L->pack = pk;
+  L->rows = rows;
+  const std::string pre = "language_model.model.layers." + std::to_string(layer) + ".mlp.";
+  const TensorInfo *rt = pk->info(pre + "gate.weight");
+  IJ_CHECK(rt && rt->dtype == NE_BF16 && rt->ndim == 2, "layer %d: %sgate.weight (BF16 [experts][hidden]) missing", layer, pre.c_str());
+  ne_moe_desc d{};
+  d.experts = (int)rt->shape[0];
+  d.hidden = (int)rt->shape[1];
+  d.top_k = config_top_k(*pk);
+  d.router_dev = pk->device(pre + "gate.weight");
+  const TensorInfo *gt = pk->info(pre + "switch_mlp.gate_proj.trellis");
+  IJ_CHECK(gt && gt->ndim == 4, "layer %d: routed experts are not EXL3-coded (no %sswitch_mlp.gate_proj.trellis)", layer, pre.c_str());
+  d.inter = (int)gt->shape[2] * 16;
+  d.expert_first = 0;
+  d.expert_count = d.experts;
+  int K = 0;
+  d.gate = stack(*pk, pre + "switch_mlp.gate_proj", d.experts, d.hidden, d.inter, &K);
+  d.up = stack(*pk, pre + "switch_mlp.up_proj", d.experts, d.hidden, d.inter, &K);
+  d.down = stack(*pk, pre + "switch_mlp.down_proj", d.experts, d.inter, d.hidden, &K);
+  d.k_expert = K;
+  if (pk->info(pre + "shared_expert_gate.weight") && pk->info(pre + "shared_expert.gate_proj.trellis")) {
+    d.shared_gate_w_dev = pk->device(pre + "shared_expert_gate.weight");
+    int ks = 0, k2 = 0;
+    d.sh_gate = single(*pk, pre + "shared_expert.gate_proj", &ks);
+    d.sh_up = single(*pk, pre + "shared_expert.up_proj", &k2);
+    IJ_CHECK(ks == k2, "shared expert gate/up use different K");
+    d.sh_down = single(*pk, pre + "shared_expert.down_proj", &k2);
+    IJ_CHECK(ks == k2, "shared expert down uses a different K");
+    IJ_CHECK(d.sh_gate.in == d.hidden && d.sh_gate.out == d.inter && d.sh_down.in == d.inter && d.sh_down.out == d.hidden, "shared expert shape mismatch");
+    d.k_shared = ks;
+  } else {
+    IJ_CHECK(!pk->info(pre + "shared_expert.gate_proj.weight"),
+             "layer %d: the shared expert is 8-bit affine; only EXL3-coded shared experts are supported", layer);
+  }
+  L->H = d.hidden; L->I = d.inter; L->E = d.experts; L->k = d.top_k;
+  L->moe = std::make_unique<Moe>(d, rows);
+  auto al = [&](size_t n) { void *p = nullptr; IJ_CUDA(cudaMalloc(&p, n)); IJ_CUDA(cudaMemset(p, 0, n)); L->owned.push_back(p); return (float *)p; };
+  const size_t R = rows, H = d.hidden;
+  L->mlp_in = al(R * H * 4);
+  L->mlp_out = al(R * H * 4);
+  L->h_mid = al(R * kHC * H * 4);
+  L->h_out = al(R * kHC * H * 4);
+  L->inj = al(R * 2 * kHC * 4);
+  L->moe->h_mid = L->h_mid; L->moe->inj = L->inj; L->moe->h_out = L->h_out; L->moe->HC = kHC;
+  IJ_CUDA(cudaEventCreate(&L->ev0));
+  IJ_CUDA(cudaEventCreate(&L->ev1));
+  return L.release();
+}
+
+struct Named {
+  float *dev;
+  size_t n;
+  bool route;
+};
+static Named named(Layer *L, const std::string &name) {
+  const size_t R = L->rows, H = L->H, I = L->I, E = L->E, k = L->k;
+  Moe &m = *L->moe;
+  if (name == "mlp_in") return {L->mlp_in, R * H, false};
+  if (name == "mlp_out") return {L->mlp_out, R * H, false};
+  if (name == "h_mid") return {L->h_mid, R * kHC * H, false};
+  if (name == "h_out") return {L->h_out, R * kHC * H, false};
+  if (name == "mlp_inj") return {L->inj, R * 2 * kHC, false};
+  if (name == "logits") return {m.logits, R * (E + 1), false};
+  if (name == "route") return {(float *)m.route, R * 2 * k, true};
+  if (name == "shared_gu") return {m.gush, R * 2 * I, false};
+  if (name == "shared_down") return {m.sho, R * H, false};
+  if (name == "experts_gu") return {nullptr, R * k * 2 * I, false};
+  return {nullptr, 0, false};
+}
+}  // namespace ijah
+
+extern "C" {
+
+NE_API ne_fn_layer *ne_fn_layer_create_rows(ne_pack *pack, int layer, int rows) {
+  Layer *l = nullptr;
+  const int rc = c_call([&] { l = make_layer(pack, layer, rows); });
+  return rc == 0 ? reinterpret_cast<ne_fn_layer *>(l) : nullptr;
+}
+NE_API ne_fn_layer *ne_fn_layer_create(ne_pack *pack, int layer) { return ne_fn_layer_create_rows(pack, layer, 1); }
+NE_API void ne_fn_layer_free(ne_fn_layer *l) { delete reinterpret_cast<Layer *>(l); }
+
+NE_API int ne_fn_layer_step(ne_fn_layer *, const float *, float *, double *) {
+  return c_call([&] {
+    fail("ne_fn_layer_step: only the MoE block of the layer is implemented (ne_fn_layer_run_stage(l, 5) or "
+         "ne_fn_layer_run_dispatch(l, 7|8|9)); attention / GDN / hyper-connection stages are not part of this library");
+  });
+}
+
+NE_API int ne_fn_layer_run_stage(ne_fn_layer *l, int block) {
+  return c_call([&] {
+    Layer *L = reinterpret_cast<Layer *>(l);
+    IJ_CHECK(L != nullptr, "null layer");
+    IJ_CHECK(block == 5, "sub-block %d is not implemented (only 5 = Moe: mlp_in, h_mid, mlp_inj -> logits ... h_out)", block);
+    L->moe->forward(L->mlp_in, L->rows, L->mlp_out, 0);
+    IJ_CUDA(cudaStreamSynchronize(0));
+    check_status_word();
+  });
+}
+
+NE_API int ne_fn_layer_run_dispatch(ne_fn_layer *l, int stage) {
+  return c_call([&] {
+    Layer *L = reinterpret_cast<Layer *>(l);
+    IJ_CHECK(L != nullptr, "null layer");
+    IJ_CHECK(stage >= 7 && stage <= 9, "dispatch %d is not implemented (7 moe_router, 8 moe_gateup, 9 moe_down)", stage);
+    L->moe->stage(stage, L->mlp_in, L->rows, L->mlp_out, 0);
+    IJ_CUDA(cudaStreamSynchronize(0));
+    check_status_word();
+  });
+}
+
+NE_API int ne_fn_set_ref_rounding(int on) {
+  return c_call([&] { IJ_CHECK(on == 0, "reference rounding (bf16 points of the MLX goldens) is not implemented; the f32 path is"); });
+}
+
+NE_API int ne_fn_layer_write(ne_fn_layer *l, const char *name, const float *src, int n) {
+  return c_call([&] {
+    Layer *L = reinterpret_cast<Layer *>(l);
+    IJ_CHECK(L && name && src, "null argument");
+    const Named t = named(L, name);
+    IJ_CHECK(t.dev != nullptr, "unknown or read-only intermediate '%s'", name);
+    IJ_CHECK(n >= 0 && (size_t)n <= t.n, "%s: n %d > size %zu", name, n, t.n);
+    IJ_CUDA(cudaMemcpy(t.dev, src, (size_t)n * 4, cudaMemcpyHostToDevice));
+  });
+}
+
+NE_API int ne_fn_layer_read(ne_fn_layer *l, const char *name, float *dst, int n) {
+  int size = -1;
+  const int rc = c_call([&] {
+    Layer *L = reinterpret_cast<Layer *>(l);
+    IJ_CHECK(L && name, "null argument");
+    const Named t = named(L, name);
+    IJ_CHECK(t.n != 0, "unknown intermediate '%s'", name);
+    size = (int)t.n;
+    IJ_CHECK(n <= size, "%s: n %d > size %d", name, n, size);
+    if (!dst || n <= 0) return;
+    if (t.dev == nullptr) {  // experts_gu: k-split partials summed on the host
+      std::vector<float> tmp(t.n);
+      IJ_CHECK(ne_moe_experts_gu(reinterpret_cast<ne_moe *>(L->moe.get()), L->rows, tmp.data()) == 0, "%s", ne_last_error());
+      memcpy(dst, tmp.data(), (size_t)n * 4);
+      return;
+    }
+    IJ_CUDA(cudaMemcpy(dst, t.dev, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  });
+  return rc == 0 ? size : -1;
+}
+
+// Differential timing as the reference does it (models/flash_next/layer.mm:642-681): (T(reps2) - T(reps1)) / (reps2 -
+// reps1), best of 5; with flush_mb > 0 a buffer of that size is overwritten between steps (evicts L2) and its own
+// differential cost is subtracted.
+NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, double *us_per_step, double *us_flush) {
+  return c_call([&] {
+    Layer *L = reinterpret_cast<Layer *>(l);
+    IJ_CHECK(L != nullptr, "null layer");
+    IJ_CHECK(reps2 > reps1 && reps1 >= 1, "bad reps %d %d", reps1, reps2);
+    void *fl = nullptr;
+    const size_t fb = (size_t)std::max(flush_mb, 0) << 20;
+    if (fb) IJ_CUDA(cudaMalloc(&fl, fb));
+    auto chain = [&](int reps, bool layer, bool flush) {
+      double best = 1e30;
+      for (int it = 0; it < 5; it++) {
+        IJ_CUDA(cudaEventRecord(L->ev0, 0));
+        for (int i = 0; i < reps; i++) {
+          if (layer) L->moe->forward(L->mlp_in, L->rows, L->mlp_out, 0);
+          if (flush) IJ_CUDA(cudaMemsetAsync(fl, i & 0xFF, fb, 0));
+        }
+        IJ_CUDA(cudaEventRecord(L->ev1, 0));
+        IJ_CUDA(cudaEventSynchronize(L->ev1));
+        float ms = 0;
+        IJ_CUDA(cudaEventElapsedTime(&ms, L->ev0, L->ev1));
+        best = std::min(best, (double)ms);
+      }
+      return best;
+    };
+    const bool f = fb != 0;
+    const double t1 = chain(reps1, true, f), t2 = chain(reps2, true, f);
+    double ff = 0;
+    if (f) ff = (chain(reps2, false, true) - chain(reps1, false, true)) * 1e3 / (reps2 - reps1);
+    if (fl) cudaFree(fl);
+    if (us_flush) *us_flush = ff;
+    if (us_per_step) *us_per_step = (t2 - t1) * 1e3 / (reps2 - reps1) - ff;
+    check_status_word();
+  });
+}
+
+// Kernels are compiled into the library; the names below are the CUDA kernels that exist. The reference's Metal
+// kernel names (fn_moe_gateup_k5_r1, t6_simd, ...) are reported absent: their argument lists bind Metal buffers of
+// the reference's scratch layout, which this library does not reproduce.
+static const char *kKernels[] = {"stream_gemm_kernel", "moe_router_kernel", "moe_plan_kernel", "moe_combine_kernel",
+                                 "linear_finish_kernel", "dequant_kernel"};
+NE_API int ne_kernel_exists(const char *fn) {
+  if (!fn) return -1;
+  for (const char *k : kKernels)
+    if (strcmp(k, fn) == 0) return 1;
+  return 0;
+}
+NE_API int ne_run_kernel(const char *fn, const ne_fconst *, int, const ne_arg *, int, const uint32_t[3], const uint32_t[3],
+                         uint32_t, int, const char *, double *) {
+  return c_call([&] {
+    fail("ne_run_kernel(%s): kernels of the CUDA build are reached through their operator entry points (ne_exl3_linear, "
+         "ne_exl3_dequant, ne_moe_stage, ne_fn_layer_run_dispatch), not by name with positional Metal-style arguments",
+         fn ? fn : "(null)");
+  });
+}
+
+}  // extern "C"

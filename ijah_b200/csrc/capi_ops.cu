@@ -1,0 +1,243 @@
+// C ABI, part 2: the dimension-explicit operators (include/ijah_b200.h): EXL3 Linear, dequant, MoE block.
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "../../include/ijah_b200.h"
+#include "capi_internal.hpp"
+#include "fn_moe.cuh"
+#include "moe_object.hpp"
+
+using namespace ijah;
+
+namespace ijah {
+
+static void check_weight(const ne_exl3_weight *w) {
+  IJ_CHECK(w && w->trellis_dev && w->suh_dev && w->svh_dev, "null EXL3 weight pointer");
+  IJ_CHECK(((uintptr_t)w->trellis_dev & 15) == 0, "trellis must be 16-byte aligned on the device");
+}
+
+// ------------------------------------------------------------------ MoE object
+Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
+  IJ_CHECK(d.hidden > 0 && d.inter > 0 && d.experts > 0 && d.top_k > 0 && d.top_k <= d.experts, "bad MoE dims");
+  IJ_CHECK(d.expert_first >= 0 && d.expert_count >= 0 && d.expert_first + d.expert_count <= d.experts, "bad expert slice");
+  IJ_CHECK(d.router_dev != nullptr, "null router weights");
+  IJ_CHECK(d.expert_count == 0 || (d.gate.trellis_dev && d.up.trellis_dev && d.down.trellis_dev), "null expert weights");
+  has_shared = d.shared_gate_w_dev != nullptr && d.sh_gate.trellis_dev != nullptr;
+  plan_moe(d.hidden, d.inter, d.experts, d.top_k, d.k_expert, d.k_shared, max_rows, has_shared);  // validates dims
+  const size_t H = d.hidden, I = d.inter, E = d.experts, k = d.top_k, R = max_rows, P = R * k;
+  // worst-case split counts over all row counts: k-tiles / 8
+  const size_t Sg = H / 16 / 8, Sd = I / 16 / 8;
+  auto al = [&](size_t n) { void *p = nullptr; IJ_CUDA(cudaMalloc(&p, std::max<size_t>(n, 16))); IJ_CUDA(cudaMemset(p, 0, std::max<size_t>(n, 16))); owned.push_back(p); return p; };
+  logits = (float *)al(R * (E + 1) * 4);
+  route = (uint32_t *)al(R * 2 * k * 4);
+  plan = (int *)al(PlanView::ints((int)P) * 4);
+  raw_gu = (float *)al(Sg * P * 2 * I * 4);
+  raw_sgu = (float *)al(Sg * R * 2 * I * 4);
+  raw_d = (float *)al(Sd * P * H * 4);
+  raw_sd = (float *)al(Sd * R * H * 4);
+  gush = (float *)al(R * 2 * I * 4);
+  sho = (float *)al(R * H * 4);
+  counter = (unsigned *)al(16);
+  x_stage = (float *)al(R * H * 4);
+  y_stage = (float *)al(R * H * 4);
+  status = device_status_word();
+}
+
+Moe::~Moe() {
+  for (void *p : owned) cudaFree(p);
+}
+
+MoeParams Moe::params(const float *x, int rows, float *y) {
+  IJ_CHECK(rows >= 1 && rows <= max_rows, "rows %d outside 1..%d", rows, max_rows);
+  MoeParams p{};
+  p.H = desc.hidden; p.I = desc.inter; p.E = desc.experts; p.topk = desc.top_k;
+  p.Kx = desc.k_expert; p.Ks = desc.k_shared;
+  p.e0 = desc.expert_first; p.ecount = desc.expert_count;
+  p.rows = rows; p.P = rows * desc.top_k; p.has_shared = has_shared ? 1 : 0;
+  p.router = (const uint16_t *)desc.router_dev;
+  p.sgate = (const uint16_t *)desc.shared_gate_w_dev;
+  auto stack = [](const ne_exl3_stack &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
+  auto single = [](const ne_exl3_weight &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
+  p.gate = stack(desc.gate); p.up = stack(desc.up); p.down = stack(desc.down);
+  p.sgt = single(desc.sh_gate); p.sup = single(desc.sh_up); p.sdn = single(desc.sh_down);
+  p.x = x; p.logits = logits; p.route = route; p.plan = plan;
+  p.raw_gu = raw_gu; p.raw_sgu = raw_sgu; p.raw_d = raw_d; p.raw_sd = raw_sd;
+  p.gush = gush; p.sho = sho; p.y = y; p.counter = counter;
+  const MoeSplits &s = splits(rows);
+  p.S_gu = s.S_gu; p.kc_gu = s.kc_gu; p.S_d = s.S_d; p.kc_d = s.kc_d;
+  p.h_mid = h_mid; p.inj = inj; p.h_out = h_out; p.HC = HC;
+  return p;
+}
+
+const MoeSplits &Moe::splits(int rows) {
+  auto it = split_cache.find(rows);
+  if (it == split_cache.end())
+    it = split_cache.emplace(rows, plan_moe(desc.hidden, desc.inter, desc.experts, desc.top_k, desc.k_expert, desc.k_shared, rows, has_shared)).first;
+  return it->second;
+}
+
+void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t st) {
+  const MoeParams p = params(x, rows, y);
+  const MoeSplits &s = splits(rows);
+  switch (stage_no) {
+    case 7: launch_moe_router(p, true, st); break;
+    case 8: launch_moe_gateup(p, s, status, st); break;
+    case 9: launch_moe_down(p, s, status, st); launch_moe_combine(p, false, st); break;
+    default: fail("bad MoE stage %d (7 router, 8 gate/up, 9 down)", stage_no);
+  }
+  last_rows = rows;
+}
+
+void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
+  const MoeParams p = params(x, rows, y);
+  const MoeSplits &s = splits(rows);
+  launch_moe_router(p, true, st);
+  launch_moe_gateup(p, s, status, st);
+  launch_moe_down(p, s, status, st);
+  launch_moe_combine(p, false, st);
+  last_rows = rows;
+}
+
+void Moe::forward_routed(const float *x, const uint32_t *route_in, int rows, float *y, cudaStream_t st) {
+  MoeParams p = params(x, rows, y);
+  IJ_CUDA(cudaMemcpyAsync(route, route_in, (size_t)rows * 2 * desc.top_k * 4, cudaMemcpyDeviceToDevice, st));
+  p.has_shared = 0;
+  const MoeSplits &s = splits(rows);
+  launch_moe_plan(p, st);
+  launch_moe_gateup(p, s, status, st);
+  launch_moe_down(p, s, status, st);
+  launch_moe_combine(p, true, st);
+  last_rows = rows;
+}
+
+}  // namespace ijah
+
+extern "C" {
+
+NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(w && w->trellis_dev && w_f16_dev, "null argument");
+    launch_dequant(w->trellis_dev, w->in, w->out, w->K, (__half *)w_f16_dev, (cudaStream_t)stream);
+  });
+}
+
+NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream) {
+  return c_call([&] {
+    check_weight(w);
+    IJ_CHECK(x_dev && y_dev, "null activation pointer");
+    const LinearPlan p = plan_linear(w->in, w->out, w->K, rows);
+    float *raw = (float *)device_scratch(p.raw_floats() * sizeof(float));
+    launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, x_dev, y_dev, raw, device_status_word(), (cudaStream_t)stream);
+  });
+}
+
+NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host) {
+  return c_call([&] {
+    check_weight(w);
+    IJ_CHECK(x_host && y_host, "null activation pointer");
+    const LinearPlan p = plan_linear(w->in, w->out, w->K, rows);
+    const size_t xb = (size_t)rows * w->in * 4, yb = (size_t)rows * w->out * 4;
+    char *s = (char *)device_scratch(p.raw_floats() * 4 + xb + yb + 512);
+    float *raw = (float *)s;
+    float *xd = (float *)(s + ((p.raw_floats() * 4 + 255) & ~(size_t)255));
+    float *yd = (float *)((char *)xd + ((xb + 255) & ~(size_t)255));
+    IJ_CUDA(cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, 0));
+    launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, xd, yd, raw, device_status_word(), 0);
+    IJ_CUDA(cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, 0));
+    IJ_CUDA(cudaStreamSynchronize(0));
+  });
+}
+
+NE_API ne_moe *ne_moe_create(const ne_moe_desc *d, int max_rows) {
+  Moe *m = nullptr;
+  const int rc = c_call([&] {
+    IJ_CHECK(d != nullptr, "null ne_moe_desc");
+    m = new Moe(*d, max_rows);
+  });
+  return rc == 0 ? reinterpret_cast<ne_moe *>(m) : nullptr;
+}
+NE_API void ne_moe_free(ne_moe *m) { delete reinterpret_cast<Moe *>(m); }
+
+NE_API int ne_moe_forward(ne_moe *m, const float *x_dev, int rows, float *y_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_dev && y_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->forward(x_dev, rows, y_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_forward_host(ne_moe *m, const float *x_host, int rows, float *y_host) {
+  return c_call([&] {
+    Moe *o = reinterpret_cast<Moe *>(m);
+    IJ_CHECK(o && x_host && y_host, "null argument");
+    IJ_CHECK(rows >= 1 && rows <= o->max_rows, "rows %d outside 1..%d", rows, o->max_rows);
+    const size_t b = (size_t)rows * o->desc.hidden * 4;
+    IJ_CUDA(cudaMemcpyAsync(o->x_stage, x_host, b, cudaMemcpyHostToDevice, 0));
+    o->forward(o->x_stage, rows, o->y_stage, 0);
+    IJ_CUDA(cudaMemcpyAsync(y_host, o->y_stage, b, cudaMemcpyDeviceToHost, 0));
+    IJ_CUDA(cudaStreamSynchronize(0));
+  });
+}
+NE_API int ne_moe_stage(ne_moe *m, int stage, const float *x_dev, int rows, float *y_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_dev && y_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->stage(stage, x_dev, rows, y_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_forward_routed(ne_moe *m, const float *x_dev, const uint32_t *route_dev, int rows, float *y_partial_dev,
+                                 void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_dev && route_dev && y_partial_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->forward_routed(x_dev, route_dev, rows, y_partial_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes) {
+  return c_call([&] {
+    Moe *o = reinterpret_cast<Moe *>(m);
+    IJ_CHECK(o && name && dev && nbytes, "null argument");
+    const size_t H = o->desc.hidden, I = o->desc.inter, E = o->desc.experts, k = o->desc.top_k, R = o->last_rows;
+    const std::string n = name;
+    if (n == "logits") { *dev = o->logits; *nbytes = R * (E + 1) * 4; }
+    else if (n == "route") { *dev = o->route; *nbytes = R * 2 * k * 4; }
+    else if (n == "shared_gu") { *dev = o->gush; *nbytes = R * 2 * I * 4; }
+    else if (n == "shared_down") { *dev = o->sho; *nbytes = R * H * 4; }
+    else if (n == "experts_gu_raw") { *dev = o->raw_gu; *nbytes = (size_t)o->splits((int)R).S_gu * R * k * 2 * I * 4; }
+    else if (n == "plan") { *dev = o->plan; *nbytes = PlanView::ints((int)(R * k)) * 4; }
+    else fail("unknown MoE buffer '%s'", name);
+  });
+}
+NE_API int ne_moe_experts_gu(ne_moe *m, int rows, float *dst_host) {
+  return c_call([&] {
+    Moe *o = reinterpret_cast<Moe *>(m);
+    IJ_CHECK(o && dst_host && rows >= 1 && rows <= o->max_rows, "bad argument");
+    const size_t n = (size_t)rows * o->desc.top_k * 2 * o->desc.inter;
+    const int S = o->splits(rows).S_gu;
+    std::vector<float> tmp(n * S);
+    IJ_CUDA(cudaDeviceSynchronize());
+    IJ_CUDA(cudaMemcpy(tmp.data(), o->raw_gu, tmp.size() * 4, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n; i++) {
+      float a = 0.0f;
+      for (int s = 0; s < S; s++) a += tmp[(size_t)s * n + i];  // split order, as the device sums them
+      dst_host[i] = a;
+    }
+  });
+}
+NE_API int ne_moe_last_bytes(ne_moe *m, int rows, uint64_t *total, uint64_t *gateup, uint64_t *down, int *distinct_experts) {
+  return c_call([&] {
+    Moe *o = reinterpret_cast<Moe *>(m);
+    IJ_CHECK(o && rows >= 1 && rows <= o->max_rows, "bad argument");
+    int nu = 0;
+    IJ_CUDA(cudaDeviceSynchronize());
+    IJ_CUDA(cudaMemcpy(&nu, o->plan, 4, cudaMemcpyDeviceToHost));
+    const uint64_t H = o->desc.hidden, I = o->desc.inter, E = o->desc.experts;
+    const uint64_t lin_x = H * I * o->desc.k_expert / 8, lin_s = H * I * o->desc.k_shared / 8;
+    const uint64_t gu = (uint64_t)nu * 2 * (lin_x + 2 * H + 2 * I) + (o->has_shared ? 2 * (lin_s + 2 * H + 2 * I) : 0);
+    const uint64_t dn = (uint64_t)nu * (lin_x + 2 * I + 2 * H) + (o->has_shared ? lin_s + 2 * I + 2 * H : 0);
+    const uint64_t rt = E * H * 2 + (o->has_shared ? H * 2 : 0);
+    if (gateup) *gateup = gu;
+    if (down) *down = dn;
+    if (total) *total = gu + dn + rt + 2ull * rows * H * 4;
+    if (distinct_experts) *distinct_experts = nu;
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,61 @@
+// Host-side plumbing shared by the C ABI sources: per-thread error text, exception -> return-code wrapper, CUDA checks,
+// and a per-device growable scratch arena. The error convention is the reference's (include/engine.h:3-5 of the
+// reference: int functions return 0 / -1, pointer functions NULL, message in ne_last_error(), per thread).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+
+namespace ijah {
+
+std::string &last_error_ref();
+
+struct Error : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+[[noreturn]] inline void fail(const char *fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  throw Error(buf);
+}
+
+#define IJ_CHECK(cond, ...) \
+  do {                      \
+    if (!(cond)) ::ijah::fail(__VA_ARGS__); \
+  } while (0)
+
+#define IJ_CUDA(expr)                                                                              \
+  do {                                                                                             \
+    cudaError_t e_ = (expr);                                                                       \
+    if (e_ != cudaSuccess) ::ijah::fail("%s: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
+  } while (0)
+
+template <class F>
+int c_call(F &&f) {
+  try {
+    f();
+    return 0;
+  } catch (const std::exception &e) {
+    last_error_ref() = e.what();
+  } catch (...) {
+    last_error_ref() = "unknown error";
+  }
+  return -1;
+}
+
+// Scratch that outlives a call: one arena per device, grown on demand (never shrunk), used by the entry points that
+// take no workspace argument. Not thread-safe across concurrent calls on the same device (as the reference: one engine
+// thread drives the device, server/ne_server.py:8-9).
+void *device_scratch(size_t bytes);
+int *device_status_word();   // zero-initialised int the kernels report bounded-wait failures into
+void check_status_word();    // throws if a kernel reported a failure (reads the word after a stream sync)
+int sm_count();
+
+}  // namespace ijah

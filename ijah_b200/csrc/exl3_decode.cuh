@@ -1,0 +1,113 @@
+// EXL3 trellis tile decode (MCG codebook, window 15) for sm_100a, register level.
+//
+// Format (reference: kernels/ne_common.h:105-161, kernels/trunk6/trunk6.metal:87-127): a 16x16 tile of W' is 8K
+// little-endian u32 words read MSB-first as a tail-biting ring of 256K bits; slot t's codeword is the 15 bits that end
+// at ring bit (t+1)K. Lane l of a warp owns slots 8l..8l+7 = rows (2q, 2q+1, 2q+8, 2q+9) of column c (slots 0-3)
+// and of column c+8 (slots 4-7), q = l & 3, c = l >> 2 -- exactly the per-thread B fragment of two
+// mma.m16n8k16 (k x n = 16 x 8) instructions, so decoded pairs go to the tensor core with no shuffle.
+//
+// A lane's 8 codewords span 15 + 7K bits starting at ring bit (8l+1)K - 15: three words cover it. For K = 5, 6, 7 the
+// start bit inside the first word depends on the lane, so the window is first left-aligned with two funnel shifts;
+// for K = 4 and 8 it is the same for all lanes and every field position is a compile-time constant.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace ijah {
+
+template <int K>
+struct Codec {
+  static_assert(K >= 4 && K <= 8, "EXL3 bits per weight");
+  static constexpr int NW = 8 * K;             // u32 words per tile
+  static constexpr int TOT = 256 * K;          // ring bits
+  static constexpr int TILE_BYTES = 32 * K;
+  static constexpr bool UNIFORM = (8 * K) % 32 == 0;  // K = 4, 8: lane-independent bit offset
+  static constexpr int A0 = (K + TOT - 15) & 31;      // that offset (start bit of lane 0's window inside its word)
+
+  struct Lane {
+    uint32_t o0, o1, o2;  // byte offsets of the window's three words inside the tile
+    uint32_t a;           // start bit inside word 0
+  };
+  static __device__ __forceinline__ Lane lane(int ln) {
+    uint32_t s = (8u * ln + 1u) * K + TOT - 15u;
+    s = s >= (uint32_t)TOT ? s - TOT : s;
+    const uint32_t i0 = s >> 5;
+    const uint32_t i1 = i0 + 1 >= (uint32_t)NW ? i0 + 1 - NW : i0 + 1;
+    const uint32_t i2 = i1 + 1 >= (uint32_t)NW ? i1 + 1 - NW : i1 + 1;
+    return Lane{i0 * 4u, i1 * 4u, i2 * 4u, s & 31u};
+  }
+};
+
+// 15-bit field starting P bits below the MSB of the 96-bit value (w0:w1:w2), P a compile-time constant
+template <int P>
+__device__ __forceinline__ uint32_t field15(uint32_t w0, uint32_t w1, uint32_t w2) {
+  constexpr int wi = P / 32, off = P % 32;
+  const uint32_t hi = wi == 0 ? w0 : (wi == 1 ? w1 : w2);
+  if constexpr (off + 15 <= 32) {
+    if constexpr (off == 17) return hi & 0x7FFFu;
+    if constexpr (off == 0) return hi >> 17;
+    return (hi << off) >> 17;
+  } else {
+    const uint32_t lo = wi == 0 ? w1 : w2;
+    return __funnelshift_l(lo, hi, off) >> 17;
+  }
+}
+
+// two codewords -> half2(value(ca), value(cb)); value = fp16(lo16(r)) + fp16(hi16(r)), r = ((cw * M) & A) ^ X
+__device__ __forceinline__ uint32_t mcg_pair(uint32_t ca, uint32_t cb) {
+  uint32_t ra = ca * 0xCBAC1FEDu, rb = cb * 0xCBAC1FEDu;
+  ra = (ra & 0x8FFF8FFFu) ^ 0x3B603B60u;
+  rb = (rb & 0x8FFF8FFFu) ^ 0x3B603B60u;
+  const uint32_t lo = __byte_perm(ra, rb, 0x5410), hi = __byte_perm(ra, rb, 0x7632);
+  const __half2 s = __hadd2(*reinterpret_cast<const __half2 *>(&lo), *reinterpret_cast<const __half2 *>(&hi));
+  return *reinterpret_cast<const uint32_t *>(&s);
+}
+
+// The lane's 8 weights from its three window words: b[0] = (slot 0, slot 1), b[1] = (2, 3): column c;
+// b[2] = (4, 5), b[3] = (6, 7): column c + 8. `a` = Codec<K>::Lane::a (ignored for K = 4, 8).
+template <int K>
+__device__ __forceinline__ void dec8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t a, uint32_t (&b)[4]) {
+  if constexpr (Codec<K>::UNIFORM) {
+    constexpr int A = Codec<K>::A0;
+    b[0] = mcg_pair(field15<A + 0 * K>(w0, w1, w2), field15<A + 1 * K>(w0, w1, w2));
+    b[1] = mcg_pair(field15<A + 2 * K>(w0, w1, w2), field15<A + 3 * K>(w0, w1, w2));
+    b[2] = mcg_pair(field15<A + 4 * K>(w0, w1, w2), field15<A + 5 * K>(w0, w1, w2));
+    b[3] = mcg_pair(field15<A + 6 * K>(w0, w1, w2), field15<A + 7 * K>(w0, w1, w2));
+  } else {
+    const uint32_t x = __funnelshift_l(w1, w0, a), y = __funnelshift_l(w2, w1, a);
+    b[0] = mcg_pair(field15<0 * K>(x, y, 0u), field15<1 * K>(x, y, 0u));
+    b[1] = mcg_pair(field15<2 * K>(x, y, 0u), field15<3 * K>(x, y, 0u));
+    b[2] = mcg_pair(field15<4 * K>(x, y, 0u), field15<5 * K>(x, y, 0u));
+    b[3] = mcg_pair(field15<6 * K>(x, y, 0u), field15<7 * K>(x, y, 0u));
+  }
+}
+
+// normalised Hadamard of size N (16..128) over a 128-element chunk held by a warp as (lane, lane+32, lane+64, lane+96);
+// butterflies over index bits 0,1,2,... then one multiply by 1/sqrt(N) (reference: kernels/ne_common.h:95-103,
+// kernels/trunk6/trunk6.metal:42-51). Blocks of N < 128 stay inside the chunk.
+__device__ __forceinline__ void fwht_chunk(float (&v)[4], int lane, int N, float scale) {
+#pragma unroll
+  for (int bit = 1; bit < 32; bit <<= 1) {
+    if (bit < N) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float p = __shfl_xor_sync(0xFFFFFFFFu, v[j], bit);
+        v[j] = (lane & bit) == 0 ? v[j] + p : p - v[j];
+      }
+    }
+  }
+  if (N >= 64) {
+    const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+    v[0] = a; v[1] = b; v[2] = c; v[3] = d;
+  }
+  if (N >= 128) {
+    const float a = v[0] + v[2], b = v[1] + v[3], c = v[0] - v[2], d = v[1] - v[3];
+    v[0] = a; v[1] = b; v[2] = c; v[3] = d;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; j++) v[j] *= scale;
+}
+
+__host__ __device__ inline int had_size(int d) { return d % 128 == 0 ? 128 : d % 64 == 0 ? 64 : d % 32 == 0 ? 32 : 16; }
+
+}  // namespace ijah

@@ -1,0 +1,129 @@
+// EXL3 Linear at decode widths: planning, the finisher, the dequantiser, launchers. See exl3_linear.cuh.
+#include <algorithm>
+
+#include "common.hpp"
+#include "exl3_linear.cuh"
+#include "launch.cuh"
+
+namespace ijah {
+
+StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm) {
+  StreamLayout l;
+  l.stage_bytes = SG_KS * SG_WARPS * 32 * Kmax;
+  l.lda = kcmax * 16 + 8;
+  l.arows = std::max(arows, 1);
+  l.stages = 3;
+  const size_t budget = (size_t)(228 / ctas_per_sm - 2) * 1024;
+  const size_t fixed = l.ring_off() + (size_t)(l.arows + 1) * l.lda * 2;
+  IJ_CHECK(fixed + 3 * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory",
+           arows, kcmax);
+  l.stages = (int)std::min<size_t>(12, (budget - fixed) / l.stage_bytes);
+  return l;
+}
+
+// k-split choice: round-robin over a persistent grid; cost = rounds * (k-tiles per unit + a fixed per-unit overhead)
+static void choose_split(int IT, int NG, int kal, int kcap, int grid, int *S, int *kc) {
+  long best = -1;
+  for (int c = kal; c <= std::max(kal, std::min(IT, kcap)); c += kal) {
+    const int s = (IT + c - 1) / c;
+    const long rounds = ((long)NG * s + grid - 1) / grid;
+    const long cost = rounds * (c + 3) + s / 4;  // tie-break towards fewer splits (less partial traffic)
+    if (best < 0 || cost < best) { best = cost; *S = s; *kc = c; }
+  }
+}
+
+LinearPlan plan_linear(int in, int out, int K, int rows) {
+  IJ_CHECK(in > 0 && out > 0 && in % 16 == 0 && out % 16 == 0, "EXL3 Linear dims must be multiples of 16 (%d -> %d)", in, out);
+  IJ_CHECK(K >= 4 && K <= 8, "EXL3 bits per weight %d outside 4..8", K);
+  IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
+  LinearPlan p{};
+  p.in = in; p.out = out; p.K = K; p.rows = rows;
+  p.IT = in / 16; p.OT = out / 16; p.NG = (p.OT + SG_WARPS - 1) / SG_WARPS;
+  p.hi = had_size(in); p.ho = had_size(out);
+  p.MT = rows <= 16 ? 1 : rows <= 32 ? 2 : 4;
+  const int kal = std::max(p.hi / 16, in % 128 == 0 ? 8 : 1);
+  const int kcap = std::max(kal, ((48 * 1024 / (2 * rows)) - 8) / 16 / kal * kal);
+  p.grid = 2 * sm_count();
+  choose_split(p.IT, p.NG, kal, kcap, p.grid, &p.S, &p.kc);
+  p.lay = make_layout(K, p.kc, rows, 2);
+  p.grid = std::min(p.grid, p.NG * p.S);
+  return p;
+}
+
+// y[r][c] = (H_ho(sum_s raw[s][r]))[c] * svh[c]; one warp per (row, 128-column chunk), splits summed in index order
+__global__ void linear_finish_kernel(const float *__restrict__ raw, const __half *__restrict__ svh, float *__restrict__ y,
+                                     int rows, int out, int S, int ho, float hscale) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = blockIdx.x * (blockDim.x >> 5) + warp, r = blockIdx.y;
+  if (chunk * 128 >= out) return;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int c = chunk * 128 + lane + 32 * j;
+    float a = 0.0f;
+    if (c < out)
+      for (int s = 0; s < S; s++) a += raw[((size_t)s * rows + r) * out + c];
+    v[j] = a;
+  }
+  fwht_chunk(v, lane, ho, hscale);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int c = chunk * 128 + lane + 32 * j;
+    if (c < out) y[(size_t)r * out + c] = v[j] * __half2float(svh[c]);
+  }
+}
+
+void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, const void *svh, const float *x, float *y,
+                   float *raw, int *status, cudaStream_t st) {
+  LinearProblem pr;
+  pr.trellis = (const char *)trellis;
+  pr.suh = (const __half *)suh;
+  pr.x = x;
+  pr.raw = raw;
+  pr.in = p.in; pr.out = p.out; pr.K = p.K; pr.rows = p.rows;
+  pr.IT = p.IT; pr.OT = p.OT; pr.NG = p.NG; pr.S = p.S; pr.kc = p.kc; pr.hi = p.hi;
+  pr.hscale = (float)(1.0 / sqrt((double)p.hi));
+  launch_stream(pr, p.MT, p.lay, p.grid, status, st);
+  const int chunks = (p.out + 127) / 128;
+  dim3 grid((chunks + 3) / 4, p.rows);
+  linear_finish_kernel<<<grid, 128, 0, st>>>(raw, (const __half *)svh, y, p.rows, p.out, p.S, p.ho,
+                                            (float)(1.0 / sqrt((double)p.ho)));
+  IJ_CUDA(cudaGetLastError());
+}
+
+// one warp per tile, straight from global memory
+template <int K>
+__global__ void dequant_kernel(const uint32_t *__restrict__ tr, int IT, int OT, __half *__restrict__ w) {
+  const int lane = threadIdx.x & 31;
+  const long tile = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tile >= (long)IT * OT) return;
+  const typename Codec<K>::Lane L = Codec<K>::lane(lane);
+  const char *t = reinterpret_cast<const char *>(tr) + tile * Codec<K>::TILE_BYTES;
+  uint32_t b[4];
+  dec8<K>(*reinterpret_cast<const uint32_t *>(t + L.o0), *reinterpret_cast<const uint32_t *>(t + L.o1),
+          *reinterpret_cast<const uint32_t *>(t + L.o2), L.a, b);
+  const int tk = (int)(tile / OT), tn = (int)(tile % OT), q = lane & 3, c = lane >> 2;
+  const int out = OT * 16;
+  const __half *h = reinterpret_cast<const __half *>(b);
+  const int rows[4] = {2 * q, 2 * q + 1, 2 * q + 8, 2 * q + 9};
+#pragma unroll
+  for (int j = 0; j < 8; j++) w[(size_t)(tk * 16 + rows[j & 3]) * out + tn * 16 + c + 8 * (j >> 2)] = h[j];
+}
+
+void launch_dequant(const void *trellis, int in, int out, int K, __half *w, cudaStream_t st) {
+  IJ_CHECK(in % 16 == 0 && out % 16 == 0 && K >= 4 && K <= 8, "bad dequant shape %d x %d K%d", in, out, K);
+  const int IT = in / 16, OT = out / 16;
+  const long tiles = (long)IT * OT;
+  const int blocks = (int)((tiles + 7) / 8);
+  const uint32_t *tr = (const uint32_t *)trellis;
+  switch (K) {
+    case 4: dequant_kernel<4><<<blocks, 256, 0, st>>>(tr, IT, OT, w); break;
+    case 5: dequant_kernel<5><<<blocks, 256, 0, st>>>(tr, IT, OT, w); break;
+    case 6: dequant_kernel<6><<<blocks, 256, 0, st>>>(tr, IT, OT, w); break;
+    case 7: dequant_kernel<7><<<blocks, 256, 0, st>>>(tr, IT, OT, w); break;
+    default: dequant_kernel<8><<<blocks, 256, 0, st>>>(tr, IT, OT, w); break;
+  }
+  IJ_CUDA(cudaGetLastError());
+}
+
+}  // namespace ijah

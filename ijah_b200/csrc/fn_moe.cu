@@ -1,0 +1,421 @@
+// Decode MoE block kernels. See fn_moe.cuh.
+#include <algorithm>
+#include <cmath>
+
+#include "common.hpp"
+#include "fn_moe.cuh"
+#include "launch.cuh"
+
+namespace ijah {
+
+// =============================================================================================== router + top-k + plan
+// Reference: kernels/fn_moe.metal:26-134 (logits = x . W in fp32 from bf16 weights, shared-gate logit as row E;
+// the last CTA to arrive selects top-k on the logits, ties -> lowest index, w = exp(l - l_max) / sum over the k).
+constexpr int RT_WARPS = 8;
+constexpr int RT_RC = 8;      // activation rows per pass
+constexpr int RT_EMAX = 1024;  // experts the finisher's shared memory covers
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+__device__ void topk_row(const MoeParams &p, int r, float *s, int lane) {
+  const int E = p.E, k = p.topk;
+  for (int i = lane; i < E; i += 32) s[i] = __ldcg(&p.logits[(size_t)r * (E + 1) + i]);
+  __syncwarp();
+  float myv = 0.0f, top = 0.0f;
+  int myi = 0;
+  for (int t = 0; t < k; t++) {
+    float best = -INFINITY;
+    int bi = 0x7FFFFFFF;
+    for (int i = lane; i < E; i += 32) {
+      const float v = s[i];
+      if (v > best || bi == 0x7FFFFFFF) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (t == 0) top = best;
+    if (lane == t) { myv = best; myi = bi; }
+    if ((bi & 31) == lane) s[bi] = -INFINITY;
+    __syncwarp();
+  }
+  const float pr = lane < k ? expf(myv - top) : 0.0f;
+  const float sum = warp_sum(pr);
+  if (lane < k) {
+    p.route[(size_t)r * 2 * k + lane] = (uint32_t)myi;
+    p.route[(size_t)r * 2 * k + k + lane] = __float_as_uint(pr / sum);
+  }
+}
+
+// Distinct local experts of the rows*topk (row, slot) pairs, in expert order, each with its pairs in row order.
+// One CTA; `buf` is >= 16 KB of shared memory.
+__device__ void build_plan_block(const MoeParams &p, unsigned char *buf) {
+  unsigned long long *mask = reinterpret_cast<unsigned long long *>(buf);  // [E] rows that use expert e
+  int *uidx = reinterpret_cast<int *>(buf + 8 * RT_EMAX);                  // [E] index among present experts
+  int *firs = uidx + RT_EMAX;                                              // [E] offset of its pairs
+  const int tid = threadIdx.x, T = blockDim.x, E = p.E, k = p.topk, P = p.P;
+  PlanView pv{p.plan, P};
+  for (int e = tid; e < E; e += T) mask[e] = 0ull;
+  __syncthreads();
+  for (int i = tid; i < P; i += T) {
+    const int r = i / k, e = (int)p.route[(size_t)r * 2 * k + (i - r * k)];
+    if (e >= p.e0 && e < p.e0 + p.ecount) atomicOr(&mask[e], 1ull << r);
+  }
+  __syncthreads();
+  if (tid < 32) {
+    int run_u = 0, run_f = 0;
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + tid;
+      const int c = e < E ? __popcll(mask[e]) : 0, pr = c > 0 ? 1 : 0;
+      int su = pr, sf = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(0xFFFFFFFFu, su, o), b = __shfl_up_sync(0xFFFFFFFFu, sf, o);
+        if (tid >= o) { su += a; sf += b; }
+      }
+      if (e < E) { uidx[e] = run_u + su - pr; firs[e] = run_f + sf - c; }
+      run_u += __shfl_sync(0xFFFFFFFFu, su, 31);
+      run_f += __shfl_sync(0xFFFFFFFFu, sf, 31);
+    }
+    if (tid == 0) *pv.nu() = run_u;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += T) {
+    const int c = __popcll(mask[e]);
+    if (c > 0) {
+      const int u = uidx[e];
+      pv.expert()[u] = e;
+      pv.nrows()[u] = c;
+      pv.first()[u] = firs[e];
+    }
+  }
+  for (int i = tid; i < P; i += T) {
+    const int r = i / k, e = (int)p.route[(size_t)r * 2 * k + (i - r * k)];
+    if (e >= p.e0 && e < p.e0 + p.ecount) pv.pairs()[firs[e] + __popcll(mask[e] & ((1ull << r) - 1ull))] = i;
+  }
+}
+
+__global__ void __launch_bounds__(32 * RT_WARPS) moe_router_kernel(const MoeParams p, int build_plan) {
+  __shared__ __align__(16) float s_log[RT_WARPS][RT_EMAX];
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * RT_WARPS + warp;
+  const int H = p.H, E = p.E;
+  if (row <= E) {
+    const uint16_t *wr = row < E ? p.router + (size_t)row * H : p.sgate;
+    for (int r0 = 0; r0 < p.rows; r0 += RT_RC) {
+      float acc[RT_RC];
+#pragma unroll
+      for (int t = 0; t < RT_RC; t++) acc[t] = 0.0f;
+      if (wr != nullptr) {
+        const uint4 *w4 = reinterpret_cast<const uint4 *>(wr);
+        for (int c = lane; c < H / 8; c += 32) {
+          const uint4 u = __ldg(&w4[c]);
+          const float w0 = __uint_as_float(u.x << 16), w1 = __uint_as_float(u.x & 0xFFFF0000u);
+          const float w2 = __uint_as_float(u.y << 16), w3 = __uint_as_float(u.y & 0xFFFF0000u);
+          const float w4_ = __uint_as_float(u.z << 16), w5 = __uint_as_float(u.z & 0xFFFF0000u);
+          const float w6 = __uint_as_float(u.w << 16), w7 = __uint_as_float(u.w & 0xFFFF0000u);
+#pragma unroll
+          for (int t = 0; t < RT_RC; t++) {
+            if (r0 + t < p.rows) {
+              const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (size_t)(r0 + t) * H) + 2 * c;
+              const float4 a = x4[0], b = x4[1];
+              acc[t] += a.x * w0 + a.y * w1 + a.z * w2 + a.w * w3 + b.x * w4_ + b.y * w5 + b.z * w6 + b.w * w7;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < RT_RC; t++) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && r0 + t < p.rows) p.logits[(size_t)(r0 + t) * (E + 1) + row] = v;
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(p.counter, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int r = warp; r < p.rows; r += RT_WARPS) topk_row(p, r, s_log[warp], lane);
+  __syncthreads();
+  if (build_plan) build_plan_block(p, reinterpret_cast<unsigned char *>(&s_log[0][0]));
+  if (threadIdx.x == 0) *p.counter = 0u;
+}
+
+__global__ void __launch_bounds__(256) moe_plan_kernel(const MoeParams p) {
+  __shared__ __align__(16) unsigned char buf[16 * RT_EMAX];
+  build_plan_block(p, buf);
+}
+
+void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st) {
+  IJ_CHECK(p.E <= RT_EMAX && p.E % 32 == 0 && p.H % 256 == 0 && p.topk <= 32, "router: unsupported dims E %d H %d k %d", p.E, p.H, p.topk);
+  const int grid = (p.E + 1 + RT_WARPS - 1) / RT_WARPS;
+  moe_router_kernel<<<grid, 32 * RT_WARPS, 0, st>>>(p, build_plan ? 1 : 0);
+  IJ_CUDA(cudaGetLastError());
+}
+
+void launch_moe_plan(const MoeParams &p, cudaStream_t st) {
+  moe_plan_kernel<<<1, 256, 0, st>>>(p);
+  IJ_CUDA(cudaGetLastError());
+}
+
+// =============================================================================================== gate / up
+// Unit order: for each distinct expert u: proj (gate, up) x k-split x column group; then the shared expert's.
+struct MoeGateUpProblem {
+  struct Unit : UnitBase {
+    int s, k0, g, proj, shared, e, first;
+  };
+  MoeParams p;
+  int IT, OT, NG, S, kc;
+  float hscale;
+
+  __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + (p.has_shared ? 1 : 0)) * 2 * S * NG; }
+  __device__ Unit unit(int u) const {
+    const PlanView pv{p.plan, p.P};
+    Unit un;
+    const int per = 2 * S * NG, q = u / per, rem = u - q * per;
+    un.proj = rem / (S * NG);
+    un.s = (rem / NG) % S;
+    un.g = rem % NG;
+    un.k0 = un.s * kc;
+    un.kc = min(kc, IT - un.k0);
+    un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
+    un.shared = q >= *pv.nu();
+    const Exl3Stack *w;
+    if (un.shared) {
+      un.e = 0; un.first = 0; un.nrows = p.rows; un.K = p.Ks;
+      w = un.proj ? &p.sup : &p.sgt;
+    } else {
+      un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx;
+      w = un.proj ? &p.up : &p.gate;
+    }
+    const size_t tile = 32u * un.K;
+    un.kstride = (uint32_t)(OT * tile);
+    un.w = w->trellis + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
+    return un;
+  }
+  __device__ void prologue(const Unit &un, __half *A, int lda, int warp, int lane) const {
+    const PlanView pv{p.plan, p.P};
+    const __half *suh = (un.shared ? (un.proj ? p.sup.suh : p.sgt.suh) : (un.proj ? p.up.suh : p.gate.suh)) + (size_t)un.e * p.H;
+    const int n = un.kc * 16, nch = n >> 7;
+    for (int job = warp; job < un.nrows * nch; job += SG_WARPS) {
+      const int i = job / nch, c = (job - i * nch) << 7;
+      const int r = un.shared ? i : pv.pairs()[un.first + i] / p.topk;
+      const float *xr = p.x + (size_t)r * p.H + un.k0 * 16 + c;
+      const __half *sr = suh + un.k0 * 16 + c;
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) v[j] = xr[lane + 32 * j] * __half2float(sr[lane + 32 * j]);
+      fwht_chunk(v, lane, 128, hscale);
+#pragma unroll
+      for (int j = 0; j < 4; j++) A[(size_t)i * lda + c + lane + 32 * j] = __float2half_rn(v[j]);
+    }
+  }
+  __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
+    float *dst;
+    if (un.shared) dst = p.raw_sgu + (((size_t)un.s * p.rows + row) * 2 + un.proj) * p.I;
+    else dst = p.raw_gu + (((size_t)un.s * p.P + PlanView{p.plan, p.P}.pairs()[un.first + row]) * 2 + un.proj) * p.I;
+    *reinterpret_cast<float2 *>(dst + un.g * 128 + col) = make_float2(v0, v1);
+  }
+};
+
+// =============================================================================================== SwiGLU + down
+// A operand (reference kernels/fn_moe.metal:370-384): g = H(raw gate) * svh_g, u = H(raw up) * svh_u,
+// hh = silu(g) * u * suh_down, then H, rounded to fp16.
+struct MoeDownProblem {
+  struct Unit : UnitBase {
+    int s, k0, g, shared, e, first;
+  };
+  MoeParams p;
+  int IT, OT, NG, S, kc;  // IT = I/16, OT = H/16
+  float hscale;
+
+  __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + (p.has_shared ? 1 : 0)) * S * NG; }
+  __device__ Unit unit(int u) const {
+    const PlanView pv{p.plan, p.P};
+    Unit un;
+    const int per = S * NG, q = u / per, rem = u - q * per;
+    un.s = rem / NG;
+    un.g = rem % NG;
+    un.k0 = un.s * kc;
+    un.kc = min(kc, IT - un.k0);
+    un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
+    un.shared = q >= *pv.nu();
+    if (un.shared) { un.e = 0; un.first = 0; un.nrows = p.rows; un.K = p.Ks; }
+    else { un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx; }
+    const size_t tile = 32u * un.K;
+    un.kstride = (uint32_t)(OT * tile);
+    un.w = (un.shared ? p.sdn.trellis : p.down.trellis) + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
+    return un;
+  }
+  __device__ void prologue(const Unit &un, __half *A, int lda, int warp, int lane) const {
+    const PlanView pv{p.plan, p.P};
+    const int I = p.I;
+    const __half *svg = (un.shared ? p.sgt.svh : p.gate.svh) + (size_t)un.e * I;
+    const __half *svu = (un.shared ? p.sup.svh : p.up.svh) + (size_t)un.e * I;
+    const __half *sud = (un.shared ? p.sdn.suh : p.down.suh) + (size_t)un.e * I;
+    const int nch = (un.kc * 16) >> 7;
+    for (int job = warp; job < un.nrows * nch; job += SG_WARPS) {
+      const int i = job / nch, c = (job - i * nch) << 7, o = un.k0 * 16 + c;
+      const float *raw;
+      size_t sstride;
+      int idx;
+      if (un.shared) { idx = i; raw = p.raw_sgu + (size_t)idx * 2 * I; sstride = (size_t)p.rows * 2 * I; }
+      else { idx = pv.pairs()[un.first + i]; raw = p.raw_gu + (size_t)idx * 2 * I; sstride = (size_t)p.P * 2 * I; }
+      float gv[4], uv[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float a = 0.0f, b = 0.0f;
+        for (int s = 0; s < p.S_gu; s++) {
+          a += raw[s * sstride + o + lane + 32 * j];
+          b += raw[s * sstride + I + o + lane + 32 * j];
+        }
+        gv[j] = a; uv[j] = b;
+      }
+      fwht_chunk(gv, lane, 128, hscale);
+      fwht_chunk(uv, lane, 128, hscale);
+      float hh[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int cc = o + lane + 32 * j;
+        gv[j] *= __half2float(svg[cc]);
+        uv[j] *= __half2float(svu[cc]);
+        hh[j] = gv[j] / (1.0f + expf(-gv[j])) * uv[j] * __half2float(sud[cc]);
+      }
+      if (un.shared && un.g == 0) {  // finished shared gate | up, kept for inspection ("shared_gu")
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          p.gush[(size_t)idx * 2 * I + o + lane + 32 * j] = gv[j];
+          p.gush[(size_t)idx * 2 * I + I + o + lane + 32 * j] = uv[j];
+        }
+      }
+      fwht_chunk(hh, lane, 128, hscale);
+#pragma unroll
+      for (int j = 0; j < 4; j++) A[(size_t)i * lda + c + lane + 32 * j] = __float2half_rn(hh[j]);
+    }
+  }
+  __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
+    float *dst;
+    if (un.shared) dst = p.raw_sd + ((size_t)un.s * p.rows + row) * p.H;
+    else dst = p.raw_d + ((size_t)un.s * p.P + PlanView{p.plan, p.P}.pairs()[un.first + row]) * p.H;
+    *reinterpret_cast<float2 *>(dst + un.g * 128 + col) = make_float2(v0, v1);
+  }
+};
+
+// =============================================================================================== combine
+// One warp per (row, 128-column block) (reference kernels/fn_moe.metal:411-451): every slot's raw down output gets
+// H * svh_down * w_k; slots are summed in slot order; + sigmoid(shared-gate logit) * shared down; optional HC write.
+__global__ void __launch_bounds__(128) moe_combine_kernel(const MoeParams p, int routed_only) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blk = blockIdx.x * 4 + warp, r = blockIdx.y;
+  if (blk * 128 >= p.H) return;
+  const int H = p.H, k = p.topk;
+  const float hs = 0.08838834764831845f;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int t = 0; t < k; t++) {
+    const int e = (int)p.route[(size_t)r * 2 * k + t];
+    if (e < p.e0 || e >= p.e0 + p.ecount) continue;
+    const float wk = __uint_as_float(p.route[(size_t)r * 2 * k + k + t]);
+    const float *raw = p.raw_d + (size_t)(r * k + t) * H + blk * 128;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a = 0.0f;
+      for (int s = 0; s < p.S_d; s++) a += raw[(size_t)s * p.P * H + lane + 32 * j];
+      v[j] = a;
+    }
+    fwht_chunk(v, lane, 128, hs);
+    const __half *sv = p.down.svh + (size_t)(e - p.e0) * H + blk * 128;
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[j] += v[j] * __half2float(sv[lane + 32 * j]) * wk;
+  }
+  if (!routed_only && p.has_shared) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a = 0.0f;
+      for (int s = 0; s < p.S_d; s++) a += p.raw_sd[((size_t)s * p.rows + r) * H + blk * 128 + lane + 32 * j];
+      v[j] = a;
+    }
+    fwht_chunk(v, lane, 128, hs);
+    const float sg = 1.0f / (1.0f + expf(-p.logits[(size_t)r * (p.E + 1) + p.E]));
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int c = blk * 128 + lane + 32 * j;
+      v[j] *= __half2float(p.sdn.svh[c]);
+      p.sho[(size_t)r * H + c] = v[j];
+      acc[j] += sg * v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int c = blk * 128 + lane + 32 * j;
+    p.y[(size_t)r * H + c] = acc[j];
+    if (p.h_mid != nullptr)
+      for (int s = 0; s < p.HC; s++)
+        p.h_out[((size_t)r * p.HC + s) * H + c] = p.h_mid[((size_t)r * p.HC + s) * H + c] + acc[j] * p.inj[(size_t)r * 2 * p.HC + s];
+  }
+}
+
+// =============================================================================================== host side
+static void choose_split_moe(int IT, int colgroups, int kcap, int grid, int *S, int *kc) {
+  long best = -1;
+  for (int c = 8; c <= std::min(IT, kcap); c += 8) {
+    const int s = (IT + c - 1) / c;
+    const long rounds = ((long)colgroups * s + grid - 1) / grid;
+    const long cost = rounds * (c + 3) + s / 4;
+    if (best < 0 || cost < best) { best = cost; *S = s; *kc = c; }
+  }
+}
+
+MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool has_shared) {
+  IJ_CHECK(H % 256 == 0 && I % 128 == 0, "MoE dims: hidden %d must be a multiple of 256, intermediate %d of 128", H, I);
+  IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
+  IJ_CHECK(Kx >= 4 && Kx <= 8 && (!has_shared || (Ks >= 4 && Ks <= 8)), "bits per weight outside 4..8");
+  MoeSplits s{};
+  s.MT = rows <= 16 ? 1 : rows <= 32 ? 2 : 4;
+  s.grid = 2 * sm_count();
+  // expected number of distinct experts under uniform routing; any actual count works, this only tunes the k-split
+  const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows)) + (has_shared ? 1 : 0);
+  const int kcap = std::max(8, ((40 * 1024 / (2 * rows)) - 8) / 16 / 8 * 8);
+  choose_split_moe(H / 16, (int)std::lround(nu * 2 * (I / 128)), kcap, s.grid, &s.S_gu, &s.kc_gu);
+  choose_split_moe(I / 16, (int)std::lround(nu * (H / 128)), kcap, s.grid, &s.S_d, &s.kc_d);
+  const int kmax = std::max(Kx, has_shared ? Ks : 0);
+  s.lay_gu = make_layout(kmax, s.kc_gu, rows, 2);
+  s.lay_d = make_layout(kmax, s.kc_d, rows, 2);
+  return s;
+}
+
+void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st) {
+  MoeGateUpProblem pr;
+  pr.p = p;
+  pr.IT = p.H / 16; pr.OT = p.I / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
+  pr.S = s.S_gu; pr.kc = s.kc_gu;
+  pr.hscale = 0.08838834764831845f;
+  launch_stream(pr, s.MT, s.lay_gu, s.grid, status, st);
+}
+
+void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st) {
+  MoeDownProblem pr;
+  pr.p = p;
+  pr.IT = p.I / 16; pr.OT = p.H / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
+  pr.S = s.S_d; pr.kc = s.kc_d;
+  pr.hscale = 0.08838834764831845f;
+  launch_stream(pr, s.MT, s.lay_d, s.grid, status, st);
+}
+
+void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st) {
+  dim3 grid((p.H / 128 + 3) / 4, p.rows);
+  moe_combine_kernel<<<grid, 128, 0, st>>>(p, routed_only ? 1 : 0);
+  IJ_CUDA(cudaGetLastError());
+}
+
+}  // namespace ijah

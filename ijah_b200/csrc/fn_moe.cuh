@@ -1,0 +1,75 @@
+// Decode MoE block on sm_100a: router + top-k, routed gate/up, SwiGLU + down, slot-ordered combine, shared expert.
+// Replaces the reference's fn_moe_router / fn_moe_gateup / fn_moe_down (kernels/fn_moe.metal:26-452) and, for rows > 1,
+// its grouped-by-expert scheduling (kernels/fn_moe.metal:135-241, 692-884): every distinct expert is streamed once and
+// multiplied with all rows that routed to it.
+#pragma once
+#include "exl3_linear.cuh"
+
+namespace ijah {
+
+struct Exl3Stack {
+  const char *trellis;
+  const __half *suh;
+  const __half *svh;
+};
+
+struct MoeParams {
+  int H, I, E, topk, Kx, Ks;
+  int e0, ecount;     // local expert slice
+  int rows;           // live rows of this run
+  int P;              // rows * topk
+  int has_shared;
+  // weights
+  const uint16_t *router;  // bf16 [E][H]
+  const uint16_t *sgate;   // bf16 [H]
+  Exl3Stack gate, up, down;        // [ecount]
+  Exl3Stack sgt, sup, sdn;         // shared expert
+  // activations / scratch (device)
+  const float *x;          // [rows][H]
+  float *logits;           // [rows][E + 1]
+  uint32_t *route;         // [rows][2 topk]
+  int *plan;               // see PlanView
+  float *raw_gu;           // [S_gu][P][2][I]
+  float *raw_sgu;          // [S_gu][rows][2][I]
+  float *raw_d;            // [S_d][P][H]
+  float *raw_sd;           // [S_d][rows][H]
+  float *gush;             // [rows][2 I]   finished shared gate | up
+  float *sho;              // [rows][H]     finished shared down
+  float *y;                // [rows][H]
+  unsigned *counter;
+  // k-splits
+  int S_gu, kc_gu, S_d, kc_d;
+  // optional hyper-connection write (reference kernels/fn_moe.metal:446-450): h_out[r][s][c] = h[r][s][c] + y[r][c] * inj[r][s]
+  const float *h_mid;      // [rows][HC][H] or null
+  const float *inj;        // [rows][2 HC]
+  float *h_out;            // [rows][HC][H]
+  int HC;
+};
+
+// plan[] layout (ints): [0] = number of distinct local experts nu; then four arrays of PMAXU = P entries each:
+// expert id, row count, offset into pairs[], and pairs[] (pair = row * topk + slot) grouped by expert, rows ascending.
+struct PlanView {
+  int *base;
+  int P;
+  __host__ __device__ int *nu() const { return base; }
+  __host__ __device__ int *expert() const { return base + 4; }
+  __host__ __device__ int *nrows() const { return base + 4 + P; }
+  __host__ __device__ int *first() const { return base + 4 + 2 * P; }
+  __host__ __device__ int *pairs() const { return base + 4 + 3 * P; }
+  static size_t ints(int P) { return 4 + 4 * (size_t)P; }
+};
+
+struct MoeSplits {
+  int S_gu, kc_gu, S_d, kc_d, MT;
+  StreamLayout lay_gu, lay_d;
+  int grid;
+};
+MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool has_shared);
+
+void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st);
+void launch_moe_plan(const MoeParams &p, cudaStream_t st);  // plan from an externally supplied route buffer
+void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
+void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
+void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st);
+
+}  // namespace ijah

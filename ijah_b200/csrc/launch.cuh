@@ -1,0 +1,30 @@
+// Host launcher for stream_gemm_kernel instantiations (included by the .cu files that define a problem type).
+#pragma once
+#include "common.hpp"
+#include "stream_gemm.cuh"
+
+namespace ijah {
+
+template <class P, int MT>
+static void launch_stream_mt(const P &prob, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
+  static bool ready = false;  // one flag per (problem, MT) instantiation: opt in to large dynamic shared memory once
+  if (!ready) {
+    IJ_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<P, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    ready = true;
+  }
+  stream_gemm_kernel<P, MT><<<grid, SG_THREADS, lay.total(), st>>>(prob, lay, status);
+  IJ_CUDA(cudaGetLastError());
+}
+
+template <class P>
+void launch_stream(const P &prob, int MT, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
+  IJ_CHECK(lay.stages >= 3 && lay.stages <= 16, "bad ring depth %d", lay.stages);
+  switch (MT) {
+    case 1: launch_stream_mt<P, 1>(prob, lay, grid, status, st); break;
+    case 2: launch_stream_mt<P, 2>(prob, lay, grid, status, st); break;
+    case 4: launch_stream_mt<P, 4>(prob, lay, grid, status, st); break;
+    default: fail("unsupported row tile count %d", MT);
+  }
+}
+
+}  // namespace ijah

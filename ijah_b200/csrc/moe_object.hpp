@@ -1,0 +1,38 @@
+// The object behind ne_moe: weights description, scratch, per-row-count launch plans.
+#pragma once
+#include <map>
+#include <vector>
+
+#include "../../include/ijah_b200.h"
+#include "fn_moe.cuh"
+
+namespace ijah {
+
+struct Moe {
+  ne_moe_desc desc;
+  int max_rows;
+  bool has_shared = false;
+  int last_rows = 1;
+  std::vector<void *> owned;
+  float *logits = nullptr, *raw_gu = nullptr, *raw_sgu = nullptr, *raw_d = nullptr, *raw_sd = nullptr, *gush = nullptr, *sho = nullptr;
+  float *x_stage = nullptr, *y_stage = nullptr;
+  uint32_t *route = nullptr;
+  int *plan = nullptr, *status = nullptr;
+  unsigned *counter = nullptr;
+  // optional hyper-connection write (set by the layer object)
+  const float *h_mid = nullptr, *inj = nullptr;
+  float *h_out = nullptr;
+  int HC = 0;
+  std::map<int, MoeSplits> split_cache;
+
+  Moe(const ne_moe_desc &d, int max_rows);
+  ~Moe();
+  Moe(const Moe &) = delete;
+  MoeParams params(const float *x, int rows, float *y);
+  const MoeSplits &splits(int rows);
+  void stage(int stage_no, const float *x, int rows, float *y, cudaStream_t st);
+  void forward(const float *x, int rows, float *y, cudaStream_t st);
+  void forward_routed(const float *x, const uint32_t *route_in, int rows, float *y, cudaStream_t st);
+};
+
+}  // namespace ijah

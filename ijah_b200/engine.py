@@ -1,0 +1,447 @@
+"""ctypes binding of libijah_b200.so: the host-side mirror of the reference's tools/engine.py (same class and method
+names for the part of the C ABI this library implements: Engine, Buf, Pack, FnLayer) plus the dimension-explicit
+operators of include/ijah_b200.h (Exl3Linear, MoeBlock).
+
+    from ijah_b200 import engine as E
+    eng = E.Engine()                       # loads ijah_b200/libijah_b200.so (NE_LIB overrides, as in the reference)
+    p = eng.pack_open(pack_dir)
+    L = eng.fn_layer(p, 0, rows=4)         # MoE block of layer 0
+    L.write("mlp_in", x); L.run_stage(5); y = L.read("mlp_out")
+
+There is no fallback: if the shared library is missing or a call fails, EngineError is raised. Device memory for the
+operator classes is held in torch CUDA tensors (torch is plumbing here: allocation, streams, torch.distributed).
+"""
+import ctypes as C
+import json
+import os
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = Path(os.environ.get("NE_LIB", HERE / "libijah_b200.so"))
+MAX_DIMS = 8
+DTYPES = {0: "F32", 1: "F16", 2: "BF16", 3: "U8", 4: "U16", 5: "U32", 6: "I32", 7: "I64", 8: "I8", 9: "I16",
+          10: "U64", 11: "F64", 12: "BOOL"}
+NP = {"F32": np.float32, "F16": np.float16, "BF16": np.uint16, "U8": np.uint8, "U16": np.uint16, "U32": np.uint32,
+      "I32": np.int32, "I64": np.int64, "I8": np.int8, "I16": np.int16, "U64": np.uint64, "F64": np.float64,
+      "BOOL": np.uint8}
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 64), ("has_nax", C.c_int), ("has_metal4", C.c_int),
+                ("max_buffer_length", C.c_uint64), ("recommended_working_set", C.c_uint64),
+                ("max_threadgroup_memory", C.c_uint64), ("backend", C.c_char * 16)]
+
+
+class TensorDescC(C.Structure):
+    _fields_ = [("dtype", C.c_int), ("ndim", C.c_int), ("shape", C.c_int64 * MAX_DIMS), ("nbytes", C.c_uint64),
+                ("file", C.c_char_p), ("file_offset", C.c_uint64), ("host", C.c_void_p), ("buf", C.c_void_p),
+                ("buf_offset", C.c_uint64)]
+
+
+class Exl3WeightC(C.Structure):
+    _fields_ = [("trellis", C.c_void_p), ("suh", C.c_void_p), ("svh", C.c_void_p), ("n_in", C.c_int),
+                ("n_out", C.c_int), ("K", C.c_int)]
+
+
+class Exl3StackC(C.Structure):
+    _fields_ = [("trellis", C.c_void_p), ("suh", C.c_void_p), ("svh", C.c_void_p)]
+
+
+class MoeDescC(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("inter", C.c_int), ("experts", C.c_int), ("top_k", C.c_int),
+                ("k_expert", C.c_int), ("k_shared", C.c_int), ("expert_first", C.c_int), ("expert_count", C.c_int),
+                ("router", C.c_void_p), ("shared_gate_w", C.c_void_p), ("gate", Exl3StackC), ("up", Exl3StackC),
+                ("down", Exl3StackC), ("sh_gate", Exl3WeightC), ("sh_up", Exl3WeightC), ("sh_down", Exl3WeightC)]
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+# every symbol include/ijah_engine.h and include/ijah_b200.h declare: (restype, argtypes)
+SIGNATURES = {
+    "ne_abi_version": (C.c_int, []), "ne_last_error": (C.c_char_p, []),
+    "ne_dtype_name": (C.c_char_p, [C.c_int]), "ne_dtype_size": (C.c_int, [C.c_int]),
+    "ne_device_query": (C.c_int, [C.POINTER(DeviceInfo)]),
+    "ne_alloc": (C.c_void_p, [C.c_uint64]), "ne_free": (None, [C.c_void_p]),
+    "ne_buf_size": (C.c_uint64, [C.c_void_p]), "ne_buf_contents": (C.c_void_p, [C.c_void_p]),
+    "ne_buf_gpu_address": (C.c_uint64, [C.c_void_p]),
+    "ne_upload": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "ne_download": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "ne_pack_open": (C.c_void_p, [C.c_char_p]), "ne_pack_close": (None, [C.c_void_p]),
+    "ne_pack_config_json": (C.c_char_p, [C.c_void_p]), "ne_pack_num_tensors": (C.c_int64, [C.c_void_p]),
+    "ne_pack_tensor_name": (C.c_char_p, [C.c_void_p, C.c_int64]),
+    "ne_tensor_info": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(TensorDescC)]),
+    "ne_pack_view_rows": (C.c_void_p, [C.c_void_p, C.c_char_p, C.c_int64, C.c_int64, C.POINTER(C.c_uint64)]),
+    "ne_kernel_exists": (C.c_int, [C.c_char_p]),
+    "ne_run_kernel": (C.c_int, [C.c_char_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                C.c_uint32, C.c_int, C.c_char_p, C.POINTER(C.c_double)]),
+    "ne_fn_layer_create": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "ne_fn_layer_create_rows": (C.c_void_p, [C.c_void_p, C.c_int, C.c_int]),
+    "ne_fn_layer_free": (None, [C.c_void_p]),
+    "ne_fn_layer_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_double)]),
+    "ne_fn_layer_run_stage": (C.c_int, [C.c_void_p, C.c_int]),
+    "ne_fn_layer_run_dispatch": (C.c_int, [C.c_void_p, C.c_int]),
+    "ne_fn_set_ref_rounding": (C.c_int, [C.c_int]),
+    "ne_fn_layer_write": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int]),
+    "ne_fn_layer_read": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int]),
+    "ne_fn_layer_time": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "ne_exl3_dequant": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_void_p]),
+    "ne_exl3_linear": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_exl3_linear_host": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_moe_create": (C.c_void_p, [C.POINTER(MoeDescC), C.c_int]), "ne_moe_free": (None, [C.c_void_p]),
+    "ne_moe_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_moe_stage": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_forward_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "ne_moe_experts_gu": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_moe_last_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
+                                    C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
+    "ne_copy_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "ne_device_wait_status": (C.c_int, []),
+}
+
+
+def load_library(path=None):
+    path = Path(path or LIB)
+    if not path.exists():
+        raise EngineError(f"{path} is not built (run `make -C ijah_b200/csrc` or __graft_entry__.build())")
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        f = getattr(lib, name)  # AttributeError if a declared symbol is not exported
+        f.restype, f.argtypes = res, args
+    return lib
+
+
+class Buf:
+    """An ne_buf handle. owned=False for pack-owned views (never freed)."""
+
+    def __init__(self, eng, ptr, owned=True):
+        self.eng, self.ptr, self.owned = eng, ptr, owned
+
+    @property
+    def size(self):
+        return self.eng.lib.ne_buf_size(self.ptr)
+
+    def contents(self):
+        return self.eng.lib.ne_buf_contents(self.ptr)
+
+    def gpu_address(self):
+        a = self.eng.lib.ne_buf_gpu_address(self.ptr)
+        if not a:
+            raise EngineError(self.eng.last_error())
+        return a
+
+    def upload(self, arr, offset=0):
+        a = np.ascontiguousarray(arr)
+        self.eng._ok(self.eng.lib.ne_upload(self.ptr, offset, a.ctypes.data, a.nbytes), "ne_upload")
+
+    def download(self, dtype=np.float32, shape=None, offset=0):
+        dtype = np.dtype(dtype)
+        n = (self.size - offset) // dtype.itemsize if shape is None else int(np.prod(shape))
+        out = np.empty(n, dtype)
+        self.eng._ok(self.eng.lib.ne_download(self.ptr, offset, out.ctypes.data, out.nbytes), "ne_download")
+        return out.reshape(shape) if shape is not None else out
+
+    def free(self):
+        if self.ptr and self.owned:
+            self.eng.lib.ne_free(self.ptr)
+        self.ptr = None
+
+
+class TensorDesc:
+    def __init__(self, eng, name, d):
+        self.name = name
+        self.dtype = DTYPES.get(d.dtype, str(d.dtype))
+        self.shape = tuple(d.shape[i] for i in range(d.ndim))
+        self.nbytes = d.nbytes
+        self.file = d.file.decode() if d.file else None
+        self.file_offset = d.file_offset
+        self.host_ptr = d.host
+        self.buf = Buf(eng, d.buf, owned=False) if d.buf else None
+        self.buf_offset = d.buf_offset
+
+    def host(self):
+        """numpy view of the read-only file mapping (valid while the pack is open)"""
+        dt = np.dtype(NP[self.dtype])
+        raw = (C.c_char * self.nbytes).from_address(self.host_ptr)
+        return np.frombuffer(raw, dt, self.nbytes // dt.itemsize).reshape(self.shape)
+
+
+class Pack:
+    def __init__(self, eng, path):
+        self.eng = eng
+        self.path = str(Path(path).expanduser())
+        self.ptr = eng.lib.ne_pack_open(self.path.encode())
+        if not self.ptr:
+            raise EngineError(f"ne_pack_open({self.path}): {eng.last_error()}")
+
+    def config(self):
+        return json.loads(self.eng.lib.ne_pack_config_json(self.ptr).decode())
+
+    def names(self):
+        n = self.eng.lib.ne_pack_num_tensors(self.ptr)
+        return [self.eng.lib.ne_pack_tensor_name(self.ptr, i).decode() for i in range(n)]
+
+    def info(self, name):
+        d = TensorDescC()
+        if self.eng.lib.ne_tensor_info(self.ptr, name.encode(), C.byref(d)) != 0:
+            raise KeyError(f"{name}: {self.eng.last_error()}")
+        return TensorDesc(self.eng, name, d)
+
+    def view_rows(self, name, row0, nrows):
+        off = C.c_uint64(0)
+        p = self.eng.lib.ne_pack_view_rows(self.ptr, name.encode(), row0, nrows, C.byref(off))
+        if not p:
+            raise EngineError(self.eng.last_error())
+        return Buf(self.eng, p), off.value
+
+    def close(self):
+        if self.ptr:
+            self.eng.lib.ne_pack_close(self.ptr)
+        self.ptr = None
+
+
+class FnLayer:
+    """The MoE block of one decoder layer behind the reference's layer entry points (f32 host I/O)."""
+
+    def __init__(self, eng, pack, layer, rows=1):
+        self.eng = eng
+        self.ptr = eng.lib.ne_fn_layer_create_rows(pack.ptr, layer, rows)
+        if not self.ptr:
+            raise EngineError(f"ne_fn_layer_create_rows(L{layer}, {rows}): {eng.last_error()}")
+        self.layer, self.rows = layer, rows
+
+    def step(self, h_in=None):
+        ms = C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_layer_step(self.ptr, None, None, C.byref(ms)), "step")
+
+    def run_stage(self, stage):
+        self.eng._ok(self.eng.lib.ne_fn_layer_run_stage(self.ptr, int(stage)), f"run_stage({stage})")
+
+    def run_dispatch(self, stage):
+        self.eng._ok(self.eng.lib.ne_fn_layer_run_dispatch(self.ptr, int(stage)), f"run_dispatch({stage})")
+
+    def size(self, name):
+        n = self.eng.lib.ne_fn_layer_read(self.ptr, name.encode(), None, 0)
+        if n < 0:
+            raise KeyError(f"{name}: {self.eng.last_error()}")
+        return n
+
+    def read(self, name):
+        n = self.size(name)
+        out = np.empty(n, np.float32)
+        if self.eng.lib.ne_fn_layer_read(self.ptr, name.encode(), out.ctypes.data, n) < 0:
+            raise EngineError(self.eng.last_error())
+        return out
+
+    def write(self, name, arr):
+        a = np.ascontiguousarray(arr, np.float32).reshape(-1)
+        self.eng._ok(self.eng.lib.ne_fn_layer_write(self.ptr, name.encode(), a.ctypes.data, a.size), f"write({name})")
+
+    def time(self, reps1=8, reps2=40, flush_mb=0):
+        us, fl = C.c_double(0), C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_layer_time(self.ptr, reps1, reps2, flush_mb, C.byref(us), C.byref(fl)), "time")
+        return us.value, fl.value
+
+    def free(self):
+        if self.ptr:
+            self.eng.lib.ne_fn_layer_free(self.ptr)
+        self.ptr = None
+
+
+class Engine:
+    def __init__(self, lib=None):
+        self.lib = load_library(lib)
+
+    def last_error(self):
+        return self.lib.ne_last_error().decode()
+
+    def _ok(self, rc, what):
+        if rc != 0:
+            raise EngineError(f"{what}: {self.last_error()}")
+
+    def device(self):
+        d = DeviceInfo()
+        self._ok(self.lib.ne_device_query(C.byref(d)), "ne_device_query")
+        return dict(name=d.name.decode(), has_nax=d.has_nax, has_metal4=d.has_metal4,
+                    max_buffer_length=d.max_buffer_length, recommended_working_set=d.recommended_working_set,
+                    max_threadgroup_memory=d.max_threadgroup_memory, backend=d.backend.decode())
+
+    def alloc(self, nbytes):
+        p = self.lib.ne_alloc(nbytes)
+        if not p:
+            raise EngineError(self.last_error())
+        return Buf(self, p)
+
+    def from_numpy(self, arr):
+        a = np.ascontiguousarray(arr)
+        b = self.alloc(a.nbytes)
+        b.upload(a)
+        return b
+
+    def pack_open(self, path):
+        return Pack(self, path)
+
+    def fn_layer(self, pack, layer, rows=1):
+        return FnLayer(self, pack, layer, rows)
+
+    def kernel_exists(self, name):
+        return self.lib.ne_kernel_exists(name.encode()) == 1
+
+
+# ------------------------------------------------------------------ dimension-explicit operators (torch for memory)
+def _torch():
+    import torch
+    return torch
+
+
+def _dev(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(_torch().cuda.current_stream().cuda_stream)
+
+
+def to_device_u16(a, device="cuda"):
+    """numpy uint16 / float16 array -> torch tensor of the same bits on the device"""
+    torch = _torch()
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.float16:
+        return torch.from_numpy(a).to(device)
+    return torch.from_numpy(a.view(np.int16)).to(device)
+
+
+class Exl3Linear:
+    """One EXL3 Linear on the device: y = x @ W through ne_exl3_linear / ne_exl3_dequant"""
+
+    def __init__(self, eng, trellis, suh, svh, device="cuda"):
+        self.eng = eng
+        tr = np.asarray(trellis)
+        assert tr.ndim == 3 and tr.dtype == np.uint16
+        self.n_in, self.n_out, self.K = tr.shape[0] * 16, tr.shape[1] * 16, tr.shape[2] // 16
+        self.t = (to_device_u16(tr, device), to_device_u16(np.asarray(suh, np.float16), device),
+                  to_device_u16(np.asarray(svh, np.float16), device))
+        self.c = Exl3WeightC(self.t[0].data_ptr(), self.t[1].data_ptr(), self.t[2].data_ptr(), self.n_in, self.n_out, self.K)
+
+    def dequant(self):
+        torch = _torch()
+        w = torch.empty((self.n_in, self.n_out), dtype=torch.float16, device=self.t[0].device)
+        self.eng._ok(self.eng.lib.ne_exl3_dequant(C.byref(self.c), _dev(w), _stream()), "ne_exl3_dequant")
+        return w
+
+    def __call__(self, x):
+        torch = _torch()
+        x = x.to(torch.float32).contiguous()
+        rows = x.shape[0]
+        y = torch.empty((rows, self.n_out), dtype=torch.float32, device=x.device)
+        self.eng._ok(self.eng.lib.ne_exl3_linear(C.byref(self.c), _dev(x), rows, _dev(y), _stream()), "ne_exl3_linear")
+        return y
+
+    def forward_host(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty((x.shape[0], self.n_out), np.float32)
+        self.eng._ok(self.eng.lib.ne_exl3_linear_host(C.byref(self.c), x.ctypes.data, x.shape[0], y.ctypes.data),
+                     "ne_exl3_linear_host")
+        return y
+
+
+class MoeBlock:
+    """One MoE block on the device from a packgen-style tensor dict (or any mapping name -> (dtype, array)).
+    expert slice [first, first + count) selects what this rank holds (expert parallel)."""
+
+    def __init__(self, eng, tensors, layer=0, top_k=10, max_rows=16, expert_first=0, expert_count=None, device="cuda"):
+        self.eng = eng
+        pre = f"language_model.model.layers.{layer}.mlp."
+        g = lambda n: np.asarray(tensors[pre + n][1])  # noqa: E731
+        router = g("gate.weight")
+        E, H = router.shape
+        count = E if expert_count is None else expert_count
+        sl = slice(expert_first, expert_first + count)
+        self.keep = []
+
+        def dev(a):
+            t = to_device_u16(a, device)
+            self.keep.append(t)
+            return t.data_ptr()
+
+        d = MoeDescC()
+        tr = g("switch_mlp.gate_proj.trellis")
+        d.hidden, d.inter, d.experts, d.top_k = H, tr.shape[2] * 16, E, top_k
+        d.k_expert = tr.shape[3] // 16
+        d.expert_first, d.expert_count = expert_first, count
+        d.router = dev(router)
+        for name, fld in (("gate", "gate"), ("up", "up"), ("down", "down")):
+            st = Exl3StackC(dev(g(f"switch_mlp.{name}_proj.trellis")[sl]), dev(g(f"switch_mlp.{name}_proj.suh")[sl]),
+                            dev(g(f"switch_mlp.{name}_proj.svh")[sl]))
+            setattr(d, fld, st)
+        if pre + "shared_expert.gate_proj.trellis" in tensors:
+            d.shared_gate_w = dev(g("shared_expert_gate.weight"))
+            for name, fld in (("gate", "sh_gate"), ("up", "sh_up"), ("down", "sh_down")):
+                t = g(f"shared_expert.{name}_proj.trellis")
+                w = Exl3WeightC(dev(t), dev(g(f"shared_expert.{name}_proj.suh")), dev(g(f"shared_expert.{name}_proj.svh")),
+                                t.shape[0] * 16, t.shape[1] * 16, t.shape[2] // 16)
+                setattr(d, fld, w)
+            d.k_shared = d.sh_gate.K
+        self.desc, self.H, self.I, self.E, self.k, self.max_rows = d, H, d.inter, E, top_k, max_rows
+        self.ptr = eng.lib.ne_moe_create(C.byref(d), max_rows)
+        if not self.ptr:
+            raise EngineError(f"ne_moe_create: {eng.last_error()}")
+
+    def forward(self, x, out=None):
+        torch = _torch()
+        rows = x.shape[0]
+        y = torch.empty((rows, self.H), dtype=torch.float32, device=x.device) if out is None else out
+        self.eng._ok(self.eng.lib.ne_moe_forward(self.ptr, _dev(x), rows, _dev(y), _stream()), "ne_moe_forward")
+        return y
+
+    def forward_host(self, x, out=None):
+        """x: numpy or pinned torch CPU float32 [rows, H]; returns numpy (or fills `out`)"""
+        xp = x.data_ptr() if hasattr(x, "data_ptr") else np.ascontiguousarray(x, np.float32).ctypes.data
+        rows = x.shape[0]
+        y = np.empty((rows, self.H), np.float32) if out is None else out
+        yp = y.data_ptr() if hasattr(y, "data_ptr") else y.ctypes.data
+        self.eng._ok(self.eng.lib.ne_moe_forward_host(self.ptr, C.c_void_p(xp), rows, C.c_void_p(yp)), "ne_moe_forward_host")
+        return y
+
+    def stage(self, stage, x, y):
+        self.eng._ok(self.eng.lib.ne_moe_stage(self.ptr, stage, _dev(x), x.shape[0], _dev(y), _stream()), f"ne_moe_stage({stage})")
+
+    def forward_routed(self, x, route, out=None):
+        torch = _torch()
+        rows = x.shape[0]
+        y = torch.empty((rows, self.H), dtype=torch.float32, device=x.device) if out is None else out
+        self.eng._ok(self.eng.lib.ne_moe_forward_routed(self.ptr, _dev(x), _dev(route), rows, _dev(y), _stream()),
+                     "ne_moe_forward_routed")
+        return y
+
+    def buffer(self, name, dtype=np.float32):
+        """host copy of a named intermediate of the last run"""
+        p, n = C.c_void_p(), C.c_uint64()
+        self.eng._ok(self.eng.lib.ne_moe_buffer(self.ptr, name.encode(), C.byref(p), C.byref(n)), f"ne_moe_buffer({name})")
+        out = np.empty(n.value // np.dtype(dtype).itemsize, dtype)
+        self.eng._ok(self.eng.lib.ne_copy_to_host(out.ctypes.data, p, n.value), "ne_copy_to_host")
+        return out
+
+    def route(self, rows):
+        r = self.buffer("route", np.uint32).reshape(rows, 2 * self.k)
+        return r[:, :self.k].astype(np.int64), r[:, self.k:].copy().view(np.float32)
+
+    def experts_gu(self, rows):
+        out = np.empty((rows, self.k, 2, self.I), np.float32)
+        self.eng._ok(self.eng.lib.ne_moe_experts_gu(self.ptr, rows, out.ctypes.data), "ne_moe_experts_gu")
+        return out
+
+    def last_bytes(self, rows):
+        t, g, d, n = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_int()
+        self.eng._ok(self.eng.lib.ne_moe_last_bytes(self.ptr, rows, C.byref(t), C.byref(g), C.byref(d), C.byref(n)), "ne_moe_last_bytes")
+        return dict(total=t.value, gateup=g.value, down=d.value, distinct_experts=n.value)
+
+    def free(self):
+        if self.ptr:
+            self.eng.lib.ne_moe_free(self.ptr)
+        self.ptr = None

@@ -1,0 +1,91 @@
+/* libijah_b200: entry points beyond the reference's engine.h, following its extension rule (reference
+ * include/engine.h:11-12: other components declare their NE_API functions in a header of their own).
+ *
+ * These are the dimension-explicit forms of the hot path: one EXL3 Linear, one MoE block (decode widths), the prefill
+ * grouped GEMM, and the expert-parallel variants. All pointers named *_dev are device pointers, `stream` is a
+ * cudaStream_t passed as void* (NULL = the default stream). Calls that take a stream only enqueue work; the *_host
+ * forms copy host inputs in, run, copy results out and return when everything is done. Errors: 0 / -1 and
+ * ne_last_error(), as in ijah_engine.h.
+ */
+#ifndef IJAH_B200_H
+#define IJAH_B200_H
+
+#include "ijah_engine.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One EXL3-coded Linear y = x @ W, W [in, out] = diag(suh) H W' H diag(svh)
+ * (replaces the reference's t6::Linear, kernels/trunk6/trunk6.h:24-32: trellis U16 [in/16][out/16][16K], suh F16 [in],
+ * svh F16 [out]; K = 4..8 bits per weight). */
+typedef struct {
+  const void *trellis_dev;
+  const void *suh_dev;
+  const void *svh_dev;
+  int in, out, K;
+} ne_exl3_weight;
+
+/* W' (the trellis decoded to its fp16 codebook values, no rotations) as F16 [in][out]: the bit-exact parity surface
+ * of the decoder (reference decoder: kernels/ne_common.h:133-157 dec_mcg/dec8, kernels/trunk6/trunk6.metal:102-127). */
+NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *stream);
+/* y[rows][out] = x[rows][in] @ W, f32 in / f32 out, rows 1..64 (replaces t6::record, kernels/trunk6/trunk6.h:60-79,
+ * kernels t6_simd / t6_prep + t6_nax, kernels/trunk6/trunk6.metal:366-539). Scratch comes from a per-device arena
+ * owned by the library (grown on demand). */
+NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
+NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host);
+
+/* ---- MoE block (router, routed experts, shared expert) at decode widths --------------------------------------
+ * Replaces the three dispatches fn_moe_router / fn_moe_gateup / fn_moe_down of the reference
+ * (kernels/fn_moe.metal:26-452, recorded by models/flash_next/layer.mm:532-564 and layer_t6.mm:191-243). */
+typedef struct {
+  const void *trellis_dev; /* U16 [n_local][in/16][out/16][16K] */
+  const void *suh_dev;     /* F16 [n_local][in] */
+  const void *svh_dev;     /* F16 [n_local][out] */
+} ne_exl3_stack;
+
+typedef struct {
+  int hidden, inter, experts, top_k;
+  int k_expert, k_shared;          /* bits per weight of the routed / shared projections */
+  int expert_first, expert_count;  /* the slice of experts whose weights this object holds (expert parallel);
+                                      single GPU: 0, experts */
+  const void *router_dev;          /* BF16 [experts][hidden], all experts */
+  const void *shared_gate_w_dev;   /* BF16 [hidden]: the sigmoid gate of the shared expert; NULL = no shared expert */
+  ne_exl3_stack gate, up, down;    /* routed experts, local slice */
+  ne_exl3_weight sh_gate, sh_up, sh_down;
+} ne_moe_desc;
+
+typedef struct ne_moe ne_moe;
+NE_API ne_moe *ne_moe_create(const ne_moe_desc *d, int max_rows); /* max_rows 1..64; allocates all scratch */
+NE_API void ne_moe_free(ne_moe *m);
+/* y[rows][hidden] = sum_k w_k expert_k(x) + sigmoid(x . w_sg) shared(x). Enqueues 5 kernels on `stream`. */
+NE_API int ne_moe_forward(ne_moe *m, const float *x_dev, int rows, float *y_dev, void *stream);
+NE_API int ne_moe_forward_host(ne_moe *m, const float *x_host, int rows, float *y_host);
+/* The same in pieces (stage numbers of the reference's ne_fn_layer_run_dispatch: 7 router, 8 gate/up, 9 down). */
+NE_API int ne_moe_stage(ne_moe *m, int stage, const float *x_dev, int rows, float *y_dev, void *stream);
+/* Expert parallel: routes come from outside (route_dev: [rows][2*top_k], ids then f32 weights, global expert ids);
+ * computes only the slots whose expert lies in this object's slice, summed per row in slot order, no shared expert:
+ * y_partial[rows][hidden]. The caller adds the partial sums of all ranks. */
+NE_API int ne_moe_forward_routed(ne_moe *m, const float *x_dev, const uint32_t *route_dev, int rows, float *y_partial_dev,
+                                 void *stream);
+/* Device pointer and size of a named intermediate of the last run: "logits" "route" "shared_gu" "shared_down"
+ * "experts_gu_raw" (per k-split partial products [S][rows*top_k][2][inter]) "plan". */
+NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes);
+/* Sum of k-split partials: experts_gu[rows][top_k][2][inter] f32, the raw inner products before the output Hadamard
+ * (the reference's "experts_gu" buffer). */
+NE_API int ne_moe_experts_gu(ne_moe *m, int rows, float *dst_host);
+/* Algorithmic bytes the last forward had to read (compressed weights of the distinct experts touched + router +
+ * shared expert + scales + activations), for roofline accounting. */
+NE_API int ne_moe_last_bytes(ne_moe *m, int rows, uint64_t *total, uint64_t *gateup, uint64_t *down, int *distinct_experts);
+
+/* Copy nbytes from a device pointer of this library (e.g. one returned by ne_moe_buffer) to host memory, after
+ * synchronising the device. */
+NE_API int ne_copy_to_host(void *dst_host, const void *src_dev, uint64_t nbytes);
+
+/* Status word of bounded device-side waits: 0 = every wait completed. Reading it synchronises the device. */
+NE_API int ne_device_wait_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
