@@ -1,0 +1,303 @@
+"""Benchmark of the EXL3 MoE decode hot path on B200 (one JSON line on stdout).
+
+Workload (named in `config.workload`): the MoE block of the decoder at decode width -- hidden 2048, 512 experts, top-10,
+expert intermediate 768, routed experts K=5, shared expert K=6 -- for `--rows` activation rows, run over `--layers`
+layers with distinct random weights (so the weights of one step are far larger than L2). A step is one pass of the rows
+through all those layers. value = rows * layers / step time = tokens per second through one MoE block.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--rows M] [--layers L] [--impl reference]
+
+N > 1 (under torchrun): expert parallel. Every rank holds experts/N experts of every layer and `rows` rows of its own;
+rows are all-gathered, each rank runs the routed experts it owns for all rows, partial outputs are reduce-scattered
+(NCCL) and the shared expert runs on the rank's own rows. value = N * rows * layers / step time (weak scaling).
+
+--impl reference: the CPU restatement of the reference's operator path (oracle/, C with all host threads) on a bounded
+sample of the same workload; the reference's own code for this path is Metal / numpy-with-a-missing-module and cannot
+run on this box.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+DIMS = dict(hidden=2048, inter=768, experts=512, k_expert=5, k_shared=6)
+TOPK = 10
+METRIC = "EXL3 MoE decode tok/s (rows through one MoE block)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up stream_gemm launch, from the ncu capture summarised in
+# profiles/ (filled in once a capture exists; None = not captured)
+NCU_TRAFFIC_BYTES = None
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region (read-only query)."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in Path(self.path).read_text().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def cpu_port_tokens_per_s(rows, budget_s):
+    """The C oracle (device-arithmetic restatement) on the host cores: MoE blocks of `rows` rows on a 64-expert layer
+    of the benchmark's dims (the work per row is the same: 10 routed experts + the shared expert), repeated until
+    about `budget_s` seconds have passed."""
+    from ijah_b200 import packgen
+    from oracle import c_oracle as CO
+    rng = np.random.default_rng(0)
+    t = packgen.moe_layer(rng, hidden=DIMS["hidden"], inter=DIMS["inter"], experts=64, k_expert=DIMS["k_expert"], k_shared=DIMS["k_shared"])
+    x = rng.standard_normal((rows, DIMS["hidden"])).astype(np.float16).astype(np.float32)
+    CO.moe_block_emul(t, x[:1], top_k=TOPK)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        CO.moe_block_emul(t, x, top_k=TOPK)
+        n += 1
+        el = time.perf_counter() - t0
+        if el > budget_s or n >= 1000:
+            break
+    return rows * n / el, CO.threads(), f"{n} MoE blocks of {rows} rows on a 64-expert layer of the same dims ({el:.1f} s)"
+
+
+def run_reference(a, rank):
+    if rank != 0:
+        return
+    per_step = max(2.0, min(20.0, 120.0 / max(a.steps + a.warmup, 1)))
+    vals = []
+    for i in range(a.warmup + a.steps):
+        v, cores, sample = cpu_port_tokens_per_s(a.rows, per_step)
+        if i >= a.warmup:
+            vals.append(v)
+    v = float(np.mean(vals))
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": 1e3 * a.rows / v, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 weights x f16 activations, f32 accumulate", "data": "synthetic",
+        "config": workload_config(a),
+        "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def workload_config(a):
+    return {"workload": f"MoE block decode: hidden 2048, 512 experts top-10, inter 768, K5 routed + K6 shared, rows {a.rows}",
+            "rows": a.rows, "layers": a.layers, "l2": "weights of a step exceed L2 (distinct layers cycled)",
+            "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--rows", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if a.impl == "reference":
+        return run_reference(a, rank)
+
+    import torch
+    import torch.distributed as dist
+    from ijah_b200 import engine as E
+    from ijah_b200 import synth
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE {world}"
+    eng = E.Engine()
+    N, M, L = world, a.rows, a.layers
+    H, Ex = DIMS["hidden"], DIMS["experts"]
+    per = Ex // N
+    blocks = []
+    for l in range(L):
+        t = synth.moe_layer(1000 + l, expert_first=rank * per, expert_count=per, router_seed=77 + l, device=dev, **DIMS)
+        blocks.append(E.MoeBlock(eng, t, top_k=TOPK, max_rows=M * N, expert_first=rank * per, expert_count=per, device=dev))
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    xs = [torch.randn((M, H), device=dev, generator=g).to(torch.float16).to(torch.float32) for _ in range(L)]
+    ys = [torch.empty((M, H), device=dev) for _ in range(L)]
+    launches_per_block = 4
+
+    if N == 1:
+        def step():
+            for l in range(L):
+                blocks[l].forward(xs[l], out=ys[l])
+    else:
+        from ijah_b200 import ep
+        eps = [ep.ExpertParallelMoe(blocks[l], dist.group.WORLD) for l in range(L)]
+        launches_per_block = eps[0].launches
+
+        def step():
+            for l in range(L):
+                eps[l].forward(xs[l], out=ys[l])
+
+    def barrier():
+        if N > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        step()
+    barrier()
+    graph = None
+    if N == 1:  # one captured graph per step: launch gaps of the 4-kernel block are what a graph removes
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        graph.replay()
+    run = graph.replay if graph is not None else step
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(a.steps):
+        run()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if N > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / a.steps
+    value = N * M * L / (ms_per_step * 1e-3)
+
+    # ---- end to end through the host-buffer entry point: pinned x in, y out, every block
+    xh = [x.cpu().pin_memory() for x in xs]
+    yh = [torch.empty((M, H)).pin_memory() for _ in range(L)]
+    if N == 1:
+        def e2e_step():
+            for l in range(L):
+                blocks[l].forward_host(xh[l], out=yh[l])
+    else:
+        def e2e_step():
+            for l in range(L):
+                xs[l].copy_(xh[l], non_blocking=True)
+                eps[l].forward(xs[l], out=ys[l])
+                yh[l].copy_(ys[l], non_blocking=True)
+            torch.cuda.synchronize()
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if N > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": N * M * L * a.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * H * 4 * L, "d2h_bytes_per_step": M * H * 4 * L}
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- roofline of the dominant kernel (routed + shared gate/up stream_gemm launch), CUDA events on its stream
+    roof, extra = None, {}
+    if N == 1:
+        peak, which = peaks()
+        evs, byt, dn_evs, dn_b, nu = [], [], [], [], []
+        for it in range(max(3, min(a.steps, 10))):
+            for l in range(L):
+                b = blocks[l]
+                b.stage(7, xs[l], ys[l])
+                s0, s1, s2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                s0.record()
+                b.stage(8, xs[l], ys[l])
+                s1.record()
+                eng._ok(eng.lib.ne_moe_stage(b.ptr, 9, E._dev(xs[l]), M, E._dev(ys[l]), E._stream()), "stage 9")
+                s2.record()
+                evs.append((s0, s1))
+                dn_evs.append((s1, s2))
+                if it == 0:
+                    lb = b.last_bytes(M)
+                    byt.append(lb["gateup"]); dn_b.append(lb["down"]); nu.append(lb["distinct_experts"])
+        torch.cuda.synchronize()
+        dur = float(np.mean([p.elapsed_time(q) for p, q in evs])) * 1e-3
+        ddur = float(np.mean([p.elapsed_time(q) for p, q in dn_evs])) * 1e-3
+        ach = float(np.mean(byt)) / dur / 1e9
+        roof = {"bound": "hbm", "kernel": "stream_gemm_kernel (gate/up)", "achieved": ach, "peak": peak, "unit": "GB/s",
+                "frac": ach / peak, "peak_source": which, "traffic": NCU_TRAFFIC_BYTES, "bytes_per_launch": float(np.mean(byt)),
+                "us_per_launch": dur * 1e6}
+        tot = float(np.mean([blocks[l].last_bytes(M)["total"] for l in range(L)]))
+        extra = {"down_plus_combine": {"achieved": float(np.mean(dn_b)) / ddur / 1e9, "us": ddur * 1e6},
+                 "distinct_experts_mean": float(np.mean(nu)),
+                 "block": {"bytes": tot, "us": ms_per_step * 1e3 / L, "achieved": tot / (ms_per_step * 1e-3 / L) / 1e9,
+                           "frac": tot / (ms_per_step * 1e-3 / L) / 1e9 / peak}}
+    status = eng.lib.ne_device_wait_status()
+    if rank == 0:
+        cpu = None
+        if N == 1:
+            v, cores, sample = cpu_port_tokens_per_s(M, a.cpu_seconds)
+            cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": N, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 weights x f16 activations, f32 accumulate", "data": "synthetic", "config": workload_config(a),
+            "e2e": e2e, "gpu_launches": launches_per_block * L * a.steps, "clocks": clocks, "roofline": roof,
+            "cpu_baseline": cpu, "extra": extra, "wait_status": status}))
+    if N > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -24,10 +24,13 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   IJ_CHECK(d.router_dev != nullptr, "null router weights");
   IJ_CHECK(d.expert_count == 0 || (d.gate.trellis_dev && d.up.trellis_dev && d.down.trellis_dev), "null expert weights");
   has_shared = d.shared_gate_w_dev != nullptr && d.sh_gate.trellis_dev != nullptr;
-  plan_moe(d.hidden, d.inter, d.experts, d.top_k, d.k_expert, d.k_shared, max_rows, has_shared);  // validates dims
+  for (int r = 1; r <= max_rows; r++) {  // validates dims; scratch is sized for the largest k-split of any row count
+    const MoeSplits &sp = splits(r);
+    max_S_gu = std::max(max_S_gu, sp.S_gu);
+    max_S_d = std::max(max_S_d, sp.S_d);
+  }
   const size_t H = d.hidden, I = d.inter, E = d.experts, k = d.top_k, R = max_rows, P = R * k;
-  // worst-case split counts over all row counts: k-tiles / 8
-  const size_t Sg = H / 16 / 8, Sd = I / 16 / 8;
+  const size_t Sg = max_S_gu, Sd = max_S_d;
   auto al = [&](size_t n) { void *p = nullptr; IJ_CUDA(cudaMalloc(&p, std::max<size_t>(n, 16))); IJ_CUDA(cudaMemset(p, 0, std::max<size_t>(n, 16))); owned.push_back(p); return p; };
   logits = (float *)al(R * (E + 1) * 4);
   route = (uint32_t *)al(R * 2 * k * 4);
@@ -36,6 +39,10 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   raw_sgu = (float *)al(Sg * R * 2 * I * 4);
   raw_d = (float *)al(Sd * P * H * 4);
   raw_sd = (float *)al(Sd * R * H * 4);
+  xh_gu = (__half *)al(P * 2 * H * 2);
+  xh_sgu = (__half *)al(R * 2 * H * 2);
+  xh_d = (__half *)al(P * I * 2);
+  xh_sd = (__half *)al(R * I * 2);
   gush = (float *)al(R * 2 * I * 4);
   sho = (float *)al(R * H * 4);
   counter = (unsigned *)al(16);
@@ -62,6 +69,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   p.gate = stack(desc.gate); p.up = stack(desc.up); p.down = stack(desc.down);
   p.sgt = single(desc.sh_gate); p.sup = single(desc.sh_up); p.sdn = single(desc.sh_down);
   p.x = x; p.logits = logits; p.route = route; p.plan = plan;
+  p.xh_gu = xh_gu; p.xh_sgu = xh_sgu; p.xh_d = xh_d; p.xh_sd = xh_sd;
   p.raw_gu = raw_gu; p.raw_sgu = raw_sgu; p.raw_d = raw_d; p.raw_sd = raw_sd;
   p.gush = gush; p.sho = sho; p.y = y; p.counter = counter;
   const MoeSplits &s = splits(rows);
@@ -82,8 +90,8 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
   const MoeSplits &s = splits(rows);
   switch (stage_no) {
     case 7: launch_moe_router(p, true, st); break;
-    case 8: launch_moe_gateup(p, s, status, st); break;
-    case 9: launch_moe_down(p, s, status, st); launch_moe_combine(p, false, st); break;
+    case 8: launch_moe_prep(p, st); launch_moe_gateup(p, s, status, st); break;
+    case 9: launch_moe_mid(p, st); launch_moe_down(p, s, status, st); launch_moe_combine(p, false, st); break;
     default: fail("bad MoE stage %d (7 router, 8 gate/up, 9 down)", stage_no);
   }
   last_rows = rows;
@@ -93,7 +101,9 @@ void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
   const MoeParams p = params(x, rows, y);
   const MoeSplits &s = splits(rows);
   launch_moe_router(p, true, st);
+  launch_moe_prep(p, st);
   launch_moe_gateup(p, s, status, st);
+  launch_moe_mid(p, st);
   launch_moe_down(p, s, status, st);
   launch_moe_combine(p, false, st);
   last_rows = rows;
@@ -105,7 +115,9 @@ void Moe::forward_routed(const float *x, const uint32_t *route_in, int rows, flo
   p.has_shared = 0;
   const MoeSplits &s = splits(rows);
   launch_moe_plan(p, st);
+  launch_moe_prep(p, st);
   launch_moe_gateup(p, s, status, st);
+  launch_moe_mid(p, st);
   launch_moe_down(p, s, status, st);
   launch_moe_combine(p, true, st);
   last_rows = rows;
@@ -127,8 +139,8 @@ NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows,
     check_weight(w);
     IJ_CHECK(x_dev && y_dev, "null activation pointer");
     const LinearPlan p = plan_linear(w->in, w->out, w->K, rows);
-    float *raw = (float *)device_scratch(p.raw_floats() * sizeof(float));
-    launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, x_dev, y_dev, raw, device_status_word(), (cudaStream_t)stream);
+    void *scratch = device_scratch(p.scratch_bytes());
+    launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, x_dev, y_dev, scratch, device_status_word(), (cudaStream_t)stream);
   });
 }
 
@@ -138,12 +150,11 @@ NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int
     IJ_CHECK(x_host && y_host, "null activation pointer");
     const LinearPlan p = plan_linear(w->in, w->out, w->K, rows);
     const size_t xb = (size_t)rows * w->in * 4, yb = (size_t)rows * w->out * 4;
-    char *s = (char *)device_scratch(p.raw_floats() * 4 + xb + yb + 512);
-    float *raw = (float *)s;
-    float *xd = (float *)(s + ((p.raw_floats() * 4 + 255) & ~(size_t)255));
+    char *s = (char *)device_scratch(p.scratch_bytes() + xb + yb + 512);
+    float *xd = (float *)(s + ((p.scratch_bytes() + 255) & ~(size_t)255));
     float *yd = (float *)((char *)xd + ((xb + 255) & ~(size_t)255));
     IJ_CUDA(cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, 0));
-    launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, xd, yd, raw, device_status_word(), 0);
+    launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, xd, yd, s, device_status_word(), 0);
     IJ_CUDA(cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, 0));
     IJ_CUDA(cudaStreamSynchronize(0));
   });

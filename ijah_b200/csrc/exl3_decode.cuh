@@ -38,29 +38,38 @@ struct Codec {
   }
 };
 
-// 15-bit field starting P bits below the MSB of the 96-bit value (w0:w1:w2), P a compile-time constant
+// Powers of two in constant memory. A left shift written as a multiply by one of these becomes an IMAD with a
+// constant-bank operand, i.e. runs on the FMA pipe; the ALU pipe (shifts, logic ops, byte permutes: 64 lanes per
+// clock per SM on B200, half the issue rate) is what bounds the decode, so every op moved off it counts.
+static __constant__ uint32_t kPow2[32] = {
+    1u << 0,  1u << 1,  1u << 2,  1u << 3,  1u << 4,  1u << 5,  1u << 6,  1u << 7,  1u << 8,  1u << 9,  1u << 10,
+    1u << 11, 1u << 12, 1u << 13, 1u << 14, 1u << 15, 1u << 16, 1u << 17, 1u << 18, 1u << 19, 1u << 20, 1u << 21,
+    1u << 22, 1u << 23, 1u << 24, 1u << 25, 1u << 26, 1u << 27, 1u << 28, 1u << 29, 1u << 30, 1u << 31};
+
+// 15-bit field starting P bits below the MSB of the 96-bit value (w0:w1:w2), P a compile-time constant:
+// bring the field to the top of a register (multiply, or one funnel shift when it straddles two words), then >> 17.
 template <int P>
 __device__ __forceinline__ uint32_t field15(uint32_t w0, uint32_t w1, uint32_t w2) {
   constexpr int wi = P / 32, off = P % 32;
   const uint32_t hi = wi == 0 ? w0 : (wi == 1 ? w1 : w2);
   if constexpr (off + 15 <= 32) {
-    if constexpr (off == 17) return hi & 0x7FFFu;
     if constexpr (off == 0) return hi >> 17;
-    return (hi << off) >> 17;
+    return (hi * kPow2[off]) >> 17;
   } else {
     const uint32_t lo = wi == 0 ? w1 : w2;
     return __funnelshift_l(lo, hi, off) >> 17;
   }
 }
 
-// two codewords -> half2(value(ca), value(cb)); value = fp16(lo16(r)) + fp16(hi16(r)), r = ((cw * M) & A) ^ X
+// two codewords -> half2(value(ca), value(cb)); value = fp16(lo16(r)) + fp16(hi16(r)), r = ((cw * M) & A) ^ X.
+// The two half adds are scalar (the compiler selects the halves with operand modifiers), one pack joins them.
 __device__ __forceinline__ uint32_t mcg_pair(uint32_t ca, uint32_t cb) {
   uint32_t ra = ca * 0xCBAC1FEDu, rb = cb * 0xCBAC1FEDu;
   ra = (ra & 0x8FFF8FFFu) ^ 0x3B603B60u;
   rb = (rb & 0x8FFF8FFFu) ^ 0x3B603B60u;
-  const uint32_t lo = __byte_perm(ra, rb, 0x5410), hi = __byte_perm(ra, rb, 0x7632);
-  const __half2 s = __hadd2(*reinterpret_cast<const __half2 *>(&lo), *reinterpret_cast<const __half2 *>(&hi));
-  return *reinterpret_cast<const uint32_t *>(&s);
+  const __half2 a = *reinterpret_cast<const __half2 *>(&ra), b = *reinterpret_cast<const __half2 *>(&rb);
+  const __half2 r = __halves2half2(__hadd(__low2half(a), __high2half(a)), __hadd(__low2half(b), __high2half(b)));
+  return *reinterpret_cast<const uint32_t *>(&r);
 }
 
 // The lane's 8 weights from its three window words: b[0] = (slot 0, slot 1), b[1] = (2, 3): column c;

@@ -12,22 +12,29 @@ StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm) {
   l.stage_bytes = SG_KS * SG_WARPS * 32 * Kmax;
   l.lda = kcmax * 16 + 8;
   l.arows = std::max(arows, 1);
-  l.stages = 3;
   const size_t budget = (size_t)(228 / ctas_per_sm - 2) * 1024;
-  const size_t fixed = l.ring_off() + (size_t)(l.arows + 1) * l.lda * 2;
-  IJ_CHECK(fixed + 3 * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory",
-           arows, kcmax);
-  l.stages = (int)std::min<size_t>(12, (budget - fixed) / l.stage_bytes);
+  const size_t base = l.ring_off() + (size_t)l.lda * 2;
+  l.aslots = base + SG_MAX_ASLOTS * l.slot_bytes() + 6 * (size_t)l.stage_bytes <= budget ? SG_MAX_ASLOTS : 2;
+  const size_t fixed = base + l.aslots * l.slot_bytes();
+  IJ_CHECK(fixed + 3 * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory", arows, kcmax);
+  l.stages = (int)std::min<size_t>(SG_MAX_STAGES, (budget - fixed) / l.stage_bytes);
   return l;
 }
 
-// k-split choice: round-robin over a persistent grid; cost = rounds * (k-tiles per unit + a fixed per-unit overhead)
-static void choose_split(int IT, int NG, int kal, int kcap, int grid, int *S, int *kc) {
-  long best = -1;
-  for (int c = kal; c <= std::max(kal, std::min(IT, kcap)); c += kal) {
+int kc_cap(int arows) {
+  // two A slots may take about 48 KB of the ~110 KB a CTA gets
+  const int cap = ((24 * 1024 / std::max(arows, 1)) - 16) / 32 / SG_KS * SG_KS;
+  return std::max(SG_KS, std::min(cap, 256));
+}
+
+// Units are dealt round-robin to a persistent grid; cost of a candidate = rounds * (k-tiles per unit + a per-unit
+// overhead that grows with the rows whose partial sums the unit writes) with a small bias towards fewer splits.
+void choose_split(int IT, int cols, int kcap, int grid, double rows_per_unit, int *S, int *kc) {
+  double best = -1;
+  for (int c = SG_KS; c <= std::max(SG_KS, std::min((IT + SG_KS - 1) / SG_KS * SG_KS, kcap)); c += SG_KS) {
     const int s = (IT + c - 1) / c;
-    const long rounds = ((long)NG * s + grid - 1) / grid;
-    const long cost = rounds * (c + 3) + s / 4;  // tie-break towards fewer splits (less partial traffic)
+    const long rounds = ((long)cols * s + grid - 1) / grid;
+    const double cost = rounds * (std::min(c, IT) + 2.0 + 0.4 * rows_per_unit) + 0.05 * s;
     if (best < 0 || cost < best) { best = cost; *S = s; *kc = c; }
   }
 }
@@ -41,13 +48,37 @@ LinearPlan plan_linear(int in, int out, int K, int rows) {
   p.IT = in / 16; p.OT = out / 16; p.NG = (p.OT + SG_WARPS - 1) / SG_WARPS;
   p.hi = had_size(in); p.ho = had_size(out);
   p.MT = rows <= 16 ? 1 : rows <= 32 ? 2 : 4;
-  const int kal = std::max(p.hi / 16, in % 128 == 0 ? 8 : 1);
-  const int kcap = std::max(kal, ((48 * 1024 / (2 * rows)) - 8) / 16 / kal * kal);
   p.grid = 2 * sm_count();
-  choose_split(p.IT, p.NG, kal, kcap, p.grid, &p.S, &p.kc);
+  choose_split(p.IT, p.NG, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
   p.lay = make_layout(K, p.kc, rows, 2);
   p.grid = std::min(p.grid, p.NG * p.S);
   return p;
+}
+
+__global__ void __launch_bounds__(128) prep_rows_kernel(const float *__restrict__ x, const __half *__restrict__ suh,
+                                                        __half *__restrict__ xh, int rows, int n, int hn, float hscale) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = blockIdx.x * 4 + warp, r = blockIdx.y;
+  if (chunk * 128 >= n) return;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = chunk * 128 + lane + 32 * j;
+    v[j] = i < n ? x[(size_t)r * n + i] * __half2float(suh[i]) : 0.0f;
+  }
+  fwht_chunk(v, lane, hn, hscale);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = chunk * 128 + lane + 32 * j;
+    if (i < n) xh[(size_t)r * n + i] = __float2half_rn(v[j]);
+  }
+}
+
+void launch_prep_rows(const float *x, const __half *suh, __half *xh, int rows, int n, cudaStream_t st) {
+  const int hn = had_size(n);
+  dim3 grid(((n + 127) / 128 + 3) / 4, rows);
+  prep_rows_kernel<<<grid, 128, 0, st>>>(x, suh, xh, rows, n, hn, (float)(1.0 / sqrt((double)hn)));
+  IJ_CUDA(cudaGetLastError());
 }
 
 // y[r][c] = (H_ho(sum_s raw[s][r]))[c] * svh[c]; one warp per (row, 128-column chunk), splits summed in index order
@@ -74,15 +105,16 @@ __global__ void linear_finish_kernel(const float *__restrict__ raw, const __half
 }
 
 void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, const void *svh, const float *x, float *y,
-                   float *raw, int *status, cudaStream_t st) {
+                   void *scratch, int *status, cudaStream_t st) {
+  float *raw = (float *)scratch;
+  __half *xh = (__half *)((char *)scratch + ((p.raw_floats() * 4 + 255) & ~(size_t)255));
+  launch_prep_rows(x, (const __half *)suh, xh, p.rows, p.in, st);
   LinearProblem pr;
   pr.trellis = (const char *)trellis;
-  pr.suh = (const __half *)suh;
-  pr.x = x;
+  pr.xh = xh;
   pr.raw = raw;
   pr.in = p.in; pr.out = p.out; pr.K = p.K; pr.rows = p.rows;
-  pr.IT = p.IT; pr.OT = p.OT; pr.NG = p.NG; pr.S = p.S; pr.kc = p.kc; pr.hi = p.hi;
-  pr.hscale = (float)(1.0 / sqrt((double)p.hi));
+  pr.IT = p.IT; pr.OT = p.OT; pr.NG = p.NG; pr.S = p.S; pr.kc = p.kc;
   launch_stream(pr, p.MT, p.lay, p.grid, status, st);
   const int chunks = (p.out + 127) / 128;
   dim3 grid((chunks + 3) / 4, p.rows);

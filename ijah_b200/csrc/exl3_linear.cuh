@@ -1,8 +1,9 @@
 // One EXL3 Linear at decode widths: y[rows][out] = x[rows][in] @ W, W = diag(suh) H_in W' H_out diag(svh)
 // (reference: kernels/trunk6/trunk6.metal:366-429 t6_simd, host plan kernels/trunk6/trunk6.mm:84-168).
 //
-// Two launches: stream_gemm (raw partial products of k-splits) and a finisher that sums the splits in index order,
-// applies H_out and svh. Used for the trunk projections (K 6/7/8) and as the building block of the tests.
+// Three launches: a prep kernel (xh = fp16(H_in(x * suh)), the A operand), stream_gemm (raw partial products of
+// k-splits) and a finisher that sums the splits in index order and applies H_out and svh. Used for the trunk
+// projections (K 6/7/8) and as the building block of the tests.
 #pragma once
 #include "stream_gemm.cuh"
 
@@ -17,6 +18,8 @@ struct LinearPlan {
   StreamLayout lay;
   int grid;
   size_t raw_floats() const { return (size_t)S * rows * out; }
+  size_t xh_halfs() const { return (size_t)rows * in; }
+  size_t scratch_bytes() const { return raw_floats() * 4 + ((xh_halfs() * 2 + 255) & ~(size_t)255) + 256; }
 };
 
 LinearPlan plan_linear(int in, int out, int K, int rows);
@@ -26,11 +29,9 @@ struct LinearProblem {
     int g, s, k0;
   };
   const char *trellis;
-  const __half *suh;
-  const float *x;
+  const __half *xh;  // [rows][in] prepared operand
   float *raw;
-  int in, out, K, rows, IT, OT, NG, S, kc, hi;
-  float hscale;
+  int in, out, K, rows, IT, OT, NG, S, kc;
 
   __device__ int num_units() const { return NG * S; }
   __device__ Unit unit(int u) const {
@@ -46,38 +47,28 @@ struct LinearProblem {
     un.w = trellis + ((size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * (32u * K);
     return un;
   }
-  // A[r][i] = half(H_hi(x[r] * suh))[k0*16 + i]: product and butterflies in fp32, one rounding to fp16
-  __device__ void prologue(const Unit &un, __half *A, int lda, int warp, int lane) const {
-    const int n = un.kc * 16, nch = (n + 127) >> 7;
-    for (int job = warp; job < rows * nch; job += SG_WARPS) {
-      const int r = job / nch, c = (job - r * nch) << 7;
-      float v[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int i = c + lane + 32 * j, gi = un.k0 * 16 + i;
-        v[j] = i < n ? x[(size_t)r * in + gi] * __half2float(suh[gi]) : 0.0f;
-      }
-      fwht_chunk(v, lane, hi, hscale);
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int i = c + lane + 32 * j;
-        if (i < n) A[(size_t)r * lda + i] = __float2half_rn(v[j]);
-      }
-    }
-  }
+  __device__ const __half *a_row(const Unit &un, int i) const { return xh + (size_t)i * in + un.k0 * 16; }
   __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
     *reinterpret_cast<float2 *>(raw + ((size_t)un.s * rows + row) * out + un.g * 128 + col) = make_float2(v0, v1);
   }
 };
 
+// `scratch` holds LinearPlan::scratch_bytes(): the k-split partials, then the prepared operand
 void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, const void *svh, const float *x, float *y,
-                   float *raw, int *status, cudaStream_t st);
+                   void *scratch, int *status, cudaStream_t st);
+
+// xh[r][i] = fp16(H_n(x[r] * suh))[i]: product and butterflies in fp32, one rounding (one warp per 128-element chunk)
+void launch_prep_rows(const float *x, const __half *suh, __half *xh, int rows, int n, cudaStream_t st);
 
 // W' as fp16 [in][out] (bit-exact codebook values), for parity checks of the decoder
 void launch_dequant(const void *trellis, int in, int out, int K, __half *w, cudaStream_t st);
 
 // shared-memory carve-up for a stream_gemm launch: kcmax k-tiles of A for arows rows, ring sized to what is left
 StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm);
+// largest k-tile count per unit whose A slots leave room for the ring
+int kc_cap(int arows);
+// k-split choice for `cols` column groups of IT k-tiles on a persistent grid: returns S and kc (multiple of 4)
+void choose_split(int IT, int cols, int kcap, int grid, double rows_per_unit, int *S, int *kc);
 
 
 }  // namespace ijah

@@ -101,41 +101,52 @@ __device__ void build_plan_block(const MoeParams &p, unsigned char *buf) {
   }
 }
 
+// Dynamic shared memory: first the activation rows of one pass (RT_RC rows x H floats, shared by the CTA's 8 expert
+// rows), later reused by the finisher (per-warp logit rows, then the plan's tables).
 __global__ void __launch_bounds__(32 * RT_WARPS) moe_router_kernel(const MoeParams p, int build_plan) {
-  __shared__ __align__(16) float s_log[RT_WARPS][RT_EMAX];
+  extern __shared__ __align__(16) float dyn[];
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * RT_WARPS + warp;
   const int H = p.H, E = p.E;
-  if (row <= E) {
-    const uint16_t *wr = row < E ? p.router + (size_t)row * H : p.sgate;
-    for (int r0 = 0; r0 < p.rows; r0 += RT_RC) {
-      float acc[RT_RC];
+  const uint16_t *wr = row < E ? p.router + (size_t)row * H : (row == E ? p.sgate : nullptr);
+  // the expert's weight row stays in registers for all passes: H / 256 x 8 bf16 per lane (H <= 4096)
+  uint4 wreg[16];
 #pragma unroll
-      for (int t = 0; t < RT_RC; t++) acc[t] = 0.0f;
-      if (wr != nullptr) {
-        const uint4 *w4 = reinterpret_cast<const uint4 *>(wr);
-        for (int c = lane; c < H / 8; c += 32) {
-          const uint4 u = __ldg(&w4[c]);
-          const float w0 = __uint_as_float(u.x << 16), w1 = __uint_as_float(u.x & 0xFFFF0000u);
-          const float w2 = __uint_as_float(u.y << 16), w3 = __uint_as_float(u.y & 0xFFFF0000u);
-          const float w4_ = __uint_as_float(u.z << 16), w5 = __uint_as_float(u.z & 0xFFFF0000u);
-          const float w6 = __uint_as_float(u.w << 16), w7 = __uint_as_float(u.w & 0xFFFF0000u);
+  for (int j = 0; j < 16; j++)
+    wreg[j] = (wr != nullptr && j * 32 + lane < H / 8) ? __ldg(reinterpret_cast<const uint4 *>(wr) + j * 32 + lane) : make_uint4(0, 0, 0, 0);
+  for (int r0 = 0; r0 < p.rows; r0 += RT_RC) {
+    const int nr = min(RT_RC, p.rows - r0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * H / 4; i += blockDim.x)
+      reinterpret_cast<float4 *>(dyn)[i] = reinterpret_cast<const float4 *>(p.x + (size_t)r0 * H)[i];
+    __syncthreads();
+    float acc[RT_RC];
 #pragma unroll
-          for (int t = 0; t < RT_RC; t++) {
-            if (r0 + t < p.rows) {
-              const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (size_t)(r0 + t) * H) + 2 * c;
-              const float4 a = x4[0], b = x4[1];
-              acc[t] += a.x * w0 + a.y * w1 + a.z * w2 + a.w * w3 + b.x * w4_ + b.y * w5 + b.z * w6 + b.w * w7;
-            }
+    for (int t = 0; t < RT_RC; t++) acc[t] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int c = j * 32 + lane;
+      if (c < H / 8) {
+        const uint4 u = wreg[j];
+        const float w0 = __uint_as_float(u.x << 16), w1 = __uint_as_float(u.x & 0xFFFF0000u);
+        const float w2 = __uint_as_float(u.y << 16), w3 = __uint_as_float(u.y & 0xFFFF0000u);
+        const float w4_ = __uint_as_float(u.z << 16), w5 = __uint_as_float(u.z & 0xFFFF0000u);
+        const float w6 = __uint_as_float(u.w << 16), w7 = __uint_as_float(u.w & 0xFFFF0000u);
+#pragma unroll
+        for (int t = 0; t < RT_RC; t++) {
+          if (t < nr) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(dyn + (size_t)t * H) + 2 * c;
+            const float4 a = x4[0], b = x4[1];
+            acc[t] += a.x * w0 + a.y * w1 + a.z * w2 + a.w * w3 + b.x * w4_ + b.y * w5 + b.z * w6 + b.w * w7;
           }
         }
       }
+    }
 #pragma unroll
-      for (int t = 0; t < RT_RC; t++) {
-        const float v = warp_sum(acc[t]);
-        if (lane == 0 && r0 + t < p.rows) p.logits[(size_t)(r0 + t) * (E + 1) + row] = v;
-      }
+    for (int t = 0; t < RT_RC; t++) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0 && t < nr && row <= E) p.logits[(size_t)(r0 + t) * (E + 1) + row] = v;
     }
   }
   __threadfence();
@@ -144,9 +155,9 @@ __global__ void __launch_bounds__(32 * RT_WARPS) moe_router_kernel(const MoePara
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int r = warp; r < p.rows; r += RT_WARPS) topk_row(p, r, s_log[warp], lane);
+  for (int r = warp; r < p.rows; r += RT_WARPS) topk_row(p, r, dyn + (size_t)warp * RT_EMAX, lane);
   __syncthreads();
-  if (build_plan) build_plan_block(p, reinterpret_cast<unsigned char *>(&s_log[0][0]));
+  if (build_plan) build_plan_block(p, reinterpret_cast<unsigned char *>(dyn));
   if (threadIdx.x == 0) *p.counter = 0u;
 }
 
@@ -157,14 +168,123 @@ __global__ void __launch_bounds__(256) moe_plan_kernel(const MoeParams p) {
 
 void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st) {
   IJ_CHECK(p.E <= RT_EMAX && p.E % 32 == 0 && p.H % 256 == 0 && p.topk <= 32, "router: unsupported dims E %d H %d k %d", p.E, p.H, p.topk);
+  IJ_CHECK(p.H <= 4096, "router: hidden %d > 4096", p.H);
   const int grid = (p.E + 1 + RT_WARPS - 1) / RT_WARPS;
-  moe_router_kernel<<<grid, 32 * RT_WARPS, 0, st>>>(p, build_plan ? 1 : 0);
+  const size_t smem = std::max((size_t)std::min(p.rows, RT_RC) * p.H * 4, (size_t)RT_WARPS * RT_EMAX * 4);
+  static bool ready = false;
+  if (!ready) {
+    IJ_CUDA(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_RC * 4096 * 4));
+    ready = true;
+  }
+  moe_router_kernel<<<grid, 32 * RT_WARPS, smem, st>>>(p, build_plan ? 1 : 0);
   IJ_CUDA(cudaGetLastError());
 }
 
 void launch_moe_plan(const MoeParams &p, cudaStream_t st) {
   moe_plan_kernel<<<1, 256, 0, st>>>(p);
   IJ_CUDA(cudaGetLastError());
+}
+
+// =============================================================================================== operand prep
+// xh_gu[pair][proj][H] = fp16(H128(x[row(pair)] * suh_proj[expert(pair)])) for every local (row, slot) pair, and
+// xh_sgu[row][proj][H] for the shared expert (reference kernels/fn_moe.metal:304-311, prefill twin
+// kernels/prefill/pf_moe.metal:88-104). One warp per (operand row, 128-element chunk).
+__global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = blockIdx.x * 4 + warp, job = blockIdx.y;  // job < P: routed pair; else shared row
+  const int H = p.H, k = p.topk;
+  if (chunk * 128 >= H) return;
+  const float hs = 0.08838834764831845f;
+  int r;
+  const __half *sg, *su;
+  __half *dst;
+  if (job < p.P) {
+    r = job / k;
+    const int e = (int)p.route[(size_t)r * 2 * k + (job - r * k)] - p.e0;
+    if (e < 0 || e >= p.ecount) return;
+    sg = p.gate.suh + (size_t)e * H;
+    su = p.up.suh + (size_t)e * H;
+    dst = p.xh_gu + (size_t)job * 2 * H;
+  } else {
+    r = job - p.P;
+    sg = p.sgt.suh;
+    su = p.sup.suh;
+    dst = p.xh_sgu + (size_t)r * 2 * H;
+  }
+  const int o = chunk * 128 + lane;
+  float xv[4], v[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) xv[j] = p.x[(size_t)r * H + o + 32 * j];
+#pragma unroll
+  for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(sg[o + 32 * j]);
+  fwht_chunk(v, lane, 128, hs);
+#pragma unroll
+  for (int j = 0; j < 4; j++) dst[o + 32 * j] = __float2half_rn(v[j]);
+#pragma unroll
+  for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(su[o + 32 * j]);
+  fwht_chunk(v, lane, 128, hs);
+#pragma unroll
+  for (int j = 0; j < 4; j++) dst[H + o + 32 * j] = __float2half_rn(v[j]);
+}
+
+// xh_d[pair][I] = fp16(H128(silu(g) * u * suh_down)), g = H128(sum_s raw gate) * svh_gate, u likewise
+// (reference kernels/fn_moe.metal:370-384, kernels/prefill/pf_moe.metal:107-125). One warp per (pair | shared row,
+// 128-element chunk of the intermediate).
+__global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = blockIdx.x * 4 + warp, job = blockIdx.y;
+  const int I = p.I, k = p.topk;
+  if (chunk * 128 >= I) return;
+  const float hs = 0.08838834764831845f;
+  const float *raw;
+  size_t sstride;
+  const __half *svg, *svu, *sud;
+  __half *dst;
+  const bool shared = job >= p.P;
+  if (!shared) {
+    const int r = job / k, e = (int)p.route[(size_t)r * 2 * k + (job - r * k)] - p.e0;
+    if (e < 0 || e >= p.ecount) return;
+    raw = p.raw_gu + (size_t)job * 2 * I;
+    sstride = (size_t)p.P * 2 * I;
+    svg = p.gate.svh + (size_t)e * I; svu = p.up.svh + (size_t)e * I; sud = p.down.suh + (size_t)e * I;
+    dst = p.xh_d + (size_t)job * I;
+  } else {
+    const int r = job - p.P;
+    raw = p.raw_sgu + (size_t)r * 2 * I;
+    sstride = (size_t)p.rows * 2 * I;
+    svg = p.sgt.svh; svu = p.sup.svh; sud = p.sdn.suh;
+    dst = p.xh_sd + (size_t)r * I;
+  }
+  const int o = chunk * 128 + lane;
+  float gv[4], uv[4], hh[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    float a = 0.0f, b = 0.0f;
+    for (int s = 0; s < p.S_gu; s++) {  // k-split partials in split order
+      a += raw[s * sstride + o + 32 * j];
+      b += raw[s * sstride + I + o + 32 * j];
+    }
+    gv[j] = a; uv[j] = b;
+  }
+  fwht_chunk(gv, lane, 128, hs);
+  fwht_chunk(uv, lane, 128, hs);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    gv[j] *= __half2float(svg[o + 32 * j]);
+    uv[j] *= __half2float(svu[o + 32 * j]);
+    hh[j] = gv[j] / (1.0f + expf(-gv[j])) * uv[j] * __half2float(sud[o + 32 * j]);
+  }
+  if (shared) {  // finished shared gate | up, kept for inspection ("shared_gu")
+    const int r = job - p.P;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      p.gush[(size_t)r * 2 * I + o + 32 * j] = gv[j];
+      p.gush[(size_t)r * 2 * I + I + o + 32 * j] = uv[j];
+    }
+  }
+  fwht_chunk(hh, lane, 128, hs);
+#pragma unroll
+  for (int j = 0; j < 4; j++) dst[o + 32 * j] = __float2half_rn(hh[j]);
 }
 
 // =============================================================================================== gate / up
@@ -175,7 +295,6 @@ struct MoeGateUpProblem {
   };
   MoeParams p;
   int IT, OT, NG, S, kc;
-  float hscale;
 
   __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + (p.has_shared ? 1 : 0)) * 2 * S * NG; }
   __device__ Unit unit(int u) const {
@@ -202,22 +321,9 @@ struct MoeGateUpProblem {
     un.w = w->trellis + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
     return un;
   }
-  __device__ void prologue(const Unit &un, __half *A, int lda, int warp, int lane) const {
-    const PlanView pv{p.plan, p.P};
-    const __half *suh = (un.shared ? (un.proj ? p.sup.suh : p.sgt.suh) : (un.proj ? p.up.suh : p.gate.suh)) + (size_t)un.e * p.H;
-    const int n = un.kc * 16, nch = n >> 7;
-    for (int job = warp; job < un.nrows * nch; job += SG_WARPS) {
-      const int i = job / nch, c = (job - i * nch) << 7;
-      const int r = un.shared ? i : pv.pairs()[un.first + i] / p.topk;
-      const float *xr = p.x + (size_t)r * p.H + un.k0 * 16 + c;
-      const __half *sr = suh + un.k0 * 16 + c;
-      float v[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) v[j] = xr[lane + 32 * j] * __half2float(sr[lane + 32 * j]);
-      fwht_chunk(v, lane, 128, hscale);
-#pragma unroll
-      for (int j = 0; j < 4; j++) A[(size_t)i * lda + c + lane + 32 * j] = __float2half_rn(v[j]);
-    }
+  __device__ const __half *a_row(const Unit &un, int i) const {
+    if (un.shared) return p.xh_sgu + ((size_t)i * 2 + un.proj) * p.H + un.k0 * 16;
+    return p.xh_gu + ((size_t)PlanView{p.plan, p.P}.pairs()[un.first + i] * 2 + un.proj) * p.H + un.k0 * 16;
   }
   __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
     float *dst;
@@ -227,16 +333,13 @@ struct MoeGateUpProblem {
   }
 };
 
-// =============================================================================================== SwiGLU + down
-// A operand (reference kernels/fn_moe.metal:370-384): g = H(raw gate) * svh_g, u = H(raw up) * svh_u,
-// hh = silu(g) * u * suh_down, then H, rounded to fp16.
+// =============================================================================================== down
 struct MoeDownProblem {
   struct Unit : UnitBase {
     int s, k0, g, shared, e, first;
   };
   MoeParams p;
   int IT, OT, NG, S, kc;  // IT = I/16, OT = H/16
-  float hscale;
 
   __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + (p.has_shared ? 1 : 0)) * S * NG; }
   __device__ Unit unit(int u) const {
@@ -256,51 +359,9 @@ struct MoeDownProblem {
     un.w = (un.shared ? p.sdn.trellis : p.down.trellis) + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
     return un;
   }
-  __device__ void prologue(const Unit &un, __half *A, int lda, int warp, int lane) const {
-    const PlanView pv{p.plan, p.P};
-    const int I = p.I;
-    const __half *svg = (un.shared ? p.sgt.svh : p.gate.svh) + (size_t)un.e * I;
-    const __half *svu = (un.shared ? p.sup.svh : p.up.svh) + (size_t)un.e * I;
-    const __half *sud = (un.shared ? p.sdn.suh : p.down.suh) + (size_t)un.e * I;
-    const int nch = (un.kc * 16) >> 7;
-    for (int job = warp; job < un.nrows * nch; job += SG_WARPS) {
-      const int i = job / nch, c = (job - i * nch) << 7, o = un.k0 * 16 + c;
-      const float *raw;
-      size_t sstride;
-      int idx;
-      if (un.shared) { idx = i; raw = p.raw_sgu + (size_t)idx * 2 * I; sstride = (size_t)p.rows * 2 * I; }
-      else { idx = pv.pairs()[un.first + i]; raw = p.raw_gu + (size_t)idx * 2 * I; sstride = (size_t)p.P * 2 * I; }
-      float gv[4], uv[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        float a = 0.0f, b = 0.0f;
-        for (int s = 0; s < p.S_gu; s++) {
-          a += raw[s * sstride + o + lane + 32 * j];
-          b += raw[s * sstride + I + o + lane + 32 * j];
-        }
-        gv[j] = a; uv[j] = b;
-      }
-      fwht_chunk(gv, lane, 128, hscale);
-      fwht_chunk(uv, lane, 128, hscale);
-      float hh[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int cc = o + lane + 32 * j;
-        gv[j] *= __half2float(svg[cc]);
-        uv[j] *= __half2float(svu[cc]);
-        hh[j] = gv[j] / (1.0f + expf(-gv[j])) * uv[j] * __half2float(sud[cc]);
-      }
-      if (un.shared && un.g == 0) {  // finished shared gate | up, kept for inspection ("shared_gu")
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          p.gush[(size_t)idx * 2 * I + o + lane + 32 * j] = gv[j];
-          p.gush[(size_t)idx * 2 * I + I + o + lane + 32 * j] = uv[j];
-        }
-      }
-      fwht_chunk(hh, lane, 128, hscale);
-#pragma unroll
-      for (int j = 0; j < 4; j++) A[(size_t)i * lda + c + lane + 32 * j] = __float2half_rn(hh[j]);
-    }
+  __device__ const __half *a_row(const Unit &un, int i) const {
+    if (un.shared) return p.xh_sd + (size_t)i * p.I + un.k0 * 16;
+    return p.xh_d + (size_t)PlanView{p.plan, p.P}.pairs()[un.first + i] * p.I + un.k0 * 16;
   }
   __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
     float *dst;
@@ -311,71 +372,76 @@ struct MoeDownProblem {
 };
 
 // =============================================================================================== combine
-// One warp per (row, 128-column block) (reference kernels/fn_moe.metal:411-451): every slot's raw down output gets
-// H * svh_down * w_k; slots are summed in slot order; + sigmoid(shared-gate logit) * shared down; optional HC write.
-__global__ void __launch_bounds__(128) moe_combine_kernel(const MoeParams p, int routed_only) {
+// One CTA per (row, 128-column block), one warp per slot plus one for the shared expert (reference
+// kernels/fn_moe.metal:411-451, kernels/prefill/pf_moe.metal:129-161): every slot's raw down output gets
+// H * svh_down * w_k into shared memory; warp 0 then sums the slots in slot order, adds
+// sigmoid(shared-gate logit) * shared down and applies the optional hyper-connection write.
+constexpr int CB_MAXK = 16;
+__global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const MoeParams p, int routed_only) {
+  __shared__ float vals[CB_MAXK + 1][128];
+  __shared__ int used[CB_MAXK + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int blk = blockIdx.x * 4 + warp, r = blockIdx.y;
-  if (blk * 128 >= p.H) return;
+  const int blk = blockIdx.x, r = blockIdx.y;
   const int H = p.H, k = p.topk;
   const float hs = 0.08838834764831845f;
-  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  for (int t = 0; t < k; t++) {
-    const int e = (int)p.route[(size_t)r * 2 * k + t];
-    if (e < p.e0 || e >= p.e0 + p.ecount) continue;
-    const float wk = __uint_as_float(p.route[(size_t)r * 2 * k + k + t]);
-    const float *raw = p.raw_d + (size_t)(r * k + t) * H + blk * 128;
-    float v[4];
+  if (warp < k) {
+    const int e = (int)p.route[(size_t)r * 2 * k + warp];
+    const bool local = e >= p.e0 && e < p.e0 + p.ecount;
+    if (lane == 0) used[warp] = local ? 1 : 0;
+    if (local) {
+      const float wk = __uint_as_float(p.route[(size_t)r * 2 * k + k + warp]);
+      const float *raw = p.raw_d + (size_t)(r * k + warp) * H + blk * 128;
+      const __half *sv = p.down.svh + (size_t)(e - p.e0) * H + blk * 128;
+      float v[4], sc[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      float a = 0.0f;
-      for (int s = 0; s < p.S_d; s++) a += raw[(size_t)s * p.P * H + lane + 32 * j];
-      v[j] = a;
+      for (int j = 0; j < 4; j++) {
+        sc[j] = __half2float(sv[lane + 32 * j]);
+        float a = 0.0f;
+        for (int s = 0; s < p.S_d; s++) a += raw[(size_t)s * p.P * H + lane + 32 * j];
+        v[j] = a;
+      }
+      fwht_chunk(v, lane, 128, hs);
+#pragma unroll
+      for (int j = 0; j < 4; j++) vals[warp][lane + 32 * j] = v[j] * sc[j] * wk;
     }
-    fwht_chunk(v, lane, 128, hs);
-    const __half *sv = p.down.svh + (size_t)(e - p.e0) * H + blk * 128;
+  } else if (warp == k) {
+    const bool on = !routed_only && p.has_shared;
+    if (lane == 0) used[k] = on ? 1 : 0;
+    if (on) {
+      float v[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[j] += v[j] * __half2float(sv[lane + 32 * j]) * wk;
+      for (int j = 0; j < 4; j++) {
+        float a = 0.0f;
+        for (int s = 0; s < p.S_d; s++) a += p.raw_sd[((size_t)s * p.rows + r) * H + blk * 128 + lane + 32 * j];
+        v[j] = a;
+      }
+      fwht_chunk(v, lane, 128, hs);
+      const float sg = 1.0f / (1.0f + expf(-p.logits[(size_t)r * (p.E + 1) + p.E]));
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int c = blk * 128 + lane + 32 * j;
+        v[j] *= __half2float(p.sdn.svh[c]);
+        p.sho[(size_t)r * H + c] = v[j];
+        vals[k][lane + 32 * j] = sg * v[j];
+      }
+    }
   }
-  if (!routed_only && p.has_shared) {
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      float a = 0.0f;
-      for (int s = 0; s < p.S_d; s++) a += p.raw_sd[((size_t)s * p.rows + r) * H + blk * 128 + lane + 32 * j];
-      v[j] = a;
-    }
-    fwht_chunk(v, lane, 128, hs);
-    const float sg = 1.0f / (1.0f + expf(-p.logits[(size_t)r * (p.E + 1) + p.E]));
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const int c = blk * 128 + lane + 32 * j;
-      v[j] *= __half2float(p.sdn.svh[c]);
-      p.sho[(size_t)r * H + c] = v[j];
-      acc[j] += sg * v[j];
-    }
-  }
+  __syncthreads();
+  if (warp != 0) return;
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int c = blk * 128 + lane + 32 * j;
-    p.y[(size_t)r * H + c] = acc[j];
+    float acc = 0.0f;
+    for (int t = 0; t <= k; t++)
+      if (used[t]) acc += vals[t][lane + 32 * j];
+    p.y[(size_t)r * H + c] = acc;
     if (p.h_mid != nullptr)
       for (int s = 0; s < p.HC; s++)
-        p.h_out[((size_t)r * p.HC + s) * H + c] = p.h_mid[((size_t)r * p.HC + s) * H + c] + acc[j] * p.inj[(size_t)r * 2 * p.HC + s];
+        p.h_out[((size_t)r * p.HC + s) * H + c] = p.h_mid[((size_t)r * p.HC + s) * H + c] + acc * p.inj[(size_t)r * 2 * p.HC + s];
   }
 }
 
 // =============================================================================================== host side
-static void choose_split_moe(int IT, int colgroups, int kcap, int grid, int *S, int *kc) {
-  long best = -1;
-  for (int c = 8; c <= std::min(IT, kcap); c += 8) {
-    const int s = (IT + c - 1) / c;
-    const long rounds = ((long)colgroups * s + grid - 1) / grid;
-    const long cost = rounds * (c + 3) + s / 4;
-    if (best < 0 || cost < best) { best = cost; *S = s; *kc = c; }
-  }
-}
-
 MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool has_shared) {
   IJ_CHECK(H % 256 == 0 && I % 128 == 0, "MoE dims: hidden %d must be a multiple of 256, intermediate %d of 128", H, I);
   IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
@@ -384,14 +450,30 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   s.MT = rows <= 16 ? 1 : rows <= 32 ? 2 : 4;
   s.grid = 2 * sm_count();
   // expected number of distinct experts under uniform routing; any actual count works, this only tunes the k-split
-  const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows)) + (has_shared ? 1 : 0);
-  const int kcap = std::max(8, ((40 * 1024 / (2 * rows)) - 8) / 16 / 8 * 8);
-  choose_split_moe(H / 16, (int)std::lround(nu * 2 * (I / 128)), kcap, s.grid, &s.S_gu, &s.kc_gu);
-  choose_split_moe(I / 16, (int)std::lround(nu * (H / 128)), kcap, s.grid, &s.S_d, &s.kc_d);
+  const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows));
+  const double rpu = std::max(1.0, rows * (double)topk / std::max(nu, 1.0));
+  const int kcap = kc_cap(rows);
+  // at most 16 splits (bounds the partial-sum scratch)
+  choose_split(H / 16, (int)std::lround((nu + (has_shared ? 1 : 0)) * 2 * (I / 128)), kcap, s.grid, rpu, &s.S_gu, &s.kc_gu);
+  if (s.S_gu > 16) { s.kc_gu = (H / 16 + 15) / 16; s.kc_gu = (s.kc_gu + SG_KS - 1) / SG_KS * SG_KS; s.S_gu = (H / 16 + s.kc_gu - 1) / s.kc_gu; }
+  choose_split(I / 16, (int)std::lround((nu + (has_shared ? 1 : 0)) * (H / 128)), kcap, s.grid, rpu, &s.S_d, &s.kc_d);
+  if (s.S_d > 16) { s.kc_d = (I / 16 + 15) / 16; s.kc_d = (s.kc_d + SG_KS - 1) / SG_KS * SG_KS; s.S_d = (I / 16 + s.kc_d - 1) / s.kc_d; }
   const int kmax = std::max(Kx, has_shared ? Ks : 0);
   s.lay_gu = make_layout(kmax, s.kc_gu, rows, 2);
   s.lay_d = make_layout(kmax, s.kc_d, rows, 2);
   return s;
+}
+
+void launch_moe_prep(const MoeParams &p, cudaStream_t st) {
+  dim3 grid((p.H / 128 + 3) / 4, p.P + (p.has_shared ? p.rows : 0));
+  moe_prep_kernel<<<grid, 128, 0, st>>>(p);
+  IJ_CUDA(cudaGetLastError());
+}
+
+void launch_moe_mid(const MoeParams &p, cudaStream_t st) {
+  dim3 grid((p.I / 128 + 3) / 4, p.P + (p.has_shared ? p.rows : 0));
+  moe_mid_kernel<<<grid, 128, 0, st>>>(p);
+  IJ_CUDA(cudaGetLastError());
 }
 
 void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st) {
@@ -399,7 +481,6 @@ void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cuda
   pr.p = p;
   pr.IT = p.H / 16; pr.OT = p.I / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
   pr.S = s.S_gu; pr.kc = s.kc_gu;
-  pr.hscale = 0.08838834764831845f;
   launch_stream(pr, s.MT, s.lay_gu, s.grid, status, st);
 }
 
@@ -408,13 +489,13 @@ void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaSt
   pr.p = p;
   pr.IT = p.I / 16; pr.OT = p.H / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
   pr.S = s.S_d; pr.kc = s.kc_d;
-  pr.hscale = 0.08838834764831845f;
   launch_stream(pr, s.MT, s.lay_d, s.grid, status, st);
 }
 
 void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st) {
-  dim3 grid((p.H / 128 + 3) / 4, p.rows);
-  moe_combine_kernel<<<grid, 128, 0, st>>>(p, routed_only ? 1 : 0);
+  IJ_CHECK(p.topk <= CB_MAXK, "combine: top_k %d > %d", p.topk, CB_MAXK);
+  dim3 grid(p.H / 128, p.rows);
+  moe_combine_kernel<<<grid, 32 * (p.topk + 1), 0, st>>>(p, routed_only ? 1 : 0);
   IJ_CUDA(cudaGetLastError());
 }
 

@@ -29,6 +29,10 @@ struct MoeParams {
   float *logits;           // [rows][E + 1]
   uint32_t *route;         // [rows][2 topk]
   int *plan;               // see PlanView
+  __half *xh_gu;           // [P][2][H]  prepared gate | up operands per (row, slot) pair
+  __half *xh_sgu;          // [rows][2][H]  the shared expert's
+  __half *xh_d;            // [P][I]  prepared down operand per pair
+  __half *xh_sd;           // [rows][I]
   float *raw_gu;           // [S_gu][P][2][I]
   float *raw_sgu;          // [S_gu][rows][2][I]
   float *raw_d;            // [S_d][P][H]
@@ -68,6 +72,8 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
 
 void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st);
 void launch_moe_plan(const MoeParams &p, cudaStream_t st);  // plan from an externally supplied route buffer
+void launch_moe_prep(const MoeParams &p, cudaStream_t st);   // gate / up operands (after routing)
+void launch_moe_mid(const MoeParams &p, cudaStream_t st);    // SwiGLU + down operand (after gate / up)
 void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
 void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
 void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st);

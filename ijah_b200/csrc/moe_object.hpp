@@ -4,6 +4,8 @@
 #include <vector>
 
 #include "../../include/ijah_b200.h"
+#include <cuda_fp16.h>
+
 #include "fn_moe.cuh"
 
 namespace ijah {
@@ -16,6 +18,8 @@ struct Moe {
   std::vector<void *> owned;
   float *logits = nullptr, *raw_gu = nullptr, *raw_sgu = nullptr, *raw_d = nullptr, *raw_sd = nullptr, *gush = nullptr, *sho = nullptr;
   float *x_stage = nullptr, *y_stage = nullptr;
+  __half *xh_gu = nullptr, *xh_sgu = nullptr, *xh_d = nullptr, *xh_sd = nullptr;
+  int max_S_gu = 1, max_S_d = 1;
   uint32_t *route = nullptr;
   int *plan = nullptr, *status = nullptr;
   unsigned *counter = nullptr;

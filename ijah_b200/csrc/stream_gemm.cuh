@@ -1,19 +1,21 @@
 // Streaming trellis GEMM for decode widths (1..64 activation rows) on sm_100a.
 //
-//   raw[rows][cols] (+)= A[rows][k] (fp16, prepared in shared memory)  x  W'[k][cols] (EXL3 tiles, decoded in registers)
+//   raw[rows][cols] = A[rows][k] (fp16, prepared beforehand in global memory)  x  W'[k][cols] (EXL3 tiles, decoded in
+//   registers)
 //
 // One CTA = 8 consumer warps + 1 producer warp and is persistent over a list of work units. A unit is a block of
-// <= 8 output tiles (128 columns) x a run of k-tiles of one matrix. The producer thread streams the unit's compressed
-// tiles global -> shared with 1-D bulk async copies into a ring of stages (mbarrier transaction counts), running ahead
-// across unit boundaries, so HBM stays busy while the consumers build the next unit's A operand. Each consumer warp owns
-// one output tile: per k-tile it reads its lane window (3 words) from the ring, decodes 8 weights per lane and issues
-// two mma.m16n8k16 per 16 activation rows; accumulators are fp32 registers. Only compressed bytes cross HBM.
+// <= 8 output tiles (128 columns) x a run of k-tiles of one matrix. The producer thread moves everything with 1-D bulk
+// async copies (global -> shared, mbarrier transaction counts): the unit's A rows into one of a few A slots, and the
+// unit's compressed tiles into a ring of stages. It runs ahead across unit boundaries, so HBM stays busy and the
+// consumers never wait for an operand that could have been fetched earlier. Each consumer warp owns one output tile:
+// per k-tile it reads its lane window (3 words) from the ring, decodes 8 weights per lane and issues two
+// mma.m16n8k16 per 16 activation rows; accumulators are fp32 registers. Only compressed bytes cross HBM.
 //
-// The "problem" type P supplies the unit list and the pre/post work:
+// The "problem" type P supplies the unit list and the operand / result addresses:
 //   int  P::num_units() const
-//   Unit P::unit(int u) const                 // where the tiles are, how many k-steps, K, rows, ...
-//   void P::prologue(const Unit&, __half *A, int lda, int warp, int lane) const   // fill A[row][k] (8 warps)
-//   void P::store(const Unit&, int row, int col, float v0, float v1) const        // raw output of (row, col..col+1)
+//   Unit P::unit(int u) const                         // where the tiles are, how many k-steps, K, rows, ...
+//   const __half *P::a_row(const Unit&, int i) const  // global address of row i's first element of the unit's k range
+//   void P::store(const Unit&, int row, int col, float v0, float v1) const   // raw output of (row, col..col+1)
 #pragma once
 #include "exl3_decode.cuh"
 #include "pipeline.cuh"
@@ -22,7 +24,9 @@ namespace ijah {
 
 constexpr int SG_WARPS = 8;               // consumer warps = output tiles per unit
 constexpr int SG_THREADS = 32 * (SG_WARPS + 1);
-constexpr int SG_KS = 4;                  // k-steps per ring stage
+constexpr int SG_KS = 8;                  // k-steps per ring stage
+constexpr int SG_MAX_STAGES = 16;
+constexpr int SG_MAX_ASLOTS = 4;
 
 struct UnitBase {
   const char *w;       // first tile of the unit: tile (k0, n0)
@@ -36,48 +40,101 @@ struct UnitBase {
 struct StreamLayout {  // dynamic shared memory carve-up (host computes, kernel mirrors)
   int stages;          // ring stages
   int stage_bytes;     // SG_KS * 8 * 32 * Kmax
-  int lda;             // A row stride in halfs (k elements + 8 pad)
-  int arows;           // A rows held (live rows only; dead MMA rows read the zero row)
-  __host__ __device__ size_t ring_off() const { return 256; }
+  int lda;             // A row stride in halfs (k elements + 8 pad: keeps ldmatrix rows on distinct banks)
+  int arows;           // rows per A slot
+  int aslots;          // A slots (units the producer may run ahead)
+  __host__ __device__ size_t ring_off() const { return 512; }
+  __host__ __device__ size_t slot_bytes() const { return (size_t)arows * lda * 2; }
   __host__ __device__ size_t a_off() const { return ring_off() + (size_t)stages * stage_bytes; }
-  __host__ __device__ size_t zero_off() const { return a_off() + (size_t)arows * lda * 2; }
+  __host__ __device__ size_t zero_off() const { return a_off() + (size_t)aslots * slot_bytes(); }
   __host__ __device__ size_t total() const { return zero_off() + (size_t)lda * 2; }
 };
 
-template <int K, int MT>
-__device__ __forceinline__ void consume_stage(const char *stage, int nsteps, int kstep_bytes, int warp, uint32_t a_addr,
-                                              const uint32_t (&a_rowoff)[MT], int kbase, const typename Codec<K>::Lane &L,
-                                              float (&acc)[MT][2][4]) {
-  const char *tile = stage + warp * Codec<K>::TILE_BYTES;
+// shared-memory loads with the constant part of the address as an immediate (no address arithmetic per tile)
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr), "n"(OFF));
+}
+
+// k-tile I of a stage for one output tile: 3 words -> 8 weights -> 2 MMAs per 16-row tile. p0..p2 / a_row[m] are the
+// addresses for k-tile 0; tile I sits I * KSTEP further in the ring and I * 32 bytes further in the A rows.
+template <int K, int MT, int I>
+__device__ __forceinline__ void tile_mma(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t la, const uint32_t (&a_row)[MT],
+                                         float (&acc)[MT][2][4]) {
+  constexpr int KSTEP = SG_WARPS * Codec<K>::TILE_BYTES;
+  uint32_t b[4];
+  dec8<K>(lds32<I * KSTEP>(p0), lds32<I * KSTEP>(p1), lds32<I * KSTEP>(p2), la, b);
 #pragma unroll
-  for (int i = 0; i < SG_KS; i++) {
-    if (i < nsteps) {
-      const char *t = tile + i * kstep_bytes;
-      const uint32_t w0 = *reinterpret_cast<const uint32_t *>(t + L.o0);
-      const uint32_t w1 = *reinterpret_cast<const uint32_t *>(t + L.o1);
-      const uint32_t w2 = *reinterpret_cast<const uint32_t *>(t + L.o2);
-      uint32_t b[4];
-      dec8<K>(w0, w1, w2, L.a, b);
-#pragma unroll
-      for (int m = 0; m < MT; m++) {
-        uint32_t a[4];
-        ldmatrix_x4(a, a_addr + a_rowoff[m] + (uint32_t)(kbase + i) * 32u);
-        mma_16816(acc[m][0], a, b[0], b[1]);
-        mma_16816(acc[m][1], a, b[2], b[3]);
-      }
-    }
+  for (int m = 0; m < MT; m++) {
+    uint32_t a[4];
+    ldsm4<I * 32>(a, a_row[m]);
+    mma_16816(acc[m][0], a, b[0], b[1]);
+    mma_16816(acc[m][1], a, b[2], b[3]);
   }
+}
+template <int K, int MT, int I, int N>
+struct TileLoop {
+  static __device__ __forceinline__ void run(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t la, const uint32_t (&a_row)[MT],
+                                             float (&acc)[MT][2][4], int n) {
+    if (I < n) tile_mma<K, MT, I>(p0, p1, p2, la, a_row, acc);
+    TileLoop<K, MT, I + 1, N>::run(p0, p1, p2, la, a_row, acc, n);
+  }
+  static __device__ __forceinline__ void run_all(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t la,
+                                                 const uint32_t (&a_row)[MT], float (&acc)[MT][2][4]) {
+    tile_mma<K, MT, I>(p0, p1, p2, la, a_row, acc);
+    TileLoop<K, MT, I + 1, N>::run_all(p0, p1, p2, la, a_row, acc);
+  }
+};
+template <int K, int MT, int N>
+struct TileLoop<K, MT, N, N> {
+  static __device__ __forceinline__ void run(uint32_t, uint32_t, uint32_t, uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4], int) {}
+  static __device__ __forceinline__ void run_all(uint32_t, uint32_t, uint32_t, uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4]) {}
+};
+
+// All k-steps of one unit for one warp. Returns false if a bounded wait gave up.
+template <int K, int MT>
+__device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int stage_bytes, int nstages, uint64_t *full,
+                                             uint64_t *empty, int &stage, uint32_t &phase, bool live, int warp, int lane,
+                                             uint32_t a_addr, const uint32_t (&a_rowoff)[MT], float (&acc)[MT][2][4],
+                                             int *status) {
+  const typename Codec<K>::Lane L = Codec<K>::lane(lane);
+  const uint32_t tb = ring_addr + (uint32_t)warp * Codec<K>::TILE_BYTES;
+  for (int k = 0; k < kc; k += SG_KS) {
+    if (!mbar_wait(&full[stage], phase, status, 2)) return false;
+    if (live) {
+      const uint32_t sb = tb + (uint32_t)stage * (uint32_t)stage_bytes;
+      const uint32_t p0 = sb + L.o0, p1 = sb + L.o1, p2 = sb + L.o2;
+      uint32_t a_row[MT];
+#pragma unroll
+      for (int m = 0; m < MT; m++) a_row[m] = a_addr + a_rowoff[m] + (uint32_t)k * 32u;
+      if (kc - k >= SG_KS) TileLoop<K, MT, 0, SG_KS>::run_all(p0, p1, p2, L.a, a_row, acc);
+      else TileLoop<K, MT, 0, SG_KS>::run(p0, p1, p2, L.a, a_row, acc, kc - k);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[stage]);
+    if (++stage == nstages) { stage = 0; phase ^= 1u; }
+  }
+  return true;
 }
 
 template <class P, int MT>
 __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob, const StreamLayout lay, int *status) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *empty = full + 16;
-  char *ring = reinterpret_cast<char *>(smem + lay.ring_off());
-  __half *A = reinterpret_cast<__half *>(smem + lay.a_off());
-  __half *zrow = reinterpret_cast<__half *>(smem + lay.zero_off());
-  __shared__ int s_abort;
+  uint64_t *empty = full + SG_MAX_STAGES;
+  uint64_t *a_full = empty + SG_MAX_STAGES;
+  uint64_t *a_empty = a_full + SG_MAX_ASLOTS;
+  unsigned char *ring = smem + lay.ring_off();
+  unsigned char *aslot = smem + lay.a_off();
+  unsigned char *zrow = smem + lay.zero_off();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -85,8 +142,11 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], SG_WARPS);
     }
+    for (int s = 0; s < lay.aslots; s++) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], SG_WARPS);
+    }
     mbar_fence_init();
-    s_abort = 0;
   }
   for (int i = threadIdx.x; i < lay.lda / 2; i += blockDim.x) reinterpret_cast<uint32_t *>(zrow)[i] = 0u;
   __syncthreads();
@@ -95,20 +155,25 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
   if (warp == SG_WARPS) {
     // ---------------------------------------------------------------- producer (one thread)
     if (lane != 0) return;
-    int stage = 0;
-    uint32_t phase = 0;
-    long issued = 0;
+    int stage = 0, slot = 0;
+    uint32_t phase = 0, aphase = 0;
     for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
       const typename P::Unit un = prob.unit(u);
-      const uint32_t kb = (uint32_t)un.ntiles * 32u * (uint32_t)un.K;
+      // A rows of this unit
+      if (!mbar_wait(&a_empty[slot], aphase ^ 1u, status, 3)) return;
+      const uint32_t rowb = (uint32_t)un.kc * 32u;
+      mbar_arrive_expect_tx(&a_full[slot], (uint32_t)un.nrows * rowb);
+      unsigned char *adst = aslot + (size_t)slot * lay.slot_bytes();
+      for (int i = 0; i < un.nrows; i++) bulk_g2s(adst + (size_t)i * lay.lda * 2, prob.a_row(un, i), rowb, &a_full[slot]);
+      if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
+      // compressed tiles, SG_KS k-steps per stage
+      const uint32_t kb = (uint32_t)un.ntiles * 32u * (uint32_t)un.K, ks = (uint32_t)SG_WARPS * 32u * (uint32_t)un.K;
       for (int k = 0; k < un.kc; k += SG_KS) {
         const int n = min(SG_KS, un.kc - k);
-        if (issued >= lay.stages && !mbar_wait(&empty[stage], phase ^ 1u, status, 1)) { s_abort = 1; return; }
-        if (*reinterpret_cast<volatile int *>(&s_abort)) return;
+        if (!mbar_wait(&empty[stage], phase ^ 1u, status, 1)) return;
         mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
-        char *dst = ring + (size_t)stage * lay.stage_bytes;
-        for (int i = 0; i < n; i++) bulk_g2s(dst + i * kb, un.w + (size_t)(k + i) * un.kstride, kb, &full[stage]);
-        issued++;
+        unsigned char *dst = ring + (size_t)stage * lay.stage_bytes;
+        for (int i = 0; i < n; i++) bulk_g2s(dst + i * ks, un.w + (size_t)(k + i) * un.kstride, kb, &full[stage]);
         if (++stage == lay.stages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -117,25 +182,21 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
 
   // ------------------------------------------------------------------ consumers (8 warps)
   const int g = lane >> 2, q = lane & 3;
-  int stage = 0;
-  uint32_t phase = 0;
+  int stage = 0, slot = 0;
+  uint32_t phase = 0, aphase = 0;
   // ldmatrix row addresses: lanes 0-7 rows 0-7 (k 0-7), 8-15 rows 8-15, 16-23 rows 0-7 (k 8-15), 24-31 rows 8-15
   const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
   const uint32_t lkof = (uint32_t)(lane >> 4) * 16u;
-  const uint32_t a_base = smem_u32(A), z_base = smem_u32(zrow);
+  const uint32_t ring_addr = smem_u32(ring), a0_addr = smem_u32(aslot), z_addr = smem_u32(zrow);
 
   for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
     const typename P::Unit un = prob.unit(u);
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * SG_WARPS));  // everyone is done reading the previous unit's A
-    prob.prologue(un, A, lay.lda, warp, lane);
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * SG_WARPS));
-
+    const uint32_t a_addr = a0_addr + (uint32_t)slot * (uint32_t)lay.slot_bytes();
     uint32_t a_rowoff[MT];
 #pragma unroll
     for (int m = 0; m < MT; m++) {
-      const int r = m * 16 + lrow;
-      // offsets are relative to a_base; dead rows are redirected to the zero row
-      a_rowoff[m] = (r < un.nrows ? (uint32_t)r * (uint32_t)lay.lda * 2u : (z_base - a_base)) + lkof;
+      const int r = m * 16 + lrow;  // dead MMA rows read the zero row
+      a_rowoff[m] = (r < un.nrows ? (uint32_t)r * (uint32_t)lay.lda * 2u : (z_addr - a_addr)) + lkof;
     }
     float acc[MT][2][4];
 #pragma unroll
@@ -145,28 +206,20 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[m][h][j] = 0.0f;
 
-    const int kb = un.ntiles * 32 * un.K;
+    if (!mbar_wait(&a_full[slot], aphase, status, 4)) return;
     const bool live = warp < un.ntiles;
-    bool ok = true;
-    for (int k = 0; k < un.kc && ok; k += SG_KS) {
-      const int n = min(SG_KS, un.kc - k);
-      ok = mbar_wait(&full[stage], phase, status, 2);
-      if (!ok) { s_abort = 1; break; }
-      const char *st = ring + (size_t)stage * lay.stage_bytes;
-      if (live) {
-        switch (un.K) {
-          case 4: consume_stage<4, MT>(st, n, kb, warp, a_base, a_rowoff, k, Codec<4>::lane(lane), acc); break;
-          case 5: consume_stage<5, MT>(st, n, kb, warp, a_base, a_rowoff, k, Codec<5>::lane(lane), acc); break;
-          case 6: consume_stage<6, MT>(st, n, kb, warp, a_base, a_rowoff, k, Codec<6>::lane(lane), acc); break;
-          case 7: consume_stage<7, MT>(st, n, kb, warp, a_base, a_rowoff, k, Codec<7>::lane(lane), acc); break;
-          default: consume_stage<8, MT>(st, n, kb, warp, a_base, a_rowoff, k, Codec<8>::lane(lane), acc); break;
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[stage]);
-      if (++stage == lay.stages) { stage = 0; phase ^= 1u; }
+    bool ok;
+    switch (un.K) {
+      case 4: ok = consume_unit<4, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
+      case 5: ok = consume_unit<5, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
+      case 6: ok = consume_unit<6, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
+      case 7: ok = consume_unit<7, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
+      default: ok = consume_unit<8, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
     }
-    if (!ok) break;
+    if (!ok) return;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&a_empty[slot]);
+    if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
     if (live) {
       const int col = warp * 16 + 2 * q;
 #pragma unroll

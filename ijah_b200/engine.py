@@ -308,8 +308,10 @@ def _stream():
 
 
 def to_device_u16(a, device="cuda"):
-    """numpy uint16 / float16 array -> torch tensor of the same bits on the device"""
+    """numpy uint16 / float16 array (or a torch tensor already on the device) -> torch tensor of the same bits"""
     torch = _torch()
+    if isinstance(a, torch.Tensor):
+        return a.to(device).contiguous()
     a = np.ascontiguousarray(a)
     if a.dtype == np.float16:
         return torch.from_numpy(a).to(device)
@@ -357,11 +359,15 @@ class MoeBlock:
     def __init__(self, eng, tensors, layer=0, top_k=10, max_rows=16, expert_first=0, expert_count=None, device="cuda"):
         self.eng = eng
         pre = f"language_model.model.layers.{layer}.mlp."
-        g = lambda n: np.asarray(tensors[pre + n][1])  # noqa: E731
+        def g(n):
+            a = tensors[pre + n][1]
+            return a if hasattr(a, "data_ptr") else np.asarray(a)
+
         router = g("gate.weight")
         E, H = router.shape
         count = E if expert_count is None else expert_count
-        sl = slice(expert_first, expert_first + count)
+        # stacks that already hold only the local experts are taken whole
+        sl = slice(None) if g("switch_mlp.gate_proj.trellis").shape[0] == count else slice(expert_first, expert_first + count)
         self.keep = []
 
         def dev(a):
