@@ -91,6 +91,8 @@ SIGNATURES = {
     "ne_exl3_dequant": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_void_p]),
     "ne_exl3_linear": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_host": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_exl3_linear_static": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_exl3_linear_static_capacity": (C.c_uint64, []),
     "ne_moe_create": (C.c_void_p, [C.POINTER(MoeDescC), C.c_int]), "ne_moe_free": (None, [C.c_void_p]),
     "ne_moe_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
@@ -342,6 +344,17 @@ class Exl3Linear:
         rows = x.shape[0]
         y = torch.empty((rows, self.n_out), dtype=torch.float32, device=x.device)
         self.eng._ok(self.eng.lib.ne_exl3_linear(C.byref(self.c), _dev(x), rows, _dev(y), _stream()), "ne_exl3_linear")
+        return y
+
+    def forward_static(self, x):
+        """the same Linear through ne_exl3_linear_static: scratch is the library's built-in device array, so the call
+        allocates nothing in the library (the output tensor below is the caller's, made by torch)"""
+        torch = _torch()
+        x = x.to(torch.float32).contiguous()
+        rows = x.shape[0]
+        y = torch.empty((rows, self.n_out), dtype=torch.float32, device=x.device)
+        self.eng._ok(self.eng.lib.ne_exl3_linear_static(C.byref(self.c), _dev(x), rows, _dev(y), _stream()),
+                     "ne_exl3_linear_static")
         return y
 
     def forward_host(self, x):

@@ -34,6 +34,19 @@ NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *strea
  * owned by the library (grown on demand). */
 NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host);
+/* ne_exl3_linear for callers that must not allocate (no counterpart in the reference, whose unified-memory engine has
+ * no such constraint). ne_exl3_linear grows a cudaMalloc'ed arena when a call needs more scratch than any call before
+ * it; that is unusable from inside an allocator or memory-pool hook, in a serving loop that was given a fixed memory
+ * budget at start-up, or next to another runtime that already owns the rest of the device memory. This variant runs
+ * the same kernels on a scratch area compiled into the library (a 256-byte aligned __device__ array of
+ * ne_exl3_linear_static_capacity() = 8 MiB bytes, held by every GPU that loads the library until the process exits)
+ * and calls no cudaMalloc / cudaFree nor any allocating routine. Same arguments and results as ne_exl3_linear. A
+ * call whose scratch need (k-split partials + fp16 operand: about rows * (4 * S * out + 2 * in) bytes, S <= 16)
+ * exceeds the capacity is refused with -1 and a message naming both sizes. The first call on a device resolves the
+ * array's device address; make it before any stream capture begins. All calls share the one area: it keeps the last
+ * call's contents (nothing needs to start at zero), and calls whose GPU work overlaps race on it. */
+NE_API int ne_exl3_linear_static(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
+NE_API uint64_t ne_exl3_linear_static_capacity(void);
 
 /* ---- MoE block (router, routed experts, shared expert) at decode widths --------------------------------------
  * Replaces the three dispatches fn_moe_router / fn_moe_gateup / fn_moe_down of the reference
