@@ -75,6 +75,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   const MoeSplits &s = splits(rows);
   p.S_gu = s.S_gu; p.kc_gu = s.kc_gu; p.S_d = s.S_d; p.kc_d = s.kc_d;
   p.h_mid = h_mid; p.inj = inj; p.h_out = h_out; p.HC = HC;
+  p.sh_row0 = 0; p.sh_rows = rows;
   return p;
 }
 
@@ -99,6 +100,23 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
 
 void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
   const MoeParams p = params(x, rows, y);
+  const MoeSplits &s = splits(rows);
+  launch_moe_router(p, true, st);
+  launch_moe_prep(p, st);
+  launch_moe_gateup(p, s, status, st);
+  launch_moe_mid(p, st);
+  launch_moe_down(p, s, status, st);
+  launch_moe_combine(p, false, st);
+  last_rows = rows;
+}
+
+// Expert parallel: all ranks' rows come in; routing runs on all of them (replicated), the plan keeps only this object's
+// experts, and the shared expert is added for the caller's own rows only. y is this rank's summand of the block output.
+void Moe::forward_ep(const float *x, int rows, int own_row0, int own_rows, float *y, cudaStream_t st) {
+  MoeParams p = params(x, rows, y);
+  IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= rows, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, rows);
+  p.sh_row0 = own_row0;
+  p.sh_rows = own_rows;
   const MoeSplits &s = splits(rows);
   launch_moe_router(p, true, st);
   launch_moe_prep(p, st);
@@ -199,6 +217,13 @@ NE_API int ne_moe_forward_routed(ne_moe *m, const float *x_dev, const uint32_t *
   return c_call([&] {
     IJ_CHECK(m && x_dev && route_dev && y_partial_dev, "null argument");
     reinterpret_cast<Moe *>(m)->forward_routed(x_dev, route_dev, rows, y_partial_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, int own_row0, int own_rows, float *y_part_dev,
+                             void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_all_dev && y_part_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->forward_ep(x_all_dev, rows_all, own_row0, own_rows, y_part_dev, (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes) {

@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
       for (int j = 0; j < 4; j++) vals[warp][lane + 32 * j] = v[j] * sc[j] * wk;
     }
   } else if (warp == k) {
-    const bool on = !routed_only && p.has_shared;
+    const bool on = !routed_only && p.has_shared && r >= p.sh_row0 && r < p.sh_row0 + p.sh_rows;
     if (lane == 0) used[k] = on ? 1 : 0;
     if (on) {
       float v[4];

@@ -48,6 +48,9 @@ struct MoeParams {
   const float *inj;        // [rows][2 HC]
   float *h_out;            // [rows][HC][H]
   int HC;
+  // rows [sh_row0, sh_row0 + sh_rows) get the shared-expert term in the combine (expert parallel: a rank adds it only
+  // for the rows it owns, so that the sum over ranks contains it once); single GPU: 0, rows
+  int sh_row0, sh_rows;
 };
 
 // plan[] layout (ints): [0] = number of distinct local experts nu; then four arrays of PMAXU = P entries each:

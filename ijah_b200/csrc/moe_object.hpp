@@ -36,6 +36,7 @@ struct Moe {
   const MoeSplits &splits(int rows);
   void stage(int stage_no, const float *x, int rows, float *y, cudaStream_t st);
   void forward(const float *x, int rows, float *y, cudaStream_t st);
+  void forward_ep(const float *x, int rows, int own_row0, int own_rows, float *y, cudaStream_t st);
   void forward_routed(const float *x, const uint32_t *route_in, int rows, float *y, cudaStream_t st);
 };
 

@@ -98,6 +98,7 @@ SIGNATURES = {
     "ne_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "ne_moe_stage": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "ne_moe_experts_gu": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "ne_moe_last_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
@@ -436,6 +437,15 @@ class MoeBlock:
         y = torch.empty((rows, self.H), dtype=torch.float32, device=x.device) if out is None else out
         self.eng._ok(self.eng.lib.ne_moe_forward_routed(self.ptr, _dev(x), _dev(route), rows, _dev(y), _stream()),
                      "ne_moe_forward_routed")
+        return y
+
+    def forward_ep(self, x_all, own_row0, own_rows, out=None):
+        """this rank's summand of the block output for the rows of all ranks (ne_moe_forward_ep)"""
+        torch = _torch()
+        rows = x_all.shape[0]
+        y = torch.empty((rows, self.H), dtype=torch.float32, device=x_all.device) if out is None else out
+        self.eng._ok(self.eng.lib.ne_moe_forward_ep(self.ptr, _dev(x_all), rows, own_row0, own_rows, _dev(y), _stream()),
+                     "ne_moe_forward_ep")
         return y
 
     def buffer(self, name, dtype=np.float32):

@@ -81,6 +81,12 @@ NE_API int ne_moe_stage(ne_moe *m, int stage, const float *x_dev, int rows, floa
  * y_partial[rows][hidden]. The caller adds the partial sums of all ranks. */
 NE_API int ne_moe_forward_routed(ne_moe *m, const float *x_dev, const uint32_t *route_dev, int rows, float *y_partial_dev,
                                  void *stream);
+/* Expert parallel, whole block (new with this library; the reference is single-device): x_all holds the rows of ALL
+ * ranks, [own_row0, own_row0 + own_rows) being the caller's. Routing runs on every row (same result on every rank),
+ * only the slots whose expert lies in this object's slice are computed, and the shared expert is added for the
+ * caller's own rows only. y_part[rows_all][hidden] is this rank's summand: the sum over ranks is the block output. */
+NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, int own_row0, int own_rows, float *y_part_dev,
+                             void *stream);
 /* Device pointer and size of a named intermediate of the last run: "logits" "route" "shared_gu" "shared_down"
  * "experts_gu_raw" (per k-split partial products [S][rows*top_k][2][inter]) "plan". */
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes);

@@ -62,9 +62,12 @@ def router_logits(w_bf16, x):
     return out
 
 
-def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_gu=False):
+def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_gu=False, expert_range=None,
+                   shared_rows=None):
     """The MoE block in the device arithmetic on a packgen-style tensor dict. Returns dict(logits [M, E+1], ids,
-    weights, routed, shared_gu, shared_down, out[, experts_gu])."""
+    weights, routed, shared_gu, shared_down, out[, experts_gu]). expert_range (e0, e1) keeps only the slots whose
+    expert lies in [e0, e1); shared_rows (r0, n) adds the shared expert for rows [r0, r0 + n) only (the summand one
+    expert-parallel rank contributes)."""
     from . import opref_port as O
     pre = f"language_model.model.layers.{layer}.mlp."
     g = lambda n: np.asarray(tensors[pre + n][1])  # noqa: E731
@@ -83,6 +86,8 @@ def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_g
     for r in range(M):
         for k in range(top_k):
             e = int(ids[r, k])
+            if expert_range is not None and not (expert_range[0] <= e < expert_range[1]):
+                continue
             a = [np.ascontiguousarray(st[p][j][e]) for p in ("gate", "up", "down") for j in range(3)]
             xr = np.ascontiguousarray(x[r])
             L.moe_expert_emul(*[_p(v) for v in a], H, I, K, _p(xr), C.c_double(float(weights[r, k])),
@@ -94,7 +99,12 @@ def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_g
         sgu = np.stack([linear_emul(*sh["gate"], x), linear_emul(*sh["up"], x)], 1)
         act = (sgu[:, 0] / (1.0 + np.exp(-sgu[:, 0]))) * sgu[:, 1]
         sdown = linear_emul(*sh["down"], act.astype(np.float32))
-        out = routed + (1.0 / (1.0 + np.exp(-sg_logit.astype(np.float64))))[:, None] * sdown
+        gate = (1.0 / (1.0 + np.exp(-sg_logit.astype(np.float64))))[:, None]
+        if shared_rows is not None:
+            keep = np.zeros((M, 1))
+            keep[shared_rows[0]:shared_rows[0] + shared_rows[1]] = 1.0
+            gate = gate * keep
+        out = routed + gate * sdown
         res.update(logits=np.concatenate([logits, sg_logit[:, None]], 1), shared_gu=sgu, shared_down=sdown)
     else:
         out = routed

@@ -1,0 +1,69 @@
+"""Host logic of the expert-parallel wrapper (ijah_b200/ep.py) on CPU: 2 gloo ranks, each with half the experts; the
+block is an oracle-backed stand-in with the interface of engine.MoeBlock.forward_ep. The combined output must equal the
+single-rank oracle block."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ijah_b200 import packgen
+from oracle import c_oracle as CO
+
+DIMS = dict(hidden=256, inter=128, experts=16)
+TOPK = 4
+ROWS = 3
+
+
+def _tensors():
+    return packgen.moe_layer(np.random.default_rng(123), **DIMS)
+
+
+def _x(rank):
+    return np.random.default_rng(50 + rank).standard_normal((ROWS, DIMS["hidden"])).astype(np.float16).astype(np.float32)
+
+
+class OracleBlock:
+    def __init__(self, tensors, e0, e1):
+        self.t, self.e0, self.e1, self.H = tensors, e0, e1, DIMS["hidden"]
+
+    def forward_ep(self, x_all, own_row0, own_rows, out=None):
+        r = CO.moe_block_emul(self.t, x_all.numpy(), top_k=TOPK, expert_range=(self.e0, self.e1), shared_rows=(own_row0, own_rows))
+        out.copy_(torch.from_numpy(r["out"]))
+        return out
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ijah_b200 import ep
+        per = DIMS["experts"] // world
+        m = ep.ExpertParallelMoe(OracleBlock(_tensors(), rank * per, (rank + 1) * per))
+        y = m.forward(torch.from_numpy(_x(rank)))
+        y2 = m.forward(torch.from_numpy(_x(rank)))  # buffers are reused on the second call
+        assert torch.equal(y, y2)
+        q.put((rank, y.numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_reproduce_the_single_rank_block():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    t = _tensors()
+    for rank in range(2):
+        want = CO.moe_block_emul(t, _x(rank), top_k=TOPK)["out"]
+        assert np.abs(got[rank] - want).max() / np.abs(want).max() < 1e-5

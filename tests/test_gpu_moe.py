@@ -146,3 +146,21 @@ def test_layer_entry_points(eng, tmp_path):
     with pytest.raises(E.EngineError):
         L.step()
     L.free()
+
+
+def test_forward_ep_summands_add_up_to_the_block(eng):
+    # two expert-parallel "ranks" as two objects on one GPU: rows of both ranks in, each returns its summand
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(12)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=32)
+    x_all = torch.from_numpy(rng.standard_normal((6, 512)).astype(np.float16).astype(np.float32)).cuda()
+    full = E.MoeBlock(eng, t, top_k=4, max_rows=8).forward(x_all).cpu().numpy()
+    total = np.zeros_like(full)
+    for r in range(2):
+        blk = E.MoeBlock(eng, t, top_k=4, max_rows=8, expert_first=16 * r, expert_count=16)
+        part = blk.forward_ep(x_all, 3 * r, 3).cpu().numpy()
+        want = CO.moe_block_emul(t, x_all.cpu().numpy(), top_k=4, expert_range=(16 * r, 16 * r + 16), shared_rows=(3 * r, 3))["out"]
+        assert rel_max(part, want) < 2e-4
+        total += part
+    assert rel_max(total, full) < 1e-5
