@@ -47,6 +47,7 @@ struct LinearProblem {
     un.w = trellis + ((size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * (32u * K);
     return un;
   }
+  __device__ int row_index(const Unit &, int i) const { return i; }
   __device__ const __half *a_row(const Unit &un, int i) const { return xh + (size_t)i * in + un.k0 * 16; }
   __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
     *reinterpret_cast<float2 *>(raw + ((size_t)un.s * rows + row) * out + un.g * 128 + col) = make_float2(v0, v1);

@@ -321,14 +321,14 @@ struct MoeGateUpProblem {
     un.w = w->trellis + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
     return un;
   }
-  __device__ const __half *a_row(const Unit &un, int i) const {
-    if (un.shared) return p.xh_sgu + ((size_t)i * 2 + un.proj) * p.H + un.k0 * 16;
-    return p.xh_gu + ((size_t)PlanView{p.plan, p.P}.pairs()[un.first + i] * 2 + un.proj) * p.H + un.k0 * 16;
+  // row index = the (row, slot) pair for routed units, the activation row for the shared expert
+  __device__ int row_index(const Unit &un, int i) const { return un.shared ? i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
+  __device__ const __half *a_row(const Unit &un, int idx) const {
+    return (un.shared ? p.xh_sgu : p.xh_gu) + ((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16;
   }
-  __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
-    float *dst;
-    if (un.shared) dst = p.raw_sgu + (((size_t)un.s * p.rows + row) * 2 + un.proj) * p.I;
-    else dst = p.raw_gu + (((size_t)un.s * p.P + PlanView{p.plan, p.P}.pairs()[un.first + row]) * 2 + un.proj) * p.I;
+  __device__ void store(const Unit &un, int idx, int col, float v0, float v1) const {
+    float *dst = un.shared ? p.raw_sgu + (((size_t)un.s * p.rows + idx) * 2 + un.proj) * p.I
+                           : p.raw_gu + (((size_t)un.s * p.P + idx) * 2 + un.proj) * p.I;
     *reinterpret_cast<float2 *>(dst + un.g * 128 + col) = make_float2(v0, v1);
   }
 };
@@ -359,14 +359,12 @@ struct MoeDownProblem {
     un.w = (un.shared ? p.sdn.trellis : p.down.trellis) + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
     return un;
   }
-  __device__ const __half *a_row(const Unit &un, int i) const {
-    if (un.shared) return p.xh_sd + (size_t)i * p.I + un.k0 * 16;
-    return p.xh_d + (size_t)PlanView{p.plan, p.P}.pairs()[un.first + i] * p.I + un.k0 * 16;
+  __device__ int row_index(const Unit &un, int i) const { return un.shared ? i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
+  __device__ const __half *a_row(const Unit &un, int idx) const {
+    return (un.shared ? p.xh_sd : p.xh_d) + (size_t)idx * p.I + un.k0 * 16;
   }
-  __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
-    float *dst;
-    if (un.shared) dst = p.raw_sd + ((size_t)un.s * p.rows + row) * p.H;
-    else dst = p.raw_d + ((size_t)un.s * p.P + PlanView{p.plan, p.P}.pairs()[un.first + row]) * p.H;
+  __device__ void store(const Unit &un, int idx, int col, float v0, float v1) const {
+    float *dst = un.shared ? p.raw_sd + ((size_t)un.s * p.rows + idx) * p.H : p.raw_d + ((size_t)un.s * p.P + idx) * p.H;
     *reinterpret_cast<float2 *>(dst + un.g * 128 + col) = make_float2(v0, v1);
   }
 };

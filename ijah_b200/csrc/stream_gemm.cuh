@@ -14,8 +14,9 @@
 // The "problem" type P supplies the unit list and the operand / result addresses:
 //   int  P::num_units() const
 //   Unit P::unit(int u) const                         // where the tiles are, how many k-steps, K, rows, ...
-//   const __half *P::a_row(const Unit&, int i) const  // global address of row i's first element of the unit's k range
-//   void P::store(const Unit&, int row, int col, float v0, float v1) const   // raw output of (row, col..col+1)
+//   int  P::row_index(const Unit&, int i) const       // which operand / result row the unit's i-th row is
+//   const __half *P::a_row(const Unit&, int idx) const  // global address of that row's first element of the unit's k range
+//   void P::store(const Unit&, int idx, int col, float v0, float v1) const   // raw output of (row idx, col..col+1)
 #pragma once
 #include "exl3_decode.cuh"
 #include "pipeline.cuh"
@@ -27,6 +28,8 @@ constexpr int SG_THREADS = 32 * (SG_WARPS + 1);
 constexpr int SG_KS = 8;                  // k-steps per ring stage
 constexpr int SG_MAX_STAGES = 16;
 constexpr int SG_MAX_ASLOTS = 4;
+constexpr int SG_DESC_UNIT_BYTES = 128;   // shared-memory room for one unit descriptor
+constexpr int SG_DESC_BYTES = SG_DESC_UNIT_BYTES + 64 * 4;  // + the row indices of up to 64 rows
 
 struct UnitBase {
   const char *w;       // first tile of the unit: tile (k0, n0)
@@ -43,7 +46,7 @@ struct StreamLayout {  // dynamic shared memory carve-up (host computes, kernel 
   int lda;             // A row stride in halfs (k elements + 8 pad: keeps ldmatrix rows on distinct banks)
   int arows;           // rows per A slot
   int aslots;          // A slots (units the producer may run ahead)
-  __host__ __device__ size_t ring_off() const { return 512; }
+  __host__ __device__ size_t ring_off() const { return 512 + SG_MAX_ASLOTS * SG_DESC_BYTES; }
   __host__ __device__ size_t slot_bytes() const { return (size_t)arows * lda * 2; }
   __host__ __device__ size_t a_off() const { return ring_off() + (size_t)stages * stage_bytes; }
   __host__ __device__ size_t zero_off() const { return a_off() + (size_t)aslots * slot_bytes(); }
@@ -127,11 +130,13 @@ __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int sta
 
 template <class P, int MT>
 __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob, const StreamLayout lay, int *status) {
+  static_assert(sizeof(typename P::Unit) <= SG_DESC_UNIT_BYTES, "unit descriptor too large for its shared-memory slot");
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + SG_MAX_STAGES;
   uint64_t *a_full = empty + SG_MAX_STAGES;
   uint64_t *a_empty = a_full + SG_MAX_ASLOTS;
+  unsigned char *desc = smem + 512;  // per A slot: the unit descriptor, then the row indices of its rows
   unsigned char *ring = smem + lay.ring_off();
   unsigned char *aslot = smem + lay.a_off();
   unsigned char *zrow = smem + lay.zero_off();
@@ -154,17 +159,25 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
 
   if (warp == SG_WARPS) {
     // ---------------------------------------------------------------- producer (one thread)
+    // It alone reads the unit list from global memory; the consumers get each unit's descriptor and row indices
+    // through shared memory together with the A rows, so no consumer ever waits on a global load.
     if (lane != 0) return;
     int stage = 0, slot = 0;
     uint32_t phase = 0, aphase = 0;
     for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
       const typename P::Unit un = prob.unit(u);
-      // A rows of this unit
       if (!mbar_wait(&a_empty[slot], aphase ^ 1u, status, 3)) return;
+      typename P::Unit *du = reinterpret_cast<typename P::Unit *>(desc + (size_t)slot * SG_DESC_BYTES);
+      int *didx = reinterpret_cast<int *>(desc + (size_t)slot * SG_DESC_BYTES + SG_DESC_UNIT_BYTES);
+      *du = un;
       const uint32_t rowb = (uint32_t)un.kc * 32u;
-      mbar_arrive_expect_tx(&a_full[slot], (uint32_t)un.nrows * rowb);
+      mbar_arrive_expect_tx(&a_full[slot], (uint32_t)un.nrows * rowb);  // release: the descriptor is visible to waiters
       unsigned char *adst = aslot + (size_t)slot * lay.slot_bytes();
-      for (int i = 0; i < un.nrows; i++) bulk_g2s(adst + (size_t)i * lay.lda * 2, prob.a_row(un, i), rowb, &a_full[slot]);
+      for (int i = 0; i < un.nrows; i++) {
+        const int idx = prob.row_index(un, i);
+        didx[i] = idx;
+        bulk_g2s(adst + (size_t)i * lay.lda * 2, prob.a_row(un, idx), rowb, &a_full[slot]);
+      }
       if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
       // compressed tiles, SG_KS k-steps per stage
       const uint32_t kb = (uint32_t)un.ntiles * 32u * (uint32_t)un.K, ks = (uint32_t)SG_WARPS * 32u * (uint32_t)un.K;
@@ -190,7 +203,15 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
   const uint32_t ring_addr = smem_u32(ring), a0_addr = smem_u32(aslot), z_addr = smem_u32(zrow);
 
   for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
-    const typename P::Unit un = prob.unit(u);
+    if (!mbar_wait(&a_full[slot], aphase, status, 4)) return;
+    const typename P::Unit un = *reinterpret_cast<const typename P::Unit *>(desc + (size_t)slot * SG_DESC_BYTES);
+    const int *didx = reinterpret_cast<const int *>(desc + (size_t)slot * SG_DESC_BYTES + SG_DESC_UNIT_BYTES);
+    int idx[MT][2];  // row indices of the accumulator rows this lane holds (rows g and g + 8 of every 16-row tile)
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+      idx[m][0] = m * 16 + g < un.nrows ? didx[m * 16 + g] : -1;
+      idx[m][1] = m * 16 + g + 8 < un.nrows ? didx[m * 16 + g + 8] : -1;
+    }
     const uint32_t a_addr = a0_addr + (uint32_t)slot * (uint32_t)lay.slot_bytes();
     uint32_t a_rowoff[MT];
 #pragma unroll
@@ -206,7 +227,6 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[m][h][j] = 0.0f;
 
-    if (!mbar_wait(&a_full[slot], aphase, status, 4)) return;
     const bool live = warp < un.ntiles;
     bool ok;
     switch (un.K) {
@@ -218,7 +238,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
     }
     if (!ok) return;
     __syncwarp();
-    if (lane == 0) mbar_arrive(&a_empty[slot]);
+    if (lane == 0) mbar_arrive(&a_empty[slot]);  // descriptor and A rows are in registers / consumed: slot may be refilled
     if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
     if (live) {
       const int col = warp * 16 + 2 * q;
@@ -226,9 +246,8 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
       for (int m = 0; m < MT; m++)
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-          const int r0 = m * 16 + g;
-          if (r0 < un.nrows) prob.store(un, r0, col + 8 * h, acc[m][h][0], acc[m][h][1]);
-          if (r0 + 8 < un.nrows) prob.store(un, r0 + 8, col + 8 * h, acc[m][h][2], acc[m][h][3]);
+          if (idx[m][0] >= 0) prob.store(un, idx[m][0], col + 8 * h, acc[m][h][0], acc[m][h][1]);
+          if (idx[m][1] >= 0) prob.store(un, idx[m][1], col + 8 * h, acc[m][h][2], acc[m][h][3]);
         }
     }
   }
