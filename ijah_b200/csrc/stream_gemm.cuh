@@ -21,6 +21,12 @@
 #include "exl3_decode.cuh"
 #include "pipeline.cuh"
 
+// SG_DBG: timing-only builds that answer "is it the decode, the MMA or the bytes" (results are wrong on purpose):
+// 1 = decode but no MMA, 2 = MMA on the undecoded words. 0 = the product.
+#ifndef SG_DBG
+#define SG_DBG 0
+#endif
+
 namespace ijah {
 
 constexpr int SG_WARPS = 8;               // consumer warps = output tiles per unit
@@ -67,14 +73,22 @@ __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
                : "r"(addr), "n"(OFF));
 }
 
-// k-tile I of a stage for one output tile: 3 words -> 8 weights -> 2 MMAs per 16-row tile. p0..p2 / a_row[m] are the
-// addresses for k-tile 0; tile I sits I * KSTEP further in the ring and I * 32 bytes further in the A rows.
+// k-tile I of a stage for one output tile: 3 words -> 8 weights -> 2 MMAs per 16-row tile. a_row[m] is the ldmatrix
+// address for k-tile 0 of the stage; tile I sits I * 32 bytes further in the A rows.
 template <int K, int MT, int I>
-__device__ __forceinline__ void tile_mma(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t la, const uint32_t (&a_row)[MT],
+__device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t la, const uint32_t (&a_row)[MT],
                                          float (&acc)[MT][2][4]) {
-  constexpr int KSTEP = SG_WARPS * Codec<K>::TILE_BYTES;
   uint32_t b[4];
-  dec8<K>(lds32<I * KSTEP>(p0), lds32<I * KSTEP>(p1), lds32<I * KSTEP>(p2), la, b);
+#if SG_DBG == 2  // timing only: no decode, the raw words go to the tensor core
+  b[0] = w0; b[1] = w1; b[2] = w2; b[3] = w0 ^ la;
+#else
+  dec8<K>(w0, w1, w2, la, b);
+#endif
+#if SG_DBG == 1  // timing only: decode without the MMA
+  acc[0][0][0] = __uint_as_float(__float_as_uint(acc[0][0][0]) ^ b[0] ^ b[1]);
+  acc[0][1][0] = __uint_as_float(__float_as_uint(acc[0][1][0]) ^ b[2] ^ b[3]);
+  (void)a_row;
+#else
 #pragma unroll
   for (int m = 0; m < MT; m++) {
     uint32_t a[4];
@@ -82,24 +96,29 @@ __device__ __forceinline__ void tile_mma(uint32_t p0, uint32_t p1, uint32_t p2, 
     mma_16816(acc[m][0], a, b[0], b[1]);
     mma_16816(acc[m][1], a, b[2], b[3]);
   }
+#endif
 }
+// A stage's SG_KS k-tiles: all window words are loaded first (3 * SG_KS independent shared loads in flight), then
+// decoded and multiplied tile by tile. N = tiles live in this stage (compile-time SG_KS for full stages).
 template <int K, int MT, int I, int N>
 struct TileLoop {
-  static __device__ __forceinline__ void run(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t la, const uint32_t (&a_row)[MT],
-                                             float (&acc)[MT][2][4], int n) {
-    if (I < n) tile_mma<K, MT, I>(p0, p1, p2, la, a_row, acc);
-    TileLoop<K, MT, I + 1, N>::run(p0, p1, p2, la, a_row, acc, n);
+  static constexpr int KSTEP = SG_WARPS * Codec<K>::TILE_BYTES;
+  static __device__ __forceinline__ void load(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t (&w)[SG_KS][3]) {
+    w[I][0] = lds32<I * KSTEP>(p0);
+    w[I][1] = lds32<I * KSTEP>(p1);
+    w[I][2] = lds32<I * KSTEP>(p2);
+    TileLoop<K, MT, I + 1, N>::load(p0, p1, p2, w);
   }
-  static __device__ __forceinline__ void run_all(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t la,
-                                                 const uint32_t (&a_row)[MT], float (&acc)[MT][2][4]) {
-    tile_mma<K, MT, I>(p0, p1, p2, la, a_row, acc);
-    TileLoop<K, MT, I + 1, N>::run_all(p0, p1, p2, la, a_row, acc);
+  static __device__ __forceinline__ void run(const uint32_t (&w)[SG_KS][3], uint32_t la, const uint32_t (&a_row)[MT],
+                                             float (&acc)[MT][2][4], int n) {
+    if (I < n) tile_mma<K, MT, I>(w[I][0], w[I][1], w[I][2], la, a_row, acc);
+    TileLoop<K, MT, I + 1, N>::run(w, la, a_row, acc, n);
   }
 };
 template <int K, int MT, int N>
 struct TileLoop<K, MT, N, N> {
-  static __device__ __forceinline__ void run(uint32_t, uint32_t, uint32_t, uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4], int) {}
-  static __device__ __forceinline__ void run_all(uint32_t, uint32_t, uint32_t, uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4]) {}
+  static __device__ __forceinline__ void load(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_KS][3]) {}
+  static __device__ __forceinline__ void run(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4], int) {}
 };
 
 // All k-steps of one unit for one warp. Returns false if a bounded wait gave up.
@@ -118,8 +137,9 @@ __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int sta
       uint32_t a_row[MT];
 #pragma unroll
       for (int m = 0; m < MT; m++) a_row[m] = a_addr + a_rowoff[m] + (uint32_t)k * 32u;
-      if (kc - k >= SG_KS) TileLoop<K, MT, 0, SG_KS>::run_all(p0, p1, p2, L.a, a_row, acc);
-      else TileLoop<K, MT, 0, SG_KS>::run(p0, p1, p2, L.a, a_row, acc, kc - k);
+      uint32_t w[SG_KS][3];
+      TileLoop<K, MT, 0, SG_KS>::load(p0, p1, p2, w);  // a short last stage loads stale ring bytes it never uses
+      TileLoop<K, MT, 0, SG_KS>::run(w, L.a, a_row, acc, min(SG_KS, kc - k));
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[stage]);
@@ -158,37 +178,51 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
   const int nunits = prob.num_units();
 
   if (warp == SG_WARPS) {
-    // ---------------------------------------------------------------- producer (one thread)
-    // It alone reads the unit list from global memory; the consumers get each unit's descriptor and row indices
-    // through shared memory together with the A rows, so no consumer ever waits on a global load.
-    if (lane != 0) return;
+    // ---------------------------------------------------------------- producer (one warp, lanes work in parallel)
+    // Only this warp reads the unit list from global memory; the consumers get each unit's descriptor and row indices
+    // through shared memory together with the A rows, so no consumer ever waits on a global load. The next unit's
+    // descriptor is fetched while the current unit's copies are issued, and lane i issues copy i, so the metadata
+    // latency and the issue cost of the copies stay off the critical path.
     int stage = 0, slot = 0;
     uint32_t phase = 0, aphase = 0;
-    for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
-      const typename P::Unit un = prob.unit(u);
+    int u = blockIdx.x;
+    typename P::Unit un;
+    if (u < nunits) un = prob.unit(u);
+    while (u < nunits) {
+      const int u_next = u + gridDim.x;
+      typename P::Unit nx;
+      if (u_next < nunits) nx = prob.unit(u_next);
+      const int i0 = lane < un.nrows ? prob.row_index(un, lane) : 0;
+      const int i1 = lane + 32 < un.nrows ? prob.row_index(un, lane + 32) : 0;
       if (!mbar_wait(&a_empty[slot], aphase ^ 1u, status, 3)) return;
       typename P::Unit *du = reinterpret_cast<typename P::Unit *>(desc + (size_t)slot * SG_DESC_BYTES);
       int *didx = reinterpret_cast<int *>(desc + (size_t)slot * SG_DESC_BYTES + SG_DESC_UNIT_BYTES);
-      *du = un;
+      didx[lane] = i0;
+      didx[lane + 32] = i1;
       const uint32_t rowb = (uint32_t)un.kc * 32u;
-      mbar_arrive_expect_tx(&a_full[slot], (uint32_t)un.nrows * rowb);  // release: the descriptor is visible to waiters
-      unsigned char *adst = aslot + (size_t)slot * lay.slot_bytes();
-      for (int i = 0; i < un.nrows; i++) {
-        const int idx = prob.row_index(un, i);
-        didx[i] = idx;
-        bulk_g2s(adst + (size_t)i * lay.lda * 2, prob.a_row(un, idx), rowb, &a_full[slot]);
+      __syncwarp();
+      if (lane == 0) {
+        *du = un;
+        mbar_arrive_expect_tx(&a_full[slot], (uint32_t)un.nrows * rowb);  // release: descriptor and indices are visible
       }
+      __syncwarp();
+      unsigned char *adst = aslot + (size_t)slot * lay.slot_bytes();
+      if (lane < un.nrows) bulk_g2s(adst + (size_t)lane * lay.lda * 2, prob.a_row(un, i0), rowb, &a_full[slot]);
+      if (lane + 32 < un.nrows) bulk_g2s(adst + (size_t)(lane + 32) * lay.lda * 2, prob.a_row(un, i1), rowb, &a_full[slot]);
       if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
-      // compressed tiles, SG_KS k-steps per stage
+      // compressed tiles, SG_KS k-steps per stage, lane i copies k-step i
       const uint32_t kb = (uint32_t)un.ntiles * 32u * (uint32_t)un.K, ks = (uint32_t)SG_WARPS * 32u * (uint32_t)un.K;
       for (int k = 0; k < un.kc; k += SG_KS) {
         const int n = min(SG_KS, un.kc - k);
         if (!mbar_wait(&empty[stage], phase ^ 1u, status, 1)) return;
-        mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
-        unsigned char *dst = ring + (size_t)stage * lay.stage_bytes;
-        for (int i = 0; i < n; i++) bulk_g2s(dst + i * ks, un.w + (size_t)(k + i) * un.kstride, kb, &full[stage]);
+        if (lane == 0) mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
+        __syncwarp();
+        if (lane < n)
+          bulk_g2s(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k + lane) * un.kstride, kb, &full[stage]);
         if (++stage == lay.stages) { stage = 0; phase ^= 1u; }
       }
+      un = nx;
+      u = u_next;
     }
     return;
   }
