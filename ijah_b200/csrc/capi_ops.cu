@@ -53,6 +53,53 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
 
 Moe::~Moe() {
   for (void *p : owned) cudaFree(p);
+  for (void *p : pf_owned) cudaFree(p);
+}
+
+// Prefill: n tokens at once through the sorted / grouped path (pf_moe.cu). Scratch grows with the largest n seen.
+void Moe::prefill(const float *x, int n, float *y, cudaStream_t st) {
+  IJ_CHECK(desc.expert_first == 0 && desc.expert_count == desc.experts, "prefill runs on an object that holds all experts");
+  IJ_CHECK(n >= 1 && n <= 65535, "prefill: %d tokens outside 1..65535", n);
+  const size_t H = desc.hidden, I = desc.inter, E = desc.experts, k = desc.top_k;
+  if (n > pf_tokens) {
+    IJ_CUDA(cudaDeviceSynchronize());
+    for (void *p : pf_owned) cudaFree(p);
+    pf_owned.clear();
+    auto al = [&](size_t b) { void *p = nullptr; IJ_CUDA(cudaMalloc(&p, std::max<size_t>(b, 16))); pf_owned.push_back(p); return p; };
+    const size_t S = (size_t)n * k, cap = pf_pos_cap(n, (int)k, (int)E, has_shared);
+    const size_t passes = S / PF_NTOK + E + n / PF_NTOK + 2;
+    pf.logits = (float *)al((size_t)n * (E + 1) * 4);
+    pf.route = (uint32_t *)al((size_t)n * 2 * k * 4);
+    pf.cnt = (int *)al(E * 4);
+    pf.off = (int *)al((E + 2) * 4);
+    pf.rank = (int *)al(S * 4);
+    pf.inv = (int *)al(S * 4);
+    pf.order = (int *)al(cap * 4);
+    pf.seid = (int *)al(cap * 4);
+    pf.xh_g = (__half *)al(cap * H * 2);
+    pf.xh_u = (__half *)al(cap * H * 2);
+    pf.raw_gu = (float *)al(cap * 2 * I * 4);
+    pf.xh_d = (__half *)al(cap * I * 2);
+    pf.raw_d = (float *)al(cap * H * 4);
+    pf.items_gu = (PfItem *)al(passes * 2 * (I / PF_NCOL) * sizeof(PfItem));
+    pf.items_d = (PfItem *)al(passes * (H / PF_NCOL) * sizeof(PfItem));
+    pf.nitems = (int *)al(16);
+    pf.sho = (float *)al((size_t)n * H * 4);
+    pf.pos_cap = (int)cap;
+    pf_tokens = n;
+  }
+  PfParams p = pf;
+  p.H = (int)H; p.I = (int)I; p.E = (int)E; p.topk = (int)k; p.Kx = desc.k_expert; p.Ks = desc.k_shared; p.has_shared = has_shared ? 1 : 0;
+  p.n = n; p.S = n * (int)k;
+  p.pos_cap = (int)pf_pos_cap(n, (int)k, (int)E, has_shared);
+  p.router = (const uint16_t *)desc.router_dev;
+  p.sgate = (const uint16_t *)desc.shared_gate_w_dev;
+  auto stack = [](const ne_exl3_stack &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
+  auto single = [](const ne_exl3_weight &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
+  p.gate = stack(desc.gate); p.up = stack(desc.up); p.down = stack(desc.down);
+  p.sgt = single(desc.sh_gate); p.sup = single(desc.sh_up); p.sdn = single(desc.sh_down);
+  p.x = x; p.y = y;
+  launch_pf_moe(p, status, st);
 }
 
 MoeParams Moe::params(const float *x, int rows, float *y) {
@@ -224,6 +271,12 @@ NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, in
   return c_call([&] {
     IJ_CHECK(m && x_all_dev && y_part_dev, "null argument");
     reinterpret_cast<Moe *>(m)->forward_ep(x_all_dev, rows_all, own_row0, own_rows, y_part_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_dev && y_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->prefill(x_dev, n_tokens, y_dev, (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes) {

@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 
 #include "fn_moe.cuh"
+#include "pf_moe.cuh"
 
 namespace ijah {
 
@@ -28,6 +29,11 @@ struct Moe {
   float *h_out = nullptr;
   int HC = 0;
   std::map<int, MoeSplits> split_cache;
+  // prefill scratch, (re)allocated when a call brings more tokens than any before it
+  PfParams pf{};
+  int pf_tokens = 0;
+  std::vector<void *> pf_owned;
+  void prefill(const float *x, int n, float *y, cudaStream_t st);
 
   Moe(const ne_moe_desc &d, int max_rows);
   ~Moe();

@@ -1,0 +1,63 @@
+// Prefill MoE: tokens sorted by expert, grouped trellis GEMM on tcgen05 / TMEM, slot-ordered finish.
+// Replaces the reference's kernels/prefill/pf_moe.metal (pf_moe_count / scan / place / prep / gemm / mid / finish,
+// recorded by models/flash_next/prefill.mm:235-276) and the router part of kernels/prefill/pf_trunk.metal:278-334.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "fn_moe.cuh"
+
+namespace ijah {
+
+constexpr int PF_NTOK = 128;   // token rows per GEMM pass (the N of the MMA)
+constexpr int PF_NCOL = 256;   // output columns per work item (two M = 128 accumulators)
+
+// One pass of the grouped GEMM: rows [row0, row0 + nrows) of the sorted (8-row padded) position space, all of one
+// expert, times 256 output columns of one projection.
+struct PfItem {
+  int expert;   // local expert index, or -1 for the shared expert
+  int proj;     // gate/up launch: 0 gate, 1 up; down launch: 0
+  int ngpair;   // which block of 256 output columns
+  int row0;     // first position (multiple of 8)
+  int nrows;    // 1..PF_NTOK
+  int pad[3];
+};
+
+struct PfParams {
+  int H, I, E, topk, Kx, Ks, has_shared;
+  int n;           // tokens
+  int S;           // n * topk slots
+  int pos_cap;     // capacity of the padded position space
+  // weights
+  const uint16_t *router, *sgate;
+  Exl3Stack gate, up, down, sgt, sup, sdn;
+  // activations / scratch
+  const float *x;        // [n][H]
+  float *logits;         // [n][E + 1]
+  uint32_t *route;       // [n][2 topk]
+  int *cnt;              // [E] slots per expert
+  int *off;              // [E + 2] first position of each expert (8-row padded); [E] = first shared position, [E + 1] = end
+  int *rank;             // [S] index of the slot among its expert's slots, in slot order
+  int *inv;              // [S] slot -> position
+  int *order;            // [pos_cap] position -> slot (S + t = shared row of token t, -1 = padding), rewritten every run
+  int *seid;             // [pos_cap] position -> expert (E = shared, -1 = padding), rewritten every run
+  __half *xh_g, *xh_u;   // [pos_cap / 8][H / 8][8][8] blocked operands (see blocked_index)
+  float *raw_gu;         // [pos_cap][2][I]
+  __half *xh_d;          // [pos_cap / 8][I / 8][8][8]
+  float *raw_d;          // [pos_cap][H]
+  PfItem *items_gu, *items_d;
+  int *nitems;           // [2]: gate/up items, down items
+  float *y;              // [n][H]
+  float *sho;            // [n][H] finished shared down (inspection)
+};
+
+// element (pos, k) of a blocked operand with `in` columns: core matrices of 8 positions x 8 k, 128 contiguous bytes each,
+// the in/8 core matrices of one 8-position group contiguous. A GEMM stage (8 k-chunks of one group) is 1 KB contiguous.
+__host__ __device__ inline size_t blocked_index(int pos, int k, int in) {
+  return (((size_t)(pos >> 3) * (in >> 3) + (k >> 3)) << 6) + ((pos & 7) << 3) + (k & 7);
+}
+
+size_t pf_pos_cap(int n, int topk, int E, bool has_shared);
+void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st);
+
+}  // namespace ijah

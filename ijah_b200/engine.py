@@ -98,6 +98,7 @@ SIGNATURES = {
     "ne_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "ne_moe_stage": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "ne_moe_experts_gu": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
@@ -437,6 +438,14 @@ class MoeBlock:
         y = torch.empty((rows, self.H), dtype=torch.float32, device=x.device) if out is None else out
         self.eng._ok(self.eng.lib.ne_moe_forward_routed(self.ptr, _dev(x), _dev(route), rows, _dev(y), _stream()),
                      "ne_moe_forward_routed")
+        return y
+
+    def prefill(self, x, out=None):
+        """n tokens at once through the sorted / grouped tcgen05 path (ne_moe_prefill); x [n, H] float32 on the device"""
+        torch = _torch()
+        n = x.shape[0]
+        y = torch.empty((n, self.H), dtype=torch.float32, device=x.device) if out is None else out
+        self.eng._ok(self.eng.lib.ne_moe_prefill(self.ptr, _dev(x), n, _dev(y), _stream()), "ne_moe_prefill")
         return y
 
     def forward_ep(self, x_all, own_row0, own_rows, out=None):

@@ -81,6 +81,13 @@ NE_API int ne_moe_stage(ne_moe *m, int stage, const float *x_dev, int rows, floa
  * y_partial[rows][hidden]. The caller adds the partial sums of all ranks. */
 NE_API int ne_moe_forward_routed(ne_moe *m, const float *x_dev, const uint32_t *route_dev, int rows, float *y_partial_dev,
                                  void *stream);
+/* Prefill: y[n][hidden] for n tokens at once (1..65535), same result definition as ne_moe_forward. Replaces the
+ * reference's chunked-prefill MoE (models/flash_next/prefill.mm:235-276 record_moe; kernels/prefill/pf_moe.metal):
+ * router GEMM + top-k, deterministic counting sort of the n*top_k slots by expert, per-expert grouped GEMMs whose
+ * trellis tiles are decoded into shared memory once per 128 rows and multiplied on tcgen05 tensor cores with TMEM
+ * accumulators, SwiGLU, slot-ordered finish. The object must hold all experts; hidden and inter must be multiples of
+ * 256. Scratch (about 300 KB per token) is allocated on the first call and grown when a later call brings more tokens. */
+NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_dev, void *stream);
 /* Expert parallel, whole block (new with this library; the reference is single-device): x_all holds the rows of ALL
  * ranks, [own_row0, own_row0 + own_rows) being the caller's. Routing runs on every row (same result on every rank),
  * only the slots whose expert lies in this object's slice are computed, and the shared expert is added for the

@@ -1,0 +1,76 @@
+"""CUDA prefill MoE (sorted tokens, tcgen05 grouped GEMM) against the decode path and the oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from ijah_b200 import packgen
+from oracle import c_oracle as CO
+from tests.helpers import rel_max
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    import torch
+    assert torch.cuda.is_available()
+    from ijah_b200 import engine as E
+    return E.Engine()
+
+
+def test_prefill_matches_oracle_small(eng):
+    # 37 tokens, 32 experts top-4: some experts empty, some with several rows, ragged 8-row padding everywhere
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(21)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=32)
+    x = rng.standard_normal((37, 512)).astype(np.float16).astype(np.float32)
+    blk = E.MoeBlock(eng, t, top_k=4, max_rows=16)
+    y = blk.prefill(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert eng.lib.ne_device_wait_status() == 0
+    want = CO.moe_block_emul(t, x, top_k=4)
+    assert rel_max(y, want["out"]) < 2e-4
+    y2 = blk.prefill(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.array_equal(y, y2), "two runs must be bit-identical"
+
+
+def test_prefill_equals_decode_path_with_skewed_routing(eng):
+    # 300 tokens whose routing is skewed so that one expert gets more than 128 rows (several passes) and many get none;
+    # the decode-width kernels (16 rows per call) are the reference here
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(22)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=32)
+    pre = "language_model.model.layers.0.mlp."
+    x = rng.standard_normal((300, 512)).astype(np.float16).astype(np.float32)
+    # bias the router: add a common direction to x and to the rows of a few experts
+    d = rng.standard_normal(512).astype(np.float32)
+    x = (x + 1.5 * d).astype(np.float16).astype(np.float32)
+    from oracle import opref_port as O
+    w = O.bf16_bits_to_f32(t[pre + "gate.weight"][1]).copy()
+    w[:3] += 0.02 * d
+    t[pre + "gate.weight"] = ("BF16", O.f32_to_bf16_bits(w))
+    blk = E.MoeBlock(eng, t, top_k=4, max_rows=16)
+    xd = torch.from_numpy(x).cuda()
+    y = blk.prefill(xd).cpu().numpy()
+    assert eng.lib.ne_device_wait_status() == 0
+    ref = np.concatenate([blk.forward(xd[i:i + 16]).cpu().numpy() for i in range(0, 300, 16)])
+    assert rel_max(y, ref) < 2e-4  # fp32 accumulation order differs (tcgen05 vs mma.sync + k-splits)
+    ids = np.concatenate([CO.moe_block_emul(t, x[i:i + 1], top_k=4)["ids"] for i in range(0, 300, 37)])
+    assert ids.shape[1] == 4
+
+
+def test_prefill_at_model_dims(eng):
+    # hidden 2048, intermediate 768, K5 / K6, top-10 of 64 experts, 200 tokens; decode path as the reference
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(23)
+    t = packgen.moe_layer(rng, hidden=2048, inter=768, experts=64)
+    x = rng.standard_normal((200, 2048)).astype(np.float16).astype(np.float32)
+    blk = E.MoeBlock(eng, t, top_k=10, max_rows=16)
+    xd = torch.from_numpy(x).cuda()
+    y = blk.prefill(xd).cpu().numpy()
+    assert eng.lib.ne_device_wait_status() == 0
+    ref = np.concatenate([blk.forward(xd[i:i + 16]).cpu().numpy() for i in range(0, 200, 16)])
+    assert rel_max(y, ref) < 2e-4  # fp32 accumulation order differs (tcgen05 vs mma.sync + k-splits)
+    want = CO.moe_block_emul(t, x[:3], top_k=10)
+    assert rel_max(y[:3], want["out"]) < 2e-4
