@@ -114,11 +114,17 @@ struct TileLoop {
     if (I < n) tile_mma<K, MT, I>(w[I][0], w[I][1], w[I][2], la, a_row, acc);
     TileLoop<K, MT, I + 1, N>::run(w, la, a_row, acc, n);
   }
+  static __device__ __forceinline__ void run_all(const uint32_t (&w)[SG_KS][3], uint32_t la, const uint32_t (&a_row)[MT],
+                                                 float (&acc)[MT][2][4]) {  // straight-line: the tiles interleave freely
+    tile_mma<K, MT, I>(w[I][0], w[I][1], w[I][2], la, a_row, acc);
+    TileLoop<K, MT, I + 1, N>::run_all(w, la, a_row, acc);
+  }
 };
 template <int K, int MT, int N>
 struct TileLoop<K, MT, N, N> {
   static __device__ __forceinline__ void load(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_KS][3]) {}
   static __device__ __forceinline__ void run(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4], int) {}
+  static __device__ __forceinline__ void run_all(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4]) {}
 };
 
 // All k-steps of one unit for one warp. Returns false if a bounded wait gave up.
@@ -139,7 +145,8 @@ __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int sta
       for (int m = 0; m < MT; m++) a_row[m] = a_addr + a_rowoff[m] + (uint32_t)k * 32u;
       uint32_t w[SG_KS][3];
       TileLoop<K, MT, 0, SG_KS>::load(p0, p1, p2, w);  // a short last stage loads stale ring bytes it never uses
-      TileLoop<K, MT, 0, SG_KS>::run(w, L.a, a_row, acc, min(SG_KS, kc - k));
+      if (kc - k >= SG_KS) TileLoop<K, MT, 0, SG_KS>::run_all(w, L.a, a_row, acc);
+      else TileLoop<K, MT, 0, SG_KS>::run(w, L.a, a_row, acc, kc - k);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[stage]);
