@@ -47,7 +47,7 @@ LinearPlan plan_linear(int in, int out, int K, int rows) {
   p.in = in; p.out = out; p.K = K; p.rows = rows;
   p.IT = in / 16; p.OT = out / 16; p.NG = (p.OT + SG_WARPS - 1) / SG_WARPS;
   p.hi = had_size(in); p.ho = had_size(out);
-  p.MT = rows <= 16 ? 1 : rows <= 32 ? 2 : 4;
+  p.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
   p.grid = 2 * sm_count();
   choose_split(p.IT, p.NG, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
   p.lay = make_layout(K, p.kc, rows, 2);

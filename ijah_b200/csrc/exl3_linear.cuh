@@ -14,7 +14,7 @@ struct LinearPlan {
   int IT, OT, NG;     // k-tiles, n-tiles, n-groups of 8 tiles
   int S, kc;          // k-splits and k-tiles per split
   int hi, ho;         // Hadamard sizes
-  int MT;             // 16-row MMA tiles
+  int MT;             // 8-row groups per unit (1, 2, 4, 8)
   StreamLayout lay;
   int grid;
   size_t raw_floats() const { return (size_t)S * rows * out; }
@@ -49,8 +49,8 @@ struct LinearProblem {
   }
   __device__ int row_index(const Unit &, int i) const { return i; }
   __device__ const __half *a_row(const Unit &un, int i) const { return xh + (size_t)i * in + un.k0 * 16; }
-  __device__ void store(const Unit &un, int row, int col, float v0, float v1) const {
-    *reinterpret_cast<float2 *>(raw + ((size_t)un.s * rows + row) * out + un.g * 128 + col) = make_float2(v0, v1);
+  __device__ void store(const Unit &un, int row, int col, float v) const {
+    raw[((size_t)un.s * rows + row) * out + un.g * 128 + col] = v;
   }
 };
 

@@ -326,10 +326,10 @@ struct MoeGateUpProblem {
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sgu : p.xh_gu) + ((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16;
   }
-  __device__ void store(const Unit &un, int idx, int col, float v0, float v1) const {
+  __device__ void store(const Unit &un, int idx, int col, float v) const {
     float *dst = un.shared ? p.raw_sgu + (((size_t)un.s * p.rows + idx) * 2 + un.proj) * p.I
                            : p.raw_gu + (((size_t)un.s * p.P + idx) * 2 + un.proj) * p.I;
-    *reinterpret_cast<float2 *>(dst + un.g * 128 + col) = make_float2(v0, v1);
+    dst[un.g * 128 + col] = v;
   }
 };
 
@@ -363,9 +363,9 @@ struct MoeDownProblem {
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sd : p.xh_d) + (size_t)idx * p.I + un.k0 * 16;
   }
-  __device__ void store(const Unit &un, int idx, int col, float v0, float v1) const {
+  __device__ void store(const Unit &un, int idx, int col, float v) const {
     float *dst = un.shared ? p.raw_sd + ((size_t)un.s * p.rows + idx) * p.H : p.raw_d + ((size_t)un.s * p.P + idx) * p.H;
-    *reinterpret_cast<float2 *>(dst + un.g * 128 + col) = make_float2(v0, v1);
+    dst[un.g * 128 + col] = v;
   }
 };
 
@@ -445,7 +445,7 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
   IJ_CHECK(Kx >= 4 && Kx <= 8 && (!has_shared || (Ks >= 4 && Ks <= 8)), "bits per weight outside 4..8");
   MoeSplits s{};
-  s.MT = rows <= 16 ? 1 : rows <= 32 ? 2 : 4;
+  s.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
   s.grid = 2 * sm_count();
   // expected number of distinct experts under uniform routing; any actual count works, this only tunes the k-split
   const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows));

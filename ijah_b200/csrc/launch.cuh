@@ -23,6 +23,7 @@ void launch_stream(const P &prob, int MT, const StreamLayout &lay, int grid, int
     case 1: launch_stream_mt<P, 1>(prob, lay, grid, status, st); break;
     case 2: launch_stream_mt<P, 2>(prob, lay, grid, status, st); break;
     case 4: launch_stream_mt<P, 4>(prob, lay, grid, status, st); break;
+    case 8: launch_stream_mt<P, 8>(prob, lay, grid, status, st); break;
     default: fail("unsupported row tile count %d", MT);
   }
 }

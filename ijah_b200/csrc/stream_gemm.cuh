@@ -16,7 +16,7 @@
 //   Unit P::unit(int u) const                         // where the tiles are, how many k-steps, K, rows, ...
 //   int  P::row_index(const Unit&, int i) const       // which operand / result row the unit's i-th row is
 //   const __half *P::a_row(const Unit&, int idx) const  // global address of that row's first element of the unit's k range
-//   void P::store(const Unit&, int idx, int col, float v0, float v1) const   // raw output of (row idx, col..col+1)
+//   void P::store(const Unit&, int idx, int col, float v) const   // raw output element (row idx, col)
 #pragma once
 #include "exl3_decode.cuh"
 #include "pipeline.cuh"
@@ -43,7 +43,7 @@ struct UnitBase {
   int kc;              // k-tiles in this unit
   int ntiles;          // output tiles (1..8)
   int K;               // bits per weight
-  int nrows;           // live activation rows (<= 16 * MT)
+  int nrows;           // live activation rows (<= 8 * MT)
 };
 
 struct StreamLayout {  // dynamic shared memory carve-up (host computes, kernel mirrors)
@@ -73,11 +73,22 @@ __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
                : "r"(addr), "n"(OFF));
 }
 
-// k-tile I of a stage for one output tile: 3 words -> 8 weights -> 2 MMAs per 16-row tile. a_row[m] is the ldmatrix
-// address for k-tile 0 of the stage; tile I sits I * 32 bytes further in the A rows.
+// k-tile I of a stage for one output tile. The tensor core computes D^T = W'^T * X^T: the decoded tile is the A operand
+// (16 output columns x 16 k; the lane's 8 decoded weights are exactly its A fragment, in the order b0, b2, b1, b3), the
+// activations are the B operand (16 k x 8 rows), so 8 activation rows cost one mma.m16n8k16 per tile. MT = number of
+// 8-row groups (1, 2, 4, 8); a_row[p] is the ldmatrix address of row-group pair p for k-tile 0 of the stage, tile I
+// sits I * 32 bytes further in the A rows. acc[g] = D^T fragment of group g: (column gq, rows 2q, 2q+1), (column gq + 8, ..).
+template <int MT>
+struct RowPairs { static constexpr int N = MT == 1 ? 1 : MT / 2; };
+
+template <int OFF>
+__device__ __forceinline__ void ldsm2(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2+%3];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr), "n"(OFF));
+}
+
 template <int K, int MT, int I>
-__device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t la, const uint32_t (&a_row)[MT],
-                                         float (&acc)[MT][2][4]) {
+__device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t la,
+                                         const uint32_t (&a_row)[RowPairs<MT>::N], float (&acc)[MT][4]) {
   uint32_t b[4];
 #if SG_DBG == 2  // timing only: no decode, the raw words go to the tensor core
   b[0] = w0; b[1] = w1; b[2] = w2; b[3] = w0 ^ la;
@@ -85,53 +96,62 @@ __device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, 
   dec8<K>(w0, w1, w2, la, b);
 #endif
 #if SG_DBG == 1  // timing only: decode without the MMA
-  acc[0][0][0] = __uint_as_float(__float_as_uint(acc[0][0][0]) ^ b[0] ^ b[1]);
-  acc[0][1][0] = __uint_as_float(__float_as_uint(acc[0][1][0]) ^ b[2] ^ b[3]);
+  acc[0][0] = __uint_as_float(__float_as_uint(acc[0][0]) ^ b[0] ^ b[1]);
+  acc[0][1] = __uint_as_float(__float_as_uint(acc[0][1]) ^ b[2] ^ b[3]);
   (void)a_row;
 #else
+  const uint32_t wa[4] = {b[0], b[2], b[1], b[3]};
+  if constexpr (MT == 1) {
+    uint32_t x[2];
+    ldsm2<I * 32>(x, a_row[0]);
+    mma_16816(acc[0], wa, x[0], x[1]);
+  } else {
 #pragma unroll
-  for (int m = 0; m < MT; m++) {
-    uint32_t a[4];
-    ldsm4<I * 32>(a, a_row[m]);
-    mma_16816(acc[m][0], a, b[0], b[1]);
-    mma_16816(acc[m][1], a, b[2], b[3]);
+    for (int p = 0; p < MT / 2; p++) {
+      uint32_t x[4];
+      ldsm4<I * 32>(x, a_row[p]);
+      mma_16816(acc[2 * p], wa, x[0], x[1]);
+      mma_16816(acc[2 * p + 1], wa, x[2], x[3]);
+    }
   }
 #endif
 }
 // A stage's SG_KS k-tiles: all window words are loaded first (3 * SG_KS independent shared loads in flight), then
-// decoded and multiplied tile by tile. N = tiles live in this stage (compile-time SG_KS for full stages).
+// decoded and multiplied tile by tile.
 template <int K, int MT, int I, int N>
 struct TileLoop {
   static constexpr int KSTEP = SG_WARPS * Codec<K>::TILE_BYTES;
+  static constexpr int NP = RowPairs<MT>::N;
   static __device__ __forceinline__ void load(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t (&w)[SG_KS][3]) {
     w[I][0] = lds32<I * KSTEP>(p0);
     w[I][1] = lds32<I * KSTEP>(p1);
     w[I][2] = lds32<I * KSTEP>(p2);
     TileLoop<K, MT, I + 1, N>::load(p0, p1, p2, w);
   }
-  static __device__ __forceinline__ void run(const uint32_t (&w)[SG_KS][3], uint32_t la, const uint32_t (&a_row)[MT],
-                                             float (&acc)[MT][2][4], int n) {
+  static __device__ __forceinline__ void run(const uint32_t (&w)[SG_KS][3], uint32_t la, const uint32_t (&a_row)[NP],
+                                             float (&acc)[MT][4], int n) {
     if (I < n) tile_mma<K, MT, I>(w[I][0], w[I][1], w[I][2], la, a_row, acc);
     TileLoop<K, MT, I + 1, N>::run(w, la, a_row, acc, n);
   }
-  static __device__ __forceinline__ void run_all(const uint32_t (&w)[SG_KS][3], uint32_t la, const uint32_t (&a_row)[MT],
-                                                 float (&acc)[MT][2][4]) {  // straight-line: the tiles interleave freely
+  static __device__ __forceinline__ void run_all(const uint32_t (&w)[SG_KS][3], uint32_t la, const uint32_t (&a_row)[NP],
+                                                 float (&acc)[MT][4]) {  // straight-line: the tiles interleave freely
     tile_mma<K, MT, I>(w[I][0], w[I][1], w[I][2], la, a_row, acc);
     TileLoop<K, MT, I + 1, N>::run_all(w, la, a_row, acc);
   }
 };
 template <int K, int MT, int N>
 struct TileLoop<K, MT, N, N> {
+  static constexpr int NP = RowPairs<MT>::N;
   static __device__ __forceinline__ void load(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_KS][3]) {}
-  static __device__ __forceinline__ void run(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4], int) {}
-  static __device__ __forceinline__ void run_all(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[MT], float (&)[MT][2][4]) {}
+  static __device__ __forceinline__ void run(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[NP], float (&)[MT][4], int) {}
+  static __device__ __forceinline__ void run_all(const uint32_t (&)[SG_KS][3], uint32_t, const uint32_t (&)[NP], float (&)[MT][4]) {}
 };
 
 // All k-steps of one unit for one warp. Returns false if a bounded wait gave up.
 template <int K, int MT>
 __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int stage_bytes, int nstages, uint64_t *full,
                                              uint64_t *empty, int &stage, uint32_t &phase, bool live, int warp, int lane,
-                                             uint32_t a_addr, const uint32_t (&a_rowoff)[MT], float (&acc)[MT][2][4],
+                                             uint32_t a_addr, const uint32_t (&a_rowoff)[RowPairs<MT>::N], float (&acc)[MT][4],
                                              int *status) {
   const typename Codec<K>::Lane L = Codec<K>::lane(lane);
   const uint32_t tb = ring_addr + (uint32_t)warp * Codec<K>::TILE_BYTES;
@@ -140,9 +160,9 @@ __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int sta
     if (live) {
       const uint32_t sb = tb + (uint32_t)stage * (uint32_t)stage_bytes;
       const uint32_t p0 = sb + L.o0, p1 = sb + L.o1, p2 = sb + L.o2;
-      uint32_t a_row[MT];
+      uint32_t a_row[RowPairs<MT>::N];
 #pragma unroll
-      for (int m = 0; m < MT; m++) a_row[m] = a_addr + a_rowoff[m] + (uint32_t)k * 32u;
+      for (int m = 0; m < RowPairs<MT>::N; m++) a_row[m] = a_addr + a_rowoff[m] + (uint32_t)k * 32u;
       uint32_t w[SG_KS][3];
       TileLoop<K, MT, 0, SG_KS>::load(p0, p1, p2, w);  // a short last stage loads stale ring bytes it never uses
       if (kc - k >= SG_KS) TileLoop<K, MT, 0, SG_KS>::run_all(w, L.a, a_row, acc);
@@ -153,6 +173,32 @@ __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int sta
     if (++stage == nstages) { stage = 0; phase ^= 1u; }
   }
   return true;
+}
+
+// per-unit dispatch on the bits per weight; units of a 16-row launch that have at most 8 live rows take the 1-group path
+template <int MT>
+__device__ __forceinline__ bool consume_any(int K, int nrows, int kc, uint32_t ring_addr, int stage_bytes, int nstages,
+                                            uint64_t *full, uint64_t *empty, int &stage, uint32_t &phase, bool live, int warp,
+                                            int lane, uint32_t a_addr, const uint32_t (&a_rowoff)[RowPairs<MT>::N],
+                                            float (&acc)[MT][4], int *status) {
+#define SG_CASE(KK)                                                                                                          \
+  case KK:                                                                                                                   \
+    if constexpr (MT == 2) {                                                                                                 \
+      if (nrows <= 8)                                                                                                        \
+        return consume_unit<KK, 1>(kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr,  \
+                                   reinterpret_cast<const uint32_t(&)[1]>(a_rowoff), reinterpret_cast<float(&)[1][4]>(acc), status); \
+    }                                                                                                                        \
+    return consume_unit<KK, MT>(kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr,     \
+                                a_rowoff, acc, status);
+  switch (K) {
+    SG_CASE(4)
+    SG_CASE(5)
+    SG_CASE(6)
+    SG_CASE(7)
+    default:
+      SG_CASE(8)
+  }
+#undef SG_CASE
 }
 
 template <class P, int MT>
@@ -238,58 +284,49 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
   const int g = lane >> 2, q = lane & 3;
   int stage = 0, slot = 0;
   uint32_t phase = 0, aphase = 0;
-  // ldmatrix row addresses: lanes 0-7 rows 0-7 (k 0-7), 8-15 rows 8-15, 16-23 rows 0-7 (k 8-15), 24-31 rows 8-15
-  const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
-  const uint32_t lkof = (uint32_t)(lane >> 4) * 16u;
+  // ldmatrix row addresses: lanes 0-7 rows 0-7 (k 0-7), 8-15 rows 0-7 (k 8-15), 16-23 rows 8-15 (k 0-7), 24-31 rows 8-15
+  // (k 8-15); the .x2 form used for <= 8 rows takes the first 16 lanes' addresses
+  const int lrow = (lane & 7) + (lane >> 4) * 8;
+  const uint32_t lkof = (uint32_t)((lane >> 3) & 1) * 16u;
   const uint32_t ring_addr = smem_u32(ring), a0_addr = smem_u32(aslot), z_addr = smem_u32(zrow);
 
   for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
     if (!mbar_wait(&a_full[slot], aphase, status, 4)) return;
     const typename P::Unit un = *reinterpret_cast<const typename P::Unit *>(desc + (size_t)slot * SG_DESC_BYTES);
     const int *didx = reinterpret_cast<const int *>(desc + (size_t)slot * SG_DESC_BYTES + SG_DESC_UNIT_BYTES);
-    int idx[MT][2];  // row indices of the accumulator rows this lane holds (rows g and g + 8 of every 16-row tile)
+    int idx[MT][2];  // row indices of the accumulator entries this lane holds: rows 8 m + 2q and 8 m + 2q + 1
 #pragma unroll
     for (int m = 0; m < MT; m++) {
-      idx[m][0] = m * 16 + g < un.nrows ? didx[m * 16 + g] : -1;
-      idx[m][1] = m * 16 + g + 8 < un.nrows ? didx[m * 16 + g + 8] : -1;
+      idx[m][0] = m * 8 + 2 * q < un.nrows ? didx[m * 8 + 2 * q] : -1;
+      idx[m][1] = m * 8 + 2 * q + 1 < un.nrows ? didx[m * 8 + 2 * q + 1] : -1;
     }
     const uint32_t a_addr = a0_addr + (uint32_t)slot * (uint32_t)lay.slot_bytes();
-    uint32_t a_rowoff[MT];
+    uint32_t a_rowoff[RowPairs<MT>::N];
 #pragma unroll
-    for (int m = 0; m < MT; m++) {
-      const int r = m * 16 + lrow;  // dead MMA rows read the zero row
+    for (int m = 0; m < RowPairs<MT>::N; m++) {
+      const int r = m * 16 + lrow;  // dead rows read the zero row
       a_rowoff[m] = (r < un.nrows ? (uint32_t)r * (uint32_t)lay.lda * 2u : (z_addr - a_addr)) + lkof;
     }
-    float acc[MT][2][4];
+    float acc[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; m++)
 #pragma unroll
-      for (int h = 0; h < 2; h++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) acc[m][h][j] = 0.0f;
+      for (int j = 0; j < 4; j++) acc[m][j] = 0.0f;
 
     const bool live = warp < un.ntiles;
-    bool ok;
-    switch (un.K) {
-      case 4: ok = consume_unit<4, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
-      case 5: ok = consume_unit<5, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
-      case 6: ok = consume_unit<6, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
-      case 7: ok = consume_unit<7, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
-      default: ok = consume_unit<8, MT>(un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status); break;
-    }
-    if (!ok) return;
+    if (!consume_any<MT>(un.K, un.nrows, un.kc, ring_addr, lay.stage_bytes, lay.stages, full, empty, stage, phase, live, warp, lane,
+                         a_addr, a_rowoff, acc, status))
+      return;
     __syncwarp();
     if (lane == 0) mbar_arrive(&a_empty[slot]);  // descriptor and A rows are in registers / consumed: slot may be refilled
     if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
     if (live) {
-      const int col = warp * 16 + 2 * q;
+      const int col = warp * 16 + g;
 #pragma unroll
-      for (int m = 0; m < MT; m++)
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-          if (idx[m][0] >= 0) prob.store(un, idx[m][0], col + 8 * h, acc[m][h][0], acc[m][h][1]);
-          if (idx[m][1] >= 0) prob.store(un, idx[m][1], col + 8 * h, acc[m][h][2], acc[m][h][3]);
-        }
+      for (int m = 0; m < MT; m++) {
+        if (idx[m][0] >= 0) { prob.store(un, idx[m][0], col, acc[m][0]); prob.store(un, idx[m][0], col + 8, acc[m][2]); }
+        if (idx[m][1] >= 0) { prob.store(un, idx[m][1], col, acc[m][1]); prob.store(un, idx[m][1], col + 8, acc[m][3]); }
+      }
     }
   }
 }
