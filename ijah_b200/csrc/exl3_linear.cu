@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(128) prep_rows_kernel(const float *__restrict_
                                                         __half *__restrict__ xh, int rows, int n, int hn, float hscale) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * 4 + warp, r = blockIdx.y;
+  pdl_wait();
+  pdl_launch();
   if (chunk * 128 >= n) return;
   float v[4];
 #pragma unroll
@@ -77,8 +79,7 @@ __global__ void __launch_bounds__(128) prep_rows_kernel(const float *__restrict_
 void launch_prep_rows(const float *x, const __half *suh, __half *xh, int rows, int n, cudaStream_t st) {
   const int hn = had_size(n);
   dim3 grid(((n + 127) / 128 + 3) / 4, rows);
-  prep_rows_kernel<<<grid, 128, 0, st>>>(x, suh, xh, rows, n, hn, (float)(1.0 / sqrt((double)hn)));
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(prep_rows_kernel, grid, dim3(128), 0, st, x, suh, xh, rows, n, hn, (float)(1.0 / sqrt((double)hn)));
 }
 
 // y[r][c] = (H_ho(sum_s raw[s][r]))[c] * svh[c]; one warp per (row, 128-column chunk), splits summed in index order
@@ -86,6 +87,8 @@ __global__ void linear_finish_kernel(const float *__restrict__ raw, const __half
                                      int rows, int out, int S, int ho, float hscale) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * (blockDim.x >> 5) + warp, r = blockIdx.y;
+  pdl_wait();
+  pdl_launch();
   if (chunk * 128 >= out) return;
   float v[4];
 #pragma unroll
@@ -118,9 +121,8 @@ void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, co
   launch_stream(pr, p.MT, p.lay, p.grid, status, st);
   const int chunks = (p.out + 127) / 128;
   dim3 grid((chunks + 3) / 4, p.rows);
-  linear_finish_kernel<<<grid, 128, 0, st>>>(raw, (const __half *)svh, y, p.rows, p.out, p.S, p.ho,
-                                            (float)(1.0 / sqrt((double)p.ho)));
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(linear_finish_kernel, grid, dim3(128), 0, st, raw, (const __half *)svh, y, p.rows, p.out, p.S, p.ho,
+             (float)(1.0 / sqrt((double)p.ho)));
 }
 
 // one warp per tile, straight from global memory

@@ -25,6 +25,7 @@ struct LinearPlan {
 LinearPlan plan_linear(int in, int out, int K, int rows);
 
 struct LinearProblem {
+  static constexpr bool kUnitsFinalAtLaunch = true;  // the unit list is arithmetic
   struct Unit : UnitBase {
     int g, s, k0;
   };

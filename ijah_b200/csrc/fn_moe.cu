@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(32 * RT_WARPS) moe_router_kernel(const MoePara
 #pragma unroll
   for (int j = 0; j < 16; j++)
     wreg[j] = (wr != nullptr && j * 32 + lane < H / 8) ? __ldg(reinterpret_cast<const uint4 *>(wr) + j * 32 + lane) : make_uint4(0, 0, 0, 0);
+  pdl_wait();  // the router weights above are static; the activations may be the preceding kernel's output
+  pdl_launch();
   for (int r0 = 0; r0 < p.rows; r0 += RT_RC) {
     const int nr = min(RT_RC, p.rows - r0);
     __syncthreads();
@@ -163,6 +165,8 @@ __global__ void __launch_bounds__(32 * RT_WARPS) moe_router_kernel(const MoePara
 
 __global__ void __launch_bounds__(256) moe_plan_kernel(const MoeParams p) {
   __shared__ __align__(16) unsigned char buf[16 * RT_EMAX];
+  pdl_wait();
+  pdl_launch();
   build_plan_block(p, buf);
 }
 
@@ -176,13 +180,11 @@ void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st) {
     IJ_CUDA(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_RC * 4096 * 4));
     ready = true;
   }
-  moe_router_kernel<<<grid, 32 * RT_WARPS, smem, st>>>(p, build_plan ? 1 : 0);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(moe_router_kernel, dim3(grid), dim3(32 * RT_WARPS), smem, st, p, build_plan ? 1 : 0);
 }
 
 void launch_moe_plan(const MoeParams &p, cudaStream_t st) {
-  moe_plan_kernel<<<1, 256, 0, st>>>(p);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(256), 0, st, p);
 }
 
 // =============================================================================================== operand prep
@@ -193,6 +195,8 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * 4 + warp, job = blockIdx.y;  // job < P: routed pair; else shared row
   const int H = p.H, k = p.topk;
+  pdl_wait();
+  pdl_launch();
   if (chunk * 128 >= H) return;
   const float hs = 0.08838834764831845f;
   int r;
@@ -234,6 +238,8 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * 4 + warp, job = blockIdx.y;
   const int I = p.I, k = p.topk;
+  pdl_wait();
+  pdl_launch();
   if (chunk * 128 >= I) return;
   const float hs = 0.08838834764831845f;
   const float *raw;
@@ -290,6 +296,7 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
 // =============================================================================================== gate / up
 // Unit order: for each distinct expert u: proj (gate, up) x k-split x column group; then the shared expert's.
 struct MoeGateUpProblem {
+  static constexpr bool kUnitsFinalAtLaunch = false;  // the plan is written by the router kernel just before
   struct Unit : UnitBase {
     int s, k0, g, proj, shared, e, first;
   };
@@ -335,6 +342,8 @@ struct MoeGateUpProblem {
 
 // =============================================================================================== down
 struct MoeDownProblem {
+  // the plan was complete before the gate/up kernel started, i.e. before the predecessor (mid) could release this launch
+  static constexpr bool kUnitsFinalAtLaunch = true;
   struct Unit : UnitBase {
     int s, k0, g, shared, e, first;
   };
@@ -381,6 +390,8 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int blk = blockIdx.x, r = blockIdx.y;
   const int H = p.H, k = p.topk;
+  pdl_wait();
+  pdl_launch();
   const float hs = 0.08838834764831845f;
   if (warp < k) {
     const int e = (int)p.route[(size_t)r * 2 * k + warp];
@@ -464,14 +475,12 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
 
 void launch_moe_prep(const MoeParams &p, cudaStream_t st) {
   dim3 grid((p.H / 128 + 3) / 4, p.P + (p.has_shared ? p.rows : 0));
-  moe_prep_kernel<<<grid, 128, 0, st>>>(p);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(moe_prep_kernel, grid, dim3(128), 0, st, p);
 }
 
 void launch_moe_mid(const MoeParams &p, cudaStream_t st) {
   dim3 grid((p.I / 128 + 3) / 4, p.P + (p.has_shared ? p.rows : 0));
-  moe_mid_kernel<<<grid, 128, 0, st>>>(p);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(moe_mid_kernel, grid, dim3(128), 0, st, p);
 }
 
 void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st) {
@@ -493,8 +502,7 @@ void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaSt
 void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st) {
   IJ_CHECK(p.topk <= CB_MAXK, "combine: top_k %d > %d", p.topk, CB_MAXK);
   dim3 grid(p.H / 128, p.rows);
-  moe_combine_kernel<<<grid, 32 * (p.topk + 1), 0, st>>>(p, routed_only ? 1 : 0);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(moe_combine_kernel, grid, dim3(32 * (p.topk + 1)), 0, st, p, routed_only ? 1 : 0);
 }
 
 }  // namespace ijah

@@ -5,6 +5,19 @@
 
 namespace ijah {
 
+// Launch with programmatic stream serialization allowed: the kernel may be scheduled while its predecessor in the
+// stream still runs and synchronises with it through pdl_wait() (also valid inside stream capture).
+template <class... KArgs, class... Args>
+void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  IJ_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
 template <class P, int MT>
 static void launch_stream_mt(const P &prob, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
   static bool ready = false;  // one flag per (problem, MT) instantiation: opt in to large dynamic shared memory once
@@ -12,8 +25,7 @@ static void launch_stream_mt(const P &prob, const StreamLayout &lay, int grid, i
     IJ_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<P, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     ready = true;
   }
-  stream_gemm_kernel<P, MT><<<grid, SG_THREADS, lay.total(), st>>>(prob, lay, status);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(stream_gemm_kernel<P, MT>, dim3(grid), dim3(SG_THREADS), lay.total(), st, prob, lay, status);
 }
 
 template <class P>

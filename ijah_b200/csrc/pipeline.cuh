@@ -64,4 +64,12 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
+// predecessor in the stream still runs. pdl_wait() blocks until the predecessor has completed and its writes are visible
+// (a no-op for a plain launch); pdl_launch() lets the successor's CTAs be scheduled once every CTA of this grid has
+// called it or exited. Every kernel of a chain calls pdl_wait() before pdl_launch() and before it touches anything an
+// earlier kernel wrote, so completion of one kernel implies completion of all kernels before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace ijah

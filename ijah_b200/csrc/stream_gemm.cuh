@@ -228,7 +228,6 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
   }
   for (int i = threadIdx.x; i < lay.lda / 2; i += blockDim.x) reinterpret_cast<uint32_t *>(zrow)[i] = 0u;
   __syncthreads();
-  const int nunits = prob.num_units();
 
   if (warp == SG_WARPS) {
     // ---------------------------------------------------------------- producer (one warp, lanes work in parallel)
@@ -236,11 +235,38 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
     // through shared memory together with the A rows, so no consumer ever waits on a global load. The next unit's
     // descriptor is fetched while the current unit's copies are issued, and lane i issues copy i, so the metadata
     // latency and the issue cost of the copies stay off the critical path.
+    //
+    // Start-up under programmatic dependent launch: the A rows (and for some problems the unit list itself) are written
+    // by the preceding kernel, the compressed weights are not. A problem whose unit list is final when the kernel is
+    // launched (P::kUnitsFinalAtLaunch) streams the first unit's weight stages into the fresh ring before it waits for
+    // the predecessor, so the ring is full when the A rows arrive.
     int stage = 0, slot = 0;
     uint32_t phase = 0, aphase = 0;
     int u = blockIdx.x;
     typename P::Unit un;
-    if (u < nunits) un = prob.unit(u);
+    int nunits = 0, k_pre = 0;
+    if constexpr (P::kUnitsFinalAtLaunch) {
+      nunits = prob.num_units();
+      if (u < nunits) {
+        un = prob.unit(u);
+        const uint32_t kb = (uint32_t)un.ntiles * 32u * (uint32_t)un.K, ks = (uint32_t)SG_WARPS * 32u * (uint32_t)un.K;
+        for (; k_pre < un.kc && stage < lay.stages; k_pre += SG_KS) {  // fresh ring: no empty-wait needed
+          const int n = min(SG_KS, un.kc - k_pre);
+          if (lane == 0) mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
+          __syncwarp();
+          if (lane < n)
+            bulk_g2s(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k_pre + lane) * un.kstride, kb, &full[stage]);
+          ++stage;
+        }
+        if (stage == lay.stages) { stage = 0; phase ^= 1u; }
+      }
+      pdl_wait();
+    } else {
+      pdl_wait();
+      nunits = prob.num_units();
+      if (u < nunits) un = prob.unit(u);
+    }
+    pdl_launch();
     while (u < nunits) {
       const int u_next = u + gridDim.x;
       typename P::Unit nx;
@@ -265,7 +291,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
       if (++slot == lay.aslots) { slot = 0; aphase ^= 1u; }
       // compressed tiles, SG_KS k-steps per stage, lane i copies k-step i
       const uint32_t kb = (uint32_t)un.ntiles * 32u * (uint32_t)un.K, ks = (uint32_t)SG_WARPS * 32u * (uint32_t)un.K;
-      for (int k = 0; k < un.kc; k += SG_KS) {
+      for (int k = k_pre; k < un.kc; k += SG_KS) {
         const int n = min(SG_KS, un.kc - k);
         if (!mbar_wait(&empty[stage], phase ^ 1u, status, 1)) return;
         if (lane == 0) mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
@@ -274,6 +300,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
           bulk_g2s(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k + lane) * un.kstride, kb, &full[stage]);
         if (++stage == lay.stages) { stage = 0; phase ^= 1u; }
       }
+      k_pre = 0;
       un = nx;
       u = u_next;
     }
@@ -290,6 +317,8 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
   const uint32_t lkof = (uint32_t)((lane >> 3) & 1) * 16u;
   const uint32_t ring_addr = smem_u32(ring), a0_addr = smem_u32(aslot), z_addr = smem_u32(zrow);
 
+  if constexpr (!P::kUnitsFinalAtLaunch) pdl_wait();  // the unit count is the predecessor's output
+  const int nunits = prob.num_units();
   for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
     if (!mbar_wait(&a_full[slot], aphase, status, 4)) return;
     const typename P::Unit un = *reinterpret_cast<const typename P::Unit *>(desc + (size_t)slot * SG_DESC_BYTES);
