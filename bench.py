@@ -33,9 +33,9 @@ sys.path.insert(0, str(ROOT))
 DIMS = dict(hidden=2048, inter=768, experts=512, k_expert=5, k_shared=6)
 TOPK = 10
 METRIC = "EXL3 MoE decode tok/s (rows through one MoE block)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up stream_gemm launch, from the ncu capture summarised in
-# profiles/ (filled in once a capture exists; None = not captured)
-NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up stream_gemm launch by rows, from the ncu captures
+# summarised under profiles/ (rows without a capture report null)
+NCU_TRAFFIC = {4: 79.48e6 + 2.12e6}
 
 
 def peaks():
@@ -174,7 +174,7 @@ def main():
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     xs = [torch.randn((M, H), device=dev, generator=g).to(torch.float16).to(torch.float32) for _ in range(L)]
     ys = [torch.empty((M, H), device=dev) for _ in range(L)]
-    launches_per_block = 4
+    launches_per_block = 6  # router + plan, operand prep, gate/up, SwiGLU + prep, down, combine
 
     if N == 1:
         def step():
@@ -198,7 +198,7 @@ def main():
         step()
     barrier()
     graph = None
-    if N == 1:  # one captured graph per step: launch gaps of the 4-kernel block are what a graph removes
+    if N == 1:  # one captured graph per step: launch gaps of the 6-kernel block are what a graph removes
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step()
@@ -251,36 +251,46 @@ def main():
     e2e = {"value": N * M * L * a.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * H * 4 * L, "d2h_bytes_per_step": M * H * 4 * L}
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- roofline of the dominant kernel (routed + shared gate/up stream_gemm launch), CUDA events on its stream
+    # ---- roofline of the dominant kernel: the gate/up stream_gemm launch (routed experts + shared expert), timed alone.
+    # The router and the operand prep of every layer run first (untimed), then one graph holding only the L gate/up
+    # launches (L distinct weight sets, far larger than L2) is replayed between CUDA events on its stream.
     roof, extra = None, {}
     if N == 1:
         peak, which = peaks()
-        evs, byt, dn_evs, dn_b, nu = [], [], [], [], []
-        for it in range(max(3, min(a.steps, 10))):
+
+        def kernel_us(code, before):
             for l in range(L):
-                b = blocks[l]
-                b.stage(7, xs[l], ys[l])
-                s0, s1, s2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-                s0.record()
-                b.stage(8, xs[l], ys[l])
-                s1.record()
-                eng._ok(eng.lib.ne_moe_stage(b.ptr, 9, E._dev(xs[l]), M, E._dev(ys[l]), E._stream()), "stage 9")
-                s2.record()
-                evs.append((s0, s1))
-                dn_evs.append((s1, s2))
-                if it == 0:
-                    lb = b.last_bytes(M)
-                    byt.append(lb["gateup"]); dn_b.append(lb["down"]); nu.append(lb["distinct_experts"])
-        torch.cuda.synchronize()
-        dur = float(np.mean([p.elapsed_time(q) for p, q in evs])) * 1e-3
-        ddur = float(np.mean([p.elapsed_time(q) for p, q in dn_evs])) * 1e-3
-        ach = float(np.mean(byt)) / dur / 1e9
-        roof = {"bound": "hbm", "kernel": "stream_gemm_kernel (gate/up)", "achieved": ach, "peak": peak, "unit": "GB/s",
-                "frac": ach / peak, "peak_source": which, "traffic": NCU_TRAFFIC_BYTES, "bytes_per_launch": float(np.mean(byt)),
-                "us_per_launch": dur * 1e6}
-        tot = float(np.mean([blocks[l].last_bytes(M)["total"] for l in range(L)]))
-        extra = {"down_plus_combine": {"achieved": float(np.mean(dn_b)) / ddur / 1e9, "us": ddur * 1e6},
-                 "distinct_experts_mean": float(np.mean(nu)),
+                for c in before:
+                    blocks[l].stage(c, xs[l], ys[l])
+            torch.cuda.synchronize()
+            gk = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gk):
+                for l in range(L):
+                    blocks[l].stage(code, xs[l], ys[l])
+            gk.replay()
+            torch.cuda.synchronize()
+            n = max(3, min(a.steps, 10))
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record()
+            for _ in range(n):
+                gk.replay()
+            k1.record()
+            torch.cuda.synchronize()
+            return k0.elapsed_time(k1) * 1e3 / n / L
+
+        gu_us = kernel_us(81, (7, 80))
+        dn_us = kernel_us(91, (81, 90))
+        lbs = [blocks[l].last_bytes(M) for l in range(L)]
+        gu_b = float(np.mean([x["gateup"] for x in lbs]))
+        dn_b = float(np.mean([x["down"] for x in lbs]))
+        tot = float(np.mean([x["total"] for x in lbs]))
+        ach = gu_b / gu_us / 1e3
+        traffic = NCU_TRAFFIC.get(M)
+        roof = {"bound": "hbm", "kernel": "stream_gemm_kernel<MoeGateUpProblem> (gate/up of routed + shared experts)",
+                "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": which + " (stream copy)",
+                "traffic": traffic, "bytes_per_launch": gu_b, "us_per_launch": gu_us}
+        extra = {"down_kernel": {"achieved": dn_b / dn_us / 1e3, "us": dn_us, "bytes_per_launch": dn_b},
+                 "distinct_experts_mean": float(np.mean([x["distinct_experts"] for x in lbs])),
                  "block": {"bytes": tot, "us": ms_per_step * 1e3 / L, "achieved": tot / (ms_per_step * 1e-3 / L) / 1e9,
                            "frac": tot / (ms_per_step * 1e-3 / L) / 1e9 / peak}}
     status = eng.lib.ne_device_wait_status()

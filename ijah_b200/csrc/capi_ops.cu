@@ -138,9 +138,15 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
   const MoeSplits &s = splits(rows);
   switch (stage_no) {
     case 7: launch_moe_router(p, true, st); break;
-    case 8: launch_moe_prep(p, st); launch_moe_gateup(p, s, status, st); break;
+    case 8: launch_moe_prep(p, false, st); launch_moe_gateup(p, s, status, st); break;
     case 9: launch_moe_mid(p, st); launch_moe_down(p, s, status, st); launch_moe_combine(p, false, st); break;
-    default: fail("bad MoE stage %d (7 router, 8 gate/up, 9 down)", stage_no);
+    // single kernels of stages 8 and 9 (for per-kernel timing; each needs the state the kernels before it leave)
+    case 80: launch_moe_prep(p, false, st); break;
+    case 81: launch_moe_gateup(p, s, status, st); break;
+    case 90: launch_moe_mid(p, st); break;
+    case 91: launch_moe_down(p, s, status, st); break;
+    case 92: launch_moe_combine(p, false, st); break;
+    default: fail("bad MoE stage %d (7 router, 8 gate/up, 9 down; 80 81 90 91 92 their single kernels)", stage_no);
   }
   last_rows = rows;
 }
@@ -148,8 +154,8 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
 void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
   const MoeParams p = params(x, rows, y);
   const MoeSplits &s = splits(rows);
-  launch_moe_router(p, true, st);
-  launch_moe_prep(p, st);
+  launch_moe_router(p, false, st);  // the plan is built beside the operand prep
+  launch_moe_prep(p, true, st);
   launch_moe_gateup(p, s, status, st);
   launch_moe_mid(p, st);
   launch_moe_down(p, s, status, st);
@@ -165,8 +171,8 @@ void Moe::forward_ep(const float *x, int rows, int own_row0, int own_rows, float
   p.sh_row0 = own_row0;
   p.sh_rows = own_rows;
   const MoeSplits &s = splits(rows);
-  launch_moe_router(p, true, st);
-  launch_moe_prep(p, st);
+  launch_moe_router(p, false, st);  // the plan is built beside the operand prep
+  launch_moe_prep(p, true, st);
   launch_moe_gateup(p, s, status, st);
   launch_moe_mid(p, st);
   launch_moe_down(p, s, status, st);
@@ -179,8 +185,7 @@ void Moe::forward_routed(const float *x, const uint32_t *route_in, int rows, flo
   IJ_CUDA(cudaMemcpyAsync(route, route_in, (size_t)rows * 2 * desc.top_k * 4, cudaMemcpyDeviceToDevice, st));
   p.has_shared = 0;
   const MoeSplits &s = splits(rows);
-  launch_moe_plan(p, st);
-  launch_moe_prep(p, st);
+  launch_moe_prep(p, true, st);
   launch_moe_gateup(p, s, status, st);
   launch_moe_mid(p, st);
   launch_moe_down(p, s, status, st);

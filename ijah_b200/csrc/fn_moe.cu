@@ -11,9 +11,11 @@ namespace ijah {
 // =============================================================================================== router + top-k + plan
 // Reference: kernels/fn_moe.metal:26-134 (logits = x . W in fp32 from bf16 weights, shared-gate logit as row E;
 // the last CTA to arrive selects top-k on the logits, ties -> lowest index, w = exp(l - l_max) / sum over the k).
-constexpr int RT_WARPS = 8;
-constexpr int RT_RC = 8;      // activation rows per pass
-constexpr int RT_EMAX = 1024;  // experts the finisher's shared memory covers
+constexpr int RT_WARPS = 8;    // expert rows per CTA (one per warp): every CTA stages all activation rows, so fewer, fuller CTAs read them less often
+constexpr int RT_THREADS = 256;
+constexpr int RT_RC = 8;       // activation rows per pass
+constexpr int RT_EMAX = 1024;  // experts the finisher covers (32 logits per lane)
+constexpr int RT_PMAX = 2048;  // (row, slot) pairs the finisher covers
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -21,182 +23,359 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__device__ void topk_row(const MoeParams &p, int r, float *s, int lane) {
-  const int E = p.E, k = p.topk;
-  for (int i = lane; i < E; i += 32) s[i] = __ldcg(&p.logits[(size_t)r * (E + 1) + i]);
-  __syncwarp();
-  float myv = 0.0f, top = 0.0f;
-  int myi = 0;
-  for (int t = 0; t < k; t++) {
-    float best = -INFINITY;
-    int bi = 0x7FFFFFFF;
-    for (int i = lane; i < E; i += 32) {
-      const float v = s[i];
-      if (v > best || bi == 0x7FFFFFFF) { best = v; bi = i; }
-    }
+// k-split partial sums of NP * 4 elements per lane (element j of pointer q: base[q][lane + 32 j] + s * sstride), added in
+// split order, four splits' loads in flight at a time (a rolled loop of dependent adds would pay one L2 round trip per split)
+template <int NP>
+__device__ __forceinline__ void sum_splits(const float *const (&base)[NP], size_t sstride, int S, int lane, float (&acc)[NP][4]) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
-      const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (t == 0) top = best;
-    if (lane == t) { myv = best; myi = bi; }
-    if ((bi & 31) == lane) s[bi] = -INFINITY;
-    __syncwarp();
+  for (int q = 0; q < NP; q++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[q][j] = 0.0f;
+  for (int s0 = 0; s0 < S; s0 += 4) {
+    float t[4][NP][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int q = 0; q < NP; q++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) t[i][q][j] = s0 + i < S ? __ldcg(base[q] + (size_t)(s0 + i) * sstride + lane + 32 * j) : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int q = 0; q < NP; q++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[q][j] += t[i][q][j];
   }
+}
+
+// float -> unsigned key with the same order (for redux.sync max); -0 was folded into +0 before
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float order_key_inv(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+// Warp-wide selection of the k largest of 32 * NV (value, id) candidates held in registers (NV per lane; unused entries
+// are -inf with id INT_MAX). Order: larger value first, ties -> lower id. Per round: two warp reductions (largest value,
+// then lowest id among its holders) and a rescan by the winning lane only. Lane t < k returns the t-th winner.
+template <int NV>
+__device__ __forceinline__ void topk_regs(float (&v)[NV], int (&id)[NV], int k, int lane, float &myv, int &myi) {
+  float best = -INFINITY;
+  int bid = 0x7FFFFFFF;
+#pragma unroll
+  for (int j = 0; j < NV; j++)
+    if (v[j] > best || (v[j] == best && id[j] < bid)) { best = v[j]; bid = id[j]; }
+  for (int t = 0; t < k; t++) {
+    const uint32_t key = order_key(best);
+    const uint32_t kmax = __reduce_max_sync(0xFFFFFFFFu, key);
+    const int cand = key == kmax ? bid : 0x7FFFFFFF;
+    const int wi = __reduce_min_sync(0xFFFFFFFFu, cand);
+    if (lane == t) { myv = order_key_inv(kmax); myi = wi; }
+    if (cand == wi && wi != 0x7FFFFFFF) {  // the winner drops its entry and rescans its registers
+      best = -INFINITY; bid = 0x7FFFFFFF;
+#pragma unroll
+      for (int j = 0; j < NV; j++) {
+        if (id[j] == wi) { v[j] = -INFINITY; id[j] = 0x7FFFFFFF; }
+        if (v[j] > best || (v[j] == best && id[j] < bid)) { best = v[j]; bid = id[j]; }
+      }
+    }
+  }
+}
+
+// candidates n0 .. n0 + n of `vals` (ids: `ids[i]`, or i itself when ids == nullptr), lane-strided, -0 folded into +0
+template <int NV>
+__device__ __forceinline__ void topk_span(const float *vals, const int *ids, int n0, int n, int k, int lane, float &myv, int &myi) {
+  float v[NV];
+  int id[NV];
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    const int i = j * 32 + lane;
+    v[j] = i < n ? (ids ? vals[n0 + i] : __ldcg(vals + n0 + i)) + 0.0f : -INFINITY;  // ids != nullptr: shared memory
+    id[j] = i < n ? (ids ? ids[n0 + i] : n0 + i) : 0x7FFFFFFF;
+  }
+  topk_regs<NV>(v, id, k, lane, myv, myi);
+}
+
+__device__ __forceinline__ void topk_any(const float *vals, const int *ids, int n0, int n, int k, int lane, float &myv, int &myi) {
+  const int nv = (n + 31) >> 5;
+  if (nv <= 1) topk_span<1>(vals, ids, n0, n, k, lane, myv, myi);
+  else if (nv <= 2) topk_span<2>(vals, ids, n0, n, k, lane, myv, myi);
+  else if (nv <= 4) topk_span<4>(vals, ids, n0, n, k, lane, myv, myi);
+  else if (nv <= 8) topk_span<8>(vals, ids, n0, n, k, lane, myv, myi);
+  else if (nv <= 16) topk_span<16>(vals, ids, n0, n, k, lane, myv, myi);
+  else topk_span<32>(vals, ids, n0, n, k, lane, myv, myi);
+}
+
+// lanes t < k hold the row's winners in order: softmax over them, write route[r] (ids, then weights) and sid[r * k ..]
+__device__ __forceinline__ void route_row(const MoeParams &p, int r, int *sid, int lane, float myv, int myi) {
+  const int k = p.topk;
+  const float top = __shfl_sync(0xFFFFFFFFu, myv, 0);
   const float pr = lane < k ? expf(myv - top) : 0.0f;
   const float sum = warp_sum(pr);
   if (lane < k) {
     p.route[(size_t)r * 2 * k + lane] = (uint32_t)myi;
     p.route[(size_t)r * 2 * k + k + lane] = __float_as_uint(pr / sum);
+    sid[r * k + lane] = myi;
   }
 }
 
+// bitonic sort across the 32 lanes of a warp, descending (lane 0 ends with the largest key): 15 exchange steps
+template <class T>
+__device__ __forceinline__ T warp_sort_desc(T key, int lane) {
+#pragma unroll
+  for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+    for (int j = k2 >> 1; j > 0; j >>= 1) {
+      const T other = __shfl_xor_sync(0xFFFFFFFFu, key, j);
+      const bool take_max = ((lane & j) == 0) == ((lane & k2) == 0);
+      key = take_max ? (key > other ? key : other) : (key < other ? key : other);
+    }
+  }
+  return key;
+}
+
+// One warp selects the k <= 32 largest logits of row r (ties -> lowest index) with few dependent warp-wide steps:
+// the k-th largest of the 32 per-lane maxima is a lower bound T of the k-th largest logit, so only logits >= T can win.
+// Those (normally a handful more than k) are compacted into `list` as 64-bit keys (ordered value, inverted index) and one
+// more warp sort puts the winners, in order, into lanes 0 .. k-1. More than 32 candidates (heavy ties): the round-based
+// selection takes over. `list`: 32 entries of shared memory owned by the warp.
+template <int NV>
+__device__ void topk_row(const MoeParams &p, int r, int *sid, unsigned long long *list, int lane) {
+  const int E = p.E, k = p.topk, nv = E >> 5;
+  const float *lg = p.logits + (size_t)r * (E + 1);
+  // all loads go out before the first use (clamped addresses instead of predicates: a guarded load per iteration would
+  // serialise one L2 round trip per 32 logits)
+  float f[NV];
+#pragma unroll
+  for (int j = 0; j < NV; j++) f[j] = __ldcg(lg + min(j * 32 + lane, E - 1));
+  uint32_t key[NV];
+  uint32_t m = 0u;
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    key[j] = j < nv ? order_key(f[j] + 0.0f) : 0u;
+    m = max(m, key[j]);
+  }
+  const uint32_t T = __shfl_sync(0xFFFFFFFFu, warp_sort_desc<uint32_t>(m, lane), k - 1);
+  // compaction (order is irrelevant, the list is sorted next): per-lane count, exclusive scan over lanes, then each lane
+  // writes its own candidates
+  int mine = 0;
+#pragma unroll
+  for (int j = 0; j < NV; j++) mine += (j < nv && key[j] >= T) ? 1 : 0;
+  int inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= o) inc += a;
+  }
+  const int count = __shfl_sync(0xFFFFFFFFu, inc, 31);
+  int pos = inc - mine;
+  if (mine > 0) {
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+      if (j < nv && key[j] >= T) {
+        if (pos < 32) list[pos] = ((unsigned long long)key[j] << 32) | (0xFFFFFFFFu - (uint32_t)(j * 32 + lane));
+        pos++;
+      }
+    }
+  }
+  __syncwarp();
+  float myv = 0.0f;
+  int myi = 0;
+  if (count <= 32) {
+    const unsigned long long c = warp_sort_desc<unsigned long long>(lane < count ? list[lane] : 0ull, lane);
+    myv = order_key_inv((uint32_t)(c >> 32));
+    myi = (int)(0xFFFFFFFFu - (uint32_t)c);
+  } else {
+    topk_any(lg, nullptr, 0, E, k, lane, myv, myi);
+  }
+  __syncwarp();
+  route_row(p, r, sid, lane, myv, myi);
+}
+
 // Distinct local experts of the rows*topk (row, slot) pairs, in expert order, each with its pairs in row order.
-// One CTA; `buf` is >= 16 KB of shared memory.
-__device__ void build_plan_block(const MoeParams &p, unsigned char *buf) {
+// One CTA (blockDim a multiple of 32, <= 1024); `buf` is 16 KB of shared memory, sid[P] the pairs' expert ids (shared).
+__device__ void build_plan_block(const MoeParams &p, unsigned char *buf, const int *sid) {
   unsigned long long *mask = reinterpret_cast<unsigned long long *>(buf);  // [E] rows that use expert e
   int *uidx = reinterpret_cast<int *>(buf + 8 * RT_EMAX);                  // [E] index among present experts
   int *firs = uidx + RT_EMAX;                                              // [E] offset of its pairs
+  __shared__ int wtot[32];
   const int tid = threadIdx.x, T = blockDim.x, E = p.E, k = p.topk, P = p.P;
+  const int lane = tid & 31, warp = tid >> 5;
   PlanView pv{p.plan, P};
   for (int e = tid; e < E; e += T) mask[e] = 0ull;
   __syncthreads();
   for (int i = tid; i < P; i += T) {
-    const int r = i / k, e = (int)p.route[(size_t)r * 2 * k + (i - r * k)];
-    if (e >= p.e0 && e < p.e0 + p.ecount) atomicOr(&mask[e], 1ull << r);
+    const int e = sid[i];
+    if (e >= p.e0 && e < p.e0 + p.ecount) atomicOr(&mask[e], 1ull << (i / k));
   }
   __syncthreads();
-  if (tid < 32) {
-    int run_u = 0, run_f = 0;
-    for (int base = 0; base < E; base += 32) {
-      const int e = base + tid;
-      const int c = e < E ? __popcll(mask[e]) : 0, pr = c > 0 ? 1 : 0;
-      int su = pr, sf = c;
+  // exclusive scan over experts of (present ? 1 : 0, pair count), packed as (present << 16) | count (count <= 2048):
+  // thread t covers experts [t * per, (t + 1) * per)
+  const int per = (E + T - 1) / T, e_lo = tid * per;
+  int mine = 0;
+  for (int e = e_lo; e < min(E, e_lo + per); e++) {
+    const int c = __popcll(mask[e]);
+    mine += c > 0 ? (1 << 16) + c : 0;
+  }
+  int inc = mine;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int a = __shfl_up_sync(0xFFFFFFFFu, su, o), b = __shfl_up_sync(0xFFFFFFFFu, sf, o);
-        if (tid >= o) { su += a; sf += b; }
-      }
-      if (e < E) { uidx[e] = run_u + su - pr; firs[e] = run_f + sf - c; }
-      run_u += __shfl_sync(0xFFFFFFFFu, su, 31);
-      run_f += __shfl_sync(0xFFFFFFFFu, sf, 31);
-    }
-    if (tid == 0) *pv.nu() = run_u;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= o) inc += a;
   }
+  if (lane == 31) wtot[warp] = inc;
   __syncthreads();
-  for (int e = tid; e < E; e += T) {
+  int run = inc - mine;
+  for (int w = 0; w < warp; w++) run += wtot[w];
+  if (tid == T - 1) *pv.nu() = (run + mine) >> 16;
+  for (int e = e_lo; e < min(E, e_lo + per); e++) {
     const int c = __popcll(mask[e]);
     if (c > 0) {
-      const int u = uidx[e];
+      const int u = run >> 16, f = run & 0xFFFF;
+      firs[e] = f;
       pv.expert()[u] = e;
       pv.nrows()[u] = c;
-      pv.first()[u] = firs[e];
+      pv.first()[u] = f;
+      run += (1 << 16) + c;
     }
   }
+  (void)uidx;
+  __syncthreads();
   for (int i = tid; i < P; i += T) {
-    const int r = i / k, e = (int)p.route[(size_t)r * 2 * k + (i - r * k)];
+    const int r = i / k, e = sid[i];
     if (e >= p.e0 && e < p.e0 + p.ecount) pv.pairs()[firs[e] + __popcll(mask[e] & ((1ull << r) - 1ull))] = i;
   }
 }
 
-// Dynamic shared memory: first the activation rows of one pass (RT_RC rows x H floats, shared by the CTA's 8 expert
-// rows), later reused by the finisher (per-warp logit rows, then the plan's tables).
-__global__ void __launch_bounds__(32 * RT_WARPS) moe_router_kernel(const MoeParams p, int build_plan) {
+// acc[t] = W row (16 x 8 bf16 per lane, chunk j covers elements [8 (32 j + lane), +8)) . activation row t of the staged pass,
+// for NR rows at once (rows >= nr repeat row nr - 1: no branches between the shared-memory loads)
+template <int NR>
+__device__ __forceinline__ void router_dot(const uint4 (&wreg)[16], const float *dyn, int H, int lane, int nr, float (&acc)[RT_RC]) {
+#pragma unroll
+  for (int t = 0; t < RT_RC; t++) acc[t] = 0.0f;
+  const float4 *x4 = reinterpret_cast<const float4 *>(dyn);
+  const int q = H / 4, h8 = H / 8;
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    const int c = j * 32 + lane;
+    if (j * 32 < h8) {  // uniform (H is a multiple of 256)
+      const uint4 u = wreg[j];
+      const float w0 = __uint_as_float(u.x << 16), w1 = __uint_as_float(u.x & 0xFFFF0000u);
+      const float w2 = __uint_as_float(u.y << 16), w3 = __uint_as_float(u.y & 0xFFFF0000u);
+      const float w4_ = __uint_as_float(u.z << 16), w5 = __uint_as_float(u.z & 0xFFFF0000u);
+      const float w6 = __uint_as_float(u.w << 16), w7 = __uint_as_float(u.w & 0xFFFF0000u);
+#pragma unroll
+      for (int t = 0; t < NR; t++) {
+        const int tt = min(t, nr - 1);
+        const float4 a = x4[tt * q + c], b = x4[tt * q + h8 + c];
+        acc[t] += a.x * w0 + a.y * w1 + a.z * w2 + a.w * w3 + b.x * w4_ + b.y * w5 + b.z * w6 + b.w * w7;
+      }
+    }
+  }
+}
+
+// Dynamic shared memory: first the activation rows of one pass (RT_RC rows x H floats, shared by the CTA's expert
+// rows), later reused by the finisher (the plan's tables, then the pairs' expert ids).
+__global__ void __launch_bounds__(RT_THREADS) moe_router_kernel(const MoeParams p, int build_plan) {
   extern __shared__ __align__(16) float dyn[];
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * RT_WARPS + warp;
   const int H = p.H, E = p.E;
-  const uint16_t *wr = row < E ? p.router + (size_t)row * H : (row == E ? p.sgate : nullptr);
+  const uint16_t *wr = warp >= RT_WARPS ? nullptr : row < E ? p.router + (size_t)row * H : (row == E ? p.sgate : nullptr);
   // the expert's weight row stays in registers for all passes: H / 256 x 8 bf16 per lane (H <= 4096)
+  // (clamped addresses, no predicates: all 16 loads are in flight at once; the dot loop skips the chunks past H / 8)
   uint4 wreg[16];
+  const uint4 *wsrc = reinterpret_cast<const uint4 *>(wr != nullptr ? wr : p.router);
 #pragma unroll
-  for (int j = 0; j < 16; j++)
-    wreg[j] = (wr != nullptr && j * 32 + lane < H / 8) ? __ldg(reinterpret_cast<const uint4 *>(wr) + j * 32 + lane) : make_uint4(0, 0, 0, 0);
+  for (int j = 0; j < 16; j++) wreg[j] = __ldg(wsrc + min(j * 32 + lane, H / 8 - 1));
   pdl_wait();  // the router weights above are static; the activations may be the preceding kernel's output
   pdl_launch();
   for (int r0 = 0; r0 < p.rows; r0 += RT_RC) {
     const int nr = min(RT_RC, p.rows - r0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nr * H / 4; i += blockDim.x)
-      reinterpret_cast<float4 *>(dyn)[i] = reinterpret_cast<const float4 *>(p.x + (size_t)r0 * H)[i];
-    __syncthreads();
-    float acc[RT_RC];
-#pragma unroll
-    for (int t = 0; t < RT_RC; t++) acc[t] = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; j++) {
-      const int c = j * 32 + lane;
-      if (c < H / 8) {
-        const uint4 u = wreg[j];
-        const float w0 = __uint_as_float(u.x << 16), w1 = __uint_as_float(u.x & 0xFFFF0000u);
-        const float w2 = __uint_as_float(u.y << 16), w3 = __uint_as_float(u.y & 0xFFFF0000u);
-        const float w4_ = __uint_as_float(u.z << 16), w5 = __uint_as_float(u.z & 0xFFFF0000u);
-        const float w6 = __uint_as_float(u.w << 16), w7 = __uint_as_float(u.w & 0xFFFF0000u);
-#pragma unroll
-        for (int t = 0; t < RT_RC; t++) {
-          if (t < nr) {
-            const float4 *x4 = reinterpret_cast<const float4 *>(dyn + (size_t)t * H) + 2 * c;
-            const float4 a = x4[0], b = x4[1];
-            acc[t] += a.x * w0 + a.y * w1 + a.z * w2 + a.w * w3 + b.x * w4_ + b.y * w5 + b.z * w6 + b.w * w7;
-          }
+    {  // asynchronous 16-byte copies: every thread's share is in flight at once
+      const uint32_t dst = smem_u32(dyn);
+      const float4 *src = reinterpret_cast<const float4 *>(p.x + (size_t)r0 * H);
+      // row t, floats [8c, 8c+4) go to float4 slot t * H/4 + c, floats [8c+4, 8c+8) to slot t * H/4 + H/8 + c: a warp's
+      // 16-byte reads of either half are then contiguous (no bank conflicts)
+      const int q = H / 4, h8 = H / 8;
+      for (int t = 0; t < nr; t++)
+        for (int w = threadIdx.x; w < q; w += blockDim.x) {
+          const int slot = t * q + (w & 1) * h8 + (w >> 1);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)slot * 16u), "l"(src + t * q + w) : "memory");
         }
-      }
+      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
     }
+    __syncthreads();
+    if (wr == nullptr) continue;
+    float acc[RT_RC];
+    if (nr == 1) router_dot<1>(wreg, dyn, H, lane, nr, acc);
+    else if (nr == 2) router_dot<2>(wreg, dyn, H, lane, nr, acc);
+    else if (nr <= 4) router_dot<4>(wreg, dyn, H, lane, nr, acc);
+    else router_dot<8>(wreg, dyn, H, lane, nr, acc);
 #pragma unroll
     for (int t = 0; t < RT_RC; t++) {
-      const float v = warp_sum(acc[t]);
-      if (lane == 0 && t < nr && row <= E) p.logits[(size_t)(r0 + t) * (E + 1) + row] = v;
+      if (t < nr) {  // uniform
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && row <= E) p.logits[(size_t)(r0 + t) * (E + 1) + row] = v;
+      }
     }
   }
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(p.counter, 1u) == gridDim.x - 1 ? 1 : 0;
   __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  for (int r = warp; r < p.rows; r += RT_WARPS) topk_row(p, r, dyn + (size_t)warp * RT_EMAX, lane);
+  if (!s_last) return;  // the finisher reads the other CTAs' logits with L2 loads (ld.global.cg), past their fences
+  unsigned char *tables = reinterpret_cast<unsigned char *>(dyn);
+  int *sid = reinterpret_cast<int *>(tables + 16 * RT_EMAX);
+  unsigned long long *lists = reinterpret_cast<unsigned long long *>(tables + 16 * RT_EMAX + 4 * RT_PMAX);
+  for (int r = warp; r < p.rows; r += RT_THREADS / 32) {
+    if (p.E <= 512) topk_row<16>(p, r, sid, lists + warp * 32, lane);
+    else topk_row<32>(p, r, sid, lists + warp * 32, lane);
+  }
   __syncthreads();
-  if (build_plan) build_plan_block(p, reinterpret_cast<unsigned char *>(dyn));
+  if (build_plan) build_plan_block(p, tables, sid);
   if (threadIdx.x == 0) *p.counter = 0u;
-}
-
-__global__ void __launch_bounds__(256) moe_plan_kernel(const MoeParams p) {
-  __shared__ __align__(16) unsigned char buf[16 * RT_EMAX];
-  pdl_wait();
-  pdl_launch();
-  build_plan_block(p, buf);
 }
 
 void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st) {
   IJ_CHECK(p.E <= RT_EMAX && p.E % 32 == 0 && p.H % 256 == 0 && p.topk <= 32, "router: unsupported dims E %d H %d k %d", p.E, p.H, p.topk);
   IJ_CHECK(p.H <= 4096, "router: hidden %d > 4096", p.H);
+  IJ_CHECK(p.P <= RT_PMAX, "router: %d (row, slot) pairs > %d", p.P, RT_PMAX);
   const int grid = (p.E + 1 + RT_WARPS - 1) / RT_WARPS;
-  const size_t smem = std::max((size_t)std::min(p.rows, RT_RC) * p.H * 4, (size_t)RT_WARPS * RT_EMAX * 4);
+  const size_t smem = std::max((size_t)std::min(p.rows, RT_RC) * p.H * 4, (size_t)16 * RT_EMAX + (size_t)RT_PMAX * 4 + 2048);  // tables, pair ids, candidate lists
   static bool ready = false;
   if (!ready) {
     IJ_CUDA(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_RC * 4096 * 4));
     ready = true;
   }
-  launch_pdl(moe_router_kernel, dim3(grid), dim3(32 * RT_WARPS), smem, st, p, build_plan ? 1 : 0);
-}
-
-void launch_moe_plan(const MoeParams &p, cudaStream_t st) {
-  launch_pdl(moe_plan_kernel, dim3(1), dim3(256), 0, st, p);
+  launch_pdl(moe_router_kernel, dim3(grid), dim3(RT_THREADS), smem, st, p, build_plan ? 1 : 0);
 }
 
 // =============================================================================================== operand prep
 // xh_gu[pair][proj][H] = fp16(H128(x[row(pair)] * suh_proj[expert(pair)])) for every local (row, slot) pair, and
 // xh_sgu[row][proj][H] for the shared expert (reference kernels/fn_moe.metal:304-311, prefill twin
-// kernels/prefill/pf_moe.metal:88-104). One warp per (operand row, 128-element chunk).
-__global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p) {
+// kernels/prefill/pf_moe.metal:88-104). One warp per (operand row, 128-element chunk). With build_plan, one extra CTA
+// (the last blockIdx.y) builds the expert plan of the stream kernels meanwhile: the plan needs the routes, not the operands.
+__global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int build_plan) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * 4 + warp, job = blockIdx.y;  // job < P: routed pair; else shared row
   const int H = p.H, k = p.topk;
   pdl_wait();
   pdl_launch();
+  if (build_plan && blockIdx.y == gridDim.y - 1) {
+    __shared__ __align__(16) unsigned char tables[16 * RT_EMAX];
+    __shared__ int sid[RT_PMAX];
+    if (blockIdx.x != 0) return;
+    for (int i = threadIdx.x; i < p.P; i += blockDim.x) sid[i] = (int)p.route[(size_t)(i / k) * 2 * k + (i % k)];
+    __syncthreads();
+    build_plan_block(p, tables, sid);
+    return;
+  }
   if (chunk * 128 >= H) return;
   const float hs = 0.08838834764831845f;
   int r;
@@ -242,43 +421,38 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
   pdl_launch();
   if (chunk * 128 >= I) return;
   const float hs = 0.08838834764831845f;
-  const float *raw;
-  size_t sstride;
+  const bool shared = job >= p.P;
+  // the partial sums' addresses do not depend on the routing: their loads go out first, together with the route entry
+  const float *raw = shared ? p.raw_sgu + (size_t)(job - p.P) * 2 * I : p.raw_gu + (size_t)job * 2 * I;
+  const size_t sstride = shared ? (size_t)p.rows * 2 * I : (size_t)p.P * 2 * I;
+  const int o = chunk * 128 + lane;
+  const float *const src[2] = {raw + chunk * 128, raw + I + chunk * 128};
+  float gu[2][4];
+  sum_splits<2>(src, sstride, p.S_gu, lane, gu);
   const __half *svg, *svu, *sud;
   __half *dst;
-  const bool shared = job >= p.P;
   if (!shared) {
     const int r = job / k, e = (int)p.route[(size_t)r * 2 * k + (job - r * k)] - p.e0;
     if (e < 0 || e >= p.ecount) return;
-    raw = p.raw_gu + (size_t)job * 2 * I;
-    sstride = (size_t)p.P * 2 * I;
     svg = p.gate.svh + (size_t)e * I; svu = p.up.svh + (size_t)e * I; sud = p.down.suh + (size_t)e * I;
     dst = p.xh_d + (size_t)job * I;
   } else {
-    const int r = job - p.P;
-    raw = p.raw_sgu + (size_t)r * 2 * I;
-    sstride = (size_t)p.rows * 2 * I;
     svg = p.sgt.svh; svu = p.sup.svh; sud = p.sdn.suh;
-    dst = p.xh_sd + (size_t)r * I;
+    dst = p.xh_sd + (size_t)(job - p.P) * I;
   }
-  const int o = chunk * 128 + lane;
-  float gv[4], uv[4], hh[4];
+  float gv[4], uv[4], hh[4], s_g[4], s_u[4], s_d[4];
 #pragma unroll
   for (int j = 0; j < 4; j++) {
-    float a = 0.0f, b = 0.0f;
-    for (int s = 0; s < p.S_gu; s++) {  // k-split partials in split order
-      a += raw[s * sstride + o + 32 * j];
-      b += raw[s * sstride + I + o + 32 * j];
-    }
-    gv[j] = a; uv[j] = b;
+    gv[j] = gu[0][j]; uv[j] = gu[1][j];
+    s_g[j] = __half2float(svg[o + 32 * j]); s_u[j] = __half2float(svu[o + 32 * j]); s_d[j] = __half2float(sud[o + 32 * j]);
   }
   fwht_chunk(gv, lane, 128, hs);
   fwht_chunk(uv, lane, 128, hs);
 #pragma unroll
   for (int j = 0; j < 4; j++) {
-    gv[j] *= __half2float(svg[o + 32 * j]);
-    uv[j] *= __half2float(svu[o + 32 * j]);
-    hh[j] = gv[j] / (1.0f + expf(-gv[j])) * uv[j] * __half2float(sud[o + 32 * j]);
+    gv[j] *= s_g[j];
+    uv[j] *= s_u[j];
+    hh[j] = gv[j] / (1.0f + expf(-gv[j])) * uv[j] * s_d[j];
   }
   if (shared) {  // finished shared gate | up, kept for inspection ("shared_gu")
     const int r = job - p.P;
@@ -394,20 +568,21 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
   pdl_launch();
   const float hs = 0.08838834764831845f;
   if (warp < k) {
+    // the partial sums' addresses do not depend on the routing: their loads go out together with the route entry
+    const float *const src[1] = {p.raw_d + (size_t)(r * k + warp) * H + blk * 128};
+    float part[1][4];
+    sum_splits<1>(src, (size_t)p.P * H, p.S_d, lane, part);
     const int e = (int)p.route[(size_t)r * 2 * k + warp];
+    const float wk = __uint_as_float(p.route[(size_t)r * 2 * k + k + warp]);
     const bool local = e >= p.e0 && e < p.e0 + p.ecount;
     if (lane == 0) used[warp] = local ? 1 : 0;
     if (local) {
-      const float wk = __uint_as_float(p.route[(size_t)r * 2 * k + k + warp]);
-      const float *raw = p.raw_d + (size_t)(r * k + warp) * H + blk * 128;
       const __half *sv = p.down.svh + (size_t)(e - p.e0) * H + blk * 128;
       float v[4], sc[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         sc[j] = __half2float(sv[lane + 32 * j]);
-        float a = 0.0f;
-        for (int s = 0; s < p.S_d; s++) a += raw[(size_t)s * p.P * H + lane + 32 * j];
-        v[j] = a;
+        v[j] = part[0][j];
       }
       fwht_chunk(v, lane, 128, hs);
 #pragma unroll
@@ -417,15 +592,14 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
     const bool on = !routed_only && p.has_shared && r >= p.sh_row0 && r < p.sh_row0 + p.sh_rows;
     if (lane == 0) used[k] = on ? 1 : 0;
     if (on) {
-      float v[4];
+      const float *const src[1] = {p.raw_sd + (size_t)r * H + blk * 128};
+      float part[1][4], v[4];
+      sum_splits<1>(src, (size_t)p.rows * H, p.S_d, lane, part);
+      const float lg = p.logits[(size_t)r * (p.E + 1) + p.E];
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        float a = 0.0f;
-        for (int s = 0; s < p.S_d; s++) a += p.raw_sd[((size_t)s * p.rows + r) * H + blk * 128 + lane + 32 * j];
-        v[j] = a;
-      }
+      for (int j = 0; j < 4; j++) v[j] = part[0][j];
       fwht_chunk(v, lane, 128, hs);
-      const float sg = 1.0f / (1.0f + expf(-p.logits[(size_t)r * (p.E + 1) + p.E]));
+      const float sg = 1.0f / (1.0f + expf(-lg));
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         const int c = blk * 128 + lane + 32 * j;
@@ -473,9 +647,10 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   return s;
 }
 
-void launch_moe_prep(const MoeParams &p, cudaStream_t st) {
-  dim3 grid((p.H / 128 + 3) / 4, p.P + (p.has_shared ? p.rows : 0));
-  launch_pdl(moe_prep_kernel, grid, dim3(128), 0, st, p);
+void launch_moe_prep(const MoeParams &p, bool build_plan, cudaStream_t st) {
+  IJ_CHECK(p.P <= RT_PMAX && p.E <= RT_EMAX, "plan: %d pairs / %d experts exceed %d / %d", p.P, p.E, RT_PMAX, RT_EMAX);
+  dim3 grid((p.H / 128 + 3) / 4, p.P + (p.has_shared ? p.rows : 0) + (build_plan ? 1 : 0));
+  launch_pdl(moe_prep_kernel, grid, dim3(128), 0, st, p, build_plan ? 1 : 0);
 }
 
 void launch_moe_mid(const MoeParams &p, cudaStream_t st) {

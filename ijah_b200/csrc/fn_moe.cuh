@@ -74,8 +74,8 @@ struct MoeSplits {
 MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool has_shared);
 
 void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st);
-void launch_moe_plan(const MoeParams &p, cudaStream_t st);  // plan from an externally supplied route buffer
-void launch_moe_prep(const MoeParams &p, cudaStream_t st);   // gate / up operands (after routing)
+// gate / up operands (after routing); build_plan: also the expert plan from the route buffer (when the router did not)
+void launch_moe_prep(const MoeParams &p, bool build_plan, cudaStream_t st);
 void launch_moe_mid(const MoeParams &p, cudaStream_t st);    // SwiGLU + down operand (after gate / up)
 void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
 void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);

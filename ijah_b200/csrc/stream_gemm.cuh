@@ -245,6 +245,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
     int u = blockIdx.x;
     typename P::Unit un;
     int nunits = 0, k_pre = 0;
+    const uint64_t wpol = l2_evict_first_policy();
     if constexpr (P::kUnitsFinalAtLaunch) {
       nunits = prob.num_units();
       if (u < nunits) {
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
           if (lane == 0) mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
           __syncwarp();
           if (lane < n)
-            bulk_g2s(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k_pre + lane) * un.kstride, kb, &full[stage]);
+            bulk_g2s_hint(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k_pre + lane) * un.kstride, kb, &full[stage], wpol);
           ++stage;
         }
         if (stage == lay.stages) { stage = 0; phase ^= 1u; }
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(SG_THREADS, 2) stream_gemm_kernel(const P prob
         if (lane == 0) mbar_arrive_expect_tx(&full[stage], (uint32_t)n * kb);
         __syncwarp();
         if (lane < n)
-          bulk_g2s(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k + lane) * un.kstride, kb, &full[stage]);
+          bulk_g2s_hint(ring + (size_t)stage * lay.stage_bytes + lane * ks, un.w + (size_t)(k + lane) * un.kstride, kb, &full[stage], wpol);
         if (++stage == lay.stages) { stage = 0; phase ^= 1u; }
       }
       k_pre = 0;

@@ -71,10 +71,13 @@ typedef struct {
 typedef struct ne_moe ne_moe;
 NE_API ne_moe *ne_moe_create(const ne_moe_desc *d, int max_rows); /* max_rows 1..64; allocates all scratch */
 NE_API void ne_moe_free(ne_moe *m);
-/* y[rows][hidden] = sum_k w_k expert_k(x) + sigmoid(x . w_sg) shared(x). Enqueues 5 kernels on `stream`. */
+/* y[rows][hidden] = sum_k w_k expert_k(x) + sigmoid(x . w_sg) shared(x). Enqueues 6 kernels on `stream`
+ * (router + plan, operand prep, gate/up, SwiGLU + operand prep, down, combine). */
 NE_API int ne_moe_forward(ne_moe *m, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API int ne_moe_forward_host(ne_moe *m, const float *x_host, int rows, float *y_host);
-/* The same in pieces (stage numbers of the reference's ne_fn_layer_run_dispatch: 7 router, 8 gate/up, 9 down). */
+/* The same in pieces (stage numbers of the reference's ne_fn_layer_run_dispatch: 7 router, 8 gate/up, 9 down), and the
+ * single kernels of stages 8 and 9 for per-kernel timing: 80 operand prep, 81 gate/up stream GEMM, 90 SwiGLU + operand
+ * prep, 91 down stream GEMM, 92 combine. */
 NE_API int ne_moe_stage(ne_moe *m, int stage, const float *x_dev, int rows, float *y_dev, void *stream);
 /* Expert parallel: routes come from outside (route_dev: [rows][2*top_k], ids then f32 weights, global expert ids);
  * computes only the slots whose expert lies in this object's slice, summed per row in slot order, no shared expert:
