@@ -72,7 +72,7 @@ void Moe::prefill(const float *x, int n, float *y, cudaStream_t st) {
     pf.route = (uint32_t *)al((size_t)n * 2 * k * 4);
     pf.cnt = (int *)al(E * 4);
     pf.off = (int *)al((E + 2) * 4);
-    pf.rank = (int *)al(S * 4);
+    pf.hist = (int *)al(((S + 255) / 256) * E * 4);
     pf.inv = (int *)al(S * 4);
     pf.order = (int *)al(cap * 4);
     pf.seid = (int *)al(cap * 4);

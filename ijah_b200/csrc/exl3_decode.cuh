@@ -98,10 +98,11 @@ __device__ __forceinline__ void fwht_chunk(float (&v)[4], int lane, int N, float
 #pragma unroll
   for (int bit = 1; bit < 32; bit <<= 1) {
     if (bit < N) {
+      const float sgn = (lane & bit) == 0 ? 1.0f : -1.0f;  // lower partner: v + p, upper: p - v; one FMA, same rounding
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         const float p = __shfl_xor_sync(0xFFFFFFFFu, v[j], bit);
-        v[j] = (lane & bit) == 0 ? v[j] + p : p - v[j];
+        v[j] = __fmaf_rn(v[j], sgn, p);
       }
     }
   }
@@ -112,6 +113,27 @@ __device__ __forceinline__ void fwht_chunk(float (&v)[4], int lane, int N, float
   if (N >= 128) {
     const float a = v[0] + v[2], b = v[1] + v[3], c = v[0] - v[2], d = v[1] - v[3];
     v[0] = a; v[1] = b; v[2] = c; v[3] = d;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; j++) v[j] *= scale;
+}
+
+// The same transform of size 128 with the chunk held as (4 lane .. 4 lane + 3) per lane, so that a lane reads and writes 16
+// contiguous bytes. Same butterflies in the same order (index bits 0, 1 inside the lane, bits 2..6 across lanes), hence
+// bit-identical to fwht_chunk.
+__device__ __forceinline__ void fwht128_contig(float (&v)[4], int lane, float scale) {
+  {
+    const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+    v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+  }
+#pragma unroll
+  for (int bit = 1; bit < 32; bit <<= 1) {
+    const float sgn = (lane & bit) == 0 ? 1.0f : -1.0f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float p = __shfl_xor_sync(0xFFFFFFFFu, v[j], bit);
+      v[j] = __fmaf_rn(v[j], sgn, p);
+    }
   }
 #pragma unroll
   for (int j = 0; j < 4; j++) v[j] *= scale;

@@ -224,41 +224,72 @@ static void launch_pf_gemm(const PgGemm &g, int *status, cudaStream_t st) {
 // (the routing, sorting, operand and finishing kernels follow)
 
 // =============================================================================================== router
-// logits[n][E + 1] = x . W^T (bf16 W, fp32 accumulate; row E = the shared expert's gate), one 64 x 64 tile per CTA.
-// Reference: the router GEMM of the chunked prefill (kernels/prefill/pf_gemm.metal:159-186) + pf_moe_route
-// (kernels/prefill/pf_trunk.metal:278-334).
+// logits[n][0 .. E) = x . W^T (bf16 W, fp32 multiply-add), 128 tokens x 128 experts per CTA, 8 x 8 outputs per thread, k in steps of
+// 16 through shared memory (k-major, so every operand read is a conflict-free float4) with the next step's global loads in
+// flight during the multiply. Reference: the router GEMM of the chunked prefill (kernels/prefill/pf_gemm.metal:159-186).
+// The shared expert's gate logit (column E) is a plain dot product in pf_route_kernel.
+constexpr int LG_T = 128, LG_K = 16;
 __global__ void __launch_bounds__(256) pf_logits_kernel(const PfParams p) {
-  __shared__ float xs[64][33], ws[64][33];
-  const int t0 = blockIdx.x * 64, c0 = blockIdx.y * 64, tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  float acc[4][4] = {};
-  for (int k0 = 0; k0 < p.H; k0 += 32) {
-    for (int i = threadIdx.x; i < 64 * 32; i += 256) {
-      const int r = i >> 5, k = i & 31;
-      xs[r][k] = t0 + r < p.n ? p.x[(size_t)(t0 + r) * p.H + k0 + k] : 0.0f;
-      const int c = c0 + r;
-      const uint16_t *wr = c < p.E ? p.router + (size_t)c * p.H : (c == p.E ? p.sgate : nullptr);
-      ws[r][k] = wr ? __uint_as_float((uint32_t)wr[k0 + k] << 16) : 0.0f;
+  __shared__ __align__(16) float xs[2][LG_K][LG_T], ws[2][LG_K][LG_T];
+  const int tid = threadIdx.x, t0 = blockIdx.x * LG_T, c0 = blockIdx.y * LG_T, H = p.H;
+  const int tx = tid & 15, ty = tid >> 4;  // outputs: tokens {4 ty .. +3, 64 + 4 ty .. +3} x experts {4 tx .. +3, 64 + 4 tx .. +3}
+  // loads: x: thread -> (token tid >> 1, 8 k's of half tid & 1) as two float4; W: thread -> (expert tid >> 1, 8 k's) as one uint4
+  const int lr = tid >> 1, lh = tid & 1;
+  const float *xrow = p.x + (size_t)min(t0 + lr, p.n - 1) * H + lh * 8;
+  const uint16_t *wrow = p.router + (size_t)min(c0 + lr, p.E - 1) * H + lh * 8;
+  float4 xa = *reinterpret_cast<const float4 *>(xrow), xb = *reinterpret_cast<const float4 *>(xrow + 4);
+  uint4 wv = *reinterpret_cast<const uint4 *>(wrow);
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+  auto stash = [&](int buf) {
+    float (*X)[LG_T] = xs[buf], (*W)[LG_T] = ws[buf];
+    const int kb = lh * 8;
+    X[kb + 0][lr] = xa.x; X[kb + 1][lr] = xa.y; X[kb + 2][lr] = xa.z; X[kb + 3][lr] = xa.w;
+    X[kb + 4][lr] = xb.x; X[kb + 5][lr] = xb.y; X[kb + 6][lr] = xb.z; X[kb + 7][lr] = xb.w;
+    W[kb + 0][lr] = __uint_as_float(wv.x << 16); W[kb + 1][lr] = __uint_as_float(wv.x & 0xFFFF0000u);
+    W[kb + 2][lr] = __uint_as_float(wv.y << 16); W[kb + 3][lr] = __uint_as_float(wv.y & 0xFFFF0000u);
+    W[kb + 4][lr] = __uint_as_float(wv.z << 16); W[kb + 5][lr] = __uint_as_float(wv.z & 0xFFFF0000u);
+    W[kb + 6][lr] = __uint_as_float(wv.w << 16); W[kb + 7][lr] = __uint_as_float(wv.w & 0xFFFF0000u);
+  };
+  stash(0);
+  __syncthreads();
+  const int nk = H / LG_K;
+  for (int ks = 0; ks < nk; ks++) {
+    const int buf = ks & 1;
+    if (ks + 1 < nk) {
+      xa = *reinterpret_cast<const float4 *>(xrow + (ks + 1) * LG_K);
+      xb = *reinterpret_cast<const float4 *>(xrow + (ks + 1) * LG_K + 4);
+      wv = *reinterpret_cast<const uint4 *>(wrow + (ks + 1) * LG_K);
     }
-    __syncthreads();
-#pragma unroll 8
-    for (int k = 0; k < 32; k++) {
-      float a[4], b[4];
 #pragma unroll
-      for (int i = 0; i < 4; i++) { a[i] = xs[ty * 4 + i][k]; b[i] = ws[tx * 4 + i][k]; }
+    for (int k = 0; k < LG_K; k++) {
+      const float4 a0 = *reinterpret_cast<const float4 *>(&xs[buf][k][4 * ty]), a1 = *reinterpret_cast<const float4 *>(&xs[buf][k][64 + 4 * ty]);
+      const float4 b0 = *reinterpret_cast<const float4 *>(&ws[buf][k][4 * tx]), b1 = *reinterpret_cast<const float4 *>(&ws[buf][k][64 + 4 * tx]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int i = 0; i < 4; i++)
+      for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] += a[i] * b[j];
+        for (int j = 0; j < 8; j++) acc[i][j] += a[i] * b[j];
     }
+    if (ks + 1 < nk) stash(buf ^ 1);  // the other buffer was last read one step ago, before the barrier below
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+  for (int i = 0; i < 8; i++) {
+    const int t = t0 + (i < 4 ? 4 * ty + i : 64 + 4 * ty + i - 4);
+    if (t >= p.n) continue;
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const int t = t0 + ty * 4 + i, c = c0 + tx * 4 + j;
-      if (t < p.n && c <= p.E) p.logits[(size_t)t * (p.E + 1) + c] = acc[i][j];
+    for (int jh = 0; jh < 2; jh++) {
+      const int c = c0 + jh * 64 + 4 * tx;
+      float *dst = p.logits + (size_t)t * (p.E + 1) + c;
+      if (c + 3 < p.E) { dst[0] = acc[i][jh * 4]; dst[1] = acc[i][jh * 4 + 1]; dst[2] = acc[i][jh * 4 + 2]; dst[3] = acc[i][jh * 4 + 3]; }
+      else for (int j = 0; j < 4; j++) if (c + j < p.E) dst[j] = acc[i][jh * 4 + j];
     }
+  }
 }
 
 // top-k on the logits (ties -> lowest index), weights = softmax over the k selected; one warp per token
@@ -269,6 +300,19 @@ __global__ void __launch_bounds__(256) pf_route_kernel(const PfParams p) {
   float *s = sl[warp];
   const int E = p.E, k = p.topk;
   for (int i = lane; i < E; i += 32) s[i] = p.logits[(size_t)t * (E + 1) + i];
+  if (p.has_shared) {  // the shared expert's gate logit: x[t] . w_sg
+    float g = 0.0f;
+    for (int i = lane * 8; i < p.H; i += 256) {
+      const float4 a = *reinterpret_cast<const float4 *>(p.x + (size_t)t * p.H + i), b = *reinterpret_cast<const float4 *>(p.x + (size_t)t * p.H + i + 4);
+      const uint4 u = *reinterpret_cast<const uint4 *>(p.sgate + i);
+      g += a.x * __uint_as_float(u.x << 16) + a.y * __uint_as_float(u.x & 0xFFFF0000u) + a.z * __uint_as_float(u.y << 16) +
+           a.w * __uint_as_float(u.y & 0xFFFF0000u) + b.x * __uint_as_float(u.z << 16) + b.y * __uint_as_float(u.z & 0xFFFF0000u) +
+           b.z * __uint_as_float(u.w << 16) + b.w * __uint_as_float(u.w & 0xFFFF0000u);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) g += __shfl_xor_sync(0xFFFFFFFFu, g, o);
+    if (lane == 0) p.logits[(size_t)t * (E + 1) + E] = g;
+  }
   __syncwarp();
   float myv = 0.0f, top = 0.0f;
   int myi = 0;
@@ -300,26 +344,44 @@ __global__ void __launch_bounds__(256) pf_route_kernel(const PfParams p) {
 }
 
 // =============================================================================================== sort by expert
-// Deterministic counting sort of the n * topk slots (reference kernels/prefill/pf_moe.metal:29-83): one CTA per
-// expert counts its slots and ranks them in slot order; one CTA lays out the experts' position ranges (padded to 8 rows,
-// the granule of the blocked operand layout) and writes the work items; one thread per slot places it.
-__global__ void __launch_bounds__(256) pf_count_kernel(const PfParams p) {
-  __shared__ int part[256];
-  const int e = blockIdx.x, tid = threadIdx.x, k = p.topk;
-  const int per = (p.S + 255) / 256, s0 = min(tid * per, p.S), s1 = min(s0 + per, p.S);
-  int c = 0;
-  for (int s = s0; s < s1; s++) c += (int)p.route[(size_t)(s / k) * 2 * k + s % k] == e ? 1 : 0;
-  part[tid] = c;
-  __syncthreads();
-  if (tid == 0) {
-    int acc = 0;
-    for (int j = 0; j < 256; j++) { const int v = part[j]; part[j] = acc; acc += v; }
-    p.cnt[blockIdx.x] = acc;
+// Deterministic counting sort of the n * topk slots by expert (reference kernels/prefill/pf_moe.metal:29-83), three passes:
+//   pf_hist_kernel   one warp per block of PS_BLOCK consecutive slots: per-expert counts of the block
+//   pf_scan_kernel   per expert, exclusive scan of the counts over the blocks (a warp per expert); then one CTA lays out
+//                    the experts' position ranges (padded to 8 rows, the granule of the blocked operand layout) and
+//                    writes the work items
+//   pf_place_kernel  the same warps walk their block in slot order: rank of a slot among its expert's slots = the block's
+//                    base + earlier equals in the block (warp match), position = expert offset + rank
+constexpr int PS_BLOCK = 256;
+__global__ void __launch_bounds__(32) pf_hist_kernel(const PfParams p, int *hist) {
+  __shared__ int cnt[1024];
+  const int b = blockIdx.x, lane = threadIdx.x, k = p.topk;
+  for (int e = lane; e < p.E; e += 32) cnt[e] = 0;
+  __syncwarp();
+  for (int i = lane; i < PS_BLOCK; i += 32) {
+    const int s = b * PS_BLOCK + i;
+    if (s < p.S) atomicAdd(&cnt[p.route[(size_t)(s / k) * 2 * k + s % k]], 1);
   }
-  __syncthreads();
-  int r = part[tid];
-  for (int s = s0; s < s1; s++)
-    if ((int)p.route[(size_t)(s / k) * 2 * k + s % k] == e) p.rank[s] = r++;
+  __syncwarp();
+  for (int e = lane; e < p.E; e += 32) hist[(size_t)b * p.E + e] = cnt[e];
+}
+
+// hist[b][e] -> exclusive scan over b (in place), cnt[e] = total; one warp per expert
+__global__ void __launch_bounds__(256) pf_blockscan_kernel(const PfParams p, int *hist, int nb) {
+  const int e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= p.E) return;
+  int run = 0;
+  for (int b0 = 0; b0 < nb; b0 += 32) {
+    const int b = b0 + lane, v = b < nb ? hist[(size_t)b * p.E + e] : 0;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += a;
+    }
+    if (b < nb) hist[(size_t)b * p.E + e] = run + inc - v;
+    run += __shfl_sync(0xFFFFFFFFu, inc, 31);
+  }
+  if (lane == 0) p.cnt[e] = run;
 }
 
 __device__ __forceinline__ int block_excl_scan(int v, int *warp_tot, int *total) {  // blockDim = 1024, all threads call
@@ -371,127 +433,191 @@ __global__ void __launch_bounds__(1024) pf_scan_kernel(const PfParams p) {
 }
 
 // order[pos] = slot (S + t for the shared expert's row of token t, -1 = padding), inv[slot] = pos, seid[pos] = expert
-// (E = shared). order / seid are pre-set to -1 by the launcher.
-__global__ void __launch_bounds__(256) pf_place_kernel(const PfParams p, int *order) {
-  const int i = blockIdx.x * 256 + threadIdx.x, k = p.topk;
-  if (i < p.S) {
-    const int e = (int)p.route[(size_t)(i / k) * 2 * k + i % k], pos = p.off[e] + p.rank[i];
-    order[pos] = i;
-    p.inv[i] = pos;
-    p.seid[pos] = e;
-  } else if (i < p.S + p.n && p.has_shared) {
-    const int t = i - p.S, pos = p.off[p.E] + t;
-    order[pos] = p.S + t;
-    p.seid[pos] = p.E;
-  }
-}
-
-// 8 positions x 128 k of fp16 in shared memory -> the blocked global layout: 16 core matrices = 2 KB contiguous
-__device__ __forceinline__ void store_blocked_chunk(const __half (*tile)[128], __half *dst_group_chunk) {
-  const int c = threadIdx.x >> 4, r = (threadIdx.x >> 1) & 7, h = threadIdx.x & 1;  // 256 threads x 8 bytes
-  *reinterpret_cast<uint2 *>(dst_group_chunk + c * 64 + r * 8 + h * 4) = *reinterpret_cast<const uint2 *>(&tile[r][c * 8 + h * 4]);
-}
-
-// gate / up operands: xh[pos] = fp16(H128(x[token(pos)] * suh[expert(pos)])), one CTA per (8-position group, 128-chunk),
-// one warp per position (reference kernels/prefill/pf_moe.metal:88-104)
-__global__ void __launch_bounds__(256) pf_prep_kernel(const PfParams p, const int *order) {
-  __shared__ __align__(16) __half tg[8][128], tu[8][128];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int chunk = blockIdx.x, grp = blockIdx.y, pos = grp * 8 + warp, H = p.H;
-  const int slot = pos < p.off[p.E + 1] ? order[pos] : -1;
-  float g[4] = {0, 0, 0, 0}, u[4] = {0, 0, 0, 0};
-  if (slot >= 0) {
-    const bool shared = slot >= p.S;
-    const int t = shared ? slot - p.S : slot / p.topk;
-    const int e = shared ? 0 : p.seid[pos];
-    const __half *sg = shared ? p.sgt.suh : p.gate.suh + (size_t)e * H, *su = shared ? p.sup.suh : p.up.suh + (size_t)e * H;
-    const int o = chunk * 128 + lane;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const float xv = p.x[(size_t)t * H + o + 32 * j];
-      g[j] = xv * __half2float(sg[o + 32 * j]);
-      u[j] = xv * __half2float(su[o + 32 * j]);
+// (E = shared). order / seid are pre-set to -1 by the launcher. Blocks 0 .. nb-1 place the routed slots, the rest the shared rows.
+__global__ void __launch_bounds__(32) pf_place_kernel(const PfParams p, int *order, const int *hist, int nb) {
+  __shared__ int base[1024];
+  const int b = blockIdx.x, lane = threadIdx.x, k = p.topk;
+  if (b >= nb) {
+    if (!p.has_shared) return;
+    for (int t = (b - nb) * PS_BLOCK + lane; t < min(p.n, (b - nb + 1) * PS_BLOCK); t += 32) {
+      const int pos = p.off[p.E] + t;
+      order[pos] = p.S + t;
+      p.seid[pos] = p.E;
     }
-    fwht_chunk(g, lane, 128, 0.08838834764831845f);
-    fwht_chunk(u, lane, 128, 0.08838834764831845f);
+    return;
   }
+  for (int e = lane; e < p.E; e += 32) base[e] = hist[(size_t)b * p.E + e] + p.off[e];
+  __syncwarp();
+  const uint32_t lt = (1u << lane) - 1u;
+  for (int i = lane; i < PS_BLOCK; i += 32) {  // 32 consecutive slots per round, rounds in slot order
+    const int s = b * PS_BLOCK + i;
+    const bool on = s < p.S;
+    const int e = on ? (int)p.route[(size_t)(s / k) * 2 * k + s % k] : -1 - lane;
+    const uint32_t same = __match_any_sync(0xFFFFFFFFu, e);
+    if (on) {
+      const int pos = base[e] + __popc(same & lt);
+      order[pos] = s;
+      p.inv[s] = pos;
+      p.seid[pos] = e;
+    }
+    __syncwarp();
+    if (on && (same & lt) == 0) base[e] += __popc(same);  // the first lane of each expert advances its base
+    __syncwarp();
+  }
+}
+
+// The three elementwise kernels below give one warp a whole operand row (one position, or one slot of one token): the
+// row's metadata is fetched once, the loads of several 128-element chunks are in flight together, and a lane owns 4
+// consecutive elements of a chunk, i.e. 8 bytes of fp16 output: half a row of a core matrix of the blocked layout.
+// All three are bound by instruction issue (the fp32 Hadamard butterflies and their shuffles), not by memory.
+constexpr float PF_HS = 0.08838834764831845f;  // 1 / sqrt(128)
+
+__device__ __forceinline__ float4 mul4(float4 a, uint2 h) {  // a * (4 halfs)
+  const __half2 h0 = *reinterpret_cast<const __half2 *>(&h.x), h1 = *reinterpret_cast<const __half2 *>(&h.y);
+  const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+  return make_float4(a.x * f0.x, a.y * f0.y, a.z * f1.x, a.w * f1.y);
+}
+__device__ __forceinline__ uint2 pack4(const float (&v)[4]) {
+  const __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+  return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+}
+// lane's 4 elements (k = chunk * 128 + 4 lane ..) of position pos in a blocked operand with `in` columns
+__device__ __forceinline__ __half *blocked_lane_ptr(__half *base, int pos, int chunk, int lane, int in) {
+  return base + (((size_t)(pos >> 3) * (in >> 3) + chunk * 16 + (lane >> 1)) << 6) + ((pos & 7) << 3) + ((lane & 1) << 2);
+}
+
+// gate / up operands: xh[pos] = fp16(H128(x[token(pos)] * suh[expert(pos)])), one warp per position (reference
+// kernels/prefill/pf_moe.metal:88-104); padding positions are written as zeros
+__global__ void __launch_bounds__(256) pf_prep_kernel(const PfParams p, const int *order) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = blockIdx.x * 8 + warp, H = p.H;
+  if (pos >= p.pos_cap) return;
+  const int slot = pos < p.off[p.E + 1] ? order[pos] : -1;
+  if (slot < 0) {
+    for (int c = 0; c < H / 128; c++) {
+      *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_g, pos, c, lane, H)) = make_uint2(0u, 0u);
+      *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_u, pos, c, lane, H)) = make_uint2(0u, 0u);
+    }
+    return;
+  }
+  const bool shared = slot >= p.S;
+  const int t = shared ? slot - p.S : slot / p.topk;
+  const int e = shared ? 0 : p.seid[pos];
+  const __half *sg = shared ? p.sgt.suh : p.gate.suh + (size_t)e * H, *su = shared ? p.sup.suh : p.up.suh + (size_t)e * H;
+  const float *xr = p.x + (size_t)t * H;
+  for (int c0 = 0; c0 < H / 128; c0 += 4) {
+    float4 xv[4];
+    uint2 gs[4], us[4];
 #pragma unroll
-  for (int j = 0; j < 4; j++) {
-    tg[warp][lane + 32 * j] = __float2half_rn(g[j]);
-    tu[warp][lane + 32 * j] = __float2half_rn(u[j]);
+    for (int i = 0; i < 4; i++) {
+      const int o = (min(c0 + i, H / 128 - 1)) * 128 + 4 * lane;
+      xv[i] = *reinterpret_cast<const float4 *>(xr + o);
+      gs[i] = *reinterpret_cast<const uint2 *>(sg + o);
+      us[i] = *reinterpret_cast<const uint2 *>(su + o);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      if (c0 + i < H / 128) {
+        const float4 g4 = mul4(xv[i], gs[i]), u4 = mul4(xv[i], us[i]);
+        float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+        fwht128_contig(g, lane, PF_HS);
+        fwht128_contig(u, lane, PF_HS);
+        *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_g, pos, c0 + i, lane, H)) = pack4(g);
+        *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_u, pos, c0 + i, lane, H)) = pack4(u);
+      }
+    }
   }
-  __syncthreads();
-  const size_t base = ((size_t)grp * (H >> 3) + chunk * 16) * 64;
-  store_blocked_chunk(tg, p.xh_g + base);
-  store_blocked_chunk(tu, p.xh_u + base);
 }
 
 // down operand: SwiGLU of the finished gate / up, times suh_down, H128, fp16 (reference pf_moe.metal:107-125)
 __global__ void __launch_bounds__(256) pf_mid_kernel(const PfParams p) {
-  __shared__ __align__(16) __half td[8][128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int chunk = blockIdx.x, grp = blockIdx.y, pos = grp * 8 + warp, I = p.I;
+  const int pos = blockIdx.x * 8 + warp, I = p.I;
+  if (pos >= p.pos_cap) return;
   const int e = pos < p.off[p.E + 1] ? p.seid[pos] : -1;
-  float hh[4] = {0, 0, 0, 0};
-  if (e >= 0) {
-    const bool shared = e == p.E;
-    const __half *svg = shared ? p.sgt.svh : p.gate.svh + (size_t)e * I, *svu = shared ? p.sup.svh : p.up.svh + (size_t)e * I;
-    const __half *sud = shared ? p.sdn.suh : p.down.suh + (size_t)e * I;
-    const float *raw = p.raw_gu + (size_t)pos * 2 * I;
-    const int o = chunk * 128 + lane;
-    float gv[4], uv[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) { gv[j] = raw[o + 32 * j]; uv[j] = raw[I + o + 32 * j]; }
-    fwht_chunk(gv, lane, 128, 0.08838834764831845f);
-    fwht_chunk(uv, lane, 128, 0.08838834764831845f);
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      gv[j] *= __half2float(svg[o + 32 * j]);
-      uv[j] *= __half2float(svu[o + 32 * j]);
-      hh[j] = gv[j] / (1.0f + expf(-gv[j])) * uv[j] * __half2float(sud[o + 32 * j]);
-    }
-    fwht_chunk(hh, lane, 128, 0.08838834764831845f);
+  if (e < 0) {
+    for (int c = 0; c < I / 128; c++) *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_d, pos, c, lane, I)) = make_uint2(0u, 0u);
+    return;
   }
+  const bool shared = e == p.E;
+  const __half *svg = shared ? p.sgt.svh : p.gate.svh + (size_t)e * I, *svu = shared ? p.sup.svh : p.up.svh + (size_t)e * I;
+  const __half *sud = shared ? p.sdn.suh : p.down.suh + (size_t)e * I;
+  const float *raw = p.raw_gu + (size_t)pos * 2 * I;
+  for (int c0 = 0; c0 < I / 128; c0 += 2) {
+    float4 gr[2], ur[2];
+    uint2 s_g[2], s_u[2], s_d[2];
 #pragma unroll
-  for (int j = 0; j < 4; j++) td[warp][lane + 32 * j] = __float2half_rn(hh[j]);
-  __syncthreads();
-  store_blocked_chunk(td, p.xh_d + ((size_t)grp * (I >> 3) + chunk * 16) * 64);
+    for (int i = 0; i < 2; i++) {
+      const int o = (min(c0 + i, I / 128 - 1)) * 128 + 4 * lane;
+      gr[i] = *reinterpret_cast<const float4 *>(raw + o);
+      ur[i] = *reinterpret_cast<const float4 *>(raw + I + o);
+      s_g[i] = *reinterpret_cast<const uint2 *>(svg + o);
+      s_u[i] = *reinterpret_cast<const uint2 *>(svu + o);
+      s_d[i] = *reinterpret_cast<const uint2 *>(sud + o);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      if (c0 + i < I / 128) {
+        float gv[4] = {gr[i].x, gr[i].y, gr[i].z, gr[i].w}, uv[4] = {ur[i].x, ur[i].y, ur[i].z, ur[i].w}, hh[4];
+        fwht128_contig(gv, lane, PF_HS);
+        fwht128_contig(uv, lane, PF_HS);
+        const float4 g4 = mul4(make_float4(gv[0], gv[1], gv[2], gv[3]), s_g[i]), u4 = mul4(make_float4(uv[0], uv[1], uv[2], uv[3]), s_u[i]);
+        const float4 d4 = mul4(make_float4(1.0f, 1.0f, 1.0f, 1.0f), s_d[i]);
+        hh[0] = g4.x / (1.0f + expf(-g4.x)) * u4.x * d4.x;
+        hh[1] = g4.y / (1.0f + expf(-g4.y)) * u4.y * d4.y;
+        hh[2] = g4.z / (1.0f + expf(-g4.z)) * u4.z * d4.z;
+        hh[3] = g4.w / (1.0f + expf(-g4.w)) * u4.w * d4.w;
+        fwht128_contig(hh, lane, PF_HS);
+        *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_d, pos, c0 + i, lane, I)) = pack4(hh);
+      }
+    }
+  }
 }
 
-// finish: per (token, 128-column block) one warp per slot + one for the shared expert; slot-ordered sum
+// finish: one CTA per (token, 512-column quarter), one warp per slot + one for the shared expert: every warp finishes its
+// slot's 4 chunks (H128, svh, routing weight) into shared memory, then the CTA sums the slots in slot order
 // (reference pf_moe.metal:129-161)
+constexpr int PF_FQ = 512;
 __global__ void __launch_bounds__(32 * 17) pf_finish_kernel(const PfParams p) {
-  __shared__ float vals[17][128];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, blk = blockIdx.x, t = blockIdx.y, H = p.H, k = p.topk;
-  const float hs = 0.08838834764831845f;
-  if (warp <= k) {
+  __shared__ __align__(16) float vals[17][PF_FQ];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q0 = blockIdx.x * PF_FQ, t = blockIdx.y, H = p.H, k = p.topk;
+  const int nslots = k + (p.has_shared ? 1 : 0);
+  const int nch = min(PF_FQ, H - q0) / 128;
+  if (warp < nslots) {
     const bool shared = warp == k;
-    if (!shared || p.has_shared) {
-      const int pos = shared ? p.off[p.E] + t : p.inv[t * k + warp];
-      const int e = shared ? 0 : (int)p.route[(size_t)t * 2 * k + warp];
-      const float w = shared ? 1.0f / (1.0f + expf(-p.logits[(size_t)t * (p.E + 1) + p.E])) : __uint_as_float(p.route[(size_t)t * 2 * k + k + warp]);
-      const __half *sv = (shared ? p.sdn.svh : p.down.svh + (size_t)e * H) + blk * 128;
-      const float *raw = p.raw_d + (size_t)pos * H + blk * 128;
-      float v[4];
+    const int pos = shared ? p.off[p.E] + t : p.inv[t * k + warp];
+    const int e = shared ? 0 : (int)p.route[(size_t)t * 2 * k + warp];
+    const float w = shared ? 1.0f / (1.0f + expf(-p.logits[(size_t)t * (p.E + 1) + p.E])) : __uint_as_float(p.route[(size_t)t * 2 * k + k + warp]);
+    const __half *sv = (shared ? p.sdn.svh : p.down.svh + (size_t)e * H) + q0;
+    const float *raw = p.raw_d + (size_t)pos * H + q0;
+    float4 rv[4];
+    uint2 sc[4];
 #pragma unroll
-      for (int j = 0; j < 4; j++) v[j] = raw[lane + 32 * j];
-      fwht_chunk(v, lane, 128, hs);
+    for (int i = 0; i < 4; i++) {
+      const int o = min(i, nch - 1) * 128 + 4 * lane;
+      rv[i] = *reinterpret_cast<const float4 *>(raw + o);
+      sc[i] = *reinterpret_cast<const uint2 *>(sv + o);
+    }
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const float f = v[j] * __half2float(sv[lane + 32 * j]);
-        if (shared) p.sho[(size_t)t * H + blk * 128 + lane + 32 * j] = f;
-        vals[warp][lane + 32 * j] = f * w;
+    for (int i = 0; i < 4; i++) {
+      if (i < nch) {
+        float v[4] = {rv[i].x, rv[i].y, rv[i].z, rv[i].w};
+        fwht128_contig(v, lane, PF_HS);
+        const float4 f = mul4(make_float4(v[0], v[1], v[2], v[3]), sc[i]);
+        if (shared) *reinterpret_cast<float4 *>(p.sho + (size_t)t * H + q0 + i * 128 + 4 * lane) = f;
+        *reinterpret_cast<float4 *>(&vals[warp][i * 128 + 4 * lane]) = make_float4(f.x * w, f.y * w, f.z * w, f.w * w);
       }
     }
   }
   __syncthreads();
-  if (warp != 0) return;
-#pragma unroll
-  for (int j = 0; j < 4; j++) {
-    float acc = 0.0f;
-    for (int s = 0; s < k + (p.has_shared ? 1 : 0); s++) acc += vals[s][lane + 32 * j];
-    p.y[(size_t)t * H + blk * 128 + lane + 32 * j] = acc;
+  const int c = threadIdx.x * 4;
+  if (c >= nch * 128) return;
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int s = 0; s < nslots; s++) {
+    const float4 v = *reinterpret_cast<const float4 *>(&vals[s][c]);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
+  *reinterpret_cast<float4 *>(p.y + (size_t)t * H + q0 + c) = acc;
 }
 
 // =============================================================================================== host side
@@ -505,12 +631,14 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   const int groups = p.pos_cap / 8;
   IJ_CUDA(cudaMemsetAsync(p.order, 0xFF, (size_t)p.pos_cap * 4, st));
   IJ_CUDA(cudaMemsetAsync(p.seid, 0xFF, (size_t)p.pos_cap * 4, st));
-  pf_logits_kernel<<<dim3((p.n + 63) / 64, (p.E + 1 + 63) / 64), 256, 0, st>>>(p);
+  pf_logits_kernel<<<dim3((p.n + LG_T - 1) / LG_T, (p.E + LG_T - 1) / LG_T), 256, 0, st>>>(p);
   pf_route_kernel<<<(p.n + 7) / 8, 256, 0, st>>>(p);
-  pf_count_kernel<<<p.E, 256, 0, st>>>(p);
+  const int nb = (p.S + PS_BLOCK - 1) / PS_BLOCK, nbs = p.has_shared ? (p.n + PS_BLOCK - 1) / PS_BLOCK : 0;
+  pf_hist_kernel<<<nb, 32, 0, st>>>(p, p.hist);
+  pf_blockscan_kernel<<<(p.E + 7) / 8, 256, 0, st>>>(p, p.hist, nb);
   pf_scan_kernel<<<1, 1024, 0, st>>>(p);
-  pf_place_kernel<<<(p.S + p.n + 255) / 256, 256, 0, st>>>(p, p.order);
-  pf_prep_kernel<<<dim3(p.H / 128, groups), 256, 0, st>>>(p, p.order);
+  pf_place_kernel<<<nb + nbs, 32, 0, st>>>(p, p.order, p.hist, nb);
+  pf_prep_kernel<<<groups, 256, 0, st>>>(p, p.order);
   IJ_CUDA(cudaGetLastError());
   PgGemm g{};
   g.items = p.items_gu; g.nitems = p.nitems;
@@ -519,7 +647,7 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   g.out[0] = p.raw_gu; g.out[1] = p.raw_gu + p.I;
   g.ldo = 2 * p.I; g.in = p.H; g.IT = p.H / 16; g.OT = p.I / 16; g.Kx = p.Kx; g.Ks = p.has_shared ? p.Ks : p.Kx;
   launch_pf_gemm(g, status, st);
-  pf_mid_kernel<<<dim3(p.I / 128, groups), 256, 0, st>>>(p);
+  pf_mid_kernel<<<groups, 256, 0, st>>>(p);
   IJ_CUDA(cudaGetLastError());
   PgGemm d{};
   d.items = p.items_d; d.nitems = p.nitems + 1;
@@ -528,7 +656,7 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   d.out[0] = p.raw_d;
   d.ldo = p.H; d.in = p.I; d.IT = p.I / 16; d.OT = p.H / 16; d.Kx = p.Kx; d.Ks = g.Ks;
   launch_pf_gemm(d, status, st);
-  pf_finish_kernel<<<dim3(p.H / 128, p.n), 32 * 17, 0, st>>>(p);
+  pf_finish_kernel<<<dim3((p.H + PF_FQ - 1) / PF_FQ, p.n), 32 * 17, 0, st>>>(p);
   IJ_CUDA(cudaGetLastError());
 }
 

@@ -37,7 +37,7 @@ struct PfParams {
   uint32_t *route;       // [n][2 topk]
   int *cnt;              // [E] slots per expert
   int *off;              // [E + 2] first position of each expert (8-row padded); [E] = first shared position, [E + 1] = end
-  int *rank;             // [S] index of the slot among its expert's slots, in slot order
+  int *hist;             // [ceil(S / 256)][E] per-block expert counts, then their exclusive scan over the blocks
   int *inv;              // [S] slot -> position
   int *order;            // [pos_cap] position -> slot (S + t = shared row of token t, -1 = padding), rewritten every run
   int *seid;             // [pos_cap] position -> expert (E = shared, -1 = padding), rewritten every run
