@@ -164,3 +164,44 @@ def test_forward_ep_summands_add_up_to_the_block(eng):
         assert rel_max(part, want) < 2e-4
         total += part
     assert rel_max(total, full) < 1e-5
+
+
+def _tie_pack(mode):
+    """Small MoE layer whose router produces exact ties: 'all' = zero router (every logit 0), 'dups' = every router row
+    repeated four times (ids 4j .. 4j+3 share a logit)."""
+    rng = np.random.default_rng(7)
+    t = packgen.moe_layer(rng, hidden=256, inter=256, experts=64, k_expert=4, k_shared=4)
+    name = "language_model.model.layers.0.mlp.gate.weight"
+    dt, w = t[name]
+    w = w.copy()
+    if mode == "all":
+        w[:] = 0
+    else:
+        w[:] = np.repeat(w[::4], 4, axis=0)
+    t[name] = (dt, w)
+    return t, rng
+
+
+@pytest.mark.parametrize("mode", ["all", "dups"])
+def test_router_ties_go_to_the_lowest_index(eng, mode):
+    import torch
+    from ijah_b200 import engine as E
+    t, rng = _tie_pack(mode)
+    rows, k = 5, 6
+    x = rng.standard_normal((rows, 256)).astype(np.float16).astype(np.float32)
+    blk = E.MoeBlock(eng, t, top_k=k, max_rows=rows)
+    y = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    ids, w = blk.route(rows)
+    want = CO.moe_block_emul(t, x, top_k=k)
+    if mode == "all":  # more candidates than a warp holds: the round-based fallback decides
+        assert np.array_equal(ids, np.tile(np.arange(k), (rows, 1)))
+        assert np.allclose(w, 1.0 / k)
+    else:
+        assert (ids[:, 0] % 4 == 0).all() and np.array_equal(ids[:, 1], ids[:, 0] + 1)
+    assert np.array_equal(ids, want["ids"])
+    assert rel_max(y, want["out"]) < 2e-4
+    # the prefill router must pick the same experts
+    yp = blk.prefill(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert rel_max(yp, want["out"]) < 2e-4
+    assert eng.lib.ne_device_wait_status() == 0
+    blk.free()
