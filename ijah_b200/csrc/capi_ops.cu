@@ -214,6 +214,16 @@ NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows,
   });
 }
 
+NE_API int ne_exl3_linear_prefill(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream) {
+  return c_call([&] {
+    check_weight(w);
+    IJ_CHECK(x_dev && y_dev, "null activation pointer");
+    void *scratch = device_scratch(pf_linear_scratch_bytes(w->in, w->out, rows));
+    launch_pf_linear(w->trellis_dev, w->suh_dev, w->svh_dev, w->in, w->out, w->K, x_dev, rows, y_dev, scratch, device_status_word(),
+                     (cudaStream_t)stream);
+  });
+}
+
 NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host) {
   return c_call([&] {
     check_weight(w);

@@ -620,6 +620,85 @@ __global__ void __launch_bounds__(32 * 17) pf_finish_kernel(const PfParams p) {
   *reinterpret_cast<float4 *>(p.y + (size_t)t * H + q0 + c) = acc;
 }
 
+// =============================================================================================== one Linear, many rows
+// y[n][out] = x[n][in] @ W for n > 64 rows (reference: t6::record_prefill, kernels/trunk6/trunk6.mm:385-492, which
+// decodes W' densely once per chunk and runs an fp16 GEMM): the same grouped GEMM with a single group that holds all
+// rows, i.e. every tile is decoded once per 128 rows straight into the tensor core's operand layout.
+__global__ void __launch_bounds__(256) pfl_prep_kernel(const float *__restrict__ x, const __half *__restrict__ suh, __half *xh, int n, int n8, int in) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = blockIdx.x * 8 + warp;
+  if (r >= n8) return;
+  for (int c0 = 0; c0 < in / 128; c0 += 4) {
+    float4 xv[4];
+    uint2 sc[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int o = min(c0 + i, in / 128 - 1) * 128 + 4 * lane;
+      xv[i] = r < n ? *reinterpret_cast<const float4 *>(x + (size_t)r * in + o) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      sc[i] = *reinterpret_cast<const uint2 *>(suh + o);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      if (c0 + i < in / 128) {
+        const float4 m = mul4(xv[i], sc[i]);
+        float v[4] = {m.x, m.y, m.z, m.w};
+        fwht128_contig(v, lane, PF_HS);
+        *reinterpret_cast<uint2 *>(blocked_lane_ptr(xh, r, c0 + i, lane, in)) = pack4(v);
+      }
+    }
+  }
+}
+
+__global__ void pfl_items_kernel(PfItem *items, int *nitems, int n, int ncb) {
+  const int passes = (n + PF_NTOK - 1) / PF_NTOK, total = passes * ncb;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int pass = i / ncb, cb = i - pass * ncb;
+    items[i] = PfItem{-1, 0, cb, pass * PF_NTOK, min(PF_NTOK, n - pass * PF_NTOK), {0, 0, 0}};
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) *nitems = total;
+}
+
+__global__ void __launch_bounds__(256) pfl_finish_kernel(const float *__restrict__ raw, const __half *__restrict__ svh, float *y, int n, int out) {
+  const int lane = threadIdx.x & 31, nc = out / 128, job = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (job >= n * nc) return;
+  const int r = job / nc, o = (job - r * nc) * 128 + 4 * lane;
+  const float4 rv = *reinterpret_cast<const float4 *>(raw + (size_t)r * out + o);
+  const uint2 sc = *reinterpret_cast<const uint2 *>(svh + o);
+  float v[4] = {rv.x, rv.y, rv.z, rv.w};
+  fwht128_contig(v, lane, PF_HS);
+  *reinterpret_cast<float4 *>(y + (size_t)r * out + o) = mul4(make_float4(v[0], v[1], v[2], v[3]), sc);
+}
+
+size_t pf_linear_scratch_bytes(int in, int out, int n) {
+  const size_t n8 = ((size_t)n + 7) & ~(size_t)7, passes = ((size_t)n + PF_NTOK - 1) / PF_NTOK;
+  return n8 * in * 2 + n8 * out * 4 + passes * (out / PF_NCOL) * sizeof(PfItem) + 1024;
+}
+
+void launch_pf_linear(const void *trellis, const void *suh, const void *svh, int in, int out, int K, const float *x, int n, float *y,
+                      void *scratch, int *status, cudaStream_t st) {
+  IJ_CHECK(in % 128 == 0 && out % 256 == 0, "prefill Linear needs in %% 128 == 0 and out %% 256 == 0 (%d -> %d)", in, out);
+  IJ_CHECK(K >= 4 && K <= 8, "EXL3 bits per weight %d outside 4..8", K);
+  IJ_CHECK(n >= 1 && n <= 65535 * 8, "prefill Linear: %d rows", n);
+  const size_t n8 = ((size_t)n + 7) & ~(size_t)7, passes = ((size_t)n + PF_NTOK - 1) / PF_NTOK;
+  char *base = (char *)scratch;
+  __half *xh = (__half *)base;
+  float *raw = (float *)(base + n8 * in * 2);
+  PfItem *items = (PfItem *)(base + n8 * in * 2 + n8 * out * 4);
+  int *nitems = (int *)((char *)items + passes * (out / PF_NCOL) * sizeof(PfItem));
+  nitems = (int *)(((uintptr_t)nitems + 15) & ~(uintptr_t)15);
+  pfl_prep_kernel<<<(int)(n8 / 8), 256, 0, st>>>(x, (const __half *)suh, xh, n, (int)n8, in);
+  pfl_items_kernel<<<8, 256, 0, st>>>(items, nitems, n, out / PF_NCOL);
+  IJ_CUDA(cudaGetLastError());
+  PgGemm g{};
+  g.items = items; g.nitems = nitems;
+  g.w_shared[0] = (const char *)trellis;
+  g.act[0] = xh;
+  g.out[0] = raw;
+  g.ldo = out; g.in = in; g.IT = in / 16; g.OT = out / 16; g.Kx = K; g.Ks = K;
+  launch_pf_gemm(g, status, st);
+  pfl_finish_kernel<<<(n * (out / 128) + 7) / 8, 256, 0, st>>>(raw, (const __half *)svh, y, n, out);
+  IJ_CUDA(cudaGetLastError());
+}
+
 // =============================================================================================== host side
 size_t pf_pos_cap(int n, int topk, int E, bool has_shared) {
   return (((size_t)n * topk + 8 * (size_t)E + (has_shared ? n : 0) + 15) / 8) * 8;

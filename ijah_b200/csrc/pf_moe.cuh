@@ -59,5 +59,9 @@ __host__ __device__ inline size_t blocked_index(int pos, int k, int in) {
 
 size_t pf_pos_cap(int n, int topk, int E, bool has_shared);
 void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st);
+// one EXL3 Linear over n rows through the grouped tensor-core GEMM; scratch: pf_linear_scratch_bytes(in, out, n)
+size_t pf_linear_scratch_bytes(int in, int out, int n);
+void launch_pf_linear(const void *trellis, const void *suh, const void *svh, int in, int out, int K, const float *x, int n, float *y,
+                      void *scratch, int *status, cudaStream_t st);
 
 }  // namespace ijah

@@ -91,6 +91,7 @@ SIGNATURES = {
     "ne_exl3_dequant": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_void_p]),
     "ne_exl3_linear": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_host": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_exl3_linear_prefill": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_static": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_static_capacity": (C.c_uint64, []),
     "ne_moe_create": (C.c_void_p, [C.POINTER(MoeDescC), C.c_int]), "ne_moe_free": (None, [C.c_void_p]),
@@ -346,6 +347,15 @@ class Exl3Linear:
         rows = x.shape[0]
         y = torch.empty((rows, self.n_out), dtype=torch.float32, device=x.device)
         self.eng._ok(self.eng.lib.ne_exl3_linear(C.byref(self.c), _dev(x), rows, _dev(y), _stream()), "ne_exl3_linear")
+        return y
+
+    def prefill(self, x):
+        """many rows at once through the grouped tensor-core GEMM (ne_exl3_linear_prefill)"""
+        torch = _torch()
+        x = x.to(torch.float32).contiguous()
+        rows = x.shape[0]
+        y = torch.empty((rows, self.n_out), dtype=torch.float32, device=x.device)
+        self.eng._ok(self.eng.lib.ne_exl3_linear_prefill(C.byref(self.c), _dev(x), rows, _dev(y), _stream()), "ne_exl3_linear_prefill")
         return y
 
     def forward_static(self, x):

@@ -34,6 +34,10 @@ NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *strea
  * owned by the library (grown on demand). */
 NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host);
+/* The same Linear for many rows (prefill chunks; replaces t6::record_prefill, kernels/trunk6/trunk6.mm:385-492): every tile is
+ * decoded once per 128 rows into shared memory and multiplied on tcgen05 tensor cores with TMEM accumulators. rows >= 1;
+ * in must be a multiple of 128, out of 256. Scratch from the library's per-device arena. */
+NE_API int ne_exl3_linear_prefill(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 /* ne_exl3_linear for callers that must not allocate (no counterpart in the reference, whose unified-memory engine has
  * no such constraint). ne_exl3_linear grows a cudaMalloc'ed arena when a call needs more scratch than any call before
  * it; that is unusable from inside an allocator or memory-pool hook, in a serving loop that was given a fixed memory

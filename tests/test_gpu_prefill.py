@@ -74,3 +74,32 @@ def test_prefill_at_model_dims(eng):
     assert rel_max(y, ref) < 2e-4  # fp32 accumulation order differs (tcgen05 vs mma.sync + k-splits)
     want = CO.moe_block_emul(t, x[:3], top_k=10)
     assert rel_max(y[:3], want["out"]) < 2e-4
+
+
+@pytest.mark.parametrize("n_in,n_out,K,rows", [(512, 256, 6, 77), (2048, 512, 8, 300), (256, 768, 4, 129)])
+def test_trunk_linear_prefill_matches_oracle_and_decode_path(eng, n_in, n_out, K, rows):
+    # one EXL3 Linear over many rows through the grouped tensor-core GEMM: ragged last pass, several 128-row passes
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(n_in + rows)
+    tr, suh, svh = packgen.exl3_linear(rng, n_in, n_out, K)
+    lin = E.Exl3Linear(eng, tr, suh, svh)
+    x = rng.standard_normal((rows, n_in)).astype(np.float16).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y = lin.prefill(xd).cpu().numpy()
+    assert eng.lib.ne_device_wait_status() == 0
+    want = np.concatenate([CO.linear_emul(tr, suh, svh, x[i:i + 64]) for i in range(0, rows, 64)])  # the oracle takes <= 64 rows
+    assert np.linalg.norm(y - want) / np.linalg.norm(want) < 5e-5
+    ref = np.concatenate([lin(xd[i:i + 64]).cpu().numpy() for i in range(0, rows, 64)])
+    assert rel_max(y, ref) < 2e-4
+    assert np.array_equal(y, lin.prefill(xd).cpu().numpy()), "two runs must be bit-identical"
+
+
+def test_trunk_linear_prefill_rejects_unsupported_dims(eng):
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(3)
+    tr, suh, svh = packgen.exl3_linear(rng, 256, 128, 4)
+    lin = E.Exl3Linear(eng, tr, suh, svh)
+    with pytest.raises(E.EngineError):
+        lin.prefill(torch.zeros((70, 256), device="cuda"))
