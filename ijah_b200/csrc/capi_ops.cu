@@ -57,9 +57,9 @@ Moe::~Moe() {
 }
 
 // Prefill: n tokens at once through the sorted / grouped path (pf_moe.cu). Scratch grows with the largest n seen.
-void Moe::prefill(const float *x, int n, float *y, cudaStream_t st) {
-  IJ_CHECK(desc.expert_first == 0 && desc.expert_count == desc.experts, "prefill runs on an object that holds all experts");
+void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st) {
   IJ_CHECK(n >= 1 && n <= 65535, "prefill: %d tokens outside 1..65535", n);
+  IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= n, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, n);
   const size_t H = desc.hidden, I = desc.inter, E = desc.experts, k = desc.top_k;
   if (n > pf_tokens) {
     IJ_CUDA(cudaDeviceSynchronize());
@@ -91,6 +91,8 @@ void Moe::prefill(const float *x, int n, float *y, cudaStream_t st) {
   PfParams p = pf;
   p.H = (int)H; p.I = (int)I; p.E = (int)E; p.topk = (int)k; p.Kx = desc.k_expert; p.Ks = desc.k_shared; p.has_shared = has_shared ? 1 : 0;
   p.n = n; p.S = n * (int)k;
+  p.e0 = desc.expert_first; p.ecount = desc.expert_count;
+  p.sh_row0 = own_row0; p.sh_rows = own_rows;
   p.pos_cap = (int)pf_pos_cap(n, (int)k, (int)E, has_shared);
   p.router = (const uint16_t *)desc.router_dev;
   p.sgate = (const uint16_t *)desc.shared_gate_w_dev;
@@ -291,7 +293,16 @@ NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, in
 NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_dev, void *stream) {
   return c_call([&] {
     IJ_CHECK(m && x_dev && y_dev, "null argument");
-    reinterpret_cast<Moe *>(m)->prefill(x_dev, n_tokens, y_dev, (cudaStream_t)stream);
+    Moe *o = reinterpret_cast<Moe *>(m);
+    IJ_CHECK(o->desc.expert_first == 0 && o->desc.expert_count == o->desc.experts,
+             "ne_moe_prefill runs on an object that holds all experts (expert parallel: ne_moe_prefill_ep)");
+    o->prefill(x_dev, n_tokens, 0, n_tokens, y_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_all_dev && y_part_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->prefill(x_all_dev, n_all, own_row0, own_rows, y_part_dev, (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes) {

@@ -33,7 +33,7 @@ struct Moe {
   PfParams pf{};
   int pf_tokens = 0;
   std::vector<void *> pf_owned;
-  void prefill(const float *x, int n, float *y, cudaStream_t st);
+  void prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st);
 
   Moe(const ne_moe_desc &d, int max_rows);
   ~Moe();

@@ -359,7 +359,10 @@ __global__ void __launch_bounds__(32) pf_hist_kernel(const PfParams p, int *hist
   __syncwarp();
   for (int i = lane; i < PS_BLOCK; i += 32) {
     const int s = b * PS_BLOCK + i;
-    if (s < p.S) atomicAdd(&cnt[p.route[(size_t)(s / k) * 2 * k + s % k]], 1);
+    if (s < p.S) {
+      const int e = (int)p.route[(size_t)(s / k) * 2 * k + s % k];
+      if (e >= p.e0 && e < p.e0 + p.ecount) atomicAdd(&cnt[e], 1);  // slots of experts held elsewhere are not placed
+    }
   }
   __syncwarp();
   for (int e = lane; e < p.E; e += 32) hist[(size_t)b * p.E + e] = cnt[e];
@@ -416,7 +419,7 @@ __global__ void __launch_bounds__(1024) pf_scan_kernel(const PfParams p) {
   const int o = block_excl_scan(c8, wt, &tot8);
   const int pb = block_excl_scan(np, wt, &totp);
   if (e < E) p.off[e] = o;
-  const int nsh = p.has_shared ? p.n : 0, shp = (nsh + PF_NTOK - 1) / PF_NTOK;
+  const int nsh = p.has_shared ? p.sh_rows : 0, shp = (nsh + PF_NTOK - 1) / PF_NTOK;
   if (e == 0) {
     p.off[E] = tot8;
     p.off[E + 1] = tot8 + ((nsh + 7) & ~7);
@@ -428,7 +431,7 @@ __global__ void __launch_bounds__(1024) pf_scan_kernel(const PfParams p) {
     for (int j = 0; j < 2 * GU; j++) p.items_gu[pass * 2 * GU + j] = PfItem{expert, j / GU, j % GU, row0, nrows, {0, 0, 0}};
     for (int j = 0; j < DN; j++) p.items_d[pass * DN + j] = PfItem{expert, 0, j, row0, nrows, {0, 0, 0}};
   };
-  for (int j = 0; j < np; j++) emit(pb + j, e, o + j * PF_NTOK, min(PF_NTOK, c - j * PF_NTOK));
+  for (int j = 0; j < np; j++) emit(pb + j, e - p.e0, o + j * PF_NTOK, min(PF_NTOK, c - j * PF_NTOK));  // index into the local stacks
   for (int j = e; j < shp; j += blockDim.x) emit(totp + j, -1, tot8 + j * PF_NTOK, min(PF_NTOK, nsh - j * PF_NTOK));
 }
 
@@ -439,9 +442,9 @@ __global__ void __launch_bounds__(32) pf_place_kernel(const PfParams p, int *ord
   const int b = blockIdx.x, lane = threadIdx.x, k = p.topk;
   if (b >= nb) {
     if (!p.has_shared) return;
-    for (int t = (b - nb) * PS_BLOCK + lane; t < min(p.n, (b - nb + 1) * PS_BLOCK); t += 32) {
-      const int pos = p.off[p.E] + t;
-      order[pos] = p.S + t;
+    for (int j = (b - nb) * PS_BLOCK + lane; j < min(p.sh_rows, (b - nb + 1) * PS_BLOCK); j += 32) {
+      const int pos = p.off[p.E] + j;
+      order[pos] = p.S + p.sh_row0 + j;
       p.seid[pos] = p.E;
     }
     return;
@@ -451,8 +454,10 @@ __global__ void __launch_bounds__(32) pf_place_kernel(const PfParams p, int *ord
   const uint32_t lt = (1u << lane) - 1u;
   for (int i = lane; i < PS_BLOCK; i += 32) {  // 32 consecutive slots per round, rounds in slot order
     const int s = b * PS_BLOCK + i;
-    const bool on = s < p.S;
-    const int e = on ? (int)p.route[(size_t)(s / k) * 2 * k + s % k] : -1 - lane;
+    const int er = s < p.S ? (int)p.route[(size_t)(s / k) * 2 * k + s % k] : -1;
+    const bool on = er >= p.e0 && er < p.e0 + p.ecount;
+    if (s < p.S && !on) p.inv[s] = -1;
+    const int e = on ? er : -1 - lane;
     const uint32_t same = __match_any_sync(0xFFFFFFFFu, e);
     if (on) {
       const int pos = base[e] + __popc(same & lt);
@@ -502,7 +507,7 @@ __global__ void __launch_bounds__(256) pf_prep_kernel(const PfParams p, const in
   }
   const bool shared = slot >= p.S;
   const int t = shared ? slot - p.S : slot / p.topk;
-  const int e = shared ? 0 : p.seid[pos];
+  const int e = shared ? 0 : p.seid[pos] - p.e0;
   const __half *sg = shared ? p.sgt.suh : p.gate.suh + (size_t)e * H, *su = shared ? p.sup.suh : p.up.suh + (size_t)e * H;
   const float *xr = p.x + (size_t)t * H;
   for (int c0 = 0; c0 < H / 128; c0 += 4) {
@@ -540,8 +545,9 @@ __global__ void __launch_bounds__(256) pf_mid_kernel(const PfParams p) {
     return;
   }
   const bool shared = e == p.E;
-  const __half *svg = shared ? p.sgt.svh : p.gate.svh + (size_t)e * I, *svu = shared ? p.sup.svh : p.up.svh + (size_t)e * I;
-  const __half *sud = shared ? p.sdn.suh : p.down.suh + (size_t)e * I;
+  const int el = shared ? 0 : e - p.e0;
+  const __half *svg = shared ? p.sgt.svh : p.gate.svh + (size_t)el * I, *svu = shared ? p.sup.svh : p.up.svh + (size_t)el * I;
+  const __half *sud = shared ? p.sdn.suh : p.down.suh + (size_t)el * I;
   const float *raw = p.raw_gu + (size_t)pos * 2 * I;
   for (int c0 = 0; c0 < I / 128; c0 += 2) {
     float4 gr[2], ur[2];
@@ -583,10 +589,16 @@ __global__ void __launch_bounds__(32 * 17) pf_finish_kernel(const PfParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q0 = blockIdx.x * PF_FQ, t = blockIdx.y, H = p.H, k = p.topk;
   const int nslots = k + (p.has_shared ? 1 : 0);
   const int nch = min(PF_FQ, H - q0) / 128;
+  bool have = false;
   if (warp < nslots) {
     const bool shared = warp == k;
-    const int pos = shared ? p.off[p.E] + t : p.inv[t * k + warp];
-    const int e = shared ? 0 : (int)p.route[(size_t)t * 2 * k + warp];
+    const int pos = shared ? (t >= p.sh_row0 && t < p.sh_row0 + p.sh_rows ? p.off[p.E] + t - p.sh_row0 : -1) : p.inv[t * k + warp];
+    have = pos >= 0;
+  }
+  if (have) {
+    const bool shared = warp == k;
+    const int pos = shared ? p.off[p.E] + t - p.sh_row0 : p.inv[t * k + warp];
+    const int e = shared ? 0 : (int)p.route[(size_t)t * 2 * k + warp] - p.e0;
     const float w = shared ? 1.0f / (1.0f + expf(-p.logits[(size_t)t * (p.E + 1) + p.E])) : __uint_as_float(p.route[(size_t)t * 2 * k + k + warp]);
     const __half *sv = (shared ? p.sdn.svh : p.down.svh + (size_t)e * H) + q0;
     const float *raw = p.raw_d + (size_t)pos * H + q0;
@@ -608,6 +620,9 @@ __global__ void __launch_bounds__(32 * 17) pf_finish_kernel(const PfParams p) {
         *reinterpret_cast<float4 *>(&vals[warp][i * 128 + 4 * lane]) = make_float4(f.x * w, f.y * w, f.z * w, f.w * w);
       }
     }
+  } else if (warp < nslots) {  // a slot computed on another rank, or a row whose shared expert runs elsewhere
+#pragma unroll
+    for (int i = 0; i < 4; i++) *reinterpret_cast<float4 *>(&vals[warp][i * 128 + 4 * lane]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   }
   __syncthreads();
   const int c = threadIdx.x * 4;
@@ -712,7 +727,9 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   IJ_CUDA(cudaMemsetAsync(p.seid, 0xFF, (size_t)p.pos_cap * 4, st));
   pf_logits_kernel<<<dim3((p.n + LG_T - 1) / LG_T, (p.E + LG_T - 1) / LG_T), 256, 0, st>>>(p);
   pf_route_kernel<<<(p.n + 7) / 8, 256, 0, st>>>(p);
-  const int nb = (p.S + PS_BLOCK - 1) / PS_BLOCK, nbs = p.has_shared ? (p.n + PS_BLOCK - 1) / PS_BLOCK : 0;
+  IJ_CHECK(p.e0 >= 0 && p.ecount >= 0 && p.e0 + p.ecount <= p.E, "prefill: bad expert slice");
+  IJ_CHECK(p.sh_row0 >= 0 && p.sh_rows >= 0 && p.sh_row0 + p.sh_rows <= p.n, "prefill: shared rows [%d, %d) outside [0, %d)", p.sh_row0, p.sh_row0 + p.sh_rows, p.n);
+  const int nb = (p.S + PS_BLOCK - 1) / PS_BLOCK, nbs = p.has_shared ? (p.sh_rows + PS_BLOCK - 1) / PS_BLOCK : 0;
   pf_hist_kernel<<<nb, 32, 0, st>>>(p, p.hist);
   pf_blockscan_kernel<<<(p.E + 7) / 8, 256, 0, st>>>(p, p.hist, nb);
   pf_scan_kernel<<<1, 1024, 0, st>>>(p);

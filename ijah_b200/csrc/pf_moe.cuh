@@ -25,6 +25,8 @@ struct PfItem {
 
 struct PfParams {
   int H, I, E, topk, Kx, Ks, has_shared;
+  int e0, ecount;  // the experts this object holds (expert parallel): slots of other experts are left to their owners
+  int sh_row0, sh_rows;  // tokens whose shared expert is computed here
   int n;           // tokens
   int S;           // n * topk slots
   int pos_cap;     // capacity of the padded position space

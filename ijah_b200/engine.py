@@ -100,6 +100,7 @@ SIGNATURES = {
     "ne_moe_stage": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_prefill_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "ne_moe_experts_gu": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
@@ -456,6 +457,15 @@ class MoeBlock:
         n = x.shape[0]
         y = torch.empty((n, self.H), dtype=torch.float32, device=x.device) if out is None else out
         self.eng._ok(self.eng.lib.ne_moe_prefill(self.ptr, _dev(x), n, _dev(y), _stream()), "ne_moe_prefill")
+        return y
+
+    def prefill_ep(self, x_all, own_row0, own_rows, out=None):
+        """this rank's summand of the prefill output for the tokens of all ranks (ne_moe_prefill_ep)"""
+        torch = _torch()
+        n = x_all.shape[0]
+        y = torch.empty((n, self.H), dtype=torch.float32, device=x_all.device) if out is None else out
+        self.eng._ok(self.eng.lib.ne_moe_prefill_ep(self.ptr, _dev(x_all), n, own_row0, own_rows, _dev(y), _stream()),
+                     "ne_moe_prefill_ep")
         return y
 
     def forward_ep(self, x_all, own_row0, own_rows, out=None):

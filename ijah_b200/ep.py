@@ -42,12 +42,13 @@ class ExpertParallelMoe:
             self._y_part = torch.empty((rows * self.world, H), dtype=torch.float32, device=x.device)
         return self._x_all, self._y_part
 
-    def forward(self, x, out=None):
-        """x [rows, H] float32 (every rank the same row count) -> y [rows, H]"""
+    def forward(self, x, out=None, prefill=False):
+        """x [rows, H] float32 (every rank the same row count) -> y [rows, H]; prefill: the many-token path
+        (block.prefill_ep: sorted slots, grouped tensor-core GEMM) instead of the decode-width kernels"""
         rows, H = x.shape
         x_all, y_part = self._buffers(x)
         dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
-        self.block.forward_ep(x_all, self.rank * rows, rows, out=y_part)
+        (self.block.prefill_ep if prefill else self.block.forward_ep)(x_all, self.rank * rows, rows, out=y_part)
         y = torch.empty_like(x) if out is None else out
         if self.backend == "gloo":  # gloo has no reduce_scatter: all_reduce and keep the own slice
             dist.all_reduce(y_part, group=self.group)

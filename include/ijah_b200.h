@@ -92,8 +92,8 @@ NE_API int ne_moe_forward_routed(ne_moe *m, const float *x_dev, const uint32_t *
  * reference's chunked-prefill MoE (models/flash_next/prefill.mm:235-276 record_moe; kernels/prefill/pf_moe.metal):
  * router GEMM + top-k, deterministic counting sort of the n*top_k slots by expert, per-expert grouped GEMMs whose
  * trellis tiles are decoded into shared memory once per 128 rows and multiplied on tcgen05 tensor cores with TMEM
- * accumulators, SwiGLU, slot-ordered finish. The object must hold all experts; hidden and inter must be multiples of
- * 256. Scratch (about 300 KB per token) is allocated on the first call and grown when a later call brings more tokens. */
+ * accumulators, SwiGLU, slot-ordered finish. The object must hold all experts (else: ne_moe_prefill_ep); hidden and inter
+ * must be multiples of 256. Scratch (about 300 KB per token) is allocated on the first call and grown when a later call brings more tokens. */
 NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_dev, void *stream);
 /* Expert parallel, whole block (new with this library; the reference is single-device): x_all holds the rows of ALL
  * ranks, [own_row0, own_row0 + own_rows) being the caller's. Routing runs on every row (same result on every rank),
@@ -101,6 +101,10 @@ NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_
  * caller's own rows only. y_part[rows_all][hidden] is this rank's summand: the sum over ranks is the block output. */
 NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, int own_row0, int own_rows, float *y_part_dev,
                              void *stream);
+/* Expert-parallel prefill: x_all holds the tokens of ALL ranks, [own_row0, own_row0 + own_rows) being the caller's. Every
+ * token is routed (same result on every rank), only the slots whose expert lies in this object's slice are sorted and
+ * computed, the shared expert runs for the caller's own tokens only. y_part[n_all][hidden] is this rank's summand. */
+NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream);
 /* Device pointer and size of a named intermediate of the last run: "logits" "route" "shared_gu" "shared_down"
  * "experts_gu_raw" (per k-split partial products [S][rows*top_k][2][inter]) "plan". */
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes);

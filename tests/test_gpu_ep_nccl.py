@@ -1,0 +1,62 @@
+"""Expert parallel over NCCL on two GPUs (skipped on a single-GPU box): decode widths and prefill against the single-GPU block."""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["IJAH_ROOT"])
+from ijah_b200 import engine as E, ep, packgen
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+eng = E.Engine()
+rng = np.random.default_rng(5)
+t = packgen.moe_layer(rng, hidden=512, inter=256, experts=32)
+per = 32 // world
+x_all = rng.standard_normal((world * 40, 512)).astype(np.float16).astype(np.float32)
+full = E.MoeBlock(eng, t, top_k=4, max_rows=16, device=dev)
+blk = E.MoeBlock(eng, t, top_k=4, max_rows=16 * world, expert_first=rank * per, expert_count=per, device=dev)
+par = ep.ExpertParallelMoe(blk, dist.group.WORLD)
+# decode widths: 6 rows per rank
+xs = torch.from_numpy(x_all[rank * 6:(rank + 1) * 6]).to(dev)
+want = full.forward(torch.from_numpy(x_all[:world * 6]).to(dev))[rank * 6:(rank + 1) * 6]
+got = par.forward(xs)
+err_d = float((got - want).abs().max() / want.abs().max())
+# prefill: 40 tokens per rank
+xp = torch.from_numpy(x_all[rank * 40:(rank + 1) * 40]).to(dev)
+wantp = full.prefill(torch.from_numpy(x_all).to(dev))[rank * 40:(rank + 1) * 40]
+gotp = par.forward(xp, prefill=True)
+err_p = float((gotp - wantp).abs().max() / wantp.abs().max())
+torch.cuda.synchronize()
+status = eng.lib.ne_device_wait_status()
+dist.barrier()
+dist.destroy_process_group()
+assert err_d < 1e-5 and err_p < 1e-5 and status == 0, (err_d, err_p, status)
+print("EP_OK", rank, err_d, err_p)
+"""
+
+
+def test_expert_parallel_matches_single_gpu_on_two_gpus(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, IJAH_ROOT=str(ROOT), NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", str(port), str(script)], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.stdout.count("EP_OK") == 2

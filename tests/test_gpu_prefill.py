@@ -103,3 +103,27 @@ def test_trunk_linear_prefill_rejects_unsupported_dims(eng):
     lin = E.Exl3Linear(eng, tr, suh, svh)
     with pytest.raises(E.EngineError):
         lin.prefill(torch.zeros((70, 256), device="cuda"))
+
+
+def test_prefill_ep_summands_add_up_to_the_block(eng):
+    # three expert-parallel "ranks" as three objects on one GPU: tokens of all ranks in, each returns its summand
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(31)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=48)
+    x = rng.standard_normal((150, 512)).astype(np.float16).astype(np.float32)
+    x_all = torch.from_numpy(x).cuda()
+    full = E.MoeBlock(eng, t, top_k=4, max_rows=8).prefill(x_all).cpu().numpy()
+    total = np.zeros_like(full)
+    for r in range(3):
+        blk = E.MoeBlock(eng, t, top_k=4, max_rows=8, expert_first=16 * r, expert_count=16)
+        part = blk.prefill_ep(x_all, 50 * r, 50).cpu().numpy()
+        assert eng.lib.ne_device_wait_status() == 0
+        for i in (0, 64, 128):
+            want = CO.moe_block_emul(t, x[i:i + 22], top_k=4, expert_range=(16 * r, 16 * r + 16),
+                                     shared_rows=(max(50 * r - i, 0), max(min(50 * r + 50, i + 22) - max(50 * r, i), 0)))["out"]
+            assert rel_max(part[i:i + 22], want) < 2e-4
+        total += part
+    assert rel_max(total, full) < 1e-5
+    with pytest.raises(E.EngineError):  # the single-GPU entry point refuses an object that holds a slice
+        blk.prefill(x_all)
