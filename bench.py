@@ -146,6 +146,7 @@ def main():
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill figure in extra (0 = skip)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     rank = int(os.environ.get("RANK", 0))
@@ -295,6 +296,44 @@ def main():
                  "distinct_experts_mean": float(np.mean([x["distinct_experts"] for x in lbs])),
                  "block": {"bytes": tot, "us": ms_per_step * 1e3 / L, "achieved": tot / (ms_per_step * 1e-3 / L) / 1e9,
                            "frac": tot / (ms_per_step * 1e-3 / L) / 1e9 / peak}}
+    # ---- prefill (config 4): one block over 4096 tokens with Zipf(1.1)-skewed routing; N > 1: the same 4096 tokens split
+    # over the ranks (strong scaling), all-gather + expert-parallel prefill + reduce-scatter
+    n_pf = a.prefill_tokens
+    if n_pf > 0:
+        last = synth.moe_layer(1000 + L - 1, expert_first=rank * per, expert_count=per, router_seed=77 + L - 1, device=dev, **DIMS)
+        synth.zipf_router_bias(last)
+        pblk = E.MoeBlock(eng, last, top_k=TOPK, max_rows=16, expert_first=rank * per, expert_count=per, device=dev)
+        gp = torch.Generator(device=dev).manual_seed(99 + rank)
+        xp = torch.randn((n_pf // N, H), device=dev, generator=gp).to(torch.float16).to(torch.float32)
+        xp[:, 0] = 1.0
+        yp = torch.empty_like(xp)
+        if N == 1:
+            def pf_step():
+                pblk.prefill(xp, out=yp)
+        else:
+            pep = ep.ExpertParallelMoe(pblk, dist.group.WORLD)
+
+            def pf_step():
+                pep.forward(xp, out=yp, prefill=True)
+        for _ in range(3):
+            pf_step()
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(5):
+            pf_step()
+        p1.record()
+        barrier()
+        pms = p0.elapsed_time(p1) / 5
+        if N > 1:
+            tt = torch.tensor([pms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            pms = float(tt.item())
+        flop = n_pf * TOPK * 3 * 2 * DIMS["hidden"] * DIMS["inter"]
+        tpeak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"] if (ROOT / "MEASURED_PEAKS.json").exists() else 1590.0
+        extra["prefill"] = {"tokens": n_pf, "ms": pms, "tok_per_s": n_pf / pms * 1e3, "routed_tflops": flop / pms / 1e9,
+                            "frac_of_dense_f16_peak": flop / pms / 1e9 / tpeak / N, "scaling": "strong" if N > 1 else None,
+                            "routing": "Zipf(1.1) bias on the router logits"}
     status = eng.lib.ne_device_wait_status()
     if rank == 0:
         cpu = None

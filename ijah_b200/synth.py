@@ -36,6 +36,14 @@ def moe_layer(seed, layer=0, hidden=2048, inter=768, experts=512, k_expert=5, k_
     return t
 
 
+def zipf_router_bias(tensors, layer=0, s=1.1):
+    """Skew the routing of a layer in place: router column 0 becomes -s * log(rank of the expert) (centred), so that with
+    activations whose channel 0 is 1 the per-expert token counts follow a Zipf(s)-like law (the prefill configuration)."""
+    w = tensors[f"{PFX}{layer}.mlp.gate.weight"][1]
+    bias = -s * torch.log(torch.arange(1, w.shape[0] + 1, device=w.device, dtype=torch.float32))
+    w[:, 0] = (bias - bias.mean()).to(torch.bfloat16)
+
+
 def to_numpy(tensors):
     """the same dict with numpy arrays (uint16 for U16 / BF16, float16 for F16), for the CPU oracle"""
     import numpy as np
