@@ -124,7 +124,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   const MoeSplits &s = splits(rows);
   p.S_gu = s.S_gu; p.kc_gu = s.kc_gu; p.S_d = s.S_d; p.kc_d = s.kc_d;
   p.h_mid = h_mid; p.inj = inj; p.h_out = h_out; p.HC = HC;
-  p.sh_row0 = 0; p.sh_rows = rows;
+  p.sh_row0 = 0; p.sh_rows = rows; p.lg_row0 = 0;
   return p;
 }
 
@@ -174,6 +174,30 @@ void Moe::forward_ep(const float *x, int rows, int own_row0, int own_rows, float
   p.sh_rows = own_rows;
   const MoeSplits &s = splits(rows);
   launch_moe_router(p, false, st);  // the plan is built beside the operand prep
+  launch_moe_prep(p, true, st);
+  launch_moe_gateup(p, s, status, st);
+  launch_moe_mid(p, st);
+  launch_moe_down(p, s, status, st);
+  launch_moe_combine(p, false, st);
+  last_rows = rows;
+}
+
+// The router alone on `rows` rows: routes to route_out ([rows][2 top_k], or the object's own buffer), logits (with the shared
+// expert's gate logit) stay in the object for a following forward_ep_routed.
+void Moe::route_rows(const float *x, int rows, uint32_t *route_out, cudaStream_t st) {
+  MoeParams p = params(x, rows, nullptr);
+  if (route_out) p.route = route_out;
+  launch_moe_router(p, false, st);
+}
+
+// Expert parallel with the routing done by each row's home rank: rows and routes of all ranks come in; the shared expert's
+// gate logits of the own rows are the ones route_rows left in the object.
+void Moe::forward_ep_routed(const float *x, const uint32_t *route_all, int rows, int own_row0, int own_rows, float *y, cudaStream_t st) {
+  MoeParams p = params(x, rows, y);
+  IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= rows, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, rows);
+  p.route = const_cast<uint32_t *>(route_all);
+  p.sh_row0 = own_row0; p.sh_rows = own_rows; p.lg_row0 = own_row0;
+  const MoeSplits &s = splits(rows);
   launch_moe_prep(p, true, st);
   launch_moe_gateup(p, s, status, st);
   launch_moe_mid(p, st);
@@ -297,6 +321,19 @@ NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_
     IJ_CHECK(o->desc.expert_first == 0 && o->desc.expert_count == o->desc.experts,
              "ne_moe_prefill runs on an object that holds all experts (expert parallel: ne_moe_prefill_ep)");
     o->prefill(x_dev, n_tokens, 0, n_tokens, y_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_route(ne_moe *m, const float *x_dev, int rows, uint32_t *route_out_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->route_rows(x_dev, rows, route_out_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, const uint32_t *route_all_dev, int rows_all, int own_row0, int own_rows,
+                                    float *y_part_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_all_dev && route_all_dev && y_part_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->forward_ep_routed(x_all_dev, route_all_dev, rows_all, own_row0, own_rows, y_part_dev, (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream) {

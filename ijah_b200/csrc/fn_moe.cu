@@ -491,7 +491,7 @@ struct MoeGateUpProblem {
     un.shared = q >= *pv.nu();
     const Exl3Stack *w;
     if (un.shared) {
-      un.e = 0; un.first = 0; un.nrows = p.rows; un.K = p.Ks;
+      un.e = 0; un.first = 0; un.nrows = p.sh_rows; un.K = p.Ks;  // only the rows whose shared expert runs here
       w = un.proj ? &p.sup : &p.sgt;
     } else {
       un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx;
@@ -503,7 +503,7 @@ struct MoeGateUpProblem {
     return un;
   }
   // row index = the (row, slot) pair for routed units, the activation row for the shared expert
-  __device__ int row_index(const Unit &un, int i) const { return un.shared ? i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
+  __device__ int row_index(const Unit &un, int i) const { return un.shared ? p.sh_row0 + i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sgu : p.xh_gu) + ((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16;
   }
@@ -535,14 +535,14 @@ struct MoeDownProblem {
     un.kc = min(kc, IT - un.k0);
     un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
     un.shared = q >= *pv.nu();
-    if (un.shared) { un.e = 0; un.first = 0; un.nrows = p.rows; un.K = p.Ks; }
+    if (un.shared) { un.e = 0; un.first = 0; un.nrows = p.sh_rows; un.K = p.Ks; }
     else { un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx; }
     const size_t tile = 32u * un.K;
     un.kstride = (uint32_t)(OT * tile);
     un.w = (un.shared ? p.sdn.trellis : p.down.trellis) + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
     return un;
   }
-  __device__ int row_index(const Unit &un, int i) const { return un.shared ? i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
+  __device__ int row_index(const Unit &un, int i) const { return un.shared ? p.sh_row0 + i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sd : p.xh_d) + (size_t)idx * p.I + un.k0 * 16;
   }
@@ -595,7 +595,7 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
       const float *const src[1] = {p.raw_sd + (size_t)r * H + blk * 128};
       float part[1][4], v[4];
       sum_splits<1>(src, (size_t)p.rows * H, p.S_d, lane, part);
-      const float lg = p.logits[(size_t)r * (p.E + 1) + p.E];
+      const float lg = p.logits[(size_t)(r - p.lg_row0) * (p.E + 1) + p.E];
 #pragma unroll
       for (int j = 0; j < 4; j++) v[j] = part[0][j];
       fwht_chunk(v, lane, 128, hs);

@@ -51,6 +51,7 @@ struct MoeParams {
   // rows [sh_row0, sh_row0 + sh_rows) get the shared-expert term in the combine (expert parallel: a rank adds it only
   // for the rows it owns, so that the sum over ranks contains it once); single GPU: 0, rows
   int sh_row0, sh_rows;
+  int lg_row0;  // logits[] holds rows [lg_row0, ..) (expert parallel with own-row routing: only the own rows were routed here)
 };
 
 // plan[] layout (ints): [0] = number of distinct local experts nu; then four arrays of PMAXU = P entries each:

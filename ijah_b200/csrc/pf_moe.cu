@@ -414,11 +414,15 @@ __device__ __forceinline__ int block_excl_scan(int v, int *warp_tot, int *total)
 
 __global__ void __launch_bounds__(1024) pf_scan_kernel(const PfParams p) {
   __shared__ int wt[32], tot8, totp;
+  __shared__ int s_pb[1024], s_off[1024], s_cnt[1024];
   const int e = threadIdx.x, E = p.E;
   const int c = e < E ? p.cnt[e] : 0, c8 = (c + 7) & ~7, np = (c + PF_NTOK - 1) / PF_NTOK;
   const int o = block_excl_scan(c8, wt, &tot8);
   const int pb = block_excl_scan(np, wt, &totp);
   if (e < E) p.off[e] = o;
+  s_pb[e] = e < E ? pb : 0x7FFFFFFF;
+  s_off[e] = o;
+  s_cnt[e] = c;
   const int nsh = p.has_shared ? p.sh_rows : 0, shp = (nsh + PF_NTOK - 1) / PF_NTOK;
   if (e == 0) {
     p.off[E] = tot8;
@@ -426,13 +430,24 @@ __global__ void __launch_bounds__(1024) pf_scan_kernel(const PfParams p) {
     p.nitems[0] = (totp + shp) * 2 * (p.I / PF_NCOL);
     p.nitems[1] = (totp + shp) * (p.H / PF_NCOL);
   }
+  __syncthreads();
   const int GU = p.I / PF_NCOL, DN = p.H / PF_NCOL;
   auto emit = [&](int pass, int expert, int row0, int nrows) {
     for (int j = 0; j < 2 * GU; j++) p.items_gu[pass * 2 * GU + j] = PfItem{expert, j / GU, j % GU, row0, nrows, {0, 0, 0}};
     for (int j = 0; j < DN; j++) p.items_d[pass * DN + j] = PfItem{expert, 0, j, row0, nrows, {0, 0, 0}};
   };
-  for (int j = 0; j < np; j++) emit(pb + j, e - p.e0, o + j * PF_NTOK, min(PF_NTOK, c - j * PF_NTOK));  // index into the local stacks
-  for (int j = e; j < shp; j += blockDim.x) emit(totp + j, -1, tot8 + j * PF_NTOK, min(PF_NTOK, nsh - j * PF_NTOK));
+  // one thread per pass: the expert of pass q is the last one whose first pass is <= q (experts without rows share the
+  // first-pass index of the next expert that has some)
+  for (int q = threadIdx.x; q < totp; q += blockDim.x) {
+    int lo = 0, hi = 1024;  // first index with s_pb > q
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s_pb[mid] <= q) lo = mid + 1; else hi = mid;
+    }
+    const int ex = lo - 1, j = q - s_pb[ex];
+    emit(q, ex - p.e0, s_off[ex] + j * PF_NTOK, min(PF_NTOK, s_cnt[ex] - j * PF_NTOK));  // expert index into the local stacks
+  }
+  for (int j = threadIdx.x; j < shp; j += blockDim.x) emit(totp + j, -1, tot8 + j * PF_NTOK, min(PF_NTOK, nsh - j * PF_NTOK));
 }
 
 // order[pos] = slot (S + t for the shared expert's row of token t, -1 = padding), inv[slot] = pos, seid[pos] = expert

@@ -175,21 +175,34 @@ __device__ __forceinline__ bool consume_unit(int kc, uint32_t ring_addr, int sta
   return true;
 }
 
-// per-unit dispatch on the bits per weight; units of a 16-row launch that have at most 8 live rows take the 1-group path
+// per-unit dispatch on the bits per weight and on the unit's live rows: a launch compiled for up to 8 * MT rows runs a unit
+// with fewer rows through the narrowest path that holds them (one MMA per 8 rows), since most units of a wide launch are
+// experts that only one or two rows selected
+template <int K, int MT, int SUB>
+__device__ __forceinline__ bool consume_rows(int nrows, int kc, uint32_t ring_addr, int stage_bytes, int nstages, uint64_t *full,
+                                             uint64_t *empty, int &stage, uint32_t &phase, bool live, int warp, int lane, uint32_t a_addr,
+                                             const uint32_t (&a_rowoff)[RowPairs<MT>::N], float (&acc)[MT][4], int *status) {
+  if constexpr (SUB < MT) {
+    if (nrows <= 8 * SUB)
+      return consume_unit<K, SUB>(kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr,
+                                  reinterpret_cast<const uint32_t(&)[RowPairs<SUB>::N]>(a_rowoff), reinterpret_cast<float(&)[SUB][4]>(acc),
+                                  status);
+    return consume_rows<K, MT, SUB * 2>(nrows, kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr,
+                                        a_rowoff, acc, status);
+  } else {
+    return consume_unit<K, MT>(kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr, a_rowoff, acc, status);
+  }
+}
+
 template <int MT>
 __device__ __forceinline__ bool consume_any(int K, int nrows, int kc, uint32_t ring_addr, int stage_bytes, int nstages,
                                             uint64_t *full, uint64_t *empty, int &stage, uint32_t &phase, bool live, int warp,
                                             int lane, uint32_t a_addr, const uint32_t (&a_rowoff)[RowPairs<MT>::N],
                                             float (&acc)[MT][4], int *status) {
-#define SG_CASE(KK)                                                                                                          \
-  case KK:                                                                                                                   \
-    if constexpr (MT == 2) {                                                                                                 \
-      if (nrows <= 8)                                                                                                        \
-        return consume_unit<KK, 1>(kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr,  \
-                                   reinterpret_cast<const uint32_t(&)[1]>(a_rowoff), reinterpret_cast<float(&)[1][4]>(acc), status); \
-    }                                                                                                                        \
-    return consume_unit<KK, MT>(kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr,     \
-                                a_rowoff, acc, status);
+#define SG_CASE(KK)                                                                                                                 \
+  case KK:                                                                                                                          \
+    return consume_rows<KK, MT, 1>(nrows, kc, ring_addr, stage_bytes, nstages, full, empty, stage, phase, live, warp, lane, a_addr, \
+                                   a_rowoff, acc, status);
   switch (K) {
     SG_CASE(4)
     SG_CASE(5)

@@ -3,11 +3,12 @@
 The reference is single-device; this is the sharding BASELINE's north star asks for. Rank g holds experts
 [g * E/N, (g+1) * E/N) of the layer (a MoeBlock created with expert_first / expert_count) and `rows` rows of its own.
 
-    dispatch   all_gather of the ranks' rows                          -> x_all [N * rows, H] on every rank
-    compute    block.forward_ep(x_all, own_row0, own_rows)            -> this rank's summand y_part [N * rows, H]:
-               routing on all rows (identical on every rank), the routed slots whose expert this rank owns (each
-               distinct expert streamed once for all rows that use it, slots summed per row in slot order) and the
-               shared expert for the rank's own rows
+    route      block.route_rows(x)                                     -> routes of the rank's own rows (decode widths)
+    dispatch   all_gather of the ranks' rows (and routes)             -> x_all [N * rows, H] on every rank
+    compute    block.forward_ep_routed(x_all, route_all, row0, rows)  -> this rank's summand y_part [N * rows, H]:
+               the routed slots whose expert this rank owns (each distinct expert streamed once for all rows that
+               use it, slots summed per row in slot order) and the shared expert for the rank's own rows.
+               (Blocks without route_rows, and the prefill path, route all rows on every rank: forward_ep / prefill_ep.)
     combine    reduce_scatter (sum) of y_part                          -> y [rows, H] of the rank's own rows
 
 At decode widths the payload is tiny (rows * H * 4 bytes per rank each way), so both collectives are latency-bound and
@@ -34,6 +35,11 @@ class ExpertParallelMoe:
         self.backend = dist.get_backend(group)
         self._x_all = None
         self._y_part = None
+        self._route = self._route_all = None
+        # blocks that can route alone (engine.MoeBlock) route each row on its home rank; others replicate the routing
+        self.own_routing = hasattr(block, "route_rows") and hasattr(block, "forward_ep_routed")
+        # ... once the gathered rows exceed this count: below it the replicated router costs less than a second all-gather
+        self.own_routing_min_rows = 16
 
     def _buffers(self, x):
         rows, H = x.shape
@@ -47,8 +53,20 @@ class ExpertParallelMoe:
         (block.prefill_ep: sorted slots, grouped tensor-core GEMM) instead of the decode-width kernels"""
         rows, H = x.shape
         x_all, y_part = self._buffers(x)
-        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
-        (self.block.prefill_ep if prefill else self.block.forward_ep)(x_all, self.rank * rows, rows, out=y_part)
+        x = x.contiguous()
+        if not prefill and self.own_routing and rows * self.world > self.own_routing_min_rows:
+            # every row is routed on its home rank only; rows and routes travel together (two small all-gathers)
+            k2 = 2 * self.block.k
+            if self._route is None or self._route.shape[0] != rows or self._route.device != x.device:
+                self._route = torch.empty((rows, k2), dtype=torch.int32, device=x.device)
+                self._route_all = torch.empty((rows * self.world, k2), dtype=torch.int32, device=x.device)
+            self.block.route_rows(x, self._route)
+            dist.all_gather_into_tensor(x_all, x, group=self.group)
+            dist.all_gather_into_tensor(self._route_all, self._route, group=self.group)
+            self.block.forward_ep_routed(x_all, self._route_all, self.rank * rows, rows, out=y_part)
+        else:
+            dist.all_gather_into_tensor(x_all, x, group=self.group)
+            (self.block.prefill_ep if prefill else self.block.forward_ep)(x_all, self.rank * rows, rows, out=y_part)
         y = torch.empty_like(x) if out is None else out
         if self.backend == "gloo":  # gloo has no reduce_scatter: all_reduce and keep the own slice
             dist.all_reduce(y_part, group=self.group)

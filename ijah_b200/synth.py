@@ -38,10 +38,16 @@ def moe_layer(seed, layer=0, hidden=2048, inter=768, experts=512, k_expert=5, k_
 
 def zipf_router_bias(tensors, layer=0, s=1.1):
     """Skew the routing of a layer in place: router column 0 becomes -s * log(rank of the expert) (centred), so that with
-    activations whose channel 0 is 1 the per-expert token counts follow a Zipf(s)-like law (the prefill configuration)."""
+    activations whose channel 0 is 1 the per-expert token counts follow a Zipf(s)-like law (the prefill configuration).
+    The same on every rank."""
     w = tensors[f"{PFX}{layer}.mlp.gate.weight"][1]
     bias = -s * torch.log(torch.arange(1, w.shape[0] + 1, device=w.device, dtype=torch.float32))
-    w[:, 0] = (bias - bias.mean()).to(torch.bfloat16)
+    # popularity rank -> expert id by a fixed permutation (a popularity that falls with the expert id would put all hot
+    # experts on the first expert-parallel rank)
+    perm = torch.randperm(w.shape[0], generator=torch.Generator().manual_seed(4242)).to(w.device)
+    col = torch.empty_like(bias)
+    col[perm] = bias - bias.mean()
+    w[:, 0] = col.to(torch.bfloat16)
 
 
 def to_numpy(tensors):

@@ -166,6 +166,28 @@ def test_forward_ep_summands_add_up_to_the_block(eng):
     assert rel_max(total, full) < 1e-5
 
 
+def test_forward_ep_with_home_rank_routing(eng):
+    # as above, but every "rank" routes only its own rows and gets the routes of all rows from outside
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(13)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=32)
+    x_all = torch.from_numpy(rng.standard_normal((20, 512)).astype(np.float16).astype(np.float32)).cuda()
+    fullb = E.MoeBlock(eng, t, top_k=4, max_rows=32)
+    full = fullb.forward(x_all).cpu().numpy()
+    blks = [E.MoeBlock(eng, t, top_k=4, max_rows=32, expert_first=16 * r, expert_count=16) for r in range(2)]
+    route_all = torch.empty((20, 8), dtype=torch.int32, device="cuda")
+    for r in range(2):
+        blks[r].route_rows(x_all[10 * r:10 * r + 10], route_all[10 * r:10 * r + 10])
+    ids, _ = fullb.route(20)
+    assert np.array_equal(route_all[:, :4].cpu().numpy(), ids)
+    total = np.zeros_like(full)
+    for r in range(2):
+        total += blks[r].forward_ep_routed(x_all, route_all, 10 * r, 10).cpu().numpy()
+    assert rel_max(total, full) < 1e-5
+    assert eng.lib.ne_device_wait_status() == 0
+
+
 def _tie_pack(mode):
     """Small MoE layer whose router produces exact ties: 'all' = zero router (every logit 0), 'dups' = every router row
     repeated four times (ids 4j .. 4j+3 share a logit)."""
