@@ -30,8 +30,11 @@ par = ep.ExpertParallelMoe(blk, dist.group.WORLD)
 # decode widths: 6 rows per rank
 xs = torch.from_numpy(x_all[rank * 6:(rank + 1) * 6]).to(dev)
 want = full.forward(torch.from_numpy(x_all[:world * 6]).to(dev))[rank * 6:(rank + 1) * 6]
-got = par.forward(xs)
+got = par.forward(xs)                      # few rows: routing replicated on every rank
 err_d = float((got - want).abs().max() / want.abs().max())
+par.own_routing_min_rows = 0               # every row routed on its home rank, routes all-gathered
+got2 = par.forward(xs)
+err_d = max(err_d, float((got2 - want).abs().max() / want.abs().max()))
 # prefill: 40 tokens per rank
 xp = torch.from_numpy(x_all[rank * 40:(rank + 1) * 40]).to(dev)
 wantp = full.prefill(torch.from_numpy(x_all).to(dev))[rank * 40:(rank + 1) * 40]
