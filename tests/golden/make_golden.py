@@ -56,7 +56,7 @@ def inputs():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository (its tools/opref.py is imported unmodified)")
     a = ap.parse_args()
     tmp = Path(tempfile.mkdtemp(prefix="ijah_golden_"))
     try:
