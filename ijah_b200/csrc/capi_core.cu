@@ -254,7 +254,7 @@ NE_API int ne_device_query(ne_device_info *out) {
     IJ_CUDA(cudaGetDevice(&d));
     cudaDeviceProp pr;
     IJ_CUDA(cudaGetDeviceProperties(&pr, d));
-    strncpy(out->name, pr.name, sizeof out->name - 1);  // the struct was zeroed: the copy stays terminated
+    memcpy(out->name, pr.name, std::min(sizeof out->name - 1, strlen(pr.name)));  // the struct was zeroed: stays terminated
     out->has_nax = pr.major >= 7 ? 1 : 0;
     out->has_metal4 = 0;
     out->max_buffer_length = pr.totalGlobalMem;
