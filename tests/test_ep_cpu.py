@@ -27,10 +27,25 @@ def _x(rank):
 
 class OracleBlock:
     def __init__(self, tensors, e0, e1):
-        self.t, self.e0, self.e1, self.H = tensors, e0, e1, DIMS["hidden"]
+        self.t, self.e0, self.e1, self.H, self.k = tensors, e0, e1, DIMS["hidden"], TOPK
 
     def forward_ep(self, x_all, own_row0, own_rows, out=None):
         r = CO.moe_block_emul(self.t, x_all.numpy(), top_k=TOPK, expert_range=(self.e0, self.e1), shared_rows=(own_row0, own_rows))
+        out.copy_(torch.from_numpy(r["out"]))
+        return out
+
+    # home-rank routing: routes as int32 [rows, 2 top_k] (ids, then the float weights' bits), as engine.MoeBlock has them
+    def route_rows(self, x, route_out):
+        r = CO.moe_block_emul(self.t, x.numpy(), top_k=TOPK)
+        route_out[:, :TOPK] = torch.from_numpy(r["ids"].astype(np.int32))
+        route_out[:, TOPK:] = torch.from_numpy(r["weights"].astype(np.float32).view(np.int32))
+        return route_out
+
+    def forward_ep_routed(self, x_all, route_all, own_row0, own_rows, out=None):
+        ids = route_all[:, :TOPK].numpy().astype(np.int64)
+        w = route_all[:, TOPK:].numpy().view(np.float32)
+        r = CO.moe_block_emul(self.t, x_all.numpy(), top_k=TOPK, ids=ids, weights=w, expert_range=(self.e0, self.e1),
+                              shared_rows=(own_row0, own_rows))
         out.copy_(torch.from_numpy(r["out"]))
         return out
 
@@ -45,6 +60,10 @@ def _worker(rank, world, port, q):
         y = m.forward(torch.from_numpy(_x(rank)))
         y2 = m.forward(torch.from_numpy(_x(rank)))  # buffers are reused on the second call
         assert torch.equal(y, y2)
+        assert m.own_routing
+        m.own_routing_min_rows = 0                  # every row routed on its home rank, routes all-gathered beside the rows
+        y3 = m.forward(torch.from_numpy(_x(rank)))
+        assert float((y3 - y).abs().max() / y.abs().max()) < 1e-6
         q.put((rank, y.numpy()))
     finally:
         dist.destroy_process_group()
