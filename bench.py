@@ -125,7 +125,7 @@ def run_reference(a, rank):
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": a.gpus, "steps": a.steps,
         "warmup": a.warmup, "ms_per_step": 1e3 * a.rows / v, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16 weights x f16 activations, f32 accumulate", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": workload_config(a),
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
@@ -133,7 +133,7 @@ def run_reference(a, rank):
 
 def workload_config(a):
     return {"workload": f"MoE block decode: hidden 2048, 512 experts top-10, inter 768, K5 routed + K6 shared, rows {a.rows}",
-            "rows": a.rows, "layers": a.layers, "l2": "weights of a step exceed L2 (distinct layers cycled)",
+            "arithmetic": "weights decoded to f16, f16 activations, f32 accumulate", "rows": a.rows, "layers": a.layers, "l2": "weights of a step exceed L2 (distinct layers cycled)",
             "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
 
 
@@ -343,7 +343,7 @@ def main():
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": N, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 weights x f16 activations, f32 accumulate", "data": "synthetic", "config": dict(workload_config(a), graph=graph is not None),
+            "dtype": "f16", "data": "synthetic", "config": dict(workload_config(a), graph=graph is not None),
             "e2e": e2e, "gpu_launches": launches_per_block * L * a.steps, "clocks": clocks, "roofline": roof,
             "cpu_baseline": cpu, "extra": extra, "wait_status": status}))
     if N > 1:
