@@ -137,6 +137,128 @@ def workload_config(a):
             "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
 
 
+def run_stack(a, rank, world):
+    """--workload stack: one decode step of `--rows` rows through a random-init decoder stack of `--layers` layers (default
+    48): per layer the four trunk projections (q 2048->4096, k, v 2048->512, o 4096->2048; K6, every fourth layer K8), a
+    stand-in for attention (the o projection takes the q output), the MoE block with residual adds, and at the end the bf16
+    LM head (151936 x 2048, a library GEMM). N > 1: experts sharded, everything else replicated, M rows per rank."""
+    import torch
+    import torch.distributed as dist
+    from ijah_b200 import engine as E
+    from ijah_b200 import synth
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    eng = E.Engine()
+    N, M, L = world, a.rows, a.layers
+    H, Ex, V = DIMS["hidden"], DIMS["experts"], 151936
+    per = Ex // N
+    blocks, trunks, wbytes = [], [], 0
+    for l in range(L):
+        t = synth.moe_layer(1000 + l, expert_first=rank * per, expert_count=per, router_seed=77 + l, device=dev, **DIMS)
+        blocks.append(E.MoeBlock(eng, t, top_k=TOPK, max_rows=M * N, expert_first=rank * per, expert_count=per, device=dev))
+        K = 8 if l % 4 == 3 else 6
+        tl = synth.trunk_layer(500 + l, K=K, device=dev)
+        trunks.append({n: E.Exl3Linear.from_device(eng, *w) for n, w in tl.items()})
+        wbytes += sum(w[0].numel() * 2 + w[1].numel() * 2 + w[2].numel() * 2 for w in tl.values())
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    head = (torch.randn((V, H), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    x0 = torch.randn((M, H), device=dev, generator=g).to(torch.float16).to(torch.float32)
+    x, q, kk, vv, o, y = (torch.empty((M, n), device=dev) for n in (H, 4096, 512, 512, H, H))
+    logits = torch.empty((M, V), device=dev, dtype=torch.bfloat16)
+    tok = torch.empty((M,), device=dev, dtype=torch.int64)
+    if N > 1:
+        from ijah_b200 import ep
+        eps = [ep.ExpertParallelMoe(b, dist.group.WORLD) for b in blocks]
+
+    xn = torch.empty_like(x)
+    norm = torch.nn.functional.rms_norm
+
+    def step():
+        x.copy_(x0)
+        for l in range(L):
+            tr = trunks[l]
+            xn.copy_(norm(x, (H,)))     # the two RMS norms of a layer are stand-ins too (no learned scale)
+            E.linear_multi(eng, (tr["q"], tr["k"], tr["v"]), xn, (q, kk, vv))  # one launch chain for the three
+            tr["o"].into(q, o)          # attention stand-in: its output has the q width
+            x.add_(o)
+            xn.copy_(norm(x, (H,)))
+            if N == 1:
+                blocks[l].forward(xn, out=y)
+            else:
+                eps[l].forward(xn, out=y)
+            x.add_(y)
+        torch.matmul(norm(x, (H,)).to(torch.bfloat16), head.t(), out=logits)
+        torch.argmax(logits, dim=1, out=tok)
+
+    def barrier():
+        if N > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        step()
+    barrier()
+    graph = None
+    if N == 1:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        graph.replay()
+    run = graph.replay if graph is not None else step
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(a.steps):
+        run()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # end to end: the step's input rows from pinned host memory, the sampled token ids back
+    xh, th = x0.cpu().pin_memory(), torch.empty((M,), dtype=torch.int64).pin_memory()
+    for _ in range(2):
+        x0.copy_(xh, non_blocking=True); run(); th.copy_(tok, non_blocking=True); torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        x0.copy_(xh, non_blocking=True); run(); th.copy_(tok, non_blocking=True); torch.cuda.synchronize()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if N > 1:
+        tt = torch.tensor([ms, e2e_s], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(tt[0].item()), float(tt[1].item())
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / a.steps
+    moe_bytes = float(np.mean([b.last_bytes(M * N if N > 1 else M)["total"] for b in blocks])) * L
+    total_bytes = moe_bytes + wbytes + V * H * 2
+    peak, which = peaks()
+    status = eng.lib.ne_device_wait_status()
+    if rank == 0:
+        per_layer = 6 + 2 * 3  # MoE block, q/k/v chain, o chain
+        print(json.dumps({
+            "metric": "EXL3 MoE decoder stack decode tok/s", "value": N * M / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": N,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"decoder stack decode step: {L} layers (trunk q/k/v/o K6/K8 + MoE block 512 experts top-10 K5 + shared K6), "
+                                   f"bf16 LM head 151936 x 2048, rows {M}, attention left as a stand-in",
+                       "rows": M, "layers": L, "l2": "weights of a step exceed L2", "graph": graph is not None,
+                       "parallelism": "single GPU" if N == 1 else f"ep{N}"},
+            "e2e": {"value": N * M * a.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * H * 4, "d2h_bytes_per_step": M * 8},
+            "gpu_launches": per_layer * L * a.steps, "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "whole step (all launches)", "achieved": total_bytes / (ms_per_step * 1e-3) / 1e9, "peak": peak,
+                         "unit": "GB/s", "frac": total_bytes / (ms_per_step * 1e-3) / 1e9 / peak, "peak_source": which + " (stream copy)",
+                         "traffic": None, "bytes_per_step": total_bytes},
+            "cpu_baseline": None, "extra": {"weights_gb_resident": (wbytes + V * H * 2 + L * per * 2966016) / 1e9}, "wait_status": status}))
+    if N > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -147,12 +269,18 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill figure in extra (0 = skip)")
+    ap.add_argument("--workload", default="block", choices=["block", "stack"],
+                    help="block: the MoE block (headline); stack: a whole random-init decoder stack step (see run_stack)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if a.impl == "reference":
         return run_reference(a, rank)
+    if a.workload == "stack":
+        if "--layers" not in sys.argv:
+            a.layers = 48
+        return run_stack(a, rank, world)
 
     import torch
     import torch.distributed as dist

@@ -240,6 +240,23 @@ NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows,
   });
 }
 
+NE_API int ne_exl3_linear_multi(const ne_exl3_weight *w, int n, const float *x_dev, int rows, float *const *y_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(w && x_dev && y_dev && n >= 1 && n <= ML_MAX, "bad arguments (1..%d Linears)", ML_MAX);
+    int out[ML_MAX], K[ML_MAX];
+    MultiLinearArgs a{};
+    for (int m = 0; m < n; m++) {
+      check_weight(&w[m]);
+      IJ_CHECK(w[m].in == w[0].in, "Linears of one call must share the input width (%d vs %d)", w[m].in, w[0].in);
+      IJ_CHECK(y_dev[m] != nullptr, "null output pointer");
+      out[m] = w[m].out; K[m] = w[m].K;
+      a.trellis[m] = w[m].trellis_dev; a.suh[m] = w[m].suh_dev; a.svh[m] = w[m].svh_dev; a.y[m] = y_dev[m];
+    }
+    const MultiLinearPlan p = plan_linear_multi(n, w[0].in, out, K, rows);
+    launch_linear_multi(p, a, x_dev, device_scratch(p.scratch_bytes()), device_status_word(), (cudaStream_t)stream);
+  });
+}
+
 NE_API int ne_exl3_linear_prefill(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream) {
   return c_call([&] {
     check_weight(w);

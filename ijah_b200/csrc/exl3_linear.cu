@@ -90,14 +90,20 @@ __global__ void linear_finish_kernel(const float *__restrict__ raw, const __half
   pdl_wait();
   pdl_launch();
   if (chunk * 128 >= out) return;
-  float v[4];
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int s0 = 0; s0 < S; s0 += 4) {  // splits in index order, four splits' loads in flight at a time
+    float t[4][4];
 #pragma unroll
-  for (int j = 0; j < 4; j++) {
-    const int c = chunk * 128 + lane + 32 * j;
-    float a = 0.0f;
-    if (c < out)
-      for (int s = 0; s < S; s++) a += raw[((size_t)s * rows + r) * out + c];
-    v[j] = a;
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int c = chunk * 128 + lane + 32 * j;
+        t[i][j] = (c < out && s0 + i < S) ? __ldcg(&raw[((size_t)(s0 + i) * rows + r) * out + c]) : 0.0f;
+      }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) v[j] += t[i][j];
   }
   fwht_chunk(v, lane, ho, hscale);
 #pragma unroll
@@ -105,6 +111,113 @@ __global__ void linear_finish_kernel(const float *__restrict__ raw, const __half
     const int c = chunk * 128 + lane + 32 * j;
     if (c < out) y[(size_t)r * out + c] = v[j] * __half2float(svh[c]);
   }
+}
+
+// ---- several Linears on the same rows
+struct MlPtrs {
+  const __half *suh[ML_MAX], *svh[ML_MAX];
+  __half *xh[ML_MAX];
+  const float *raw[ML_MAX];
+  float *y[ML_MAX];
+  int out[ML_MAX], ho[ML_MAX];
+  float hs[ML_MAX];  // 1 / sqrt(ho), rounded once on the host like everywhere else
+};
+
+__global__ void __launch_bounds__(128) prep_rows_multi_kernel(const float *__restrict__ x, const MlPtrs a, int rows, int n, int hn, float hscale) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = blockIdx.x * 4 + warp, r = blockIdx.y, m = blockIdx.z;
+  pdl_wait();
+  pdl_launch();
+  if (chunk * 128 >= n) return;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = chunk * 128 + lane + 32 * j;
+    v[j] = i < n ? x[(size_t)r * n + i] * __half2float(a.suh[m][i]) : 0.0f;
+  }
+  fwht_chunk(v, lane, hn, hscale);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int i = chunk * 128 + lane + 32 * j;
+    if (i < n) a.xh[m][(size_t)r * n + i] = __float2half_rn(v[j]);
+  }
+}
+
+__global__ void __launch_bounds__(128) linear_finish_multi_kernel(const MlPtrs a, int rows, int S) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = blockIdx.x * 4 + warp, r = blockIdx.y, m = blockIdx.z, out = a.out[m], ho = a.ho[m];
+  pdl_wait();
+  pdl_launch();
+  if (chunk * 128 >= out) return;
+  const float *raw = a.raw[m];
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int s0 = 0; s0 < S; s0 += 4) {
+    float t[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int c = chunk * 128 + lane + 32 * j;
+        t[i][j] = (c < out && s0 + i < S) ? __ldcg(&raw[((size_t)(s0 + i) * rows + r) * out + c]) : 0.0f;
+      }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) v[j] += t[i][j];
+  }
+  fwht_chunk(v, lane, ho, a.hs[m]);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int c = chunk * 128 + lane + 32 * j;
+    if (c < out) a.y[m][(size_t)r * out + c] = v[j] * __half2float(a.svh[m][c]);
+  }
+}
+
+MultiLinearPlan plan_linear_multi(int n, int in, const int *out, const int *K, int rows) {
+  IJ_CHECK(n >= 1 && n <= ML_MAX, "%d Linears in one call (1..%d)", n, ML_MAX);
+  IJ_CHECK(in > 0 && in % 16 == 0, "EXL3 Linear input width %d must be a multiple of 16", in);
+  IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
+  MultiLinearPlan p{};
+  p.n = n; p.in = in; p.rows = rows; p.IT = in / 16; p.hi = had_size(in);
+  int ng = 0, kmax = 0;
+  for (int m = 0; m < n; m++) {
+    IJ_CHECK(out[m] > 0 && out[m] % 16 == 0, "EXL3 Linear output width %d must be a multiple of 16", out[m]);
+    IJ_CHECK(K[m] >= 4 && K[m] <= 8, "EXL3 bits per weight %d outside 4..8", K[m]);
+    p.out[m] = out[m]; p.K[m] = K[m]; p.OT[m] = out[m] / 16; p.NG[m] = (p.OT[m] + SG_WARPS - 1) / SG_WARPS; p.ho[m] = had_size(out[m]);
+    ng += p.NG[m];
+    kmax = std::max(kmax, K[m]);
+  }
+  p.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
+  p.grid = 2 * sm_count();
+  choose_split(p.IT, ng, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
+  p.lay = make_layout(kmax, p.kc, rows, 2);
+  p.grid = std::min(p.grid, ng * p.S);
+  return p;
+}
+
+void launch_linear_multi(const MultiLinearPlan &p, const MultiLinearArgs &a, const float *x, void *scratch, int *status, cudaStream_t st) {
+  MultiLinearProblem pr{};
+  MlPtrs q{};
+  char *cur = (char *)scratch;
+  int maxout = 0;
+  pr.n = p.n; pr.in = p.in; pr.rows = p.rows; pr.IT = p.IT; pr.S = p.S; pr.kc = p.kc;
+  pr.ubase[0] = 0;
+  for (int m = 0; m < p.n; m++) {
+    float *raw = (float *)cur;
+    cur += (p.raw_floats(m) * 4 + 255) & ~(size_t)255;
+    __half *xh = (__half *)cur;
+    cur += ((size_t)p.rows * p.in * 2 + 255) & ~(size_t)255;
+    pr.trellis[m] = (const char *)a.trellis[m]; pr.xh[m] = xh; pr.raw[m] = raw;
+    pr.out[m] = p.out[m]; pr.K[m] = p.K[m]; pr.OT[m] = p.OT[m]; pr.NG[m] = p.NG[m];
+    pr.ubase[m + 1] = pr.ubase[m] + p.NG[m] * p.S;
+    q.suh[m] = (const __half *)a.suh[m]; q.svh[m] = (const __half *)a.svh[m]; q.xh[m] = xh; q.raw[m] = raw; q.y[m] = a.y[m];
+    q.out[m] = p.out[m]; q.ho[m] = p.ho[m]; q.hs[m] = (float)(1.0 / sqrt((double)p.ho[m]));
+    maxout = std::max(maxout, p.out[m]);
+  }
+  launch_pdl(prep_rows_multi_kernel, dim3(((p.in + 127) / 128 + 3) / 4, p.rows, p.n), dim3(128), 0, st, x, q, p.rows, p.in, p.hi,
+             (float)(1.0 / sqrt((double)p.hi)));
+  launch_stream(pr, p.MT, p.lay, p.grid, status, st);
+  launch_pdl(linear_finish_multi_kernel, dim3(((maxout + 127) / 128 + 3) / 4, p.rows, p.n), dim3(128), 0, st, q, p.rows, p.S);
 }
 
 void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, const void *svh, const float *x, float *y,

@@ -55,6 +55,65 @@ struct LinearProblem {
   }
 };
 
+// Several Linears that read the same activation rows (the q, k, v projections of a layer; reference: t6::record_multi,
+// kernels/trunk6/trunk6.h:60-79) as ONE chain of three launches: the units of all matrices share the persistent grid, so
+// small matrices (k, v: 0.8 MB) no longer pay a launch chain each nor leave most of the GPU idle.
+constexpr int ML_MAX = 4;
+struct MultiLinearPlan {
+  int n, in, rows, IT, S, kc, MT, grid, hi;
+  int out[ML_MAX], K[ML_MAX], OT[ML_MAX], NG[ML_MAX], ho[ML_MAX];
+  StreamLayout lay;
+  size_t raw_floats(int m) const { return (size_t)S * rows * out[m]; }
+  size_t scratch_bytes() const {
+    size_t b = 256;
+    for (int m = 0; m < n; m++) b += ((raw_floats(m) * 4 + 255) & ~(size_t)255) + (((size_t)rows * in * 2 + 255) & ~(size_t)255);
+    return b;
+  }
+};
+MultiLinearPlan plan_linear_multi(int n, int in, const int *out, const int *K, int rows);
+
+struct MultiLinearProblem {
+  static constexpr bool kUnitsFinalAtLaunch = true;  // the unit list is arithmetic
+  struct Unit : UnitBase {
+    int g, s, k0, m;
+  };
+  const char *trellis[ML_MAX];
+  const __half *xh[ML_MAX];  // [rows][in] prepared operand per matrix (the scale vectors differ)
+  float *raw[ML_MAX];
+  int out[ML_MAX], K[ML_MAX], OT[ML_MAX], NG[ML_MAX], ubase[ML_MAX + 1];  // ubase[m]: first unit of matrix m
+  int n, in, rows, IT, S, kc;
+
+  __device__ int num_units() const { return ubase[n]; }
+  __device__ Unit unit(int u) const {
+    Unit un;
+    int m = 0;
+    while (m + 1 < n && u >= ubase[m + 1]) m++;
+    const int v = u - ubase[m];
+    un.m = m;
+    un.g = v % NG[m];
+    un.s = v / NG[m];
+    un.k0 = un.s * kc;
+    un.kc = min(kc, IT - un.k0);
+    un.ntiles = min(SG_WARPS, OT[m] - un.g * SG_WARPS);
+    un.K = K[m];
+    un.nrows = rows;
+    un.kstride = (uint32_t)OT[m] * 32u * (uint32_t)K[m];
+    un.w = trellis[m] + ((size_t)un.k0 * OT[m] + (size_t)un.g * SG_WARPS) * (32u * K[m]);
+    return un;
+  }
+  __device__ int row_index(const Unit &, int i) const { return i; }
+  __device__ const __half *a_row(const Unit &un, int i) const { return xh[un.m] + (size_t)i * in + un.k0 * 16; }
+  __device__ void store(const Unit &un, int row, int col, float v) const {
+    raw[un.m][((size_t)un.s * rows + row) * out[un.m] + un.g * 128 + col] = v;
+  }
+};
+
+struct MultiLinearArgs {  // per matrix: device pointers of the caller
+  const void *trellis[ML_MAX], *suh[ML_MAX], *svh[ML_MAX];
+  float *y[ML_MAX];
+};
+void launch_linear_multi(const MultiLinearPlan &p, const MultiLinearArgs &a, const float *x, void *scratch, int *status, cudaStream_t st);
+
 // `scratch` holds LinearPlan::scratch_bytes(): the k-split partials, then the prepared operand
 void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, const void *svh, const float *x, float *y,
                    void *scratch, int *status, cudaStream_t st);

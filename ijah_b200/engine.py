@@ -91,6 +91,7 @@ SIGNATURES = {
     "ne_exl3_dequant": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_void_p]),
     "ne_exl3_linear": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_host": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_exl3_linear_multi": (C.c_int, [C.POINTER(Exl3WeightC), C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
     "ne_exl3_linear_prefill": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_static": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_static_capacity": (C.c_uint64, []),
@@ -338,6 +339,21 @@ class Exl3Linear:
                   to_device_u16(np.asarray(svh, np.float16), device))
         self.c = Exl3WeightC(self.t[0].data_ptr(), self.t[1].data_ptr(), self.t[2].data_ptr(), self.n_in, self.n_out, self.K)
 
+    @classmethod
+    def from_device(cls, eng, trellis, suh, svh):
+        """the same from tensors that already live on the device (int16 / uint16 trellis words, float16 scale vectors)"""
+        self = cls.__new__(cls)
+        self.eng = eng
+        self.n_in, self.n_out, self.K = trellis.shape[0] * 16, trellis.shape[1] * 16, trellis.shape[2] // 16
+        self.t = (trellis, suh, svh)
+        self.c = Exl3WeightC(trellis.data_ptr(), suh.data_ptr(), svh.data_ptr(), self.n_in, self.n_out, self.K)
+        return self
+
+    def into(self, x, y):
+        """y = x @ W for float32 device tensors the caller owns (no allocation, capturable)"""
+        self.eng._ok(self.eng.lib.ne_exl3_linear(C.byref(self.c), _dev(x), x.shape[0], _dev(y), _stream()), "ne_exl3_linear")
+        return y
+
     def dequant(self):
         torch = _torch()
         w = torch.empty((self.n_in, self.n_out), dtype=torch.float16, device=self.t[0].device)
@@ -378,6 +394,16 @@ class Exl3Linear:
         self.eng._ok(self.eng.lib.ne_exl3_linear_host(C.byref(self.c), x.ctypes.data, x.shape[0], y.ctypes.data),
                      "ne_exl3_linear_host")
         return y
+
+
+def linear_multi(eng, linears, x, outs):
+    """outs[i] = x @ W_i for up to 4 Exl3Linear objects that share the input width, in one launch chain
+    (ne_exl3_linear_multi); x and outs are float32 device tensors the caller owns"""
+    n = len(linears)
+    ws = (Exl3WeightC * n)(*[l.c for l in linears])
+    ys = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    eng._ok(eng.lib.ne_exl3_linear_multi(ws, n, _dev(x), x.shape[0], ys, _stream()), "ne_exl3_linear_multi")
+    return outs
 
 
 class MoeBlock:

@@ -36,6 +36,14 @@ def moe_layer(seed, layer=0, hidden=2048, inter=768, experts=512, k_expert=5, k_
     return t
 
 
+def trunk_layer(seed, hidden=2048, q_out=4096, kv_out=512, K=6, device="cuda"):
+    """the four attention projections of one layer as (trellis, suh, svh) triples: q, k, v (hidden -> q_out / kv_out) and o
+    (q_out -> hidden)"""
+    g = torch.Generator(device=device).manual_seed(seed * 7919 + 3)
+    return {"q": _exl3(g, hidden, q_out, K, device=device), "k": _exl3(g, hidden, kv_out, K, device=device),
+            "v": _exl3(g, hidden, kv_out, K, device=device), "o": _exl3(g, q_out, hidden, K, device=device)}
+
+
 def zipf_router_bias(tensors, layer=0, s=1.1):
     """Skew the routing of a layer in place: router column 0 becomes -s * log(rank of the expert) (centred), so that with
     activations whose channel 0 is 1 the per-expert token counts follow a Zipf(s)-like law (the prefill configuration).

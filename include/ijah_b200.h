@@ -34,6 +34,11 @@ NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *strea
  * owned by the library (grown on demand). */
 NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host);
+/* n (1..4) Linears applied to the SAME rows x (the q, k, v projections of a layer; replaces t6::record_multi,
+ * kernels/trunk6/trunk6.h:60-79): one chain of three launches whose stream kernel holds the units of all matrices, so small
+ * matrices neither pay a launch chain each nor leave most of the GPU idle. All w[i].in must be equal; y_dev[i] receives
+ * [rows][w[i].out]. rows 1..64. */
+NE_API int ne_exl3_linear_multi(const ne_exl3_weight *w, int n, const float *x_dev, int rows, float *const *y_dev, void *stream);
 /* The same Linear for many rows (prefill chunks; replaces t6::record_prefill, kernels/trunk6/trunk6.mm:385-492): every tile is
  * decoded once per 128 rows into shared memory and multiplied on tcgen05 tensor cores with TMEM accumulators. rows >= 1;
  * in must be a multiple of 128, out of 256. Scratch from the library's per-device arena. */

@@ -122,3 +122,33 @@ def test_bad_arguments_are_refused(eng):
     assert eng.lib.ne_exl3_linear(C.byref(bad), C.c_void_p(x.data_ptr()), 1, C.c_void_p(y.data_ptr()), None) == -1
     assert "multiples of 16" in eng.last_error()
     assert eng.lib.ne_device_wait_status() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 8, 32])
+def test_linears_on_shared_rows_in_one_chain(eng, rows):
+    # the q, k, v projections of the trunk configuration (K6, one of them K8) through ne_exl3_linear_multi
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(40 + rows)
+    shapes = [(2048, 4096, 6), (2048, 512, 6), (2048, 512, 8), (2048, 320, 5)]
+    lins, packs = [], []
+    for n_in, n_out, K in shapes:
+        tr, su, sv = packgen.exl3_linear(rng, n_in, n_out, K)
+        packs.append((tr, su, sv))
+        lins.append(E.Exl3Linear(eng, tr, su, sv))
+    x = rng.standard_normal((rows, 2048)).astype(np.float16).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    outs = [torch.empty((rows, s[1]), device="cuda") for s in shapes]
+    E.linear_multi(eng, lins, xd, outs)
+    for lin, pk, o in zip(lins, packs, outs):
+        got = o.cpu().numpy()
+        want = CO.linear_emul(*pk, x)
+        assert np.linalg.norm(got - want) / np.linalg.norm(want) < 5e-5
+        assert rel_max(got, lin(xd).cpu().numpy()) < 1e-5
+    again = [torch.empty_like(o) for o in outs]
+    E.linear_multi(eng, lins, xd, again)
+    assert all(torch.equal(a, b) for a, b in zip(outs, again)), "two runs must be bit-identical"
+    assert eng.lib.ne_device_wait_status() == 0
+    with pytest.raises(E.EngineError):  # different input widths
+        tr, su, sv = packgen.exl3_linear(rng, 256, 256, 4)
+        E.linear_multi(eng, [lins[0], E.Exl3Linear(eng, tr, su, sv)], xd, outs[:2])
