@@ -56,7 +56,7 @@ struct LinearProblem {
 };
 
 // Several Linears that read the same activation rows (the q, k, v projections of a layer; reference: t6::record_multi,
-// kernels/trunk6/trunk6.h:60-79) as ONE chain of three launches: the units of all matrices share the persistent grid, so
+// kernels/trunk6/trunk6.h:78-79, which also takes one input per Linear) as ONE chain of three launches: the units of all matrices share the persistent grid, so
 // small matrices (k, v: 0.8 MB) no longer pay a launch chain each nor leave most of the GPU idle.
 constexpr int ML_MAX = 4;
 struct MultiLinearPlan {

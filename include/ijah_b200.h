@@ -35,7 +35,7 @@ NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *strea
 NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host);
 /* n (1..4) Linears applied to the SAME rows x (the q, k, v projections of a layer; replaces t6::record_multi,
- * kernels/trunk6/trunk6.h:60-79): one chain of three launches whose stream kernel holds the units of all matrices, so small
+ * kernels/trunk6/trunk6.h:78-79, for the case of one shared input): one chain of three launches whose stream kernel holds the units of all matrices, so small
  * matrices neither pay a launch chain each nor leave most of the GPU idle. All w[i].in must be equal; y_dev[i] receives
  * [rows][w[i].out]. rows 1..64. */
 NE_API int ne_exl3_linear_multi(const ne_exl3_weight *w, int n, const float *x_dev, int rows, float *const *y_dev, void *stream);
