@@ -263,8 +263,9 @@ NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, 
 // Kernels are compiled into the library; the names below are the CUDA kernels that exist. The reference's Metal
 // kernel names (fn_moe_gateup_k5_r1, t6_simd, ...) are reported absent: their argument lists bind Metal buffers of
 // the reference's scratch layout, which this library does not reproduce.
-static const char *kKernels[] = {"stream_gemm_kernel", "moe_router_kernel", "moe_plan_kernel", "moe_combine_kernel",
-                                 "linear_finish_kernel", "dequant_kernel"};
+static const char *kKernels[] = {"stream_gemm_kernel", "moe_router_kernel", "moe_prep_kernel", "moe_mid_kernel", "moe_combine_kernel",
+                                 "prep_rows_kernel", "linear_finish_kernel", "dequant_kernel", "pf_gemm_kernel", "pf_logits_kernel",
+                                 "pf_route_kernel", "pf_prep_kernel", "pf_mid_kernel", "pf_finish_kernel"};
 NE_API int ne_kernel_exists(const char *fn) {
   if (!fn) return -1;
   for (const char *k : kKernels)
