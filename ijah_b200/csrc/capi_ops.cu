@@ -125,6 +125,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   p.S_gu = s.S_gu; p.kc_gu = s.kc_gu; p.S_d = s.S_d; p.kc_d = s.kc_d;
   p.h_mid = h_mid; p.inj = inj; p.h_out = h_out; p.HC = HC;
   p.sh_row0 = 0; p.sh_rows = rows; p.lg_row0 = 0;
+  p.ldx = desc.hidden; p.ldr = 2 * desc.top_k;
   return p;
 }
 
@@ -184,16 +185,21 @@ void Moe::forward_ep(const float *x, int rows, int own_row0, int own_rows, float
 
 // The router alone on `rows` rows: routes to route_out ([rows][2 top_k], or the object's own buffer), logits (with the shared
 // expert's gate logit) stay in the object for a following forward_ep_routed.
-void Moe::route_rows(const float *x, int rows, uint32_t *route_out, cudaStream_t st) {
+void Moe::route_rows(const float *x, int rows, uint32_t *route_out, int ld_route, cudaStream_t st) {
   MoeParams p = params(x, rows, nullptr);
-  if (route_out) p.route = route_out;
+  if (route_out) { p.route = route_out; p.ldr = ld_route > 0 ? ld_route : p.ldr; }
+  IJ_CHECK(p.ldr >= 2 * desc.top_k, "route row stride %d < %d", p.ldr, 2 * desc.top_k);
   launch_moe_router(p, false, st);
 }
 
 // Expert parallel with the routing done by each row's home rank: rows and routes of all ranks come in; the shared expert's
 // gate logits of the own rows are the ones route_rows left in the object.
-void Moe::forward_ep_routed(const float *x, const uint32_t *route_all, int rows, int own_row0, int own_rows, float *y, cudaStream_t st) {
+void Moe::forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all, int ld_route, int rows, int own_row0, int own_rows, float *y,
+                            cudaStream_t st) {
   MoeParams p = params(x, rows, y);
+  if (ld_x > 0) p.ldx = ld_x;
+  if (ld_route > 0) p.ldr = ld_route;
+  IJ_CHECK(p.ldx >= desc.hidden && p.ldr >= 2 * desc.top_k, "row strides %d / %d too small", p.ldx, p.ldr);
   IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= rows, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, rows);
   p.route = const_cast<uint32_t *>(route_all);
   p.sh_row0 = own_row0; p.sh_rows = own_rows; p.lg_row0 = own_row0;
@@ -340,17 +346,18 @@ NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_
     o->prefill(x_dev, n_tokens, 0, n_tokens, y_dev, (cudaStream_t)stream);
   });
 }
-NE_API int ne_moe_route(ne_moe *m, const float *x_dev, int rows, uint32_t *route_out_dev, void *stream) {
+NE_API int ne_moe_route(ne_moe *m, const float *x_dev, int rows, uint32_t *route_out_dev, int ld_route, void *stream) {
   return c_call([&] {
     IJ_CHECK(m && x_dev, "null argument");
-    reinterpret_cast<Moe *>(m)->route_rows(x_dev, rows, route_out_dev, (cudaStream_t)stream);
+    reinterpret_cast<Moe *>(m)->route_rows(x_dev, rows, route_out_dev, ld_route, (cudaStream_t)stream);
   });
 }
-NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, const uint32_t *route_all_dev, int rows_all, int own_row0, int own_rows,
-                                    float *y_part_dev, void *stream) {
+NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, int ld_x, const uint32_t *route_all_dev, int ld_route, int rows_all,
+                                    int own_row0, int own_rows, float *y_part_dev, void *stream) {
   return c_call([&] {
     IJ_CHECK(m && x_all_dev && route_all_dev && y_part_dev, "null argument");
-    reinterpret_cast<Moe *>(m)->forward_ep_routed(x_all_dev, route_all_dev, rows_all, own_row0, own_rows, y_part_dev, (cudaStream_t)stream);
+    reinterpret_cast<Moe *>(m)->forward_ep_routed(x_all_dev, ld_x, route_all_dev, ld_route, rows_all, own_row0, own_rows, y_part_dev,
+                                                  (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream) {

@@ -116,8 +116,8 @@ __device__ __forceinline__ void route_row(const MoeParams &p, int r, int *sid, i
   const float pr = lane < k ? expf(myv - top) : 0.0f;
   const float sum = warp_sum(pr);
   if (lane < k) {
-    p.route[(size_t)r * 2 * k + lane] = (uint32_t)myi;
-    p.route[(size_t)r * 2 * k + k + lane] = __float_as_uint(pr / sum);
+    p.route[(size_t)r * p.ldr + lane] = (uint32_t)myi;
+    p.route[(size_t)r * p.ldr + k + lane] = __float_as_uint(pr / sum);
     sid[r * k + lane] = myi;
   }
 }
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int bu
     __shared__ __align__(16) unsigned char tables[16 * RT_EMAX];
     __shared__ int sid[RT_PMAX];
     if (blockIdx.x != 0) return;
-    for (int i = threadIdx.x; i < p.P; i += blockDim.x) sid[i] = (int)p.route[(size_t)(i / k) * 2 * k + (i % k)];
+    for (int i = threadIdx.x; i < p.P; i += blockDim.x) sid[i] = (int)p.route[(size_t)(i / k) * p.ldr + (i % k)];
     __syncthreads();
     build_plan_block(p, tables, sid);
     return;
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int bu
   __half *dst;
   if (job < p.P) {
     r = job / k;
-    const int e = (int)p.route[(size_t)r * 2 * k + (job - r * k)] - p.e0;
+    const int e = (int)p.route[(size_t)r * p.ldr + (job - r * k)] - p.e0;
     if (e < 0 || e >= p.ecount) return;
     sg = p.gate.suh + (size_t)e * H;
     su = p.up.suh + (size_t)e * H;
@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int bu
   const int o = chunk * 128 + lane;
   float xv[4], v[4];
 #pragma unroll
-  for (int j = 0; j < 4; j++) xv[j] = p.x[(size_t)r * H + o + 32 * j];
+  for (int j = 0; j < 4; j++) xv[j] = p.x[(size_t)r * p.ldx + o + 32 * j];
 #pragma unroll
   for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(sg[o + 32 * j]);
   fwht_chunk(v, lane, 128, hs);
@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
   const __half *svg, *svu, *sud;
   __half *dst;
   if (!shared) {
-    const int r = job / k, e = (int)p.route[(size_t)r * 2 * k + (job - r * k)] - p.e0;
+    const int r = job / k, e = (int)p.route[(size_t)r * p.ldr + (job - r * k)] - p.e0;
     if (e < 0 || e >= p.ecount) return;
     svg = p.gate.svh + (size_t)e * I; svu = p.up.svh + (size_t)e * I; sud = p.down.suh + (size_t)e * I;
     dst = p.xh_d + (size_t)job * I;
@@ -572,8 +572,8 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
     const float *const src[1] = {p.raw_d + (size_t)(r * k + warp) * H + blk * 128};
     float part[1][4];
     sum_splits<1>(src, (size_t)p.P * H, p.S_d, lane, part);
-    const int e = (int)p.route[(size_t)r * 2 * k + warp];
-    const float wk = __uint_as_float(p.route[(size_t)r * 2 * k + k + warp]);
+    const int e = (int)p.route[(size_t)r * p.ldr + warp];
+    const float wk = __uint_as_float(p.route[(size_t)r * p.ldr + k + warp]);
     const bool local = e >= p.e0 && e < p.e0 + p.ecount;
     if (lane == 0) used[warp] = local ? 1 : 0;
     if (local) {

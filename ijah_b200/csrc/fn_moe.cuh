@@ -51,6 +51,7 @@ struct MoeParams {
   // rows [sh_row0, sh_row0 + sh_rows) get the shared-expert term in the combine (expert parallel: a rank adds it only
   // for the rows it owns, so that the sum over ranks contains it once); single GPU: 0, rows
   int sh_row0, sh_rows;
+  int ldx, ldr;  // row strides of x (floats) and route (words): H and 2 topk unless rows and routes arrive packed side by side
   int lg_row0;  // logits[] holds rows [lg_row0, ..) (expert parallel with own-row routing: only the own rows were routed here)
 };
 

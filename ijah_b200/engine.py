@@ -101,8 +101,9 @@ SIGNATURES = {
     "ne_moe_stage": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
-    "ne_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
-    "ne_moe_forward_ep_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_moe_forward_ep_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                           C.c_void_p]),
     "ne_moe_prefill_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
@@ -488,17 +489,21 @@ class MoeBlock:
         return y
 
     def route_rows(self, x, route_out):
-        """the router alone on x; routes (ids, then float weights, as uint32 [rows, 2 top_k]) into the device tensor route_out"""
-        self.eng._ok(self.eng.lib.ne_moe_route(self.ptr, _dev(x), x.shape[0], _dev(route_out), _stream()), "ne_moe_route")
+        """the router alone on x; routes (ids, then float weights, as 32-bit words [rows, 2 top_k]) into the device tensor
+        route_out, which may be a column slice of a wider row-major tensor (its row stride is passed on)"""
+        ld = route_out.stride(0) if route_out.dim() == 2 else 0
+        self.eng._ok(self.eng.lib.ne_moe_route(self.ptr, _dev(x), x.shape[0], C.c_void_p(route_out.data_ptr()), ld, _stream()), "ne_moe_route")
         return route_out
 
     def forward_ep_routed(self, x_all, route_all, own_row0, own_rows, out=None):
-        """this rank's summand from the gathered rows and routes (ne_moe_forward_ep_routed); route_rows must have run on the own rows"""
+        """this rank's summand from the gathered rows and routes (ne_moe_forward_ep_routed); route_rows must have run on the
+        own rows. x_all / route_all may be column slices of one packed row-major float32 / int32 tensor."""
         torch = _torch()
         rows = x_all.shape[0]
         y = torch.empty((rows, self.H), dtype=torch.float32, device=x_all.device) if out is None else out
-        self.eng._ok(self.eng.lib.ne_moe_forward_ep_routed(self.ptr, _dev(x_all), _dev(route_all), rows, own_row0, own_rows, _dev(y), _stream()),
-                     "ne_moe_forward_ep_routed")
+        self.eng._ok(self.eng.lib.ne_moe_forward_ep_routed(self.ptr, C.c_void_p(x_all.data_ptr()), x_all.stride(0),
+                                                           C.c_void_p(route_all.data_ptr()), route_all.stride(0), rows, own_row0, own_rows,
+                                                           _dev(y), _stream()), "ne_moe_forward_ep_routed")
         return y
 
     def prefill_ep(self, x_all, own_row0, own_rows, out=None):

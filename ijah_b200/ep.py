@@ -4,7 +4,8 @@ The reference is single-device; this is the sharding BASELINE's north star asks 
 [g * E/N, (g+1) * E/N) of the layer (a MoeBlock created with expert_first / expert_count) and `rows` rows of its own.
 
     route      block.route_rows(x)                                     -> routes of the rank's own rows (decode widths)
-    dispatch   all_gather of the ranks' rows (and routes)             -> x_all [N * rows, H] on every rank
+    dispatch   all_gather of the ranks' rows (with their routes       -> x_all [N * rows, H] on every rank
+               packed beside them: one collective)
     compute    block.forward_ep_routed(x_all, route_all, row0, rows)  -> this rank's summand y_part [N * rows, H]:
                the routed slots whose expert this rank owns (each distinct expert streamed once for all rows that
                use it, slots summed per row in slot order) and the shared expert for the rank's own rows.
@@ -35,12 +36,12 @@ class ExpertParallelMoe:
         self.backend = dist.get_backend(group)
         self._x_all = None
         self._y_part = None
-        self._route = self._route_all = None
+        self._pack = self._pack_all = self._views = None
         # blocks that can route alone (engine.MoeBlock) route each row on its home rank; others replicate the routing
         self.own_routing = hasattr(block, "route_rows") and hasattr(block, "forward_ep_routed")
-        # ... once the gathered rows exceed this count: below it the replicated router costs less than a second all-gather plus
-        # a separate router launch (measured on 2 GPUs: +24 us per block; the replicated router takes 11 / 23 / 42 us at 4 / 16 / 32 rows)
-        self.own_routing_min_rows = 32
+        # ... once the gathered rows exceed this count (the replicated router takes 11 / 14 / 23 / 42 us at 4 / 8 / 16 / 32 rows,
+        # home-rank routing 11 us plus a small copy)
+        self.own_routing_min_rows = 8
 
     def _buffers(self, x):
         rows, H = x.shape
@@ -56,15 +57,19 @@ class ExpertParallelMoe:
         x_all, y_part = self._buffers(x)
         x = x.contiguous()
         if not prefill and self.own_routing and rows * self.world > self.own_routing_min_rows:
-            # every row is routed on its home rank only; rows and routes travel together (two small all-gathers)
-            k2 = 2 * self.block.k
-            if self._route is None or self._route.shape[0] != rows or self._route.device != x.device:
-                self._route = torch.empty((rows, k2), dtype=torch.int32, device=x.device)
-                self._route_all = torch.empty((rows * self.world, k2), dtype=torch.int32, device=x.device)
-            self.block.route_rows(x, self._route)
-            dist.all_gather_into_tensor(x_all, x, group=self.group)
-            dist.all_gather_into_tensor(self._route_all, self._route, group=self.group)
-            self.block.forward_ep_routed(x_all, self._route_all, self.rank * rows, rows, out=y_part)
+            # every row is routed on its home rank only; a row and its route travel side by side in ONE all-gather:
+            # packed row = [x (H floats) | ids (k) | weights (k)], the kernels read both parts with the packed row stride
+            k2, W = 2 * self.block.k, H + 2 * self.block.k
+            if self._pack is None or self._pack.shape != (rows, W) or self._pack.device != x.device:
+                self._pack = torch.empty((rows, W), dtype=torch.float32, device=x.device)
+                self._pack_all = torch.empty((rows * self.world, W), dtype=torch.float32, device=x.device)
+                self._views = (self._pack[:, :H], self._pack[:, H:].view(torch.int32),
+                               self._pack_all[:, :H], self._pack_all[:, H:].view(torch.int32))
+            own_x, own_r, all_x, all_r = self._views
+            own_x.copy_(x)
+            self.block.route_rows(x, own_r)
+            dist.all_gather_into_tensor(self._pack_all, self._pack, group=self.group)
+            self.block.forward_ep_routed(all_x, all_r, self.rank * rows, rows, out=y_part)
         else:
             dist.all_gather_into_tensor(x_all, x, group=self.group)
             (self.block.prefill_ep if prefill else self.block.forward_ep)(x_all, self.rank * rows, rows, out=y_part)

@@ -107,12 +107,14 @@ NE_API int ne_moe_prefill(ne_moe *m, const float *x_dev, int n_tokens, float *y_
 NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, int own_row0, int own_rows, float *y_part_dev,
                              void *stream);
 /* Expert parallel with every row routed on its home rank only (the router's cost then does not grow with the number of
- * ranks): ne_moe_route runs the router alone on the caller's rows (routes to route_out_dev [rows][2*top_k], or into the
- * object when NULL; the gate logits of the shared expert stay in the object); the ranks exchange rows AND routes
- * (all-gather), then ne_moe_forward_ep_routed computes this rank's summand from the gathered rows and routes. */
-NE_API int ne_moe_route(ne_moe *m, const float *x_dev, int rows, uint32_t *route_out_dev, void *stream);
-NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, const uint32_t *route_all_dev, int rows_all, int own_row0, int own_rows,
-                                    float *y_part_dev, void *stream);
+ * ranks): ne_moe_route runs the router alone on the caller's rows (routes to route_out_dev, row stride ld_route words, 0 =
+ * 2*top_k; or into the object when NULL; the gate logits of the shared expert stay in the object); the ranks exchange rows
+ * AND routes, then ne_moe_forward_ep_routed computes this rank's summand from the gathered rows and routes. ld_x (floats)
+ * and ld_route (words) are the row strides of x_all and route_all, 0 = dense: with ld_x = ld_route = hidden + 2*top_k and
+ * route_all = (uint32_t *)x_all + hidden the rows and routes travel packed side by side in ONE all-gather. */
+NE_API int ne_moe_route(ne_moe *m, const float *x_dev, int rows, uint32_t *route_out_dev, int ld_route, void *stream);
+NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, int ld_x, const uint32_t *route_all_dev, int ld_route, int rows_all,
+                                    int own_row0, int own_rows, float *y_part_dev, void *stream);
 /* Expert-parallel prefill: x_all holds the tokens of ALL ranks, [own_row0, own_row0 + own_rows) being the caller's. Every
  * token is routed (same result on every rank), only the slots whose expert lies in this object's slice are sorted and
  * computed, the shared expert runs for the caller's own tokens only. y_part[n_all][hidden] is this rank's summand. */

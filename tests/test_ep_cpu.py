@@ -35,16 +35,16 @@ class OracleBlock:
         return out
 
     # home-rank routing: routes as int32 [rows, 2 top_k] (ids, then the float weights' bits), as engine.MoeBlock has them
-    def route_rows(self, x, route_out):
+    def route_rows(self, x, route_out):  # route_out: a column slice of the packed rows
         r = CO.moe_block_emul(self.t, x.numpy(), top_k=TOPK)
         route_out[:, :TOPK] = torch.from_numpy(r["ids"].astype(np.int32))
         route_out[:, TOPK:] = torch.from_numpy(r["weights"].astype(np.float32).view(np.int32))
         return route_out
 
     def forward_ep_routed(self, x_all, route_all, own_row0, own_rows, out=None):
-        ids = route_all[:, :TOPK].numpy().astype(np.int64)
-        w = route_all[:, TOPK:].numpy().view(np.float32)
-        r = CO.moe_block_emul(self.t, x_all.numpy(), top_k=TOPK, ids=ids, weights=w, expert_range=(self.e0, self.e1),
+        ids = route_all[:, :TOPK].contiguous().numpy().astype(np.int64)
+        w = route_all[:, TOPK:].contiguous().numpy().view(np.float32)
+        r = CO.moe_block_emul(self.t, x_all.contiguous().numpy(), top_k=TOPK, ids=ids, weights=w, expert_range=(self.e0, self.e1),
                               shared_rows=(own_row0, own_rows))
         out.copy_(torch.from_numpy(r["out"]))
         return out

@@ -185,6 +185,16 @@ def test_forward_ep_with_home_rank_routing(eng):
     for r in range(2):
         total += blks[r].forward_ep_routed(x_all, route_all, 10 * r, 10).cpu().numpy()
     assert rel_max(total, full) < 1e-5
+    # the same with rows and routes packed side by side (what one all-gather delivers)
+    packed = torch.zeros((20, 512 + 8), dtype=torch.float32, device="cuda")
+    packed[:, :512] = x_all
+    for r in range(2):
+        blks[r].route_rows(x_all[10 * r:10 * r + 10], packed[10 * r:10 * r + 10, 512:].view(torch.int32))
+    assert torch.equal(packed[:, 512:].view(torch.int32), route_all)
+    total2 = np.zeros_like(full)
+    for r in range(2):
+        total2 += blks[r].forward_ep_routed(packed[:, :512], packed[:, 512:].view(torch.int32), 10 * r, 10).cpu().numpy()
+    assert np.array_equal(total2, total)
     assert eng.lib.ne_device_wait_status() == 0
 
 
