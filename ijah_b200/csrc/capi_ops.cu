@@ -401,9 +401,10 @@ NE_API int ne_moe_last_bytes(ne_moe *m, int rows, uint64_t *total, uint64_t *gat
   return c_call([&] {
     Moe *o = reinterpret_cast<Moe *>(m);
     IJ_CHECK(o && rows >= 1 && rows <= o->max_rows, "bad argument");
-    int nu = 0;
+    int head[2] = {0, 0};  // entries, distinct experts
     IJ_CUDA(cudaDeviceSynchronize());
-    IJ_CUDA(cudaMemcpy(&nu, o->plan, 4, cudaMemcpyDeviceToHost));
+    IJ_CUDA(cudaMemcpy(head, o->plan, 8, cudaMemcpyDeviceToHost));
+    const int nu = head[1];
     const uint64_t H = o->desc.hidden, I = o->desc.inter, E = o->desc.experts;
     const uint64_t lin_x = H * I * o->desc.k_expert / 8, lin_s = H * I * o->desc.k_shared / 8;
     const uint64_t gu = (uint64_t)nu * 2 * (lin_x + 2 * H + 2 * I) + (o->has_shared ? 2 * (lin_s + 2 * H + 2 * I) : 0);

@@ -195,8 +195,10 @@ __device__ void topk_row(const MoeParams &p, int r, int *sid, unsigned long long
   route_row(p, r, sid, lane, myv, myi);
 }
 
-// Distinct local experts of the rows*topk (row, slot) pairs, in expert order, each with its pairs in row order.
-// One CTA (blockDim a multiple of 32, <= 1024); `buf` is 16 KB of shared memory, sid[P] the pairs' expert ids (shared).
+// The local experts that the rows*topk (row, slot) pairs use, in expert order, each with its pairs in row order, cut into
+// entries of at most PLAN_ROWS rows: one entry = one pass of the stream kernels over that expert's weights (an expert that
+// more than PLAN_ROWS rows selected is streamed once per entry, which at decode widths is rare). One CTA (blockDim a
+// multiple of 32, <= 1024); `buf` is 16 KB of shared memory, sid[P] the pairs' expert ids (shared).
 __device__ void build_plan_block(const MoeParams &p, unsigned char *buf, const int *sid) {
   unsigned long long *mask = reinterpret_cast<unsigned long long *>(buf);  // [E] rows that use expert e
   int *uidx = reinterpret_cast<int *>(buf + 8 * RT_EMAX);                  // [E] index among present experts
@@ -212,13 +214,14 @@ __device__ void build_plan_block(const MoeParams &p, unsigned char *buf, const i
     if (e >= p.e0 && e < p.e0 + p.ecount) atomicOr(&mask[e], 1ull << (i / k));
   }
   __syncthreads();
-  // exclusive scan over experts of (present ? 1 : 0, pair count), packed as (present << 16) | count (count <= 2048):
+  // exclusive scan over experts of (entries, pair count), packed as (entries << 16) | count (count <= 2048):
   // thread t covers experts [t * per, (t + 1) * per)
   const int per = (E + T - 1) / T, e_lo = tid * per;
-  int mine = 0;
+  int mine = 0, distinct = 0;
   for (int e = e_lo; e < min(E, e_lo + per); e++) {
     const int c = __popcll(mask[e]);
-    mine += c > 0 ? (1 << 16) + c : 0;
+    mine += (((c + PLAN_ROWS - 1) / PLAN_ROWS) << 16) + c;
+    distinct += c > 0 ? 1 : 0;
   }
   int inc = mine;
 #pragma unroll
@@ -231,18 +234,23 @@ __device__ void build_plan_block(const MoeParams &p, unsigned char *buf, const i
   int run = inc - mine;
   for (int w = 0; w < warp; w++) run += wtot[w];
   if (tid == T - 1) *pv.nu() = (run + mine) >> 16;
+  if (tid == 0) *pv.distinct() = 0;
   for (int e = e_lo; e < min(E, e_lo + per); e++) {
     const int c = __popcll(mask[e]);
     if (c > 0) {
-      const int u = run >> 16, f = run & 0xFFFF;
+      const int u = run >> 16, f = run & 0xFFFF, ng = (c + PLAN_ROWS - 1) / PLAN_ROWS;
       firs[e] = f;
-      pv.expert()[u] = e;
-      pv.nrows()[u] = c;
-      pv.first()[u] = f;
-      run += (1 << 16) + c;
+      for (int g = 0; g < ng; g++) {
+        pv.expert()[u + g] = e;
+        pv.nrows()[u + g] = min(PLAN_ROWS, c - g * PLAN_ROWS);
+        pv.first()[u + g] = f + g * PLAN_ROWS;
+      }
+      run += (ng << 16) + c;
     }
   }
   (void)uidx;
+  __syncthreads();
+  if (distinct) atomicAdd(pv.distinct(), distinct);
   __syncthreads();
   for (int i = tid; i < P; i += T) {
     const int r = i / k, e = sid[i];
@@ -477,7 +485,8 @@ struct MoeGateUpProblem {
   MoeParams p;
   int IT, OT, NG, S, kc;
 
-  __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + (p.has_shared ? 1 : 0)) * 2 * S * NG; }
+  __device__ int shared_groups() const { return p.has_shared ? (p.sh_rows + PLAN_ROWS - 1) / PLAN_ROWS : 0; }
+  __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + shared_groups()) * 2 * S * NG; }
   __device__ Unit unit(int u) const {
     const PlanView pv{p.plan, p.P};
     Unit un;
@@ -490,8 +499,8 @@ struct MoeGateUpProblem {
     un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
     un.shared = q >= *pv.nu();
     const Exl3Stack *w;
-    if (un.shared) {
-      un.e = 0; un.first = 0; un.nrows = p.sh_rows; un.K = p.Ks;  // only the rows whose shared expert runs here
+    if (un.shared) {  // only the rows whose shared expert runs here, PLAN_ROWS at a time
+      un.e = 0; un.first = (q - *pv.nu()) * PLAN_ROWS; un.nrows = min(PLAN_ROWS, p.sh_rows - un.first); un.K = p.Ks;
       w = un.proj ? &p.sup : &p.sgt;
     } else {
       un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx;
@@ -503,7 +512,9 @@ struct MoeGateUpProblem {
     return un;
   }
   // row index = the (row, slot) pair for routed units, the activation row for the shared expert
-  __device__ int row_index(const Unit &un, int i) const { return un.shared ? p.sh_row0 + i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
+  __device__ int row_index(const Unit &un, int i) const {
+    return un.shared ? p.sh_row0 + un.first + i : PlanView{p.plan, p.P}.pairs()[un.first + i];
+  }
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sgu : p.xh_gu) + ((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16;
   }
@@ -524,7 +535,8 @@ struct MoeDownProblem {
   MoeParams p;
   int IT, OT, NG, S, kc;  // IT = I/16, OT = H/16
 
-  __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + (p.has_shared ? 1 : 0)) * S * NG; }
+  __device__ int shared_groups() const { return p.has_shared ? (p.sh_rows + PLAN_ROWS - 1) / PLAN_ROWS : 0; }
+  __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + shared_groups()) * S * NG; }
   __device__ Unit unit(int u) const {
     const PlanView pv{p.plan, p.P};
     Unit un;
@@ -535,14 +547,16 @@ struct MoeDownProblem {
     un.kc = min(kc, IT - un.k0);
     un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
     un.shared = q >= *pv.nu();
-    if (un.shared) { un.e = 0; un.first = 0; un.nrows = p.sh_rows; un.K = p.Ks; }
+    if (un.shared) { un.e = 0; un.first = (q - *pv.nu()) * PLAN_ROWS; un.nrows = min(PLAN_ROWS, p.sh_rows - un.first); un.K = p.Ks; }
     else { un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx; }
     const size_t tile = 32u * un.K;
     un.kstride = (uint32_t)(OT * tile);
     un.w = (un.shared ? p.sdn.trellis : p.down.trellis) + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
     return un;
   }
-  __device__ int row_index(const Unit &un, int i) const { return un.shared ? p.sh_row0 + i : PlanView{p.plan, p.P}.pairs()[un.first + i]; }
+  __device__ int row_index(const Unit &un, int i) const {
+    return un.shared ? p.sh_row0 + un.first + i : PlanView{p.plan, p.P}.pairs()[un.first + i];
+  }
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sd : p.xh_d) + (size_t)idx * p.I + un.k0 * 16;
   }
@@ -630,20 +644,22 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   IJ_CHECK(rows >= 1 && rows <= 64, "rows %d outside 1..64", rows);
   IJ_CHECK(Kx >= 4 && Kx <= 8 && (!has_shared || (Ks >= 4 && Ks <= 8)), "bits per weight outside 4..8");
   MoeSplits s{};
-  s.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
+  s.MT = 1;  // every unit has at most PLAN_ROWS = 8 rows (the plan cuts experts with more rows into several entries)
   s.grid = 2 * sm_count();
+  const int urows = std::min(rows, PLAN_ROWS);
   // expected number of distinct experts under uniform routing; any actual count works, this only tunes the k-split
   const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows));
-  const double rpu = std::max(1.0, rows * (double)topk / std::max(nu, 1.0));
-  const int kcap = kc_cap(rows);
+  const double rpu = std::min((double)urows, std::max(1.0, rows * (double)topk / std::max(nu, 1.0)));
+  const double nsh = has_shared ? (rows + PLAN_ROWS - 1) / PLAN_ROWS : 0;
+  const int kcap = kc_cap(urows);
   // at most 16 splits (bounds the partial-sum scratch)
-  choose_split(H / 16, (int)std::lround((nu + (has_shared ? 1 : 0)) * 2 * (I / 128)), kcap, s.grid, rpu, &s.S_gu, &s.kc_gu);
+  choose_split(H / 16, (int)std::lround((nu + nsh) * 2 * (I / 128)), kcap, s.grid, rpu, &s.S_gu, &s.kc_gu);
   if (s.S_gu > 16) { s.kc_gu = (H / 16 + 15) / 16; s.kc_gu = (s.kc_gu + SG_KS - 1) / SG_KS * SG_KS; s.S_gu = (H / 16 + s.kc_gu - 1) / s.kc_gu; }
-  choose_split(I / 16, (int)std::lround((nu + (has_shared ? 1 : 0)) * (H / 128)), kcap, s.grid, rpu, &s.S_d, &s.kc_d);
+  choose_split(I / 16, (int)std::lround((nu + nsh) * (H / 128)), kcap, s.grid, rpu, &s.S_d, &s.kc_d);
   if (s.S_d > 16) { s.kc_d = (I / 16 + 15) / 16; s.kc_d = (s.kc_d + SG_KS - 1) / SG_KS * SG_KS; s.S_d = (I / 16 + s.kc_d - 1) / s.kc_d; }
   const int kmax = std::max(Kx, has_shared ? Ks : 0);
-  s.lay_gu = make_layout(kmax, s.kc_gu, rows, 2);
-  s.lay_d = make_layout(kmax, s.kc_d, rows, 2);
+  s.lay_gu = make_layout(kmax, s.kc_gu, urows, 2);
+  s.lay_d = make_layout(kmax, s.kc_d, urows, 2);
   return s;
 }
 

@@ -55,12 +55,15 @@ struct MoeParams {
   int lg_row0;  // logits[] holds rows [lg_row0, ..) (expert parallel with own-row routing: only the own rows were routed here)
 };
 
-// plan[] layout (ints): [0] = number of distinct local experts nu; then four arrays of PMAXU = P entries each:
-// expert id, row count, offset into pairs[], and pairs[] (pair = row * topk + slot) grouped by expert, rows ascending.
+// plan[] layout (ints): [0] = number of entries nu, [1] = number of distinct local experts; then four arrays of P entries
+// each: expert id, row count (<= PLAN_ROWS), offset into pairs[], and pairs[] (pair = row * topk + slot) grouped by
+// expert, rows ascending. An expert with more than PLAN_ROWS rows has several consecutive entries.
+constexpr int PLAN_ROWS = 8;
 struct PlanView {
   int *base;
   int P;
   __host__ __device__ int *nu() const { return base; }
+  __host__ __device__ int *distinct() const { return base + 1; }
   __host__ __device__ int *expert() const { return base + 4; }
   __host__ __device__ int *nrows() const { return base + 4 + P; }
   __host__ __device__ int *first() const { return base + 4 + 2 * P; }
