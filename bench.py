@@ -269,6 +269,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill figure in extra (0 = skip)")
+    ap.add_argument("--nccl-exchange", action="store_true", help="N > 1: exchange rows and partial outputs with NCCL collectives "
+                    "instead of the peer-memory kernels")
     ap.add_argument("--workload", default="block", choices=["block", "stack"],
                     help="block: the MoE block (headline); stack: a whole random-init decoder stack step (see run_stack)")
     a = ap.parse_args()
@@ -312,7 +314,11 @@ def main():
     else:
         from ijah_b200 import ep
         eps = [ep.ExpertParallelMoe(blocks[l], dist.group.WORLD) for l in range(L)]
-        launches_per_block = eps[0].launches
+        launches_per_block = eps[0].launches + 2  # + the exchange and the sum kernel
+        if not a.nccl_exchange:  # both exchange steps of a block over NVLink peer memory (no library collective in the block)
+            xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, M, H, TOPK)
+            for e_ in eps:
+                e_.use_exchange(xchg)
 
         def step():
             for l in range(L):

@@ -126,6 +126,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   p.h_mid = h_mid; p.inj = inj; p.h_out = h_out; p.HC = HC;
   p.sh_row0 = 0; p.sh_rows = rows; p.lg_row0 = 0;
   p.ldx = desc.hidden; p.ldr = 2 * desc.top_k;
+  p.ep = nullptr; p.ep_rows = 0; p.ep_epoch = 0;
   return p;
 }
 
@@ -210,6 +211,35 @@ void Moe::forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all,
   launch_moe_down(p, s, status, st);
   launch_moe_combine(p, false, st);
   last_rows = rows;
+}
+
+// The whole expert-parallel block over peer memory: route the own rows, exchange packed rows, compute this rank's experts
+// for all rows with the combine writing into the owners' memory, sum the partial rows that arrived here.
+void Moe::forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own, cudaStream_t st) {
+  const int H = desc.hidden, k = desc.top_k, world = c.host.world, all = rows * world;
+  IJ_CHECK(c.connected, "expert-parallel context is not connected");
+  IJ_CHECK(c.host.H == H && c.top_k == k, "expert-parallel context was made for other dims");
+  IJ_CHECK(rows >= 1 && rows <= c.host.rows_cap && all <= max_rows, "rows %d x %d ranks exceed the context (%d) or the object (%d)", rows, world,
+           c.host.rows_cap, max_rows);
+  const int W = c.host.W;
+  const uint32_t epoch = ++c.epoch;
+  IJ_CUDA(cudaMemcpy2DAsync(c.pack_own, (size_t)W * 4, x_own, (size_t)H * 4, (size_t)H * 4, rows, cudaMemcpyDeviceToDevice, st));
+  route_rows(x_own, rows, reinterpret_cast<uint32_t *>(c.pack_own + H), W, st);
+  launch_ep_exchange(c, rows, epoch, status, st);
+  const float *gathered = c.host.gather[c.host.rank];
+  MoeParams p = params(gathered, all, y_own);
+  p.ldx = W; p.ldr = W;
+  p.route = reinterpret_cast<uint32_t *>(const_cast<float *>(gathered) + H);
+  p.sh_row0 = c.host.rank * rows; p.sh_rows = rows; p.lg_row0 = p.sh_row0;
+  p.ep = c.dev; p.ep_rows = rows; p.ep_epoch = epoch;
+  const MoeSplits &s = splits(all);
+  launch_moe_prep(p, true, st);
+  launch_moe_gateup(p, s, status, st);
+  launch_moe_mid(p, st);
+  launch_moe_down(p, s, status, st);
+  launch_moe_combine(p, false, st);
+  launch_ep_sum(c, rows, epoch, y_own, status, st);
+  last_rows = all;
 }
 
 void Moe::forward_routed(const float *x, const uint32_t *route_in, int rows, float *y, cudaStream_t st) {
@@ -358,6 +388,77 @@ NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, int ld_x,
     IJ_CHECK(m && x_all_dev && route_all_dev && y_part_dev, "null argument");
     reinterpret_cast<Moe *>(m)->forward_ep_routed(x_all_dev, ld_x, route_all_dev, ld_route, rows_all, own_row0, own_rows, y_part_dev,
                                                   (cudaStream_t)stream);
+  });
+}
+// ---- expert-parallel exchange context (ep_exchange.cuh)
+NE_API ne_ep *ne_ep_create(int rank, int world, int rows_cap, int hidden, int top_k) {
+  ne_ep *out = nullptr;
+  c_call([&] {
+    IJ_CHECK(world >= 1 && world <= EP_MAX_RANKS && rank >= 0 && rank < world, "bad rank %d of %d (at most %d ranks)", rank, world, EP_MAX_RANKS);
+    IJ_CHECK(rows_cap >= 1 && hidden % 4 == 0 && top_k >= 1 && (2 * top_k) % 4 == 0, "bad dims (hidden and 2 * top_k must be multiples of 4)");
+    auto c = std::make_unique<EpCtx>();
+    c->top_k = top_k;
+    EpDev &h = c->host;
+    h.rank = rank; h.world = world; h.rows_cap = rows_cap; h.H = hidden; h.W = hidden + 2 * top_k;
+    auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    c->off_gather = 0;
+    c->off_part = up((size_t)world * rows_cap * h.W * 4);
+    c->off_flags = c->off_part + up((size_t)world * rows_cap * hidden * 4);
+    c->bytes = c->off_flags + 256;  // two flag arrays of EP_MAX_RANKS words
+    IJ_CUDA(cudaMalloc(&c->local, c->bytes));
+    IJ_CUDA(cudaMemset(c->local, 0, c->bytes));
+    IJ_CUDA(cudaMalloc((void **)&c->pack_own, (size_t)rows_cap * h.W * 4));
+    IJ_CUDA(cudaMalloc((void **)&h.counter, 16));
+    IJ_CUDA(cudaMemset(h.counter, 0, 16));
+    IJ_CUDA(cudaMalloc((void **)&c->dev, sizeof(EpDev)));
+    IJ_CUDA(cudaDeviceSynchronize());
+    out = reinterpret_cast<ne_ep *>(c.release());
+  });
+  return out;
+}
+NE_API int ne_ep_handle(ne_ep *e, void *handle64) {
+  return c_call([&] {
+    IJ_CHECK(e && handle64, "null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    IJ_CUDA(cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t *>(handle64), reinterpret_cast<EpCtx *>(e)->local));
+  });
+}
+NE_API int ne_ep_connect(ne_ep *e, const void *handles64) {
+  return c_call([&] {
+    EpCtx *c = reinterpret_cast<EpCtx *>(e);
+    IJ_CHECK(c && handles64 && !c->connected, "null argument or already connected");
+    EpDev &h = c->host;
+    for (int r = 0; r < h.world; r++) {
+      char *base;
+      if (r == h.rank) base = (char *)c->local;
+      else {
+        cudaIpcMemHandle_t hd;
+        memcpy(&hd, (const char *)handles64 + 64 * r, 64);
+        IJ_CUDA(cudaIpcOpenMemHandle(&c->peer[r], hd, cudaIpcMemLazyEnablePeerAccess));
+        base = (char *)c->peer[r];
+      }
+      h.gather[r] = (float *)(base + c->off_gather);
+      h.part[r] = (float *)(base + c->off_part);
+      h.gflag[r] = (uint32_t *)(base + c->off_flags);
+      h.pflag[r] = (uint32_t *)(base + c->off_flags + 128);
+    }
+    IJ_CUDA(cudaMemcpy(c->dev, &h, sizeof h, cudaMemcpyHostToDevice));
+    c->connected = true;
+  });
+}
+NE_API void ne_ep_free(ne_ep *e) {
+  EpCtx *c = reinterpret_cast<EpCtx *>(e);
+  if (!c) return;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->host.world; r++)
+    if (c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+  cudaFree(c->local); cudaFree(c->pack_own); cudaFree(c->host.counter); cudaFree(c->dev);
+  delete c;
+}
+NE_API int ne_moe_forward_ep_fused(ne_moe *m, ne_ep *e, const float *x_own_dev, int rows, float *y_own_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && e && x_own_dev && y_own_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->forward_ep_fused(*reinterpret_cast<EpCtx *>(e), x_own_dev, rows, y_own_dev, (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream) {

@@ -631,10 +631,25 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
     float acc = 0.0f;
     for (int t = 0; t <= k; t++)
       if (used[t]) acc += vals[t][lane + 32 * j];
-    p.y[(size_t)r * H + c] = acc;
+    if (p.ep != nullptr) {  // straight into the memory of the rank that owns row r (peer store over NVLink)
+      const int dest = r / p.ep_rows;
+      p.ep->part[dest][((size_t)p.ep->rank * p.ep->rows_cap + (r - dest * p.ep_rows)) * H + c] = acc;
+    } else {
+      p.y[(size_t)r * H + c] = acc;
+    }
     if (p.h_mid != nullptr)
       for (int s = 0; s < p.HC; s++)
         p.h_out[((size_t)r * p.HC + s) * H + c] = p.h_mid[((size_t)r * p.HC + s) * H + c] + acc * p.inj[(size_t)r * 2 * p.HC + s];
+  }
+  if (p.ep != nullptr) {  // the last CTA to get here tells every peer that this rank's partial rows are in place
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0 && atomicAdd(p.ep->counter, 1u) == gridDim.x * gridDim.y - 1) {
+      *p.ep->counter = 0u;
+      __threadfence_system();
+      for (int d = 0; d < p.ep->world; d++)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ep->pflag[d] + p.ep->rank), "r"(p.ep_epoch) : "memory");
+    }
   }
 }
 

@@ -44,6 +44,7 @@ struct Moe {
   void forward(const float *x, int rows, float *y, cudaStream_t st);
   void forward_ep(const float *x, int rows, int own_row0, int own_rows, float *y, cudaStream_t st);
   void forward_routed(const float *x, const uint32_t *route_in, int rows, float *y, cudaStream_t st);
+  void forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own, cudaStream_t st);
   void route_rows(const float *x, int rows, uint32_t *route_out, int ld_route, cudaStream_t st);
   void forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all, int ld_route, int rows, int own_row0, int own_rows, float *y,
                          cudaStream_t st);

@@ -104,6 +104,11 @@ SIGNATURES = {
     "ne_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "ne_moe_forward_ep_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                            C.c_void_p]),
+    "ne_ep_create": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "ne_ep_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ne_ep_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ne_ep_free": (None, [C.c_void_p]),
+    "ne_moe_forward_ep_fused": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_prefill_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
@@ -397,6 +402,31 @@ class Exl3Linear:
         return y
 
 
+class EpExchange:
+    """This rank's NVLink peer-memory exchange context (ne_ep_*): create, export the 64-byte IPC handle, connect with the
+    handles of all ranks (rank order). One context serves every layer of a model."""
+
+    def __init__(self, eng, rank, world, rows_cap, hidden, top_k):
+        self.eng, self.rank, self.world = eng, rank, world
+        self.ptr = eng.lib.ne_ep_create(rank, world, rows_cap, hidden, top_k)
+        if not self.ptr:
+            raise EngineError(eng.last_error())
+
+    def handle(self):
+        buf = C.create_string_buffer(64)
+        self.eng._ok(self.eng.lib.ne_ep_handle(self.ptr, buf), "ne_ep_handle")
+        return buf.raw
+
+    def connect(self, handles):
+        assert len(handles) == self.world and all(len(h) == 64 for h in handles)
+        self.eng._ok(self.eng.lib.ne_ep_connect(self.ptr, C.create_string_buffer(b"".join(handles), 64 * self.world)), "ne_ep_connect")
+
+    def free(self):
+        if self.ptr:
+            self.eng.lib.ne_ep_free(self.ptr)
+            self.ptr = None
+
+
 def linear_multi(eng, linears, x, outs):
     """outs[i] = x @ W_i for up to 4 Exl3Linear objects that share the input width, in one launch chain
     (ne_exl3_linear_multi); x and outs are float32 device tensors the caller owns"""
@@ -504,6 +534,14 @@ class MoeBlock:
         self.eng._ok(self.eng.lib.ne_moe_forward_ep_routed(self.ptr, C.c_void_p(x_all.data_ptr()), x_all.stride(0),
                                                            C.c_void_p(route_all.data_ptr()), route_all.stride(0), rows, own_row0, own_rows,
                                                            _dev(y), _stream()), "ne_moe_forward_ep_routed")
+        return y
+
+    def forward_ep_fused(self, xchg, x, out=None):
+        """the whole expert-parallel block for this rank's rows x with both exchange steps over NVLink peer memory
+        (ne_moe_forward_ep_fused); every rank calls with the same row count, in the same order"""
+        torch = _torch()
+        y = torch.empty_like(x) if out is None else out
+        self.eng._ok(self.eng.lib.ne_moe_forward_ep_fused(self.ptr, xchg.ptr, _dev(x), x.shape[0], _dev(y), _stream()), "ne_moe_forward_ep_fused")
         return y
 
     def prefill_ep(self, x_all, own_row0, own_rows, out=None):

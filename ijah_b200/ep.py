@@ -17,6 +17,10 @@ the win is the N-fold drop in weight bytes per GPU. The sum over ranks changes t
 added (per-rank partial sums in slot order, then ranks in the collective's order); the result stays within the 2e-3
 output bound and is noted as a deviation from the single-GPU slot order.
 
+With use_exchange(make_exchange(...)) both exchange steps run over NVLink peer memory instead (ijah_b200/csrc/
+ep_exchange.cuh): packed rows are written straight into every peer's gather area, the combine kernel stores each finished
+row into the owning rank's memory, flags signal arrival; no library collective remains in the block.
+
 `block` only needs `forward_ep(x_all, own_row0, own_rows, out=None)` and `H`; the CPU tests pass an oracle-backed
 stand-in, the GPU path passes ijah_b200.engine.MoeBlock.
 """
@@ -37,11 +41,30 @@ class ExpertParallelMoe:
         self._x_all = None
         self._y_part = None
         self._pack = self._pack_all = self._views = None
+        self.xchg = None
         # blocks that can route alone (engine.MoeBlock) route each row on its home rank; others replicate the routing
         self.own_routing = hasattr(block, "route_rows") and hasattr(block, "forward_ep_routed")
         # ... once the gathered rows exceed this count (the replicated router takes 11 / 14 / 23 / 42 us at 4 / 8 / 16 / 32 rows,
         # home-rank routing 11 us plus a small copy)
         self.own_routing_min_rows = 8
+
+    @staticmethod
+    def make_exchange(eng, group, rows_cap, hidden, top_k):
+        """an NVLink peer-memory exchange context shared by all layers (engine.EpExchange), connected across `group`;
+        attach it to wrappers with use_exchange()"""
+        from . import engine as E
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        x = E.EpExchange(eng, rank, world, rows_cap, hidden, top_k)
+        handles = [None] * world
+        dist.all_gather_object(handles, x.handle(), group=group)
+        x.connect(handles)
+        dist.barrier(group=group)
+        return x
+
+    def use_exchange(self, xchg):
+        """decode-width forwards go through block.forward_ep_fused: no library collective in the block"""
+        self.xchg = xchg
+        return self
 
     def _buffers(self, x):
         rows, H = x.shape
@@ -54,8 +77,11 @@ class ExpertParallelMoe:
         """x [rows, H] float32 (every rank the same row count) -> y [rows, H]; prefill: the many-token path
         (block.prefill_ep: sorted slots, grouped tensor-core GEMM) instead of the decode-width kernels"""
         rows, H = x.shape
-        x_all, y_part = self._buffers(x)
         x = x.contiguous()
+        if not prefill and self.xchg is not None:
+            y = torch.empty_like(x) if out is None else out
+            return self.block.forward_ep_fused(self.xchg, x, out=y)
+        x_all, y_part = self._buffers(x)
         if not prefill and self.own_routing and rows * self.world > self.own_routing_min_rows:
             # every row is routed on its home rank only; a row and its route travel side by side in ONE all-gather:
             # packed row = [x (H floats) | ids (k) | weights (k)], the kernels read both parts with the packed row stride

@@ -115,6 +115,20 @@ NE_API int ne_moe_forward_ep(ne_moe *m, const float *x_all_dev, int rows_all, in
 NE_API int ne_moe_route(ne_moe *m, const float *x_dev, int rows, uint32_t *route_out_dev, int ld_route, void *stream);
 NE_API int ne_moe_forward_ep_routed(ne_moe *m, const float *x_all_dev, int ld_x, const uint32_t *route_all_dev, int ld_route, int rows_all,
                                     int own_row0, int own_rows, float *y_part_dev, void *stream);
+/* The same block with both exchange steps over NVLink peer memory instead of library collectives (one process per GPU
+ * of one node). ne_ep_create allocates this rank's exchange buffer (gather area for world * rows_cap packed rows, part area
+ * for the partial output rows peers send, flag words); every rank exports its buffer (ne_ep_handle: 64 bytes, a CUDA IPC
+ * handle), the ranks exchange the handles by any means (e.g. an all-gather of bytes) and each calls ne_ep_connect with all
+ * of them in rank order. ne_moe_forward_ep_fused then runs one block for `rows` own rows (the same count on every rank, all
+ * ranks call in the same order): router on the own rows, packed rows written into every peer's gather area, this rank's
+ * experts for all rows with the combine kernel storing each finished row into the owning rank's memory, rank-ordered sum of
+ * the partial rows that arrived. All device-side waits are bounded (ne_device_wait_status). One context serves all layers. */
+typedef struct ne_ep ne_ep;
+NE_API ne_ep *ne_ep_create(int rank, int world, int rows_cap, int hidden, int top_k);
+NE_API int ne_ep_handle(ne_ep *e, void *handle64);
+NE_API int ne_ep_connect(ne_ep *e, const void *handles64 /* world x 64 bytes, rank order */);
+NE_API void ne_ep_free(ne_ep *e);
+NE_API int ne_moe_forward_ep_fused(ne_moe *m, ne_ep *e, const float *x_own_dev, int rows, float *y_own_dev, void *stream);
 /* Expert-parallel prefill: x_all holds the tokens of ALL ranks, [own_row0, own_row0 + own_rows) being the caller's. Every
  * token is routed (same result on every rank), only the slots whose expert lies in this object's slice are sorted and
  * computed, the shared expert runs for the caller's own tokens only. y_part[n_all][hidden] is this rank's summand. */

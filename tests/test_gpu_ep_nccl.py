@@ -35,6 +35,13 @@ err_d = float((got - want).abs().max() / want.abs().max())
 par.own_routing_min_rows = 0               # every row routed on its home rank, routes all-gathered
 got2 = par.forward(xs)
 err_d = max(err_d, float((got2 - want).abs().max() / want.abs().max()))
+# the same block with both exchange steps over NVLink peer memory (two layers share one context; repeated calls)
+xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, 16, 512, 4)
+par.use_exchange(xchg)
+for _ in range(3):
+    got3 = par.forward(xs)
+    err_d = max(err_d, float((got3 - want).abs().max() / want.abs().max()))
+par.use_exchange(None)
 # prefill: 40 tokens per rank
 xp = torch.from_numpy(x_all[rank * 40:(rank + 1) * 40]).to(dev)
 wantp = full.prefill(torch.from_numpy(x_all).to(dev))[rank * 40:(rank + 1) * 40]
