@@ -223,9 +223,8 @@ void Moe::forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own,
            c.host.rows_cap, max_rows);
   const int W = c.host.W;
   const uint32_t epoch = ++c.epoch;
-  IJ_CUDA(cudaMemcpy2DAsync(c.pack_own, (size_t)W * 4, x_own, (size_t)H * 4, (size_t)H * 4, rows, cudaMemcpyDeviceToDevice, st));
-  route_rows(x_own, rows, reinterpret_cast<uint32_t *>(c.pack_own + H), W, st);
-  launch_ep_exchange(c, rows, epoch, status, st);
+  route_rows(x_own, rows, c.route_own, 0, st);
+  launch_ep_exchange(c, x_own, c.route_own, rows, epoch, status, st);
   const float *gathered = c.host.gather[c.host.rank];
   MoeParams p = params(gathered, all, y_own);
   p.ldx = W; p.ldr = W;
@@ -407,7 +406,7 @@ NE_API ne_ep *ne_ep_create(int rank, int world, int rows_cap, int hidden, int to
     c->bytes = c->off_flags + 256;  // two flag arrays of EP_MAX_RANKS words
     IJ_CUDA(cudaMalloc(&c->local, c->bytes));
     IJ_CUDA(cudaMemset(c->local, 0, c->bytes));
-    IJ_CUDA(cudaMalloc((void **)&c->pack_own, (size_t)rows_cap * h.W * 4));
+    IJ_CUDA(cudaMalloc((void **)&c->route_own, (size_t)rows_cap * 2 * top_k * 4));
     IJ_CUDA(cudaMalloc((void **)&h.counter, 16));
     IJ_CUDA(cudaMemset(h.counter, 0, 16));
     IJ_CUDA(cudaMalloc((void **)&c->dev, sizeof(EpDev)));
@@ -452,7 +451,7 @@ NE_API void ne_ep_free(ne_ep *e) {
   cudaDeviceSynchronize();
   for (int r = 0; r < c->host.world; r++)
     if (c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
-  cudaFree(c->local); cudaFree(c->pack_own); cudaFree(c->host.counter); cudaFree(c->dev);
+  cudaFree(c->local); cudaFree(c->route_own); cudaFree(c->host.counter); cudaFree(c->dev);
   delete c;
 }
 NE_API int ne_moe_forward_ep_fused(ne_moe *m, ne_ep *e, const float *x_own_dev, int rows, float *y_own_dev, void *stream) {

@@ -1,6 +1,9 @@
 // Expert-parallel exchange kernels and their host context. See ep_exchange.cuh.
+#include <algorithm>
+
 #include "common.hpp"
 #include "ep_exchange.cuh"
+#include "launch.cuh"
 
 namespace ijah {
 
@@ -22,13 +25,18 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t *flag, uint32_t epoch,
   return false;
 }
 
-// CTA d: this rank's packed rows -> rank d's gather buffer, then the flag; afterwards CTA s waits for source s.
-__global__ void __launch_bounds__(256) ep_exchange_kernel(const EpDev *ep, const float *pack_own, int rows, uint32_t epoch, int *status) {
-  const int d = blockIdx.x, me = ep->rank;
-  const int n4 = rows * ep->W / 4;  // W is a multiple of 4
-  const float4 *src = reinterpret_cast<const float4 *>(pack_own);
+// CTA d: this rank's rows, packed as (x row | route row), -> rank d's gather buffer, then the flag; afterwards CTA s waits
+// for source s. x_own [rows][H] floats and route_own [rows][2 top_k] words are the router's input and output.
+__global__ void __launch_bounds__(256) ep_exchange_kernel(const EpDev *ep, const float *x_own, const uint32_t *route_own, int rows, uint32_t epoch,
+                                                          int *status) {
+  pdl_wait();
+  pdl_launch();
+  const int d = blockIdx.x, me = ep->rank, H4 = ep->H / 4, W4 = ep->W / 4, R4 = W4 - H4;
   float4 *dst = reinterpret_cast<float4 *>(ep->gather[d] + (size_t)me * rows * ep->W);
-  for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = src[i];
+  for (int i = threadIdx.x; i < rows * W4; i += blockDim.x) {
+    const int r = i / W4, c = i - r * W4;
+    dst[i] = c < H4 ? reinterpret_cast<const float4 *>(x_own)[r * H4 + c] : reinterpret_cast<const float4 *>(route_own)[r * R4 + c - H4];
+  }
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -40,6 +48,8 @@ __global__ void __launch_bounds__(256) ep_exchange_kernel(const EpDev *ep, const
 // y_own[r][c] = sum over source ranks (in rank order) of part[s][r][c], once every source's flag shows this epoch
 __global__ void __launch_bounds__(256) ep_sum_kernel(const EpDev *ep, int rows, uint32_t epoch, float *y_own, int *status) {
   __shared__ int ok;
+  pdl_wait();
+  pdl_launch();
   const int me = ep->rank, world = ep->world, H = ep->H;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
@@ -57,15 +67,13 @@ __global__ void __launch_bounds__(256) ep_sum_kernel(const EpDev *ep, int rows, 
   }
 }
 
-void launch_ep_exchange(const EpCtx &c, int rows, uint32_t epoch, int *status, cudaStream_t st) {
-  ep_exchange_kernel<<<c.host.world, 256, 0, st>>>(c.dev, c.pack_own, rows, epoch, status);
-  IJ_CUDA(cudaGetLastError());
+void launch_ep_exchange(const EpCtx &c, const float *x_own, const uint32_t *route_own, int rows, uint32_t epoch, int *status, cudaStream_t st) {
+  launch_pdl(ep_exchange_kernel, dim3(c.host.world), dim3(256), 0, st, (const EpDev *)c.dev, x_own, route_own, rows, epoch, status);
 }
 
 void launch_ep_sum(const EpCtx &c, int rows, uint32_t epoch, float *y_own, int *status, cudaStream_t st) {
   const int n4 = rows * c.host.H / 4;
-  ep_sum_kernel<<<std::max(1, std::min(32, (n4 + 255) / 256)), 256, 0, st>>>(c.dev, rows, epoch, y_own, status);
-  IJ_CUDA(cudaGetLastError());
+  launch_pdl(ep_sum_kernel, dim3(std::max(1, std::min(32, (n4 + 255) / 256))), dim3(256), 0, st, (const EpDev *)c.dev, rows, epoch, y_own, status);
 }
 
 }  // namespace ijah

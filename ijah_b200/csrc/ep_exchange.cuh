@@ -3,7 +3,7 @@
 // The two exchange steps of an expert-parallel MoE block move a few KB per rank, so with a library collective they
 // cost launch + protocol latency (about 12 us each at 2 ranks, 22 us at 8). Here the ranks write straight into each
 // other's memory with ordinary stores and signal with one flag word per (destination, source):
-//   dispatch  ep_exchange_kernel: CTA d copies this rank's packed rows (x | route) into rank d's gather buffer, fences,
+//   dispatch  ep_exchange_kernel: CTA d writes this rank's rows, packed as (x | route), into rank d's gather buffer, fences,
 //             writes the epoch into rank d's flag word of this rank; then CTA s waits for the flag of source s.
 //   combine   moe_combine_kernel writes each finished output row into the part buffer of the rank that owns the row
 //             (fused with the slot-ordered sum); the last CTA to finish fences and raises this rank's flag on every peer;
@@ -32,14 +32,14 @@ struct EpCtx {
   EpDev *dev = nullptr;  // device copy
   void *local = nullptr; // this rank's exchange buffer (cudaMalloc, exported with cudaIpcGetMemHandle)
   void *peer[EP_MAX_RANKS] = {};
-  float *pack_own = nullptr;  // [rows_cap][W] staging of this rank's packed rows
+  uint32_t *route_own = nullptr;  // [rows_cap][2 top_k] routes of this rank's rows (the router's output)
   size_t off_gather = 0, off_part = 0, off_flags = 0, bytes = 0;
   int top_k = 0;
   uint32_t epoch = 0;
   bool connected = false;
 };
 
-void launch_ep_exchange(const EpCtx &c, int rows, uint32_t epoch, int *status, cudaStream_t st);
+void launch_ep_exchange(const EpCtx &c, const float *x_own, const uint32_t *route_own, int rows, uint32_t epoch, int *status, cudaStream_t st);
 void launch_ep_sum(const EpCtx &c, int rows, uint32_t epoch, float *y_own, int *status, cudaStream_t st);
 
 }  // namespace ijah
