@@ -314,11 +314,13 @@ def main():
     else:
         from ijah_b200 import ep
         eps = [ep.ExpertParallelMoe(blocks[l], dist.group.WORLD) for l in range(L)]
-        launches_per_block = eps[0].launches + 2  # + the exchange and the sum kernel
-        if not a.nccl_exchange:  # both exchange steps of a block over NVLink peer memory (no library collective in the block)
+        launches_per_block = eps[0].launches
+        if not a.nccl_exchange:
+            launches_per_block += 2  # + the dispatch and the sum kernel  # both exchange steps of a block over NVLink peer memory (no library collective in the block)
             xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, M, H, TOPK)
             for e_ in eps:
                 e_.use_exchange(xchg)
+        exchange = "nccl" if a.nccl_exchange else "nvlink peer memory (own kernels)"
 
         def step():
             for l in range(L):
@@ -477,7 +479,7 @@ def main():
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": N, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic", "config": dict(workload_config(a), graph=graph is not None),
+            "dtype": "f16", "data": "synthetic", "config": dict(workload_config(a), graph=graph is not None, **({"exchange": exchange} if N > 1 else {})),
             "e2e": e2e, "gpu_launches": launches_per_block * L * a.steps, "clocks": clocks, "roofline": roof,
             "cpu_baseline": cpu, "extra": extra, "wait_status": status}))
     if N > 1:
