@@ -316,7 +316,8 @@ def main():
         eps = [ep.ExpertParallelMoe(blocks[l], dist.group.WORLD) for l in range(L)]
         launches_per_block = eps[0].launches
         if not a.nccl_exchange:
-            launches_per_block += 2  # + the dispatch and the sum kernel  # both exchange steps of a block over NVLink peer memory (no library collective in the block)
+            # both exchange steps of a block over NVLink peer memory (no library collective in the block): + dispatch and sum kernels
+            launches_per_block += 2
             xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, M, H, TOPK)
             for e_ in eps:
                 e_.use_exchange(xchg)
