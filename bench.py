@@ -317,10 +317,13 @@ def main():
         launches_per_block = eps[0].launches
         if not a.nccl_exchange:
             # both exchange steps of a block over NVLink peer memory (no library collective in the block): + dispatch and sum kernels
-            launches_per_block += 2
             xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, M, H, TOPK)
-            for e_ in eps:
-                e_.use_exchange(xchg)
+            if xchg is not None:
+                launches_per_block += 2
+                for e_ in eps:
+                    e_.use_exchange(xchg)
+            else:
+                a.nccl_exchange = True
         exchange = "nccl" if a.nccl_exchange else "nvlink peer memory (own kernels)"
 
         def step():

@@ -51,14 +51,32 @@ class ExpertParallelMoe:
     @staticmethod
     def make_exchange(eng, group, rows_cap, hidden, top_k):
         """an NVLink peer-memory exchange context shared by all layers (engine.EpExchange), connected across `group`;
-        attach it to wrappers with use_exchange()"""
+        attach it to wrappers with use_exchange(). Returns None on every rank if any rank could not set it up (the
+        wrappers then keep the NCCL exchange)."""
         from . import engine as E
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        x = E.EpExchange(eng, rank, world, rows_cap, hidden, top_k)
+        x, err = None, None
+        try:
+            x = E.EpExchange(eng, rank, world, rows_cap, hidden, top_k)
+            mine = x.handle()
+        except Exception as ex:  # keep taking part in the collectives below so that no rank is left waiting
+            mine, err = b"\0" * 64, ex
         handles = [None] * world
-        dist.all_gather_object(handles, x.handle(), group=group)
-        x.connect(handles)
-        dist.barrier(group=group)
+        dist.all_gather_object(handles, mine, group=group)
+        if err is None:
+            try:
+                x.connect(handles)
+            except Exception as ex:
+                err = ex
+        oks = [None] * world
+        dist.all_gather_object(oks, err is None, group=group)
+        if not all(oks):  # one rank could not set up peer access: every rank falls back (returns None)
+            if x is not None:
+                x.free()
+            if err is not None:
+                import sys
+                print(f"[rank {rank}] peer-memory exchange unavailable: {err}", file=sys.stderr)
+            return None
         return x
 
     def use_exchange(self, xchg):
