@@ -26,6 +26,11 @@ std::string &last_error_ref() {
 }
 
 // ------------------------------------------------------------------ per-device scratch + status word
+// The word the kernels report bounded-wait failures into is part of the library image (zero when the library is loaded on
+// a device), so neither reporting nor reading it ever allocates; every entry point, ne_exl3_linear_static included, hands
+// this one word to its kernels and ne_device_wait_status() reads it.
+static __device__ int g_wait_status;
+
 struct DeviceState {
   void *scratch = nullptr;
   size_t scratch_bytes = 0;
@@ -56,9 +61,10 @@ void *device_scratch(size_t bytes) {
 }
 int *device_status_word() {
   DeviceState &s = dev_state();
-  if (!s.status) {
-    IJ_CUDA(cudaMalloc(&s.status, sizeof(int)));
-    IJ_CUDA(cudaMemset(s.status, 0, sizeof(int)));
+  if (!s.status) {  // in host code the symbol is only a handle: its device address is looked up once per device
+    void *p = nullptr;
+    IJ_CUDA(cudaGetSymbolAddress(&p, g_wait_status));
+    s.status = static_cast<int *>(p);
   }
   return s.status;
 }
@@ -70,6 +76,28 @@ void check_status_word() {
     fail("a device-side bounded wait gave up (code %d: 1 = ring slot never freed, 2 = tiles never arrived)", v);
   }
 }
+void make_trellis_map(CUtensorMap *out, const void *base, int E, int IT, int OT, int K, int ks) {
+  typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static encode_fn encode = nullptr;  // the driver's cuTensorMapEncodeTiled, looked up through the runtime (no link against libcuda)
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    IJ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    IJ_CHECK(fn != nullptr && q == cudaDriverEntryPointSuccess, "the driver does not provide cuTensorMapEncodeTiled");
+    encode = reinterpret_cast<encode_fn>(fn);
+  }
+  IJ_CHECK(((uintptr_t)base & 15) == 0, "trellis must be 16-byte aligned on the device");
+  IJ_CHECK(E >= 1 && IT >= 1 && OT >= 1 && K >= 4 && K <= 8 && ks >= 1 && ks <= 256, "bad trellis dims for a tensor map");
+  const cuuint64_t dims[3] = {(cuuint64_t)OT * 4 * K, (cuuint64_t)IT, (cuuint64_t)E};
+  const cuuint64_t strides[2] = {(cuuint64_t)OT * 32 * K, (cuuint64_t)IT * OT * 32 * K};
+  const cuuint32_t box[3] = {(cuuint32_t)(8 * 4 * K), (cuuint32_t)ks, 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult rc = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  IJ_CHECK(rc == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed (%d) for a trellis of %d x %d x %d tiles, K%d", (int)rc, E, IT, OT, K);
+}
+
 int sm_count() {
   DeviceState &s = dev_state();
   if (!s.sms) {

@@ -49,6 +49,18 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   x_stage = (float *)al(R * H * 4);
   y_stage = (float *)al(R * H * 4);
   status = device_status_word();
+  const int IT = d.hidden / 16, OT = d.inter / 16;
+  if (d.expert_count > 0) {
+    make_trellis_map(&maps.gate, d.gate.trellis_dev, d.expert_count, IT, OT, d.k_expert, SG_KS);
+    make_trellis_map(&maps.up, d.up.trellis_dev, d.expert_count, IT, OT, d.k_expert, SG_KS);
+    make_trellis_map(&maps.down, d.down.trellis_dev, d.expert_count, OT, IT, d.k_expert, SG_KS);
+  }
+  if (has_shared) {
+    IJ_CHECK(d.sh_up.trellis_dev && d.sh_down.trellis_dev, "null shared-expert weights");
+    make_trellis_map(&maps.sgt, d.sh_gate.trellis_dev, 1, IT, OT, d.k_shared, SG_KS);
+    make_trellis_map(&maps.sup, d.sh_up.trellis_dev, 1, IT, OT, d.k_shared, SG_KS);
+    make_trellis_map(&maps.sdn, d.sh_down.trellis_dev, 1, OT, IT, d.k_shared, SG_KS);
+  }
 }
 
 Moe::~Moe() {
@@ -101,6 +113,7 @@ void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, c
   p.gate = stack(desc.gate); p.up = stack(desc.up); p.down = stack(desc.down);
   p.sgt = single(desc.sh_gate); p.sup = single(desc.sh_up); p.sdn = single(desc.sh_down);
   p.x = x; p.y = y;
+  pf_last_n = n;
   launch_pf_moe(p, status, st);
 }
 
@@ -142,13 +155,13 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
   const MoeSplits &s = splits(rows);
   switch (stage_no) {
     case 7: launch_moe_router(p, true, st); break;
-    case 8: launch_moe_prep(p, false, st); launch_moe_gateup(p, s, status, st); break;
-    case 9: launch_moe_mid(p, st); launch_moe_down(p, s, status, st); launch_moe_combine(p, false, st); break;
+    case 8: launch_moe_prep(p, false, st); launch_moe_gateup(p, maps, s, true, status, st); break;
+    case 9: launch_moe_mid(p, st); launch_moe_down(p, maps, s, status, st); launch_moe_combine(p, false, st); break;
     // single kernels of stages 8 and 9 (for per-kernel timing; each needs the state the kernels before it leave)
     case 80: launch_moe_prep(p, false, st); break;
-    case 81: launch_moe_gateup(p, s, status, st); break;
+    case 81: launch_moe_gateup(p, maps, s, true, status, st); break;
     case 90: launch_moe_mid(p, st); break;
-    case 91: launch_moe_down(p, s, status, st); break;
+    case 91: launch_moe_down(p, maps, s, status, st); break;
     case 92: launch_moe_combine(p, false, st); break;
     default: fail("bad MoE stage %d (7 router, 8 gate/up, 9 down; 80 81 90 91 92 their single kernels)", stage_no);
   }
@@ -158,11 +171,11 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
 void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
   const MoeParams p = params(x, rows, y);
   const MoeSplits &s = splits(rows);
-  launch_moe_router(p, false, st);  // the plan is built beside the operand prep
-  launch_moe_prep(p, true, st);
-  launch_moe_gateup(p, s, status, st);
+  launch_moe_router(p, true, st);  // the finisher also builds the plan: final before the gate/up kernel can start
+  launch_moe_prep(p, false, st);
+  launch_moe_gateup(p, maps, s, true, status, st);
   launch_moe_mid(p, st);
-  launch_moe_down(p, s, status, st);
+  launch_moe_down(p, maps, s, status, st);
   launch_moe_combine(p, false, st);
   last_rows = rows;
 }
@@ -175,11 +188,11 @@ void Moe::forward_ep(const float *x, int rows, int own_row0, int own_rows, float
   p.sh_row0 = own_row0;
   p.sh_rows = own_rows;
   const MoeSplits &s = splits(rows);
-  launch_moe_router(p, false, st);  // the plan is built beside the operand prep
-  launch_moe_prep(p, true, st);
-  launch_moe_gateup(p, s, status, st);
+  launch_moe_router(p, true, st);  // the finisher also builds the plan: final before the gate/up kernel can start
+  launch_moe_prep(p, false, st);
+  launch_moe_gateup(p, maps, s, true, status, st);
   launch_moe_mid(p, st);
-  launch_moe_down(p, s, status, st);
+  launch_moe_down(p, maps, s, status, st);
   launch_moe_combine(p, false, st);
   last_rows = rows;
 }
@@ -206,9 +219,9 @@ void Moe::forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all,
   p.sh_row0 = own_row0; p.sh_rows = own_rows; p.lg_row0 = own_row0;
   const MoeSplits &s = splits(rows);
   launch_moe_prep(p, true, st);
-  launch_moe_gateup(p, s, status, st);
+  launch_moe_gateup(p, maps, s, false, status, st);
   launch_moe_mid(p, st);
-  launch_moe_down(p, s, status, st);
+  launch_moe_down(p, maps, s, status, st);
   launch_moe_combine(p, false, st);
   last_rows = rows;
 }
@@ -233,9 +246,9 @@ void Moe::forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own,
   p.ep = c.dev; p.ep_rows = rows; p.ep_epoch = epoch;
   const MoeSplits &s = splits(all);
   launch_moe_prep(p, true, st);
-  launch_moe_gateup(p, s, status, st);
+  launch_moe_gateup(p, maps, s, false, status, st);
   launch_moe_mid(p, st);
-  launch_moe_down(p, s, status, st);
+  launch_moe_down(p, maps, s, status, st);
   launch_moe_combine(p, false, st);
   launch_ep_sum(c, rows, epoch, y_own, status, st);
   last_rows = all;
@@ -247,9 +260,9 @@ void Moe::forward_routed(const float *x, const uint32_t *route_in, int rows, flo
   p.has_shared = 0;
   const MoeSplits &s = splits(rows);
   launch_moe_prep(p, true, st);
-  launch_moe_gateup(p, s, status, st);
+  launch_moe_gateup(p, maps, s, false, status, st);
   launch_moe_mid(p, st);
-  launch_moe_down(p, s, status, st);
+  launch_moe_down(p, maps, s, status, st);
   launch_moe_combine(p, true, st);
   last_rows = rows;
 }
@@ -478,6 +491,9 @@ NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbyt
     else if (n == "shared_down") { *dev = o->sho; *nbytes = R * H * 4; }
     else if (n == "experts_gu_raw") { *dev = o->raw_gu; *nbytes = (size_t)o->splits((int)R).S_gu * R * k * 2 * I * 4; }
     else if (n == "plan") { *dev = o->plan; *nbytes = PlanView::ints((int)(R * k)) * 4; }
+    else if (n == "prefill_route") { *dev = o->pf.route; *nbytes = (size_t)o->pf_last_n * 2 * k * 4; }
+    else if (n == "prefill_counts") { *dev = o->pf.cnt; *nbytes = E * 4; }
+    else if (n == "prefill_logits") { *dev = o->pf.logits; *nbytes = (size_t)o->pf_last_n * (E + 1) * 4; }
     else fail("unknown MoE buffer '%s'", name);
   });
 }

@@ -21,15 +21,14 @@ using namespace ijah;
 
 namespace {
 
-constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: rows <= 16 of any trunk / expert shape, see the header
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB; the header says what fits
 constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-static __device__ int g_static_status;  // bounded-wait status word of these launches (zero at load)
 
 struct DeviceSlots {
   void *scratch = nullptr;
-  int *status = nullptr;
+  int *status = nullptr;  // the library's bounded-wait status word (also part of the image: ne_device_wait_status reads it)
 };
 DeviceSlots g_slots[kMaxDevices];
 
@@ -41,10 +40,9 @@ DeviceSlots &slots_of_current_device() {
   IJ_CHECK(d >= 0 && d < kMaxDevices, "device ordinal %d not supported by the static scratch table", d);
   DeviceSlots &s = g_slots[d];
   if (s.scratch == nullptr) {
-    void *p = nullptr, *q = nullptr;
+    void *p = nullptr;
     IJ_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-    IJ_CUDA(cudaGetSymbolAddress(&q, g_static_status));
-    s.status = static_cast<int *>(q);
+    s.status = device_status_word();
     s.scratch = p;
   }
   return s;

@@ -2,6 +2,7 @@
 // and a per-device growable scratch arena. The error convention is the reference's (include/engine.h:3-5 of the
 // reference: int functions return 0 / -1, pointer functions NULL, message in ne_last_error(), per thread).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -57,5 +58,11 @@ void *device_scratch(size_t bytes);
 int *device_status_word();   // zero-initialised int the kernels report bounded-wait failures into
 void check_status_word();    // throws if a kernel reported a failure (reads the word after a stream sync)
 int sm_count();
+
+// Tensor map over an EXL3 trellis for the stream kernels' tiled TMA loads: the trellis of E matrices of IT x OT tiles of
+// 32K bytes each is described as a 3-D array of 8-byte elements, x = position along a row of tiles (OT * 4K elements),
+// y = k-tile (stride OT * 32K bytes), z = matrix (stride IT * OT * 32K bytes); box = (8 tiles, ks k-tiles, 1). Host-side
+// arithmetic only (no allocation, no device work). `base` must be 16-byte aligned.
+void make_trellis_map(CUtensorMap *out, const void *base, int E, int IT, int OT, int K, int ks);
 
 }  // namespace ijah

@@ -46,27 +46,47 @@ static __constant__ uint32_t kPow2[32] = {
     1u << 11, 1u << 12, 1u << 13, 1u << 14, 1u << 15, 1u << 16, 1u << 17, 1u << 18, 1u << 19, 1u << 20, 1u << 21,
     1u << 22, 1u << 23, 1u << 24, 1u << 25, 1u << 26, 1u << 27, 1u << 28, 1u << 29, 1u << 30, 1u << 31};
 
-// 15-bit field starting P bits below the MSB of the 96-bit value (w0:w1:w2), P a compile-time constant:
-// bring the field to the top of a register (multiply, or one funnel shift when it straddles two words), then >> 17.
-template <int P>
-__device__ __forceinline__ uint32_t field15(uint32_t w0, uint32_t w1, uint32_t w2) {
+// The two constants of the codebook function, read from constant memory into registers once per kernel (McgConst::load).
+// Written as immediates, (r & A) ^ X compiles to TWO logic instructions per weight (an instruction encodes one
+// immediate); as register operands of one three-input lop3 it is one.
+static __constant__ uint32_t kMcgMaskXor[2] = {0x8FFF8FFFu, 0x3B603B60u};
+struct McgConst {
+  uint32_t mask, flip;
+  static __device__ __forceinline__ McgConst load() { return McgConst{kMcgMaskXor[0], kMcgMaskXor[1]}; }
+};
+
+// 15-bit field whose first bit is `off` bits below the MSB of `w` (off + 15 <= 32): shift it to the top with a
+// multiply (FMA pipe), then >> 17.
+template <int off>
+__device__ __forceinline__ uint32_t top15(uint32_t w) {
+  static_assert(off >= 0 && off + 15 <= 32, "field must lie inside the word");
+  if constexpr (off == 0) return w >> 17;
+  else return (w * kPow2[off]) >> 17;
+}
+
+// 15-bit field starting P bits below the MSB of the 96-bit value (w0:w1:w2), P a compile-time constant. A field that
+// straddles two words is read from `mid` = bits [16, 48) of the value when MID is set (one byte permute serves every
+// straddling field of the tile), else through a funnel shift of its own.
+template <int P, bool MID>
+__device__ __forceinline__ uint32_t field15(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t mid) {
   constexpr int wi = P / 32, off = P % 32;
-  const uint32_t hi = wi == 0 ? w0 : (wi == 1 ? w1 : w2);
   if constexpr (off + 15 <= 32) {
-    if constexpr (off == 0) return hi >> 17;
-    return (hi * kPow2[off]) >> 17;
+    return top15<off>(wi == 0 ? w0 : (wi == 1 ? w1 : w2));
+  } else if constexpr (MID && wi == 0) {
+    return top15<P - 16>(mid);
   } else {
-    const uint32_t lo = wi == 0 ? w1 : w2;
+    const uint32_t hi = wi == 0 ? w0 : w1, lo = wi == 0 ? w1 : w2;
     return __funnelshift_l(lo, hi, off) >> 17;
   }
 }
 
 // two codewords -> half2(value(ca), value(cb)); value = fp16(lo16(r)) + fp16(hi16(r)), r = ((cw * M) & A) ^ X.
-// The two half adds are scalar (the compiler selects the halves with operand modifiers), one pack joins them.
-__device__ __forceinline__ uint32_t mcg_pair(uint32_t ca, uint32_t cb) {
+// One multiply and one three-input logic op per codeword, two half adds (the halves are selected by operand
+// modifiers of the add), one pack.
+__device__ __forceinline__ uint32_t mcg_pair(uint32_t ca, uint32_t cb, const McgConst &c) {
   uint32_t ra = ca * 0xCBAC1FEDu, rb = cb * 0xCBAC1FEDu;
-  ra = (ra & 0x8FFF8FFFu) ^ 0x3B603B60u;
-  rb = (rb & 0x8FFF8FFFu) ^ 0x3B603B60u;
+  asm("lop3.b32 %0, %0, %1, %2, 0x6A;" : "+r"(ra) : "r"(c.mask), "r"(c.flip));  // (a & b) ^ c
+  asm("lop3.b32 %0, %0, %1, %2, 0x6A;" : "+r"(rb) : "r"(c.mask), "r"(c.flip));
   const __half2 a = *reinterpret_cast<const __half2 *>(&ra), b = *reinterpret_cast<const __half2 *>(&rb);
   const __half2 r = __halves2half2(__hadd(__low2half(a), __high2half(a)), __hadd(__low2half(b), __high2half(b)));
   return *reinterpret_cast<const uint32_t *>(&r);
@@ -75,19 +95,25 @@ __device__ __forceinline__ uint32_t mcg_pair(uint32_t ca, uint32_t cb) {
 // The lane's 8 weights from its three window words: b[0] = (slot 0, slot 1), b[1] = (2, 3): column c;
 // b[2] = (4, 5), b[3] = (6, 7): column c + 8. `a` = Codec<K>::Lane::a (ignored for K = 4, 8).
 template <int K>
-__device__ __forceinline__ void dec8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t a, uint32_t (&b)[4]) {
+__device__ __forceinline__ void dec8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t a, const McgConst &c, uint32_t (&b)[4]) {
   if constexpr (Codec<K>::UNIFORM) {
     constexpr int A = Codec<K>::A0;
-    b[0] = mcg_pair(field15<A + 0 * K>(w0, w1, w2), field15<A + 1 * K>(w0, w1, w2));
-    b[1] = mcg_pair(field15<A + 2 * K>(w0, w1, w2), field15<A + 3 * K>(w0, w1, w2));
-    b[2] = mcg_pair(field15<A + 4 * K>(w0, w1, w2), field15<A + 5 * K>(w0, w1, w2));
-    b[3] = mcg_pair(field15<A + 6 * K>(w0, w1, w2), field15<A + 7 * K>(w0, w1, w2));
+    // K = 4: three fields straddle w0 | w1 and share the middle word; K = 8: one field per boundary, funnel shifts
+    constexpr bool MID = K == 4;
+    const uint32_t mid = MID ? __byte_perm(w0, w1, 0x1076) : 0u;  // (w0 << 16) | (w1 >> 16)
+    b[0] = mcg_pair(field15<A + 0 * K, MID>(w0, w1, w2, mid), field15<A + 1 * K, MID>(w0, w1, w2, mid), c);
+    b[1] = mcg_pair(field15<A + 2 * K, MID>(w0, w1, w2, mid), field15<A + 3 * K, MID>(w0, w1, w2, mid), c);
+    b[2] = mcg_pair(field15<A + 4 * K, MID>(w0, w1, w2, mid), field15<A + 5 * K, MID>(w0, w1, w2, mid), c);
+    b[3] = mcg_pair(field15<A + 6 * K, MID>(w0, w1, w2, mid), field15<A + 7 * K, MID>(w0, w1, w2, mid), c);
   } else {
+    // K = 5, 6, 7: align the lane's window to bit 0 of x (two funnel shifts), then every field position is a constant;
+    // the three fields that straddle x | y are read from the middle word
     const uint32_t x = __funnelshift_l(w1, w0, a), y = __funnelshift_l(w2, w1, a);
-    b[0] = mcg_pair(field15<0 * K>(x, y, 0u), field15<1 * K>(x, y, 0u));
-    b[1] = mcg_pair(field15<2 * K>(x, y, 0u), field15<3 * K>(x, y, 0u));
-    b[2] = mcg_pair(field15<4 * K>(x, y, 0u), field15<5 * K>(x, y, 0u));
-    b[3] = mcg_pair(field15<6 * K>(x, y, 0u), field15<7 * K>(x, y, 0u));
+    const uint32_t mid = __byte_perm(x, y, 0x1076);
+    b[0] = mcg_pair(field15<0 * K, true>(x, y, 0u, mid), field15<1 * K, true>(x, y, 0u, mid), c);
+    b[1] = mcg_pair(field15<2 * K, true>(x, y, 0u, mid), field15<3 * K, true>(x, y, 0u, mid), c);
+    b[2] = mcg_pair(field15<4 * K, true>(x, y, 0u, mid), field15<5 * K, true>(x, y, 0u, mid), c);
+    b[3] = mcg_pair(field15<6 * K, true>(x, y, 0u, mid), field15<7 * K, true>(x, y, 0u, mid), c);
   }
 }
 

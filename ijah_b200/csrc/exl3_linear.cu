@@ -14,16 +14,18 @@ StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm) {
   l.arows = std::max(arows, 1);
   const size_t budget = (size_t)(228 / ctas_per_sm - 2) * 1024;
   const size_t base = l.ring_off() + (size_t)l.lda * 2;
-  l.aslots = base + SG_MAX_ASLOTS * l.slot_bytes() + 6 * (size_t)l.stage_bytes <= budget ? SG_MAX_ASLOTS : 2;
+  const size_t want_stages = SG_KS >= 16 ? 3 : 6;
+  // at least three A slots: the producer issues the rows of unit u + 2 while the consumers may still be on unit u
+  l.aslots = base + SG_MAX_ASLOTS * l.slot_bytes() + want_stages * (size_t)l.stage_bytes <= budget ? SG_MAX_ASLOTS : 3;
   const size_t fixed = base + l.aslots * l.slot_bytes();
-  IJ_CHECK(fixed + 3 * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory", arows, kcmax);
+  IJ_CHECK(fixed + (SG_KS >= 16 ? 2 : 3) * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory", arows, kcmax);
   l.stages = (int)std::min<size_t>(SG_MAX_STAGES, (budget - fixed) / l.stage_bytes);
   return l;
 }
 
 int kc_cap(int arows) {
-  // two A slots may take about 48 KB of the ~110 KB a CTA gets
-  const int cap = ((24 * 1024 / std::max(arows, 1)) - 16) / 32 / SG_KS * SG_KS;
+  // three A slots may take about 48 KB of the ~110 KB a CTA gets (with two CTAs per SM; less with more)
+  const int cap = ((16 * 1024 * 2 / SG_CTAS / std::max(arows, 1)) - 16) / 32 / SG_KS * SG_KS;
   return std::max(SG_KS, std::min(cap, 256));
 }
 
@@ -48,9 +50,9 @@ LinearPlan plan_linear(int in, int out, int K, int rows) {
   p.IT = in / 16; p.OT = out / 16; p.NG = (p.OT + SG_WARPS - 1) / SG_WARPS;
   p.hi = had_size(in); p.ho = had_size(out);
   p.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
-  p.grid = 2 * sm_count();
+  p.grid = SG_CTAS * sm_count();
   choose_split(p.IT, p.NG, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
-  p.lay = make_layout(K, p.kc, rows, 2);
+  p.lay = make_layout(K, p.kc, rows, SG_CTAS);
   p.grid = std::min(p.grid, p.NG * p.S);
   return p;
 }
@@ -188,9 +190,9 @@ MultiLinearPlan plan_linear_multi(int n, int in, const int *out, const int *K, i
     kmax = std::max(kmax, K[m]);
   }
   p.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
-  p.grid = 2 * sm_count();
+  p.grid = SG_CTAS * sm_count();
   choose_split(p.IT, ng, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
-  p.lay = make_layout(kmax, p.kc, rows, 2);
+  p.lay = make_layout(kmax, p.kc, rows, SG_CTAS);
   p.grid = std::min(p.grid, ng * p.S);
   return p;
 }
@@ -207,7 +209,8 @@ void launch_linear_multi(const MultiLinearPlan &p, const MultiLinearArgs &a, con
     cur += (p.raw_floats(m) * 4 + 255) & ~(size_t)255;
     __half *xh = (__half *)cur;
     cur += ((size_t)p.rows * p.in * 2 + 255) & ~(size_t)255;
-    pr.trellis[m] = (const char *)a.trellis[m]; pr.xh[m] = xh; pr.raw[m] = raw;
+    make_trellis_map(&pr.maps[m], a.trellis[m], 1, p.IT, p.OT[m], p.K[m], SG_KS);
+    pr.xh[m] = xh; pr.raw[m] = raw;
     pr.out[m] = p.out[m]; pr.K[m] = p.K[m]; pr.OT[m] = p.OT[m]; pr.NG[m] = p.NG[m];
     pr.ubase[m + 1] = pr.ubase[m] + p.NG[m] * p.S;
     q.suh[m] = (const __half *)a.suh[m]; q.svh[m] = (const __half *)a.svh[m]; q.xh[m] = xh; q.raw[m] = raw; q.y[m] = a.y[m];
@@ -226,7 +229,7 @@ void launch_linear(const LinearPlan &p, const void *trellis, const void *suh, co
   __half *xh = (__half *)((char *)scratch + ((p.raw_floats() * 4 + 255) & ~(size_t)255));
   launch_prep_rows(x, (const __half *)suh, xh, p.rows, p.in, st);
   LinearProblem pr;
-  pr.trellis = (const char *)trellis;
+  make_trellis_map(&pr.map, trellis, 1, p.IT, p.OT, p.K, SG_KS);
   pr.xh = xh;
   pr.raw = raw;
   pr.in = p.in; pr.out = p.out; pr.K = p.K; pr.rows = p.rows;
@@ -248,7 +251,7 @@ __global__ void dequant_kernel(const uint32_t *__restrict__ tr, int IT, int OT, 
   const char *t = reinterpret_cast<const char *>(tr) + tile * Codec<K>::TILE_BYTES;
   uint32_t b[4];
   dec8<K>(*reinterpret_cast<const uint32_t *>(t + L.o0), *reinterpret_cast<const uint32_t *>(t + L.o1),
-          *reinterpret_cast<const uint32_t *>(t + L.o2), L.a, b);
+          *reinterpret_cast<const uint32_t *>(t + L.o2), L.a, McgConst::load(), b);
   const int tk = (int)(tile / OT), tn = (int)(tile % OT), q = lane & 3, c = lane >> 2;
   const int out = OT * 16;
   const __half *h = reinterpret_cast<const __half *>(b);

@@ -25,15 +25,16 @@ struct LinearPlan {
 LinearPlan plan_linear(int in, int out, int K, int rows);
 
 struct LinearProblem {
-  static constexpr bool kUnitsFinalAtLaunch = true;  // the unit list is arithmetic
+  __device__ bool units_final() const { return true; }  // the unit list is arithmetic
   struct Unit : UnitBase {
     int g, s, k0;
   };
-  const char *trellis;
+  alignas(64) CUtensorMap map;  // over the trellis (make_trellis_map)
   const __half *xh;  // [rows][in] prepared operand
   float *raw;
   int in, out, K, rows, IT, OT, NG, S, kc;
 
+  __device__ const CUtensorMap *tmap(int) const { return &map; }
   __device__ int num_units() const { return NG * S; }
   __device__ Unit unit(int u) const {
     Unit un;
@@ -44,15 +45,13 @@ struct LinearProblem {
     un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
     un.K = K;
     un.nrows = rows;
-    un.kstride = (uint32_t)OT * 32u * (uint32_t)K;
-    un.w = trellis + ((size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * (32u * K);
+    un.map = 0; un.x = un.g * SG_WARPS * 4 * K; un.y = un.k0; un.z = 0;
     return un;
   }
   __device__ int row_index(const Unit &, int i) const { return i; }
   __device__ const __half *a_row(const Unit &un, int i) const { return xh + (size_t)i * in + un.k0 * 16; }
-  __device__ void store(const Unit &un, int row, int col, float v) const {
-    raw[((size_t)un.s * rows + row) * out + un.g * 128 + col] = v;
-  }
+  __device__ float *out_base(const Unit &un) const { return raw + (size_t)un.s * rows * out + un.g * 128; }
+  __device__ int out_row_off(const Unit &, int row) const { return row * out; }
 };
 
 // Several Linears that read the same activation rows (the q, k, v projections of a layer; reference: t6::record_multi,
@@ -73,16 +72,17 @@ struct MultiLinearPlan {
 MultiLinearPlan plan_linear_multi(int n, int in, const int *out, const int *K, int rows);
 
 struct MultiLinearProblem {
-  static constexpr bool kUnitsFinalAtLaunch = true;  // the unit list is arithmetic
+  __device__ bool units_final() const { return true; }  // the unit list is arithmetic
   struct Unit : UnitBase {
     int g, s, k0, m;
   };
-  const char *trellis[ML_MAX];
+  alignas(64) CUtensorMap maps[ML_MAX];  // one per trellis
   const __half *xh[ML_MAX];  // [rows][in] prepared operand per matrix (the scale vectors differ)
   float *raw[ML_MAX];
   int out[ML_MAX], K[ML_MAX], OT[ML_MAX], NG[ML_MAX], ubase[ML_MAX + 1];  // ubase[m]: first unit of matrix m
   int n, in, rows, IT, S, kc;
 
+  __device__ const CUtensorMap *tmap(int i) const { return &maps[i]; }
   __device__ int num_units() const { return ubase[n]; }
   __device__ Unit unit(int u) const {
     Unit un;
@@ -97,15 +97,13 @@ struct MultiLinearProblem {
     un.ntiles = min(SG_WARPS, OT[m] - un.g * SG_WARPS);
     un.K = K[m];
     un.nrows = rows;
-    un.kstride = (uint32_t)OT[m] * 32u * (uint32_t)K[m];
-    un.w = trellis[m] + ((size_t)un.k0 * OT[m] + (size_t)un.g * SG_WARPS) * (32u * K[m]);
+    un.map = m; un.x = un.g * SG_WARPS * 4 * K[m]; un.y = un.k0; un.z = 0;
     return un;
   }
   __device__ int row_index(const Unit &, int i) const { return i; }
   __device__ const __half *a_row(const Unit &un, int i) const { return xh[un.m] + (size_t)i * in + un.k0 * 16; }
-  __device__ void store(const Unit &un, int row, int col, float v) const {
-    raw[un.m][((size_t)un.s * rows + row) * out[un.m] + un.g * 128 + col] = v;
-  }
+  __device__ float *out_base(const Unit &un) const { return raw[un.m] + (size_t)un.s * rows * out[un.m] + un.g * 128; }
+  __device__ int out_row_off(const Unit &un, int row) const { return row * out[un.m]; }
 };
 
 struct MultiLinearArgs {  // per matrix: device pointers of the caller

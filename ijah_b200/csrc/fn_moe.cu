@@ -300,8 +300,8 @@ __global__ void __launch_bounds__(RT_THREADS) moe_router_kernel(const MoeParams 
   const uint4 *wsrc = reinterpret_cast<const uint4 *>(wr != nullptr ? wr : p.router);
 #pragma unroll
   for (int j = 0; j < 16; j++) wreg[j] = __ldg(wsrc + min(j * 32 + lane, H / 8 - 1));
-  pdl_wait();  // the router weights above are static; the activations may be the preceding kernel's output
   pdl_launch();
+  pdl_wait();  // the router weights above are static; the activations may be the preceding kernel's output
   for (int r0 = 0; r0 < p.rows; r0 += RT_RC) {
     const int nr = min(RT_RC, p.rows - r0);
     __syncthreads();
@@ -425,8 +425,8 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * 4 + warp, job = blockIdx.y;
   const int I = p.I, k = p.topk;
+  pdl_launch();  // the down kernel's CTAs may take the places the gate/up kernel's CTAs leave and stream their first weights
   pdl_wait();
-  pdl_launch();
   if (chunk * 128 >= I) return;
   const float hs = 0.08838834764831845f;
   const bool shared = job >= p.P;
@@ -478,12 +478,17 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
 // =============================================================================================== gate / up
 // Unit order: for each distinct expert u: proj (gate, up) x k-split x column group; then the shared expert's.
 struct MoeGateUpProblem {
-  static constexpr bool kUnitsFinalAtLaunch = false;  // the plan is written by the router kernel just before
+  // The plan is final at launch when the router kernel wrote it (the operand prep in between only lets this launch go
+  // once the router has completed); when the prep kernel itself builds the plan (routes from outside) it is not.
+  __device__ bool units_final() const { return plan_final != 0; }
   struct Unit : UnitBase {
     int s, k0, g, proj, shared, e, first;
   };
+  alignas(64) CUtensorMap maps[4];  // gate, up, shared gate, shared up
   MoeParams p;
-  int IT, OT, NG, S, kc;
+  int IT, OT, NG, S, kc, plan_final;
+
+  __device__ const CUtensorMap *tmap(int i) const { return &maps[i]; }
 
   __device__ int shared_groups() const { return p.has_shared ? (p.sh_rows + PLAN_ROWS - 1) / PLAN_ROWS : 0; }
   __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + shared_groups()) * 2 * S * NG; }
@@ -498,17 +503,14 @@ struct MoeGateUpProblem {
     un.kc = min(kc, IT - un.k0);
     un.ntiles = min(SG_WARPS, OT - un.g * SG_WARPS);
     un.shared = q >= *pv.nu();
-    const Exl3Stack *w;
     if (un.shared) {  // only the rows whose shared expert runs here, PLAN_ROWS at a time
       un.e = 0; un.first = (q - *pv.nu()) * PLAN_ROWS; un.nrows = min(PLAN_ROWS, p.sh_rows - un.first); un.K = p.Ks;
-      w = un.proj ? &p.sup : &p.sgt;
+      un.map = 2 + un.proj;
     } else {
       un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx;
-      w = un.proj ? &p.up : &p.gate;
+      un.map = un.proj;
     }
-    const size_t tile = 32u * un.K;
-    un.kstride = (uint32_t)(OT * tile);
-    un.w = w->trellis + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
+    un.x = un.g * SG_WARPS * 4 * un.K; un.y = un.k0; un.z = un.e;
     return un;
   }
   // row index = the (row, slot) pair for routed units, the activation row for the shared expert
@@ -518,22 +520,24 @@ struct MoeGateUpProblem {
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sgu : p.xh_gu) + ((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16;
   }
-  __device__ void store(const Unit &un, int idx, int col, float v) const {
-    float *dst = un.shared ? p.raw_sgu + (((size_t)un.s * p.rows + idx) * 2 + un.proj) * p.I
-                           : p.raw_gu + (((size_t)un.s * p.P + idx) * 2 + un.proj) * p.I;
-    dst[un.g * 128 + col] = v;
+  __device__ float *out_base(const Unit &un) const {
+    return (un.shared ? p.raw_sgu + ((size_t)un.s * p.rows * 2 + un.proj) * p.I : p.raw_gu + ((size_t)un.s * p.P * 2 + un.proj) * p.I) + un.g * 128;
   }
+  __device__ int out_row_off(const Unit &, int idx) const { return idx * 2 * p.I; }
 };
 
 // =============================================================================================== down
 struct MoeDownProblem {
   // the plan was complete before the gate/up kernel started, i.e. before the predecessor (mid) could release this launch
-  static constexpr bool kUnitsFinalAtLaunch = true;
+  __device__ bool units_final() const { return true; }
   struct Unit : UnitBase {
     int s, k0, g, shared, e, first;
   };
+  alignas(64) CUtensorMap maps[2];  // down, shared down
   MoeParams p;
   int IT, OT, NG, S, kc;  // IT = I/16, OT = H/16
+
+  __device__ const CUtensorMap *tmap(int i) const { return &maps[i]; }
 
   __device__ int shared_groups() const { return p.has_shared ? (p.sh_rows + PLAN_ROWS - 1) / PLAN_ROWS : 0; }
   __device__ int num_units() const { return (*PlanView{p.plan, p.P}.nu() + shared_groups()) * S * NG; }
@@ -549,9 +553,8 @@ struct MoeDownProblem {
     un.shared = q >= *pv.nu();
     if (un.shared) { un.e = 0; un.first = (q - *pv.nu()) * PLAN_ROWS; un.nrows = min(PLAN_ROWS, p.sh_rows - un.first); un.K = p.Ks; }
     else { un.e = pv.expert()[q] - p.e0; un.first = pv.first()[q]; un.nrows = pv.nrows()[q]; un.K = p.Kx; }
-    const size_t tile = 32u * un.K;
-    un.kstride = (uint32_t)(OT * tile);
-    un.w = (un.shared ? p.sdn.trellis : p.down.trellis) + ((size_t)un.e * IT * OT + (size_t)un.k0 * OT + (size_t)un.g * SG_WARPS) * tile;
+    un.map = un.shared ? 1 : 0;
+    un.x = un.g * SG_WARPS * 4 * un.K; un.y = un.k0; un.z = un.e;
     return un;
   }
   __device__ int row_index(const Unit &un, int i) const {
@@ -560,10 +563,10 @@ struct MoeDownProblem {
   __device__ const __half *a_row(const Unit &un, int idx) const {
     return (un.shared ? p.xh_sd : p.xh_d) + (size_t)idx * p.I + un.k0 * 16;
   }
-  __device__ void store(const Unit &un, int idx, int col, float v) const {
-    float *dst = un.shared ? p.raw_sd + ((size_t)un.s * p.rows + idx) * p.H : p.raw_d + ((size_t)un.s * p.P + idx) * p.H;
-    dst[un.g * 128 + col] = v;
+  __device__ float *out_base(const Unit &un) const {
+    return (un.shared ? p.raw_sd + (size_t)un.s * p.rows * p.H : p.raw_d + (size_t)un.s * p.P * p.H) + un.g * 128;
   }
+  __device__ int out_row_off(const Unit &, int idx) const { return idx * p.H; }
 };
 
 // =============================================================================================== combine
@@ -578,8 +581,8 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int blk = blockIdx.x, r = blockIdx.y;
   const int H = p.H, k = p.topk;
-  pdl_wait();
   pdl_launch();
+  pdl_wait();
   const float hs = 0.08838834764831845f;
   if (warp < k) {
     // the partial sums' addresses do not depend on the routing: their loads go out together with the route entry
@@ -660,7 +663,7 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   IJ_CHECK(Kx >= 4 && Kx <= 8 && (!has_shared || (Ks >= 4 && Ks <= 8)), "bits per weight outside 4..8");
   MoeSplits s{};
   s.MT = 1;  // every unit has at most PLAN_ROWS = 8 rows (the plan cuts experts with more rows into several entries)
-  s.grid = 2 * sm_count();
+  s.grid = SG_CTAS * sm_count();
   const int urows = std::min(rows, PLAN_ROWS);
   // expected number of distinct experts under uniform routing; any actual count works, this only tunes the k-split
   const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows));
@@ -673,8 +676,8 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   choose_split(I / 16, (int)std::lround((nu + nsh) * (H / 128)), kcap, s.grid, rpu, &s.S_d, &s.kc_d);
   if (s.S_d > 16) { s.kc_d = (I / 16 + 15) / 16; s.kc_d = (s.kc_d + SG_KS - 1) / SG_KS * SG_KS; s.S_d = (I / 16 + s.kc_d - 1) / s.kc_d; }
   const int kmax = std::max(Kx, has_shared ? Ks : 0);
-  s.lay_gu = make_layout(kmax, s.kc_gu, urows, 2);
-  s.lay_d = make_layout(kmax, s.kc_d, urows, 2);
+  s.lay_gu = make_layout(kmax, s.kc_gu, urows, SG_CTAS);
+  s.lay_d = make_layout(kmax, s.kc_d, urows, SG_CTAS);
   return s;
 }
 
@@ -689,16 +692,19 @@ void launch_moe_mid(const MoeParams &p, cudaStream_t st) {
   launch_pdl(moe_mid_kernel, grid, dim3(128), 0, st, p);
 }
 
-void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st) {
+void launch_moe_gateup(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s, bool plan_final, int *status, cudaStream_t st) {
   MoeGateUpProblem pr;
+  pr.maps[0] = maps.gate; pr.maps[1] = maps.up; pr.maps[2] = maps.sgt; pr.maps[3] = maps.sup;
   pr.p = p;
+  pr.plan_final = plan_final ? 1 : 0;
   pr.IT = p.H / 16; pr.OT = p.I / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
   pr.S = s.S_gu; pr.kc = s.kc_gu;
   launch_stream(pr, s.MT, s.lay_gu, s.grid, status, st);
 }
 
-void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st) {
+void launch_moe_down(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s, int *status, cudaStream_t st) {
   MoeDownProblem pr;
+  pr.maps[0] = maps.down; pr.maps[1] = maps.sdn;
   pr.p = p;
   pr.IT = p.I / 16; pr.OT = p.H / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
   pr.S = s.S_d; pr.kc = s.kc_d;

@@ -77,6 +77,11 @@ struct PlanView {
   static size_t ints(int P) { return 4 + 4 * (size_t)P; }
 };
 
+// tensor maps over the six trellis stacks of a block (make_trellis_map), built once per MoE object
+struct MoeMaps {
+  alignas(64) CUtensorMap gate, up, down, sgt, sup, sdn;
+};
+
 struct MoeSplits {
   int S_gu, kc_gu, S_d, kc_d, MT;
   StreamLayout lay_gu, lay_d;
@@ -88,8 +93,10 @@ void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st);
 // gate / up operands (after routing); build_plan: also the expert plan from the route buffer (when the router did not)
 void launch_moe_prep(const MoeParams &p, bool build_plan, cudaStream_t st);
 void launch_moe_mid(const MoeParams &p, cudaStream_t st);    // SwiGLU + down operand (after gate / up)
-void launch_moe_gateup(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
-void launch_moe_down(const MoeParams &p, const MoeSplits &s, int *status, cudaStream_t st);
+// plan_final: the plan was written by a kernel that completed before this launch can start (the router, with the prep kernel
+// in between), so the first weights are streamed before the wait on the predecessor
+void launch_moe_gateup(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s, bool plan_final, int *status, cudaStream_t st);
+void launch_moe_down(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s, int *status, cudaStream_t st);
 void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st);
 
 }  // namespace ijah

@@ -30,7 +30,7 @@ static void launch_stream_mt(const P &prob, const StreamLayout &lay, int grid, i
 
 template <class P>
 void launch_stream(const P &prob, int MT, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
-  IJ_CHECK(lay.stages >= 3 && lay.stages <= 16, "bad ring depth %d", lay.stages);
+  IJ_CHECK(lay.stages >= 2 && lay.stages <= 16, "bad ring depth %d", lay.stages);
   switch (MT) {
     case 1: launch_stream_mt<P, 1>(prob, lay, grid, status, st); break;
     case 2: launch_stream_mt<P, 2>(prob, lay, grid, status, st); break;

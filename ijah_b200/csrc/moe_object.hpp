@@ -29,9 +29,10 @@ struct Moe {
   float *h_out = nullptr;
   int HC = 0;
   std::map<int, MoeSplits> split_cache;
+  MoeMaps maps{};  // tensor maps over the trellis stacks
   // prefill scratch, (re)allocated when a call brings more tokens than any before it
   PfParams pf{};
-  int pf_tokens = 0;
+  int pf_tokens = 0, pf_last_n = 0;
   std::vector<void *> pf_owned;
   void prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st);
 

@@ -48,13 +48,14 @@ struct PgSmem {
 template <int K>
 __device__ __forceinline__ void pg_decode_stage(const unsigned char *ring_stage, unsigned char *a_stage, int dw, int lane) {
   const typename Codec<K>::Lane L = Codec<K>::lane(lane);
+  const McgConst mc = McgConst::load();
   const int ng = dw >> 3, t = dw & 7, q = lane & 3, c = lane >> 2;
 #pragma unroll
   for (int ks = 0; ks < PG_KS; ks++) {
     const unsigned char *tile = ring_stage + (size_t)(ks * 16 + dw) * Codec<K>::TILE_BYTES;
     uint32_t b[4];
     dec8<K>(*reinterpret_cast<const uint32_t *>(tile + L.o0), *reinterpret_cast<const uint32_t *>(tile + L.o1),
-            *reinterpret_cast<const uint32_t *>(tile + L.o2), L.a, b);
+            *reinterpret_cast<const uint32_t *>(tile + L.o2), L.a, mc, b);
     // lane (q, c): b[0] = k (2q, 2q+1) of column c, b[1] = k (2q+8, 2q+9) of column c, b[2], b[3] the same of column c + 8
     unsigned char *dst = a_stage + (size_t)(ks * 2 + ng) * 4096 + (2 * t) * 128 + c * 16 + q * 4;
     *reinterpret_cast<uint32_t *>(dst) = b[0];

@@ -50,10 +50,14 @@ NE_API int ne_exl3_linear_prefill(const ne_exl3_weight *w, const float *x_dev, i
  * the same kernels on a scratch area compiled into the library (a 256-byte aligned __device__ array of
  * ne_exl3_linear_static_capacity() = 8 MiB bytes, held by every GPU that loads the library until the process exits)
  * and calls no cudaMalloc / cudaFree nor any allocating routine. Same arguments and results as ne_exl3_linear. A
- * call whose scratch need (k-split partials + fp16 operand: about rows * (4 * S * out + 2 * in) bytes, S <= 16)
- * exceeds the capacity is refused with -1 and a message naming both sizes. The first call on a device resolves the
- * array's device address; make it before any stream capture begins. All calls share the one area: it keeps the last
- * call's contents (nothing needs to start at zero), and calls whose GPU work overlaps race on it. */
+ * call whose scratch need exceeds the capacity is refused with -1 and a message naming both sizes. The need is
+ * rows * (4 * S * out + 2 * in) bytes plus padding, S = the number of k-splits the launch plan picks to fill the GPU
+ * (1 for matrices with many output columns, up to in / 128 for small ones: 4096 x 4096 at 64 rows takes S = 32 and does
+ * not fit, every trunk and expert shape of the benchmark configurations fits at <= 32 rows). The first call on a device
+ * resolves the array's device address; make it before any stream capture begins. All calls share the one area: it keeps
+ * the last call's contents (nothing needs to start at zero), and calls whose GPU work overlaps race on it. A bounded
+ * device-side wait that gives up is reported in the same status word as for every other entry point
+ * (ne_device_wait_status, which allocates nothing either). */
 NE_API int ne_exl3_linear_static(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API uint64_t ne_exl3_linear_static_capacity(void);
 
@@ -134,7 +138,9 @@ NE_API int ne_moe_forward_ep_fused(ne_moe *m, ne_ep *e, const float *x_own_dev, 
  * computed, the shared expert runs for the caller's own tokens only. y_part[n_all][hidden] is this rank's summand. */
 NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream);
 /* Device pointer and size of a named intermediate of the last run: "logits" "route" "shared_gu" "shared_down"
- * "experts_gu_raw" (per k-split partial products [S][rows*top_k][2][inter]) "plan". */
+ * "experts_gu_raw" (per k-split partial products [S][rows*top_k][2][inter]) "plan"; of the last ne_moe_prefill:
+ * "prefill_route" [n][2*top_k] (ids, then f32 weights), "prefill_counts" [experts] slots per expert,
+ * "prefill_logits" [n][experts + 1]. */
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes);
 /* Sum of k-split partials: experts_gu[rows][top_k][2][inter] f32, the raw inner products before the output Hadamard
  * (the reference's "experts_gu" buffer). */

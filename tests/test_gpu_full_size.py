@@ -1,0 +1,200 @@
+"""Parity at the sizes the benchmark configurations state (512 experts, top-10, hidden 2048, intermediate 768, K5 routed +
+K6 shared; trunk projections at K6 / K8; 4096-token prefill with Zipf-skewed routing), through the C ABI.
+
+Weights are generated on the device (ijah_b200.synth) and copied to the host once for the CPU oracle, which decodes
+only the experts a case touches. Tolerances: router ids exact; against the device-arithmetic emulation 2e-4 max-abs
+relative (linears: 5e-5 relative L2, the reference's own kernel tolerance, tests/trunk6/check_kernels.py:79-105);
+against the float64 operator reference (tools/opref.py semantics) 2e-3.
+"""
+import numpy as np
+import pytest
+
+from oracle import c_oracle as CO
+from oracle import exl3_codec as X
+from oracle import opref_port as O
+from tests.helpers import MoeView, rel_max
+
+pytestmark = pytest.mark.gpu
+
+DIMS = dict(hidden=2048, inter=768, experts=512, k_expert=5, k_shared=6)
+TOPK = 10
+
+
+@pytest.fixture(scope="module")
+def eng():
+    import torch
+    assert torch.cuda.is_available()
+    from ijah_b200 import engine as E
+    return E.Engine()
+
+
+@pytest.fixture(scope="module")
+def full_layer():
+    """(device tensors, host copies) of one full-size MoE layer"""
+    from ijah_b200 import synth
+    t = synth.moe_layer(4321, **DIMS)
+    return t, synth.to_numpy(t)
+
+
+class FastView(MoeView):
+    """MoeView whose decoded W' comes from the C oracle (same values as the numpy codec, 250x faster)"""
+
+    @staticmethod
+    def _lin(tr, su, sv):
+        l = O.Exl3Linear(tr, su, sv)
+        l._inner = CO.decode_inner(l.trellis)
+        return l
+
+    def expert(self, e):
+        if e not in self._cache:
+            self._cache[e] = tuple(self._lin(self.raw(f"switch_mlp.{p}_proj.trellis")[e], self.raw(f"switch_mlp.{p}_proj.suh")[e],
+                                             self.raw(f"switch_mlp.{p}_proj.svh")[e]) for p in ("gate", "up", "down"))
+        return self._cache[e]
+
+    @property
+    def shared(self):
+        if "s" not in self._cache:
+            self._cache["s"] = tuple(self._lin(self.raw(f"shared_expert.{p}_proj.trellis"), self.raw(f"shared_expert.{p}_proj.suh"),
+                                               self.raw(f"shared_expert.{p}_proj.svh")) for p in ("gate", "up", "down"))
+        return self._cache["s"]
+
+
+def exact_block(view, x, top_k):
+    return O.moe_block_exact(x, view.router, view.sgate, view.expert, view.shared, top_k)
+
+
+@pytest.mark.parametrize("rows", [1, 4, 16])
+def test_decode_block_512_experts(eng, full_layer, rows):
+    # BASELINE configuration 2 as stated: the router's full 512-wide top-k, a plan over 512 mask words, 512 x 3 trellis stacks
+    import torch
+    from ijah_b200 import engine as E
+    td, th = full_layer
+    rng = np.random.default_rng(200 + rows)
+    x = rng.standard_normal((rows, DIMS["hidden"])).astype(np.float16).astype(np.float32)
+    blk = E.MoeBlock(eng, td, top_k=TOPK, max_rows=rows)
+    xd = torch.from_numpy(x).cuda()
+    y = blk.forward(xd).cpu().numpy()
+    assert eng.lib.ne_device_wait_status() == 0
+    ids, w = blk.route(rows)
+    want = CO.moe_block_emul(th, x, top_k=TOPK, want_gu=True)
+    assert np.array_equal(ids, want["ids"]), "router top-k ids must match exactly at 512 experts"
+    assert np.allclose(w, want["weights"], rtol=1e-5, atol=1e-7)
+    assert rel_max(blk.buffer("logits").reshape(rows, -1), want["logits"]) < 1e-5
+    assert rel_max(blk.experts_gu(rows), want["experts_gu"]) < 2e-4
+    assert rel_max(blk.buffer("shared_down").reshape(rows, -1), want["shared_down"]) < 2e-4
+    assert rel_max(y, want["out"]) < 2e-4
+    assert np.array_equal(y, blk.forward(xd).cpu().numpy()), "two runs must be bit-identical"
+    # float64 operator reference on the first rows (dense reconstruction of every touched expert)
+    n = min(rows, 2)
+    ex = exact_block(FastView(th), x[:n], TOPK)
+    assert np.array_equal(ids[:n], ex["ids"])
+    assert rel_max(y[:n], ex["out"]) < 2e-3
+    blk.free()
+
+
+def test_router_ties_at_512_experts(eng, full_layer):
+    # duplicate router rows give exactly equal logits: the lower expert id must win at full width too (heavy-tie fallback
+    # included: 40 copies of one row compete for 10 places)
+    import torch
+    from ijah_b200 import engine as E
+    td, th = full_layer
+    pre = "language_model.model.layers.0.mlp.gate.weight"
+    t2 = dict(td)
+    w = td[pre][1].clone()
+    w[100:140] = w[7]
+    w[300] = w[299]
+    t2[pre] = ("BF16", w)
+    th2 = dict(th)
+    th2[pre] = ("BF16", w.cpu().view(torch.int16).numpy().view(np.uint16))
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((8, DIMS["hidden"])).astype(np.float16).astype(np.float32)
+    x[0] = O.bf16_bits_to_f32(th2[pre][1][7]) * 40.0  # row 0 points at expert 7 and its 40 copies
+    x = x.astype(np.float16).astype(np.float32)
+    blk = E.MoeBlock(eng, t2, top_k=TOPK, max_rows=8)
+    blk.forward(torch.from_numpy(x).cuda())
+    ids, _ = blk.route(8)
+    logits = CO.router_logits(th2[pre][1], x)
+    want, _ = O.route_device_order(logits, TOPK)
+    assert np.array_equal(ids, want)
+    assert set(ids[0]) <= {7, *range(100, 140)} and ids[0][0] == 7
+    blk.free()
+
+
+@pytest.mark.parametrize("K", [6, 8])
+@pytest.mark.parametrize("rows", [1, 8, 32])
+def test_trunk_projections(eng, K, rows):
+    # BASELINE configuration 3: q 2048->4096, k / v 2048->512, o 4096->2048 at K6 and K8, through ne_exl3_linear and, for the
+    # three projections that share their input, ne_exl3_linear_multi
+    import torch
+    from ijah_b200 import engine as E
+    from ijah_b200 import synth
+    tl = synth.trunk_layer(900 + K, K=K)
+    lins = {n: E.Exl3Linear.from_device(eng, *w) for n, w in tl.items()}
+    host = {n: tuple(a.cpu().numpy().view(np.uint16) if a.dtype == torch.int16 else a.cpu().numpy() for a in w) for n, w in tl.items()}
+    rng = np.random.default_rng(K * 100 + rows)
+    x = rng.standard_normal((rows, 2048)).astype(np.float16).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    outs = {n: torch.empty((rows, lins[n].n_out), device="cuda") for n in ("q", "k", "v")}
+    E.linear_multi(eng, [lins[n] for n in ("q", "k", "v")], xd, [outs[n] for n in ("q", "k", "v")])
+    for n in ("q", "k", "v"):
+        want = CO.linear_emul(*host[n], x)
+        single = lins[n](xd).cpu().numpy()
+        assert np.linalg.norm(single - want) / np.linalg.norm(want) < 5e-5
+        # the chain picks its own k-split, so the partial sums are added in another order than in the single call
+        assert rel_max(outs[n].cpu().numpy(), single) < 1e-5
+        assert np.linalg.norm(outs[n].cpu().numpy() - want) / np.linalg.norm(want) < 5e-5
+    xo = rng.standard_normal((rows, 4096)).astype(np.float16).astype(np.float32)
+    yo = lins["o"](torch.from_numpy(xo).cuda()).cpu().numpy()
+    want = CO.linear_emul(*host["o"], xo)
+    assert np.linalg.norm(yo - want) / np.linalg.norm(want) < 5e-5
+    # float64 operator reference of one projection
+    ex = O.exl3_linear_exact(x[:1], host["k"][0], host["k"][1], host["k"][2]) if rows == 1 else None
+    if ex is not None:
+        assert rel_max(outs["k"].cpu().numpy()[:1], ex) < 2e-3
+    assert eng.lib.ne_device_wait_status() == 0
+
+
+def test_prefill_4096_tokens_zipf(eng):
+    # BASELINE configuration 4: 4096 tokens, top-10 of 512 experts, router biased to a Zipf(1.1) popularity law
+    import torch
+    from ijah_b200 import engine as E
+    from ijah_b200 import synth
+    td = synth.moe_layer(2024, **DIMS)
+    synth.zipf_router_bias(td)
+    th = synth.to_numpy(td)
+    n = 4096
+    g = torch.Generator(device="cuda").manual_seed(99)
+    xd = torch.randn((n, DIMS["hidden"]), device="cuda", generator=g).to(torch.float16).to(torch.float32)
+    xd[:, 0] = 1.0
+    x = xd.cpu().numpy()
+    blk = E.MoeBlock(eng, td, top_k=TOPK, max_rows=16)
+    y = blk.prefill(xd).cpu().numpy()
+    assert eng.lib.ne_device_wait_status() == 0
+    # routing of all 4096 tokens: ids exact, per-expert counts equal the oracle's histogram
+    logits = CO.router_logits(th["language_model.model.layers.0.mlp.gate.weight"][1], x)
+    want_ids, want_w = O.route_device_order(logits, TOPK)
+    route = blk.buffer("prefill_route", np.uint32).reshape(n, 2 * TOPK)
+    ids = route[:, :TOPK].astype(np.int64)
+    assert np.array_equal(ids, want_ids), "all 4096 x 10 routed ids must match"
+    # the biased logits are large: float32 accumulation-order differences of the logits show at the 1e-5 level in the weights
+    assert np.allclose(route[:, TOPK:].copy().view(np.float32), want_w, rtol=1e-4, atol=1e-6)
+    counts = blk.buffer("prefill_counts", np.int32)
+    hist = np.bincount(want_ids.reshape(-1), minlength=DIMS["experts"])
+    assert np.array_equal(counts, hist)
+    assert hist.max() > 128 * 3 and (hist < 16).sum() > 20, "the skew must produce multi-pass experts and nearly empty ones"
+    # outputs of 64 sampled tokens: the 24 that use the most popular experts, the 24 that use the rarest, 16 random
+    pop = hist[want_ids]                      # [n, k] popularity of each token's experts
+    hot = np.argsort(-pop.max(1))[:24]
+    cold = np.argsort(pop.min(1))[:24]
+    rnd = np.random.default_rng(5).choice(n, 16, replace=False)
+    sample = np.unique(np.concatenate([hot, cold, rnd]))
+    want = CO.moe_block_emul(th, x[sample], top_k=TOPK)
+    assert np.array_equal(want["ids"], want_ids[sample])
+    assert rel_max(y[sample], want["out"]) < 2e-4
+    ex = exact_block(FastView(th), x[sample[:4]], TOPK)
+    assert rel_max(y[sample[:4]], ex["out"]) < 2e-3
+    # the decode-width kernels give the same rows
+    ref = blk.forward(xd[sample[:16]].contiguous()).cpu().numpy()
+    assert rel_max(y[sample[:16]], ref) < 2e-4
+    assert np.array_equal(y, blk.prefill(xd).cpu().numpy()), "two runs must be bit-identical"
+    blk.free()
