@@ -1,0 +1,448 @@
+// Glue kernels of the decoder stack. See stack.cuh.
+#include <algorithm>
+#include <cmath>
+
+#include "common.hpp"
+#include "launch.cuh"
+#include "stack.cuh"
+
+namespace ijah {
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {  // round to nearest even (finite inputs)
+  const uint32_t u = __float_as_uint(f);
+  return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+
+// =============================================================================================== embedding, norm
+__global__ void embed_kernel(const int *__restrict__ tokens, const uint16_t *__restrict__ embed, int vocab, int H, float *__restrict__ x) {
+  const int r = blockIdx.y;
+  pdl_launch();
+  pdl_wait();
+  int t = tokens[r];
+  t = (t < 0 || t >= vocab) ? 0 : t;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) x[(size_t)r * H + i] = bf16_bits_to_float(embed[(size_t)t * H + i]);
+}
+
+void launch_embed(const int *tokens, const uint16_t *embed_bf16, int vocab, int H, int rows, float *x, cudaStream_t st) {
+  launch_pdl(embed_kernel, dim3((H + 255) / 256, rows), dim3(256), 0, st, tokens, embed_bf16, vocab, H, x);
+}
+
+__global__ void __launch_bounds__(256) rms_add_kernel(float *__restrict__ x, const float *__restrict__ add, float *__restrict__ xn,
+                                                      const uint16_t *__restrict__ w, int H, float eps) {
+  __shared__ float red[8];
+  const int r = blockIdx.x;
+  float *xr = x + (size_t)r * H;
+  float ss = 0.0f;
+  pdl_launch();
+  pdl_wait();
+  for (int i = threadIdx.x; i < H; i += 256) {
+    float v = xr[i];
+    if (add) { v += add[(size_t)r * H + i]; xr[i] = v; }
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) tot += red[i];
+  const float sc = rsqrtf(tot / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += 256) xn[(size_t)r * H + i] = xr[i] * sc * (w ? bf16_bits_to_float(w[i]) : 1.0f);
+}
+
+void launch_rms_add(float *x, const float *add, float *xn, const uint16_t *w_bf16, int rows, int H, float eps, cudaStream_t st) {
+  launch_pdl(rms_add_kernel, dim3(rows), dim3(256), 0, st, x, add, xn, w_bf16, H, eps);
+}
+
+// =============================================================================================== attention stand-in
+// partial: one CTA per (block of 64 cached positions, KV head). K and V of the block are staged once in shared memory
+// and used for every query vector of the head group (rows x heads / kv_heads of them), 16 at a time:
+//   S = Q K^T (warp w: positions 16 w .. 16 w + 15), block max and sum over the four warps, P = exp(S - max) as fp16,
+//   O = P V (warp w: a quarter of the head dimension).
+// Per (query vector, block) it leaves max, sum and the unnormalised O; the merge kernel combines the blocks.
+constexpr int AT_PB = 64;  // positions per block
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restrict__ q, const __half *__restrict__ kc, const __half *__restrict__ vc, int rows,
+                                                           int heads, int kv_heads, int nsplit, float *__restrict__ part, float *__restrict__ ml) {
+  constexpr int LD = HD + 8;          // padded row length in halfs (ldmatrix rows on distinct banks)
+  constexpr int LDP = AT_PB + 8;
+  extern __shared__ __align__(16) unsigned char at_smem[];
+  __half *Ks = reinterpret_cast<__half *>(at_smem);
+  __half *Vs = Ks + AT_PB * LD;
+  __half *Qs = Vs + AT_PB * LD;
+  __half *Ps = Qs + 16 * LD;
+  float *red = reinterpret_cast<float *>(Ps + 16 * LDP);  // [2][4][16]: per-warp max, per-warp sum
+  const int split = blockIdx.x, kvh = blockIdx.y, G = heads / kv_heads, NQ = rows * G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qq = lane & 3;
+  // stage K and V of the block (static data: before the wait on the preceding kernel)
+  {
+    const size_t rstride = (size_t)kv_heads * HD;
+    const __half *ksrc = kc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
+    const __half *vsrc = vc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
+    for (int i = threadIdx.x; i < AT_PB * (HD / 8); i += 128) {
+      const int p = i / (HD / 8), c = i % (HD / 8);
+      *reinterpret_cast<uint4 *>(Ks + p * LD + c * 8) = *reinterpret_cast<const uint4 *>(ksrc + p * rstride + c * 8);
+      *reinterpret_cast<uint4 *>(Vs + p * LD + c * 8) = *reinterpret_cast<const uint4 *>(vsrc + p * rstride + c * 8);
+    }
+  }
+  pdl_launch();
+  pdl_wait();
+  const float scale = rsqrtf((float)HD);
+  const uint32_t Qa = smem_u32(Qs), Ka = smem_u32(Ks), Va = smem_u32(Vs), Pa = smem_u32(Ps);
+  for (int qt = 0; qt * 16 < NQ; qt++) {
+    __syncthreads();  // previous tile's readers of Qs / Ps / red are done (first pass: K / V are in place)
+    for (int i = threadIdx.x; i < 16 * (HD / 4); i += 128) {
+      const int j = i / (HD / 4), c = i % (HD / 4), qi = qt * 16 + j;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (qi < NQ) v = *reinterpret_cast<const float4 *>(q + ((size_t)(qi / G) * heads + kvh * G + qi % G) * HD + c * 4);
+      __half2 *dst = reinterpret_cast<__half2 *>(Qs + j * LD + c * 4);
+      dst[0] = __floats2half2_rn(v.x * scale, v.y * scale);
+      dst[1] = __floats2half2_rn(v.z * scale, v.w * scale);
+    }
+    __syncthreads();
+    // ---- S = Q K^T for this warp's 16 positions
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+      uint32_t a[4], b[4];
+      ldsm_x4(a, Qa + (uint32_t)(((lane & 15) * LD + kk * 16 + (lane >> 4) * 8) * 2));
+      const int m = lane >> 3;
+      ldsm_x4(b, Ka + (uint32_t)(((warp * 16 + (lane & 7) + (m >> 1) * 8) * LD + kk * 16 + (m & 1) * 8) * 2));
+      mma_16816(s[0], a, b[0], b[1]);
+      mma_16816(s[1], a, b[2], b[3]);
+    }
+    // ---- block max and sum per query row (rows g and g + 8 of the tile)
+    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])), mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
+    }
+    if (qq == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
+    __syncthreads();
+    float m0 = red[g], m1 = red[g + 8];
+#pragma unroll
+    for (int w = 1; w < 4; w++) { m0 = fmaxf(m0, red[w * 16 + g]); m1 = fmaxf(m1, red[w * 16 + g + 8]); }
+    float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+      const float p0 = __expf(s[nt][0] - m0), p1 = __expf(s[nt][1] - m0), p2 = __expf(s[nt][2] - m1), p3 = __expf(s[nt][3] - m1);
+      const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+      // the sums use the rounded values the tensor core will multiply with
+      l0 += __low2float(h01) + __high2float(h01);
+      l1 += __low2float(h23) + __high2float(h23);
+      *reinterpret_cast<__half2 *>(Ps + g * LDP + warp * 16 + nt * 8 + 2 * qq) = h01;
+      *reinterpret_cast<__half2 *>(Ps + (g + 8) * LDP + warp * 16 + nt * 8 + 2 * qq) = h23;
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, o);
+      l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
+    }
+    if (qq == 0) { red[64 + warp * 16 + g] = l0; red[64 + warp * 16 + g + 8] = l1; }
+    __syncthreads();
+    // ---- O = P V for this warp's quarter of the head dimension
+    constexpr int NTW = HD / 4 / 8;  // n-tiles per warp
+    float o_acc[NTW][4];
+#pragma unroll
+    for (int n = 0; n < NTW; n++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) o_acc[n][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < AT_PB / 16; ks++) {
+      uint32_t a[4];
+      ldsm_x4(a, Pa + (uint32_t)(((lane & 15) * LDP + ks * 16 + (lane >> 4) * 8) * 2));
+#pragma unroll
+      for (int n2 = 0; n2 < NTW / 2; n2++) {
+        uint32_t b[4];
+        const int m = lane >> 3, n0 = warp * (HD / 4) + n2 * 16;
+        ldsm_x4_trans(b, Va + (uint32_t)(((ks * 16 + (lane & 7) + (m & 1) * 8) * LD + n0 + (m >> 1) * 8) * 2));
+        mma_16816(o_acc[2 * n2], a, b[0], b[1]);
+        mma_16816(o_acc[2 * n2 + 1], a, b[2], b[3]);
+      }
+    }
+    // ---- partial results of the tile's live query vectors
+    const int q0 = qt * 16 + g, q1 = q0 + 8;
+    if (warp == 0 && qq == 0) {
+      float la = 0.f, lb = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; w++) { la += red[64 + w * 16 + g]; lb += red[64 + w * 16 + g + 8]; }
+      if (q0 < NQ) { ml[(((size_t)kvh * NQ + q0) * nsplit + split) * 2] = m0; ml[(((size_t)kvh * NQ + q0) * nsplit + split) * 2 + 1] = la; }
+      if (q1 < NQ) { ml[(((size_t)kvh * NQ + q1) * nsplit + split) * 2] = m1; ml[(((size_t)kvh * NQ + q1) * nsplit + split) * 2 + 1] = lb; }
+    }
+#pragma unroll
+    for (int n = 0; n < NTW; n++) {
+      const int d = warp * (HD / 4) + n * 8 + 2 * qq;
+      if (q0 < NQ) *reinterpret_cast<float2 *>(part + (((size_t)kvh * NQ + q0) * nsplit + split) * HD + d) = make_float2(o_acc[n][0], o_acc[n][1]);
+      if (q1 < NQ) *reinterpret_cast<float2 *>(part + (((size_t)kvh * NQ + q1) * nsplit + split) * HD + d) = make_float2(o_acc[n][2], o_acc[n][3]);
+    }
+  }
+}
+
+// merge: one CTA per query vector (row, head), one thread per dimension; also adds the row's own (k, v) as one more position
+__global__ void attn_merge_kernel(const float *__restrict__ q, const float *__restrict__ knew, const float *__restrict__ vnew, const float *__restrict__ part,
+                                  const float *__restrict__ ml, int rows, int heads, int kv_heads, int hd, int nsplit, float *__restrict__ out) {
+  __shared__ float red[8];
+  __shared__ float s_self;
+  const int r = blockIdx.x / heads, h = blockIdx.x % heads, G = heads / kv_heads, kvh = h / G, NQ = rows * G, qi = r * G + h % G;
+  const int d = threadIdx.x;
+  pdl_launch();
+  pdl_wait();
+  float dot = d < hd ? q[((size_t)r * heads + h) * hd + d] * knew[((size_t)r * kv_heads + kvh) * hd + d] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
+  if ((d & 31) == 0) red[d >> 5] = dot;
+  __syncthreads();
+  if (d == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += red[i];
+    s_self = t * rsqrtf((float)hd);
+  }
+  __syncthreads();
+  const float *mlq = ml + ((size_t)kvh * NQ + qi) * nsplit * 2;
+  float M = s_self;
+  for (int s = 0; s < nsplit; s++) M = fmaxf(M, mlq[2 * s]);
+  if (d >= hd) return;
+  const float wself = __expf(s_self - M);
+  float num = wself * vnew[((size_t)r * kv_heads + kvh) * hd + d], den = wself;
+  const float *pq = part + ((size_t)kvh * NQ + qi) * nsplit * hd + d;
+  for (int s = 0; s < nsplit; s++) {
+    const float w = __expf(mlq[2 * s] - M);
+    num += w * pq[(size_t)s * hd];
+    den += w * mlq[2 * s + 1];
+  }
+  out[((size_t)r * heads + h) * hd + d] = num / den;
+}
+
+size_t attn_scratch_bytes(int rows, int heads, int hd, int T) {
+  const size_t nsplit = T / AT_PB;
+  return (size_t)rows * heads * nsplit * (hd + 2) * 4 + 256;
+}
+
+template <int HD>
+static void launch_attn_partial(const float *q, const __half *kc, const __half *vc, int rows, int heads, int kv_heads, int nsplit, float *part, float *ml,
+                                cudaStream_t st) {
+  const size_t smem = (size_t)(2 * AT_PB * (HD + 8) + 16 * (HD + 8) + 16 * (AT_PB + 8)) * 2 + 128 * 4;
+  IJ_CUDA(cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  launch_pdl(attn_partial_kernel<HD>, dim3(nsplit, kv_heads), dim3(128), smem, st, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml);
+}
+
+void launch_attn_standin(const float *q, const float *knew, const float *vnew, const __half *kc, const __half *vc, int rows, int heads, int kv_heads,
+                         int hd, int T, float *out, void *scratch, cudaStream_t st) {
+  IJ_CHECK(T % AT_PB == 0 && T >= AT_PB, "attention stand-in: cache length %d must be a multiple of %d", T, AT_PB);
+  IJ_CHECK(heads % kv_heads == 0 && (hd == 64 || hd == 128 || hd == 256), "attention stand-in: heads %d / %d, head dim %d not supported", heads, kv_heads, hd);
+  const int nsplit = T / AT_PB;
+  float *part = (float *)scratch;
+  float *ml = part + (size_t)rows * heads * nsplit * hd;
+  switch (hd) {
+    case 64: launch_attn_partial<64>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
+    case 128: launch_attn_partial<128>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
+    default: launch_attn_partial<256>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
+  }
+  launch_pdl(attn_merge_kernel, dim3(rows * heads), dim3((hd + 31) / 32 * 32), 0, st, q, knew, vnew, (const float *)part, (const float *)ml, rows, heads,
+             kv_heads, hd, nsplit, out);
+}
+
+// =============================================================================================== LM head
+__global__ void to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, size_t n) {
+  pdl_launch();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = float_to_bf16_bits(x[i]);
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One warp per 16 vocabulary rows, 8 warps per CTA. The head is streamed from global memory straight into the A fragments
+// (each lane reads 16 contiguous bytes of rows g and g + 8 per 32 k: the k order inside a step is permuted the same way
+// for both operands, which a dot product does not mind); the activations (bf16) are staged per block of 256 k in shared
+// memory for all rows. NT = 8-row groups of activations.
+constexpr int LH_KB = 256;
+template <int NT>
+__global__ void __launch_bounds__(256) lm_head_kernel(const uint16_t *__restrict__ xb, const uint16_t *__restrict__ head, int vocab, int H, int rows,
+                                                      float *__restrict__ logits) {
+  constexpr int LDX = LH_KB + 8;  // halfs per staged row (+16 bytes: the lanes' 16-byte reads of 8 rows fall on distinct banks)
+  constexpr int XS_BYTES = NT * 8 * LDX * 2, OUT_BYTES = 8 * NT * 8 * 17 * 4;
+  __shared__ __align__(16) unsigned char lh_buf[XS_BYTES > OUT_BYTES ? XS_BYTES : OUT_BYTES];  // staged activations, later the output transpose
+  uint16_t *xs = reinterpret_cast<uint16_t *>(lh_buf);
+  float(*outt)[NT * 8][17] = reinterpret_cast<float(*)[NT * 8][17]>(lh_buf);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qq = lane & 3;
+  const int v0 = (blockIdx.x * 8 + warp) * 16;
+  const uint16_t *w0 = head + (size_t)min(v0 + g, vocab - 1) * H + 8 * qq;
+  const uint16_t *w1 = head + (size_t)min(v0 + g + 8, vocab - 1) * H + 8 * qq;
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; n++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[n][j] = 0.f;
+  pdl_launch();
+  pdl_wait();
+  for (int kb = 0; kb < H; kb += LH_KB) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < NT * 8 * (LH_KB / 8); i += 256) {
+      const int r = i / (LH_KB / 8), c = i % (LH_KB / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) v = *reinterpret_cast<const uint4 *>(xb + (size_t)r * H + kb + c * 8);
+      *reinterpret_cast<uint4 *>(xs + r * LDX + c * 8) = v;
+    }
+    __syncthreads();
+    uint4 wa[LH_KB / 32], wb[LH_KB / 32];
+#pragma unroll
+    for (int ks = 0; ks < LH_KB / 32; ks++) {
+      wa[ks] = __ldg(reinterpret_cast<const uint4 *>(w0 + kb + ks * 32));
+      wb[ks] = __ldg(reinterpret_cast<const uint4 *>(w1 + kb + ks * 32));
+    }
+#pragma unroll
+    for (int ks = 0; ks < LH_KB / 32; ks++) {
+#pragma unroll
+      for (int n = 0; n < NT; n++) {
+        const uint4 b = *reinterpret_cast<const uint4 *>(xs + (n * 8 + g) * LDX + ks * 32 + 8 * qq);
+        mma_bf16_16816(acc[n], wa[ks].x, wb[ks].x, wa[ks].y, wb[ks].y, b.x, b.y);
+        mma_bf16_16816(acc[n], wa[ks].z, wb[ks].z, wa[ks].w, wb[ks].w, b.z, b.w);
+      }
+    }
+  }
+  // acc[n]: (vocab row g, activation rows 8n + 2qq, +1), (vocab row g + 8, the same rows): transpose through shared memory
+  __syncthreads();  // every warp is done with the staged activations
+#pragma unroll
+  for (int n = 0; n < NT; n++) {
+    outt[warp][n * 8 + 2 * qq][g] = acc[n][0];
+    outt[warp][n * 8 + 2 * qq + 1][g] = acc[n][1];
+    outt[warp][n * 8 + 2 * qq][g + 8] = acc[n][2];
+    outt[warp][n * 8 + 2 * qq + 1][g + 8] = acc[n][3];
+  }
+  __syncwarp();
+  for (int i = lane; i < rows * 16; i += 32) {
+    const int r = i >> 4, c = i & 15;
+    if (v0 + c < vocab) logits[(size_t)r * vocab + v0 + c] = outt[warp][r][c];
+  }
+}
+
+size_t lm_head_scratch_bytes(int rows, int H) { return (size_t)rows * H * 2 + 256; }
+
+void launch_lm_head(const float *xn, const uint16_t *head_bf16, int vocab, int H, int rows, float *logits, void *scratch, cudaStream_t st) {
+  IJ_CHECK(rows >= 1 && rows <= 64 && H % LH_KB == 0, "LM head: rows %d outside 1..64 or hidden %d not a multiple of %d", rows, H, LH_KB);
+  uint16_t *xb = (uint16_t *)scratch;
+  launch_pdl(to_bf16_kernel, dim3(std::min(64, (rows * H + 255) / 256)), dim3(256), 0, st, xn, xb, (size_t)rows * H);
+  const dim3 grid((vocab + 127) / 128), block(256);
+  const uint16_t *xc = xb;
+  if (rows <= 8) launch_pdl(lm_head_kernel<1>, grid, block, 0, st, xc, head_bf16, vocab, H, rows, logits);
+  else if (rows <= 16) launch_pdl(lm_head_kernel<2>, grid, block, 0, st, xc, head_bf16, vocab, H, rows, logits);
+  else if (rows <= 32) launch_pdl(lm_head_kernel<4>, grid, block, 0, st, xc, head_bf16, vocab, H, rows, logits);
+  else launch_pdl(lm_head_kernel<8>, grid, block, 0, st, xc, head_bf16, vocab, H, rows, logits);
+}
+
+// =============================================================================================== greedy sampling
+__global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restrict__ logits, int vocab, float *__restrict__ pv, int *__restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int r = blockIdx.y, per = (vocab + ARGMAX_BLOCKS - 1) / ARGMAX_BLOCKS, lo = blockIdx.x * per, hi = min(vocab, lo + per);
+  float best = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  pdl_launch();
+  pdl_wait();
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    const float v = logits[(size_t)r * vocab + i];
+    if (v > best) { best = v; bi = i; }  // ascending i: the first maximum wins
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+    const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; w++)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    pv[r * ARGMAX_BLOCKS + blockIdx.x] = best;
+    pi[r * ARGMAX_BLOCKS + blockIdx.x] = bi;
+  }
+}
+__global__ void argmax_final_kernel(const float *__restrict__ pv, const int *__restrict__ pi, int *__restrict__ next) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  pdl_launch();
+  pdl_wait();
+  for (int i = lane; i < ARGMAX_BLOCKS; i += 32) {
+    const float v = pv[r * ARGMAX_BLOCKS + i];
+    const int id = pi[r * ARGMAX_BLOCKS + i];
+    if (v > best || (v == best && id < bi)) { best = v; bi = id; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+    const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) next[r] = bi;
+}
+
+void launch_argmax(const float *logits, int vocab, int rows, int *next, void *scratch, cudaStream_t st) {
+  float *pv = (float *)scratch;
+  int *pi = (int *)(pv + (size_t)rows * ARGMAX_BLOCKS);
+  launch_pdl(argmax_part_kernel, dim3(ARGMAX_BLOCKS, rows), dim3(256), 0, st, logits, vocab, pv, pi);
+  launch_pdl(argmax_final_kernel, dim3(rows), dim3(32), 0, st, (const float *)pv, (const int *)pi, next);
+}
+
+// =============================================================================================== synthetic weights
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {  // splitmix64 finaliser
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ float unit_normal(uint64_t h) {  // Box-Muller on the two halves of a hash
+  const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777217.0f), u2 = (float)(uint32_t)((h >> 8) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+  return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+template <int MODE>  // 0 trellis words (4 per hash), 1 signs f16, 2 scales f16, 3 normal bf16, 4 normal f16
+__global__ void fill_kernel(uint16_t *dst, size_t n, float scale, uint64_t seed, size_t first) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if constexpr (MODE == 0) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i * 4 < n; i += stride) {
+      const uint64_t h = mix64(seed ^ ((first / 4 + i) * 0xD1B54A32D192ED03ull));
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (i * 4 + j < n) dst[i * 4 + j] = (uint16_t)(h >> (16 * j));
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+      const uint64_t h = mix64(seed ^ ((first + i) * 0xD1B54A32D192ED03ull));
+      if (MODE == 1) dst[i] = (h & 1) ? 0x3C00u : 0xBC00u;
+      else if (MODE == 2) dst[i] = __half_as_ushort(__float2half_rn(((h & 1) ? 1.0f : -1.0f) * fabsf(unit_normal(h)) * scale));
+      else if (MODE == 3) dst[i] = float_to_bf16_bits(unit_normal(h) * scale);
+      else dst[i] = __half_as_ushort(__float2half_rn(unit_normal(h) * scale));
+    }
+  }
+}
+template <int MODE>
+static void fill(void *dst, size_t n, float scale, uint64_t seed, cudaStream_t st, size_t first) {
+  if (n == 0) return;
+  IJ_CHECK(MODE != 0 || first % 4 == 0, "trellis fill offset must be a multiple of 4 words");
+  const size_t work = MODE == 0 ? (n + 3) / 4 : n;
+  fill_kernel<MODE><<<(unsigned)std::min<size_t>((work + 255) / 256, 148 * 16), 256, 0, st>>>((uint16_t *)dst, n, scale, seed, first);
+  IJ_CUDA(cudaGetLastError());
+}
+void fill_trellis(void *dst, size_t n_u16, uint64_t seed, cudaStream_t st, size_t first) { fill<0>(dst, n_u16, 0.f, seed, st, first); }
+void fill_signs_f16(void *dst, size_t n, uint64_t seed, cudaStream_t st, size_t first) { fill<1>(dst, n, 0.f, seed, st, first); }
+void fill_scales_f16(void *dst, size_t n, float scale, uint64_t seed, cudaStream_t st, size_t first) { fill<2>(dst, n, scale, seed, st, first); }
+void fill_normal_bf16(void *dst, size_t n, float scale, uint64_t seed, cudaStream_t st, size_t first) { fill<3>(dst, n, scale, seed, st, first); }
+void fill_normal_f16(void *dst, size_t n, float scale, uint64_t seed, cudaStream_t st, size_t first) { fill<4>(dst, n, scale, seed, st, first); }
+
+}  // namespace ijah

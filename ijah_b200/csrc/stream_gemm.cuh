@@ -38,7 +38,7 @@
 namespace ijah {
 
 #ifndef SG_KS_STEPS
-#define SG_KS_STEPS 8
+#define SG_KS_STEPS 16
 #endif
 #ifndef SG_CTAS_PER_SM
 #define SG_CTAS_PER_SM 2

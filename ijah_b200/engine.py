@@ -56,6 +56,12 @@ class MoeDescC(C.Structure):
                 ("down", Exl3StackC), ("sh_gate", Exl3WeightC), ("sh_up", Exl3WeightC), ("sh_down", Exl3WeightC)]
 
 
+class ModelDescC(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("layers", "hidden", "inter", "experts", "top_k", "k_expert", "k_shared", "q_out", "kv_out",
+                                       "heads", "kv_heads", "head_dim", "k_trunk", "k_trunk_alt", "alt_every", "vocab",
+                                       "kv_positions", "expert_first", "expert_count")]
+
+
 class EngineError(RuntimeError):
     pass
 
@@ -115,6 +121,20 @@ SIGNATURES = {
     "ne_moe_experts_gu": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "ne_moe_last_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
                                     C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
+    "ne_fn_model_create": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "ne_fn_model_create_rows": (C.c_void_p, [C.c_void_p, C.c_int, C.c_int]),
+    "ne_fn_model_create_synthetic": (C.c_void_p, [C.POINTER(ModelDescC), C.c_uint64, C.c_int]),
+    "ne_fn_model_free": (None, [C.c_void_p]), "ne_fn_model_reset": (C.c_int, [C.c_void_p]),
+    "ne_fn_model_step": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_float),
+                                   C.POINTER(C.c_int), C.POINTER(C.c_double)]),
+    "ne_fn_model_step_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_double)]),
+    "ne_fn_model_time": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "ne_fn_model_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ne_fn_model_desc_of": (C.c_int, [C.c_void_p, C.POINTER(ModelDescC)]),
+    "ne_fn_model_set_ep": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ne_fn_model_read": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.c_void_p, C.c_uint64]),
+    "ne_fn_model_weight_bytes": (C.c_uint64, [C.c_void_p]),
+    "ne_fn_model_last_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
     "ne_copy_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
     "ne_device_wait_status": (C.c_int, []),
 }
@@ -268,6 +288,78 @@ class FnLayer:
         self.ptr = None
 
 
+class FnModel:
+    """The decoder stack behind ne_fn_model_*: numpy in, numpy out (tokens and results cross the C ABI as host memory).
+    Made from an open pack (`pack`) or, with `desc` (a dict of ne_fn_model_desc fields), from synthetic weights the
+    library generates on the device."""
+
+    def __init__(self, eng, pack=None, tmax=64, max_rows=8, desc=None, seed=1):
+        self.eng = eng
+        if desc is not None:
+            d = ModelDescC(**desc)
+            self.ptr = eng.lib.ne_fn_model_create_synthetic(C.byref(d), seed, max_rows)
+        else:
+            self.ptr = eng.lib.ne_fn_model_create_rows(pack.ptr, tmax, max_rows)
+        if not self.ptr:
+            raise EngineError(f"ne_fn_model_create: {eng.last_error()}")
+        d = ModelDescC()
+        eng._ok(eng.lib.ne_fn_model_desc_of(self.ptr, C.byref(d)), "ne_fn_model_desc_of")
+        self.desc = {n: getattr(d, n) for n, _ in ModelDescC._fields_}
+        self.max_rows = max_rows
+
+    def step(self, token, head=True):
+        """the reference's one-token step: (logits f32 [vocab], next, logprob, gpu_ms)"""
+        lg = np.empty(self.desc["vocab"], np.float32)
+        nx, lp, ms = C.c_int(0), C.c_float(0), C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_step(self.ptr, int(token), int(head), lg.ctypes.data, C.byref(nx), C.byref(lp), None,
+                                                   C.byref(ms)), "ne_fn_model_step")
+        return lg, nx.value, lp.value, ms.value
+
+    def step_rows(self, tokens, head=True, want_logits=False):
+        """one decode step for len(tokens) rows: (next ids int32 [rows], logits f32 [rows, vocab] or None, gpu_ms)"""
+        t = np.ascontiguousarray(tokens, np.int32)
+        rows = t.shape[0]
+        nx = np.zeros(rows, np.int32)
+        lg = np.empty((rows, self.desc["vocab"]), np.float32) if want_logits else None
+        ms = C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_step_rows(self.ptr, t.ctypes.data, rows, int(head), lg.ctypes.data if want_logits else None,
+                                                        nx.ctypes.data, C.byref(ms)), "ne_fn_model_step_rows")
+        return nx, lg, ms.value
+
+    def time(self, reps=10):
+        a, b, c = C.c_double(0), C.c_double(0), C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_time(self.ptr, 0, reps, C.byref(a), C.byref(b), C.byref(c)), "ne_fn_model_time")
+        return a.value, b.value, c.value
+
+    def info(self):
+        a, b, t = C.c_int(0), C.c_int(0), C.c_int(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_info(self.ptr, C.byref(a), C.byref(b), C.byref(t)), "ne_fn_model_info")
+        return dict(launches_full=a.value, launches_body=b.value, T=t.value)
+
+    def read(self, name, layer=0, dtype=np.float32, count=None):
+        if name in ("kv_k", "kv_v"):
+            dtype, count = np.float16, self.desc["kv_positions"] * self.desc["kv_out"]
+        out = np.empty(count, dtype)
+        self.eng._ok(self.eng.lib.ne_fn_model_read(self.ptr, name.encode(), layer, out.ctypes.data, out.nbytes), f"ne_fn_model_read({name})")
+        return out
+
+    def set_ep(self, xchg):
+        self.eng._ok(self.eng.lib.ne_fn_model_set_ep(self.ptr, xchg.ptr if xchg is not None else None), "ne_fn_model_set_ep")
+
+    def weight_bytes(self):
+        return self.eng.lib.ne_fn_model_weight_bytes(self.ptr)
+
+    def last_bytes(self, rows):
+        t, n = C.c_uint64(0), C.c_int(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_last_bytes(self.ptr, rows, C.byref(t), C.byref(n)), "ne_fn_model_last_bytes")
+        return dict(total=t.value, distinct_experts_mean=n.value)
+
+    def free(self):
+        if self.ptr:
+            self.eng.lib.ne_fn_model_free(self.ptr)
+        self.ptr = None
+
+
 class Engine:
     def __init__(self, lib=None):
         self.lib = load_library(lib)
@@ -303,6 +395,9 @@ class Engine:
 
     def fn_layer(self, pack, layer, rows=1):
         return FnLayer(self, pack, layer, rows)
+
+    def fn_model(self, pack=None, tmax=64, max_rows=8, desc=None, seed=1):
+        return FnModel(self, pack, tmax, max_rows, desc, seed)
 
     def kernel_exists(self, name):
         return self.lib.ne_kernel_exists(name.encode()) == 1

@@ -149,6 +149,35 @@ NE_API int ne_moe_experts_gu(ne_moe *m, int rows, float *dst_host);
  * shared expert + scales + activations), for roofline accounting. */
 NE_API int ne_moe_last_bytes(ne_moe *m, int rows, uint64_t *total, uint64_t *gateup, uint64_t *down, int *distinct_experts);
 
+/* ---- decoder stack beyond the reference's one-token step (ijah_engine.h: ne_fn_model_*) ---------------------------
+ * Dimension-explicit description of a stack; ne_fn_model_create_synthetic generates every weight on the device from
+ * `seed` (uniform trellis words, suh +-1, svh +-|N(0,1)| * 0.02, router / gate / head N(0, 0.02) in bf16, embedding and KV
+ * cache N(0, 1)), so a full-size stack (tens of GB) needs no pack on disk. expert_first / expert_count select the experts
+ * this rank holds (0, 0 = all); every other weight is replicated and identical for equal seeds. */
+typedef struct {
+  int layers, hidden, inter, experts, top_k, k_expert, k_shared; /* k_shared 0 = no shared expert */
+  int q_out, kv_out;             /* attention projections: q hidden -> q_out, k / v hidden -> kv_out, o q_out -> hidden */
+  int heads, kv_heads, head_dim; /* q_out = heads * head_dim, kv_out = kv_heads * head_dim; head_dim 64, 128 or 256 */
+  int k_trunk, k_trunk_alt, alt_every; /* trunk bits per weight; every alt_every-th layer uses k_trunk_alt (0 = never) */
+  int vocab, kv_positions;       /* kv_positions: cached positions the attention stand-in reads (multiple of 64) */
+  int expert_first, expert_count;
+} ne_fn_model_desc;
+NE_API ne_fn_model *ne_fn_model_create_synthetic(const ne_fn_model_desc *d, uint64_t seed, int max_rows);
+NE_API ne_fn_model *ne_fn_model_create_rows(ne_pack *pack, int tmax, int max_rows); /* ne_fn_model_create for up to max_rows rows per step */
+/* One decode step for `rows` rows (1..max_rows: concurrent sequences x verify width), one token id per row, from HOST
+ * memory; logits_host f32 [rows][vocab] and next_host [rows] (greedy) may be NULL. The step is replayed from the model's
+ * CUDA graph for this row count (captured on first use); host -> device copy of the tokens and device -> host copies of the
+ * results are part of the call. */
+NE_API int ne_fn_model_step_rows(ne_fn_model *m, const int *tokens_host, int rows, int head, float *logits_host, int *next_host, double *gpu_ms);
+NE_API int ne_fn_model_desc_of(ne_fn_model *m, ne_fn_model_desc *out);
+/* Expert parallel: the MoE blocks of every layer exchange rows over the given peer-memory context (ne_ep_*); NULL = off. */
+NE_API int ne_fn_model_set_ep(ne_fn_model *m, ne_ep *e);
+/* Host copy of "kv_k" / "kv_v" (f16 [kv_positions][kv_heads][head_dim] of `layer`), "hidden" (f32, final normed rows) or "logits". */
+NE_API int ne_fn_model_read(ne_fn_model *m, const char *name, int layer, void *dst_host, uint64_t nbytes);
+NE_API uint64_t ne_fn_model_weight_bytes(ne_fn_model *m); /* bytes of weights resident on this device */
+/* Algorithmic bytes the last step of `rows` rows had to read (weights of the distinct experts touched + trunk + KV + head). */
+NE_API int ne_fn_model_last_bytes(ne_fn_model *m, int rows, uint64_t *total, int *distinct_experts_mean);
+
 /* Copy nbytes from a device pointer of this library (e.g. one returned by ne_moe_buffer) to host memory, after
  * synchronising the device. */
 NE_API int ne_copy_to_host(void *dst_host, const void *src_dev, uint64_t nbytes);

@@ -109,6 +109,25 @@ NE_API int ne_fn_layer_write(ne_fn_layer *l, const char *name, const float *src,
 NE_API int ne_fn_layer_read(ne_fn_layer *l, const char *name, float *dst, int n); /* layer.h:264: returns the size */
 NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, double *us_per_step, double *us_flush); /* layer.h:267 */
 
+/* ---- whole decoder stack: reference models/flash_next/model.h:160-246 ----------------------------------------
+ * The model object owns the weights of every layer (EXL3 trunk projections q, k, v, o around an attention stand-in over a
+ * fixed KV cache; the MoE block), the bf16 embedding and LM head, and the decode step recorded once per row count into a
+ * CUDA graph that every later step replays (the reference records into its Recorder, core/recorder.h:45-99). Attention
+ * proper, GDN, hyper-connections, MTP and the sampler's knobs are not part of this library: ne_fn_model_step runs the
+ * stand-in stack and samples greedily. Pack tensors read: language_model.model.embed_tokens.weight BF16 [vocab][hidden],
+ * language_model.lm_head.weight (optional: tied otherwise), per layer self_attn.{q,k,v,o}_proj.{trellis,suh,svh} and the
+ * mlp.* tensors of ne_fn_layer_create; config.json: num_hidden_layers, num_attention_heads, num_key_value_heads, head_dim,
+ * num_experts_per_tok. */
+typedef struct ne_fn_model ne_fn_model;
+NE_API ne_fn_model *ne_fn_model_create(ne_pack *pack, int tmax);  /* model.h:163; tmax = cached positions (rounded up to 64) */
+NE_API void ne_fn_model_free(ne_fn_model *m);                     /* model.h:168 */
+NE_API int ne_fn_model_reset(ne_fn_model *m);                     /* model.h:169 */
+/* model.h:204-207: one step for `token`; logits f32 [vocab], next, logprob, argmax may be NULL; head = 0: layers only */
+NE_API int ne_fn_model_step(ne_fn_model *m, int token, int head, float *logits, int *next, float *logprob, int *argmax, double *gpu_ms);
+/* model.h:217-218: GPU time of the full decode step: median / min over reps graph replays, wall time per synchronous step */
+NE_API int ne_fn_model_time(ne_fn_model *m, int T, int reps, double *gpu_ms_median, double *gpu_ms_min, double *wall_ms_median);
+NE_API int ne_fn_model_info(ne_fn_model *m, int *n_dispatch_full, int *n_dispatch_body, int *T); /* model.h:219 */
+
 #ifdef __cplusplus
 }
 #endif
