@@ -1,19 +1,27 @@
-"""Benchmark of the EXL3 MoE decode hot path on B200 (one JSON line on stdout).
+"""Benchmark of the EXL3 MoE decoder hot path on B200 (one JSON line on stdout).
 
-Workload (named in `config.workload`): the MoE block of the decoder at decode width -- hidden 2048, 512 experts, top-10,
-expert intermediate 768, routed experts K=5, shared expert K=6 -- for `--rows` activation rows, run over `--layers`
-layers with distinct random weights (so the weights of one step are far larger than L2). A step is one pass of the rows
-through all those layers. value = rows * layers / step time = tokens per second through one MoE block.
+Headline workload (`config.workload`): one decode step of a random-init 48-layer MoE decoder stack -- hidden 2048, vocab
+151936 (bf16 embedding and LM head), per layer the trunk projections q 2048->4096, k / v 2048->512, o 4096->2048 at K6
+(every fourth layer K8), an attention stand-in over a fixed cache of 8192 random fp16 positions (16 query / 2 KV heads of
+dimension 256), and the MoE block: 512 routed experts (top-10, intermediate 768, K5) plus one shared expert (K6) -- for
+`--batch` concurrent sequences x `--verify` tokens each (default 2 x 4 = 8 rows per GPU). The whole step runs inside
+libijah_b200.so behind ne_fn_model_* and is replayed from a CUDA graph the library owns; weights are generated on the
+device by the library (about 75 GB resident on one GPU). value = rows / step time.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--rows M] [--layers L] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--verify M] [--impl reference] [--workload stack|block]
 
-N > 1 (under torchrun): expert parallel. Every rank holds experts/N experts of every layer and `rows` rows of its own;
-rows are all-gathered, each rank runs the routed experts it owns for all rows, partial outputs are reduce-scattered
-(NCCL) and the shared expert runs on the rank's own rows. value = N * rows * layers / step time (weak scaling).
+N > 1 (under torchrun): expert parallel, weak scaling. Every rank holds experts/N experts of every layer and B x M rows of
+its own; per MoE block the ranks exchange rows and partial outputs over NVLink peer memory (the library's own kernels),
+everything else is replicated. value = N * rows / step time. Rank 0 also holds the full model and checks the ranks' logits
+against a single-GPU step over all rows (`ep_check`).
+
+`e2e` is the same step through ne_fn_model_step_rows with the token ids in host memory and the sampled ids copied back.
+`roofline` is the dominant kernel (the gate/up stream GEMM of the MoE block) timed alone over layers with distinct weights.
+`--workload block` times the MoE block alone (the earlier headline; also what the ncu recipes under profiles/ run).
 
 --impl reference: the CPU restatement of the reference's operator path (oracle/, C with all host threads) on a bounded
-sample of the same workload; the reference's own code for this path is Metal / numpy-with-a-missing-module and cannot
-run on this box.
+sample of the same workload; the reference's own code for this path is Metal / numpy-with-a-missing-module and cannot run
+on this box.
 """
 import argparse
 import json
@@ -21,7 +29,6 @@ import os
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 from pathlib import Path
 
@@ -32,10 +39,10 @@ sys.path.insert(0, str(ROOT))
 
 DIMS = dict(hidden=2048, inter=768, experts=512, k_expert=5, k_shared=6)
 TOPK = 10
-METRIC = "EXL3 MoE decode tok/s (rows through one MoE block)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up stream_gemm launch by rows, from the ncu captures
-# summarised under profiles/ (rows without a capture report null)
-NCU_TRAFFIC = {4: 79.48e6 + 3.25e6}
+STACK = dict(layers=48, hidden=2048, inter=768, experts=512, top_k=TOPK, k_expert=5, k_shared=6, q_out=4096, kv_out=512, heads=16,
+             kv_heads=2, head_dim=256, k_trunk=6, k_trunk_alt=8, alt_every=4, vocab=151936, kv_positions=8192)
+METRIC = "EXL3 MoE decoder stack decode tok/s"
+BLOCK_METRIC = "EXL3 MoE decode tok/s (rows through one MoE block)"
 
 
 def peaks():
@@ -46,7 +53,7 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples during the timed region (read-only query)."""
+    """nvidia-smi clock / throttle-reason samples during the timed regions (read-only query)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -73,7 +80,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for line in Path(self.path).read_text().splitlines():
             c = [x.strip() for x in line.split(",")]
             if len(c) < 9:
@@ -81,6 +88,7 @@ class ClockSampler:
             try:
                 sm.append(float(c[1]))
                 mx.append(float(c[2]))
+                pw.append(float(c[3]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
@@ -88,206 +96,219 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if sm:
-            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            busy = [s for s, p in zip(sm, pw) if p > 0.5 * max(pw)]  # samples taken under load
+            out = {"sm_mhz": float(np.median(busy or sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                   "samples_under_load": len(busy), "power_w_max": max(pw)}
         return out
 
 
-def cpu_port_tokens_per_s(rows, budget_s):
-    """The C oracle (device-arithmetic restatement) on the host cores: MoE blocks of `rows` rows on a 64-expert layer
-    of the benchmark's dims (the work per row is the same: 10 routed experts + the shared expert), repeated until
-    about `budget_s` seconds have passed."""
-    from ijah_b200 import packgen
+# ---------------------------------------------------------------------------------------------- CPU legs (oracle/)
+_CPU_LAYER = {}
+
+
+def cpu_layer():
+    """one full-size MoE layer (512 experts) and one trunk layer as host arrays for the CPU legs"""
+    if not _CPU_LAYER:
+        from ijah_b200 import packgen
+        rng = np.random.default_rng(0)
+        _CPU_LAYER["moe"] = packgen.moe_layer(rng, **DIMS)
+        _CPU_LAYER["trunk"] = packgen.trunk_layer(rng, hidden=STACK["hidden"], q_out=STACK["q_out"], kv_out=STACK["kv_out"], K=6)
+    return _CPU_LAYER["moe"], _CPU_LAYER["trunk"]
+
+
+def cpu_port_layer_seconds(rows, budget_s):
+    """The C oracle (device-arithmetic restatement of the reference's operators, all host threads) on ONE decoder layer of
+    the workload: the four trunk projections and the MoE block (router, top-10 of 512 experts, shared expert) for `rows`
+    rows, repeated until about budget_s seconds have passed. Returns (seconds per layer, threads, layers done)."""
     from oracle import c_oracle as CO
-    rng = np.random.default_rng(0)
-    t = packgen.moe_layer(rng, hidden=DIMS["hidden"], inter=DIMS["inter"], experts=64, k_expert=DIMS["k_expert"], k_shared=DIMS["k_shared"])
-    x = rng.standard_normal((rows, DIMS["hidden"])).astype(np.float16).astype(np.float32)
-    CO.moe_block_emul(t, x[:1], top_k=TOPK)
+    moe, trunk = cpu_layer()
+    pre = "language_model.model.layers.0.self_attn."
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((rows, STACK["hidden"])).astype(np.float16).astype(np.float32)
+    xo = rng.standard_normal((rows, STACK["q_out"])).astype(np.float16).astype(np.float32)
+
+    def layer():
+        for p_ in ("q", "k", "v"):
+            CO.linear_emul(trunk[pre + p_ + "_proj.trellis"][1], trunk[pre + p_ + "_proj.suh"][1], trunk[pre + p_ + "_proj.svh"][1], x)
+        CO.linear_emul(trunk[pre + "o_proj.trellis"][1], trunk[pre + "o_proj.suh"][1], trunk[pre + "o_proj.svh"][1], xo)
+        CO.moe_block_emul(moe, x, top_k=TOPK)
+
     n, t0 = 0, time.perf_counter()
     while True:
-        CO.moe_block_emul(t, x, top_k=TOPK)
+        layer()
         n += 1
         el = time.perf_counter() - t0
-        if el > budget_s or n >= 1000:
+        if el > budget_s or n >= 200:
             break
-    return rows * n / el, CO.threads(), f"{n} MoE blocks of {rows} rows on a 64-expert layer of the same dims ({el:.1f} s)"
+    return el / n, CO.threads(), n
+
+
+def cpu_numpy_row_seconds():
+    """The numpy restatement of the reference's tools/opref.py operators (float64 dense reconstruction of every touched
+    expert, BLAS threads as numpy has them) on ONE row of one MoE block. Returns seconds."""
+    from oracle import c_oracle as CO
+    from oracle import opref_port as O
+    moe, _ = cpu_layer()
+    pre = "language_model.model.layers.0.mlp."
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((1, STACK["hidden"])).astype(np.float16).astype(np.float32)
+
+    def lin(tr, su, sv):
+        l = O.Exl3Linear(tr, su, sv)
+        l._inner = CO.decode_inner(l.trellis)  # the codec table lookup itself in C: the numpy codec would take most of the time
+        return l
+
+    def expert(e):
+        return tuple(lin(moe[f"{pre}switch_mlp.{p}_proj.trellis"][1][e], moe[f"{pre}switch_mlp.{p}_proj.suh"][1][e],
+                         moe[f"{pre}switch_mlp.{p}_proj.svh"][1][e]) for p in ("gate", "up", "down"))
+
+    shared = tuple(lin(moe[f"{pre}shared_expert.{p}_proj.trellis"][1], moe[f"{pre}shared_expert.{p}_proj.suh"][1],
+                       moe[f"{pre}shared_expert.{p}_proj.svh"][1]) for p in ("gate", "up", "down"))
+    t0 = time.perf_counter()
+    O.moe_block_exact(x, O.bf16_bits_to_f32(moe[pre + "gate.weight"][1]), O.bf16_bits_to_f32(moe[pre + "shared_expert_gate.weight"][1]), expert,
+                      shared, TOPK)
+    return time.perf_counter() - t0
+
+
+def stack_config(a, rows):
+    return {"workload": f"decoder stack decode step: {a.layers} layers (EXL3 trunk q/k/v/o K6/K8 + attention stand-in over 8192 cached positions + "
+                        f"MoE block 512 experts top-10 K5 + shared K6), bf16 LM head 151936 x 2048; {a.batch} sequences x {a.verify} verify "
+                        f"tokens = {rows} rows per GPU",
+            "arithmetic": "weights decoded to f16, f16 activations, f32 accumulate", "rows": rows, "layers": a.layers,
+            "l2": "weights of a step (tens of GB) exceed L2", "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
 
 
 def run_reference(a, rank):
     if rank != 0:
         return
+    rows = a.batch * a.verify if a.workload == "stack" else a.rows
     per_step = max(2.0, min(20.0, 120.0 / max(a.steps + a.warmup, 1)))
-    vals = []
+    vals, cores, done = [], 1, 0
     for i in range(a.warmup + a.steps):
-        v, cores, sample = cpu_port_tokens_per_s(a.rows, per_step)
+        sec, cores, n = cpu_port_layer_seconds(rows, per_step)
+        done = n
         if i >= a.warmup:
-            vals.append(v)
-    v = float(np.mean(vals))
+            vals.append(sec)
+    sec = float(np.mean(vals))
+    layers = a.layers if a.workload == "stack" else 1
+    v = rows / (sec * layers)
+    sample = (f"each step: {done} x one decoder layer (4 trunk projections + MoE block on a full 512-expert layer) for {rows} rows in the C "
+              f"port; tok/s = rows / (seconds per layer x {layers} layers); LM head and attention stand-in not included")
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": a.gpus, "steps": a.steps,
-        "warmup": a.warmup, "ms_per_step": 1e3 * a.rows / v, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC if a.workload == "stack" else BLOCK_METRIC, "value": v, "unit": "tok/s", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 * rows / v, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": workload_config(a),
+        "config": stack_config(a, rows) if a.workload == "stack" else block_config(a),
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
-def workload_config(a):
+def block_config(a):
     return {"workload": f"MoE block decode: hidden 2048, 512 experts top-10, inter 768, K5 routed + K6 shared, rows {a.rows}",
-            "arithmetic": "weights decoded to f16, f16 activations, f32 accumulate", "rows": a.rows, "layers": a.layers, "l2": "weights of a step exceed L2 (distinct layers cycled)",
-            "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
+            "arithmetic": "weights decoded to f16, f16 activations, f32 accumulate", "rows": a.rows, "layers": a.layers,
+            "l2": "weights of a step exceed L2 (distinct layers cycled)", "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
 
 
-def run_stack(a, rank, world):
-    """--workload stack: one decode step of `--rows` rows through a random-init decoder stack of `--layers` layers (default
-    48): per layer the four trunk projections (q 2048->4096, k, v 2048->512, o 4096->2048; K6, every fourth layer K8), a
-    stand-in for attention (the o projection takes the q output), the MoE block with residual adds, and at the end the bf16
-    LM head (151936 x 2048, a library GEMM). N > 1: experts sharded, everything else replicated, M rows per rank."""
+# ---------------------------------------------------------------------------------------------- MoE block figures
+def block_figures(eng, rows, layers, steps, dev, want_kernels=True):
+    """The MoE block alone at `rows` rows over `layers` layers with distinct weights (one CUDA graph per pass): block time and,
+    timed alone, the gate/up and down stream-GEMM launches. Returns a dict; frees its weights."""
     import torch
-    import torch.distributed as dist
     from ijah_b200 import engine as E
     from ijah_b200 import synth
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    eng = E.Engine()
-    N, M, L = world, a.rows, a.layers
-    H, Ex, V = DIMS["hidden"], DIMS["experts"], 151936
-    per = Ex // N
-    blocks, trunks, wbytes = [], [], 0
-    for l in range(L):
-        t = synth.moe_layer(1000 + l, expert_first=rank * per, expert_count=per, router_seed=77 + l, device=dev, **DIMS)
-        blocks.append(E.MoeBlock(eng, t, top_k=TOPK, max_rows=M * N, expert_first=rank * per, expert_count=per, device=dev))
-        K = 8 if l % 4 == 3 else 6
-        tl = synth.trunk_layer(500 + l, K=K, device=dev)
-        trunks.append({n: E.Exl3Linear.from_device(eng, *w) for n, w in tl.items()})
-        wbytes += sum(w[0].numel() * 2 + w[1].numel() * 2 + w[2].numel() * 2 for w in tl.values())
-    g = torch.Generator(device=dev).manual_seed(5 + rank)
-    head = (torch.randn((V, H), device=dev, generator=g) * 0.02).to(torch.bfloat16)
-    x0 = torch.randn((M, H), device=dev, generator=g).to(torch.float16).to(torch.float32)
-    x, q, kk, vv, o, y = (torch.empty((M, n), device=dev) for n in (H, 4096, 512, 512, H, H))
-    logits = torch.empty((M, V), device=dev, dtype=torch.bfloat16)
-    tok = torch.empty((M,), device=dev, dtype=torch.int64)
-    if N > 1:
-        from ijah_b200 import ep
-        eps = [ep.ExpertParallelMoe(b, dist.group.WORLD) for b in blocks]
-
-    xn = torch.empty_like(x)
-    norm = torch.nn.functional.rms_norm
-
-    def step():
-        x.copy_(x0)
-        for l in range(L):
-            tr = trunks[l]
-            xn.copy_(norm(x, (H,)))     # the two RMS norms of a layer are stand-ins too (no learned scale)
-            E.linear_multi(eng, (tr["q"], tr["k"], tr["v"]), xn, (q, kk, vv))  # one launch chain for the three
-            tr["o"].into(q, o)          # attention stand-in: its output has the q width
-            x.add_(o)
-            xn.copy_(norm(x, (H,)))
-            if N == 1:
-                blocks[l].forward(xn, out=y)
-            else:
-                eps[l].forward(xn, out=y)
-            x.add_(y)
-        torch.matmul(norm(x, (H,)).to(torch.bfloat16), head.t(), out=logits)
-        torch.argmax(logits, dim=1, out=tok)
-
-    def barrier():
-        if N > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(a.warmup):
-        step()
-    barrier()
-    graph = None
-    if N == 1:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        graph.replay()
-    run = graph.replay if graph is not None else step
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(a.steps):
-        run()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    # end to end: the step's input rows from pinned host memory, the sampled token ids back
-    xh, th = x0.cpu().pin_memory(), torch.empty((M,), dtype=torch.int64).pin_memory()
-    for _ in range(2):
-        x0.copy_(xh, non_blocking=True); run(); th.copy_(tok, non_blocking=True); torch.cuda.synchronize()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(a.steps):
-        x0.copy_(xh, non_blocking=True); run(); th.copy_(tok, non_blocking=True); torch.cuda.synchronize()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    if N > 1:
-        tt = torch.tensor([ms, e2e_s], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(tt[0].item()), float(tt[1].item())
-    clocks = sampler.stop() if rank == 0 else None
-    ms_per_step = ms / a.steps
-    moe_bytes = float(np.mean([b.last_bytes(M * N if N > 1 else M)["total"] for b in blocks])) * L
-    total_bytes = moe_bytes + wbytes + V * H * 2
     peak, which = peaks()
+    H = DIMS["hidden"]
+    blocks = [E.MoeBlock(eng, synth.moe_layer(1000 + l, router_seed=77 + l, device=dev, **DIMS), top_k=TOPK, max_rows=rows, device=dev)
+              for l in range(layers)]
+    g = torch.Generator(device=dev).manual_seed(5)
+    xs = [torch.randn((rows, H), device=dev, generator=g).to(torch.float16).to(torch.float32) for _ in range(layers)]
+    ys = [torch.empty((rows, H), device=dev) for _ in range(layers)]
+
+    def timed_graph(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        gk = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gk):
+            fn()
+        gk.replay()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(n):
+            gk.replay()
+        k1.record()
+        torch.cuda.synchronize()
+        return k0.elapsed_time(k1) * 1e3 / n / layers
+
+    def fwd():
+        for l in range(layers):
+            blocks[l].forward(xs[l], out=ys[l])
+
+    def stage(code):
+        def f():
+            for l in range(layers):
+                blocks[l].stage(code, xs[l], ys[l])
+        return f
+
+    n = max(5, min(steps, 20))
+    out = {"rows": rows, "block_us": timed_graph(fwd, n)}
+    lbs = [b.last_bytes(rows) for b in blocks]
+    out["block_bytes"] = float(np.mean([x["total"] for x in lbs]))
+    out["block_gbs"] = out["block_bytes"] / out["block_us"] / 1e3
+    out["distinct_experts_mean"] = float(np.mean([x["distinct_experts"] for x in lbs]))
+    if want_kernels:
+        for c in (7, 80):
+            stage(c)()
+        gu_us = timed_graph(stage(81), n)
+        for c in (81, 90):
+            stage(c)()
+        dn_us = timed_graph(stage(91), n)
+        gu_b = float(np.mean([x["gateup"] for x in lbs]))
+        dn_b = float(np.mean([x["down"] for x in lbs]))
+        out.update(gateup_us=gu_us, gateup_bytes=gu_b, gateup_gbs=gu_b / gu_us / 1e3, gateup_frac=gu_b / gu_us / 1e3 / peak,
+                   down_us=dn_us, down_bytes=dn_b, down_gbs=dn_b / dn_us / 1e3, down_frac=dn_b / dn_us / 1e3 / peak)
     status = eng.lib.ne_device_wait_status()
-    if rank == 0:
-        per_layer = 6 + 2 * 3  # MoE block, q/k/v chain, o chain
-        print(json.dumps({
-            "metric": "EXL3 MoE decoder stack decode tok/s", "value": N * M / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": N,
-            "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"decoder stack decode step: {L} layers (trunk q/k/v/o K6/K8 + MoE block 512 experts top-10 K5 + shared K6), "
-                                   f"bf16 LM head 151936 x 2048, rows {M}, attention left as a stand-in",
-                       "rows": M, "layers": L, "l2": "weights of a step exceed L2", "graph": graph is not None,
-                       "parallelism": "single GPU" if N == 1 else f"ep{N}"},
-            "e2e": {"value": N * M * a.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * H * 4, "d2h_bytes_per_step": M * 8},
-            "gpu_launches": per_layer * L * a.steps, "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "whole step (all launches)", "achieved": total_bytes / (ms_per_step * 1e-3) / 1e9, "peak": peak,
-                         "unit": "GB/s", "frac": total_bytes / (ms_per_step * 1e-3) / 1e9 / peak, "peak_source": which + " (stream copy)",
-                         "traffic": None, "bytes_per_step": total_bytes},
-            "cpu_baseline": None, "extra": {"weights_gb_resident": (wbytes + V * H * 2 + L * per * 2966016) / 1e9}, "wait_status": status}))
-    if N > 1:
-        dist.destroy_process_group()
+    assert status == 0, f"a device-side bounded wait gave up ({status})"
+    for b in blocks:
+        b.free()
+    del blocks, xs, ys
+    torch.cuda.empty_cache()
+    return out
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--rows", type=int, default=4)
-    ap.add_argument("--layers", type=int, default=8)
-    ap.add_argument("--impl", default="ours")
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill figure in extra (0 = skip)")
-    ap.add_argument("--nccl-exchange", action="store_true", help="N > 1: exchange rows and partial outputs with NCCL collectives "
-                    "instead of the peer-memory kernels")
-    ap.add_argument("--workload", default="block", choices=["block", "stack"],
-                    help="block: the MoE block (headline); stack: a whole random-init decoder stack step (see run_stack)")
-    a = ap.parse_args()
-    a.warmup = max(a.warmup, 3)
-    rank = int(os.environ.get("RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    if a.impl == "reference":
-        return run_reference(a, rank)
-    if a.workload == "stack":
-        if "--layers" not in sys.argv:
-            a.layers = 48
-        return run_stack(a, rank, world)
+def prefill_figure(eng, n_pf, dev):
+    import torch
+    from ijah_b200 import engine as E
+    from ijah_b200 import synth
+    last = synth.moe_layer(1007, router_seed=84, device=dev, **DIMS)
+    synth.zipf_router_bias(last)
+    pblk = E.MoeBlock(eng, last, top_k=TOPK, max_rows=16, device=dev)
+    gp = torch.Generator(device=dev).manual_seed(99)
+    xp = torch.randn((n_pf, DIMS["hidden"]), device=dev, generator=gp).to(torch.float16).to(torch.float32)
+    xp[:, 0] = 1.0
+    yp = torch.empty_like(xp)
+    for _ in range(3):
+        pblk.prefill(xp, out=yp)
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for _ in range(5):
+        pblk.prefill(xp, out=yp)
+    p1.record()
+    torch.cuda.synchronize()
+    pms = p0.elapsed_time(p1) / 5
+    flop = n_pf * TOPK * 3 * 2 * DIMS["hidden"] * DIMS["inter"]
+    tpeak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"] if (ROOT / "MEASURED_PEAKS.json").exists() else 1590.0
+    pblk.free()
+    return {"tokens": n_pf, "ms": pms, "tok_per_s": n_pf / pms * 1e3, "routed_tflops": flop / pms / 1e9,
+            "frac_of_dense_f16_peak": flop / pms / 1e9 / tpeak, "routing": "Zipf(1.1) bias on the router logits"}
 
+
+# ---------------------------------------------------------------------------------------------- the stack (headline)
+def run_stack(a, rank, world):
     import torch
     import torch.distributed as dist
     from ijah_b200 import engine as E
-    from ijah_b200 import synth
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -295,199 +316,182 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE {world}"
     eng = E.Engine()
-    N, M, L = world, a.rows, a.layers
-    H, Ex = DIMS["hidden"], DIMS["experts"]
-    per = Ex // N
-    blocks = []
-    for l in range(L):
-        t = synth.moe_layer(1000 + l, expert_first=rank * per, expert_count=per, router_seed=77 + l, device=dev, **DIMS)
-        blocks.append(E.MoeBlock(eng, t, top_k=TOPK, max_rows=M * N, expert_first=rank * per, expert_count=per, device=dev))
-    g = torch.Generator(device=dev).manual_seed(5 + rank)
-    xs = [torch.randn((M, H), device=dev, generator=g).to(torch.float16).to(torch.float32) for _ in range(L)]
-    ys = [torch.empty((M, H), device=dev) for _ in range(L)]
-    launches_per_block = 6  # router + plan, operand prep, gate/up, SwiGLU + prep, down, combine
-
-    if N == 1:
-        def step():
-            for l in range(L):
-                blocks[l].forward(xs[l], out=ys[l])
-    else:
+    N, rows = world, a.batch * a.verify
+    assert rows * N <= 64, f"{rows} rows x {N} ranks: the decode-width MoE block takes at most 64 gathered rows"
+    per = STACK["experts"] // N
+    desc = dict(STACK, layers=a.layers, expert_first=rank * per, expert_count=per, ep_world=N)
+    max_rows = 64 if N == 1 else rows
+    model = eng.fn_model(desc=desc, seed=a.seed, max_rows=max_rows)
+    xchg = None
+    if N > 1:
         from ijah_b200 import ep
-        eps = [ep.ExpertParallelMoe(blocks[l], dist.group.WORLD) for l in range(L)]
-        launches_per_block = eps[0].launches
-        if not a.nccl_exchange:
-            # both exchange steps of a block over NVLink peer memory (no library collective in the block): + dispatch and sum kernels
-            xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, M, H, TOPK)
-            if xchg is not None:
-                launches_per_block += 2
-                for e_ in eps:
-                    e_.use_exchange(xchg)
-            else:
-                a.nccl_exchange = True
-        exchange = "nccl" if a.nccl_exchange else "nvlink peer memory (own kernels)"
-
-        def step():
-            for l in range(L):
-                eps[l].forward(xs[l], out=ys[l])
+        xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, rows, STACK["hidden"], TOPK)
+        assert xchg is not None, "the NVLink peer-memory exchange could not be set up on every rank"
+        model.set_ep(xchg)
 
     def barrier():
         if N > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    rng = np.random.default_rng(100 + rank)
+    tokens = rng.integers(0, STACK["vocab"], rows).astype(np.int32)
     for _ in range(a.warmup):
-        step()
+        model.step_rows(tokens)
     barrier()
-    graph = None
-    if N == 1:  # one captured graph per step: launch gaps of the 6-kernel block are what a graph removes
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        graph.replay()
-    # N > 1: eager steps. Capturing the step with its two NCCL collectives per block into a CUDA graph did not come back
-    # on 2 GPUs (the call ran into its time limit), so the expert-parallel step is not captured.
-    run = graph.replay if graph is not None else step
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- value: exactly K replays of the captured step, inputs resident, device-timed on the model's stream
     barrier()
-    e0.record()
-    for _ in range(a.steps):
-        run()
-    e1.record()
+    ms = model.replay(rows, a.steps)
     barrier()
-    ms = e0.elapsed_time(e1)
-    if N > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / a.steps
-    value = N * M * L / (ms_per_step * 1e-3)
-
-    # ---- end to end through the host-buffer entry point: pinned x in, y out, every block
-    xh = [x.cpu().pin_memory() for x in xs]
-    yh = [torch.empty((M, H)).pin_memory() for _ in range(L)]
-    if N == 1:
-        def e2e_step():
-            for l in range(L):
-                blocks[l].forward_host(xh[l], out=yh[l])
-    else:
-        def e2e_step():
-            for l in range(L):
-                xs[l].copy_(xh[l], non_blocking=True)
-                eps[l].forward(xs[l], out=ys[l])
-                yh[l].copy_(ys[l], non_blocking=True)
-            torch.cuda.synchronize()
-    for _ in range(3):
-        e2e_step()
-    barrier()
+    # ---- e2e: K steps through the host-buffer entry point (token ids in, sampled ids out), wall clock
     t0 = time.perf_counter()
     for _ in range(a.steps):
-        e2e_step()
+        nxt, _, _ = model.step_rows(tokens)
     barrier()
     e2e_s = time.perf_counter() - t0
+    # ---- sustained: at least about 2 s of back-to-back replays (clocks settle under load)
+    k_sus = max(a.steps, int(2000.0 / max(ms / a.steps, 1e-3)) + 1) if a.sustain else 0
+    ms_sus = model.replay(rows, k_sus) if k_sus else None
+    barrier()
     if N > 1:
-        t = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e = {"value": N * M * L * a.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * H * 4 * L, "d2h_bytes_per_step": M * H * 4 * L}
+        tt = torch.tensor([ms, e2e_s, ms_sus or 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_s, ms_sus = float(tt[0]), float(tt[1]), float(tt[2]) or None
     clocks = sampler.stop() if rank == 0 else None
-
-    # ---- roofline of the dominant kernel: the gate/up stream_gemm launch (routed experts + shared expert), timed alone.
-    # The router and the operand prep of every layer run first (untimed), then one graph holding only the L gate/up
-    # launches (L distinct weight sets, far larger than L2) is replayed between CUDA events on its stream.
-    roof, extra = None, {}
-    if N == 1:
-        peak, which = peaks()
-
-        def kernel_us(code, before):
-            for l in range(L):
-                for c in before:
-                    blocks[l].stage(c, xs[l], ys[l])
-            torch.cuda.synchronize()
-            gk = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gk):
-                for l in range(L):
-                    blocks[l].stage(code, xs[l], ys[l])
-            gk.replay()
-            torch.cuda.synchronize()
-            n = max(3, min(a.steps, 10))
-            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            k0.record()
-            for _ in range(n):
-                gk.replay()
-            k1.record()
-            torch.cuda.synchronize()
-            return k0.elapsed_time(k1) * 1e3 / n / L
-
-        gu_us = kernel_us(81, (7, 80))
-        dn_us = kernel_us(91, (81, 90))
-        lbs = [blocks[l].last_bytes(M) for l in range(L)]
-        gu_b = float(np.mean([x["gateup"] for x in lbs]))
-        dn_b = float(np.mean([x["down"] for x in lbs]))
-        tot = float(np.mean([x["total"] for x in lbs]))
-        ach = gu_b / gu_us / 1e3
-        traffic = NCU_TRAFFIC.get(M)
-        roof = {"bound": "hbm", "kernel": "stream_gemm_kernel<MoeGateUpProblem> (gate/up of routed + shared experts)",
-                "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": which + " (stream copy)",
-                "traffic": traffic, "bytes_per_launch": gu_b, "us_per_launch": gu_us}
-        extra = {"down_kernel": {"achieved": dn_b / dn_us / 1e3, "us": dn_us, "bytes_per_launch": dn_b},
-                 "distinct_experts_mean": float(np.mean([x["distinct_experts"] for x in lbs])),
-                 "block": {"bytes": tot, "us": ms_per_step * 1e3 / L, "achieved": tot / (ms_per_step * 1e-3 / L) / 1e9,
-                           "frac": tot / (ms_per_step * 1e-3 / L) / 1e9 / peak}}
-    # ---- prefill (config 4): one block over 4096 tokens with Zipf(1.1)-skewed routing; N > 1: the same 4096 tokens split
-    # over the ranks (strong scaling), all-gather + expert-parallel prefill + reduce-scatter
-    n_pf = a.prefill_tokens
-    if n_pf > 0:
-        last = synth.moe_layer(1000 + L - 1, expert_first=rank * per, expert_count=per, router_seed=77 + L - 1, device=dev, **DIMS)
-        synth.zipf_router_bias(last)
-        pblk = E.MoeBlock(eng, last, top_k=TOPK, max_rows=16, expert_first=rank * per, expert_count=per, device=dev)
-        gp = torch.Generator(device=dev).manual_seed(99 + rank)
-        xp = torch.randn((n_pf // N, H), device=dev, generator=gp).to(torch.float16).to(torch.float32)
-        xp[:, 0] = 1.0
-        yp = torch.empty_like(xp)
-        if N == 1:
-            def pf_step():
-                pblk.prefill(xp, out=yp)
-        else:
-            pep = ep.ExpertParallelMoe(pblk, dist.group.WORLD)
-
-            def pf_step():
-                pep.forward(xp, out=yp, prefill=True)
-        for _ in range(3):
-            pf_step()
-        barrier()
-        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        p0.record()
-        for _ in range(5):
-            pf_step()
-        p1.record()
-        barrier()
-        pms = p0.elapsed_time(p1) / 5
-        if N > 1:
-            tt = torch.tensor([pms], device=dev)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            pms = float(tt.item())
-        flop = n_pf * TOPK * 3 * 2 * DIMS["hidden"] * DIMS["inter"]
-        tpeak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"] if (ROOT / "MEASURED_PEAKS.json").exists() else 1590.0
-        extra["prefill"] = {"tokens": n_pf, "ms": pms, "tok_per_s": n_pf / pms * 1e3, "routed_tflops": flop / pms / 1e9,
-                            "frac_of_dense_f16_peak": flop / pms / 1e9 / tpeak / N, "scaling": "strong" if N > 1 else None,
-                            "routing": "Zipf(1.1) bias on the router logits"}
+    ms_per_step = ms / a.steps
+    value = N * rows / (ms_per_step * 1e-3)
+    info = model.info()
+    lb = model.last_bytes(rows)
+    wbytes = model.weight_bytes()
     status = eng.lib.ne_device_wait_status()
+    peak, which = peaks()
+    extra = {"weights_gb_resident": wbytes / 1e9, "distinct_experts_per_layer": lb["distinct_experts_mean"],
+             "step": {"bytes": lb["total"], "gbs": lb["total"] / (ms_per_step * 1e-3) / 1e9, "frac_of_hbm": lb["total"] / (ms_per_step * 1e-3) / 1e9 / peak},
+             "graph": True, "exchange": "nvlink peer memory (own kernels)" if N > 1 else None}
+    if ms_sus:
+        extra["sustained"] = {"steps": k_sus, "seconds": ms_sus * 1e-3, "tok_per_s": N * rows * k_sus / (ms_sus * 1e-3)}
+        if clocks and clocks.get("sm_mhz"):
+            extra["sustained"]["sm_mhz_median_under_load"] = clocks["sm_mhz"]
+            extra["sustained"]["mcycles_per_step"] = ms_sus / k_sus * 1e-3 * clocks["sm_mhz"]
+
+    # ---- expert parallel: every rank's logits against a single-GPU step over all rows on rank 0 (outside the timed regions)
+    if N > 1:
+        nx, lg, _ = model.step_rows(tokens, want_logits=True)
+        all_tok, all_lg = [None] * N, [None] * N
+        dist.gather_object(tokens, all_tok if rank == 0 else None, dst=0)
+        dist.gather_object(lg, all_lg if rank == 0 else None, dst=0)
+        if rank == 0:
+            full = eng.fn_model(desc=dict(STACK, layers=a.layers, expert_first=0, expert_count=0, ep_world=1), seed=a.seed, max_rows=rows * N)
+            fnx, flg, _ = full.step_rows(np.concatenate(all_tok), want_logits=True)
+            got = np.concatenate(all_lg)
+            extra["ep_check"] = {"max_rel_err": float(np.abs(got - flg).max() / np.abs(flg).max()),
+                                 "next_equal": bool(np.array_equal(got.argmax(1), fnx)), "rows": int(rows * N)}
+            full.free()
+        dist.barrier()
+    model.free()
+    if xchg is not None:
+        xchg.free(barrier=lambda: dist.barrier())
+    torch.cuda.empty_cache()
+
+    roof, cpu = None, None
+    if N == 1 and rank == 0:
+        # ---- roofline of the dominant kernel: the gate/up stream-GEMM launch at this row count, timed alone over 8 layers
+        bf = block_figures(eng, rows, 8, a.steps, dev)
+        roof = {"bound": "hbm", "kernel": "stream_gemm_kernel<MoeGateUpProblem> (gate/up of routed + shared experts)",
+                "achieved": bf["gateup_gbs"], "peak": peak, "unit": "GB/s", "frac": bf["gateup_frac"], "peak_source": which + " (stream copy)",
+                "traffic": None, "bytes_per_launch": bf["gateup_bytes"], "us_per_launch": bf["gateup_us"]}
+        if clocks and clocks.get("sm_mhz"):
+            roof["kcycles_per_launch_at_median_mhz"] = bf["gateup_us"] * clocks["sm_mhz"] * 1e-3
+        extra["block"] = {str(rows): bf}
+        if a.extras:
+            for r in (1, 4, 16):
+                if r != rows:
+                    extra["block"][str(r)] = block_figures(eng, r, 8, a.steps, dev)
+            extra["prefill"] = prefill_figure(eng, 4096, dev)
+            big = eng.fn_model(desc=dict(STACK, layers=a.layers, ep_world=1, expert_first=0, expert_count=0), seed=a.seed, max_rows=64)
+            extra["stack_rows"] = {}
+            for r in (4, 64):
+                big.step_rows(np.zeros(r, np.int32))
+                t = big.replay(r, 5) / 5
+                extra["stack_rows"][str(r)] = {"ms_per_step": t, "tok_per_s": r / t * 1e3}
+            big.free()
+        if a.cpu_seconds > 0:
+            sec, cores, n = cpu_port_layer_seconds(rows, a.cpu_seconds)
+            cpu = {"value": rows / (sec * a.layers), "unit": "tok/s", "cores": cores, "kind": "port",
+                   "sample": f"{n} x one decoder layer (4 trunk projections + MoE block on a full 512-expert layer) for {rows} rows in the C port; "
+                             f"tok/s = rows / (seconds per layer x {a.layers} layers); LM head and attention stand-in not included"}
+            t_np = cpu_numpy_row_seconds()
+            extra["cpu_numpy"] = {"seconds_per_block_row": t_np, "tok_per_s": 1.0 / (t_np * a.layers), "threads": os.cpu_count(),
+                                  "sample": "one row of one MoE block in the numpy restatement of the reference's tools/opref.py operators "
+                                            "(float64 dense reconstruction of the 11 touched experts); tok/s = 1 / (seconds x layers), MoE blocks only"}
     if rank == 0:
-        cpu = None
-        if N == 1:
-            v, cores, sample = cpu_port_tokens_per_s(M, a.cpu_seconds)
-            cpu = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps({
-            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": N, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic", "config": dict(workload_config(a), graph=graph is not None, **({"exchange": exchange} if N > 1 else {})),
-            "e2e": e2e, "gpu_launches": launches_per_block * L * a.steps, "clocks": clocks, "roofline": roof,
-            "cpu_baseline": cpu, "extra": extra, "wait_status": status}))
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": N, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": stack_config(a, rows),
+            "e2e": {"value": N * rows * a.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * 4},
+            "gpu_launches": info["launches_full"] * a.steps, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "extra": extra,
+            "wait_status": status}))
     if N > 1:
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------- the MoE block alone
+def run_block(a, rank, world):
+    import torch
+    from ijah_b200 import engine as E
+    assert world == 1, "--workload block is a single-GPU measurement"
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    eng = E.Engine()
+    peak, which = peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    bf = block_figures(eng, a.rows, a.layers, a.steps, dev)
+    clocks = sampler.stop()
+    extra = {"block": bf}
+    if a.prefill_tokens > 0:
+        extra["prefill"] = prefill_figure(eng, a.prefill_tokens, dev)
+    print(json.dumps({
+        "metric": BLOCK_METRIC, "value": a.rows / (bf["block_us"] * 1e-6), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": bf["block_us"] * a.layers * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": block_config(a), "e2e": None, "gpu_launches": 6 * a.layers * a.steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "stream_gemm_kernel<MoeGateUpProblem> (gate/up of routed + shared experts)", "achieved": bf["gateup_gbs"],
+                     "peak": peak, "unit": "GB/s", "frac": bf["gateup_frac"], "peak_source": which + " (stream copy)", "traffic": None,
+                     "bytes_per_launch": bf["gateup_bytes"], "us_per_launch": bf["gateup_us"]},
+        "cpu_baseline": None, "extra": extra, "wait_status": eng.lib.ne_device_wait_status()}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=2, help="concurrent sequences per GPU")
+    ap.add_argument("--verify", type=int, default=4, help="verify tokens per sequence (rows per GPU = batch x verify)")
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-extras", dest="extras", action="store_false", help="skip the extra block / prefill / other-row-count figures")
+    ap.add_argument("--no-sustain", dest="sustain", action="store_false", help="skip the >= 2 s sustained replay")
+    ap.add_argument("--workload", default="stack", choices=["stack", "block"])
+    ap.add_argument("--rows", type=int, default=4, help="--workload block: activation rows")
+    ap.add_argument("--prefill-tokens", type=int, default=0, help="--workload block: tokens of a prefill figure (0 = skip)")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if a.workload == "block" and "--layers" not in " ".join(sys.argv):
+        a.layers = 8
+    if a.impl == "reference":
+        return run_reference(a, rank)
+    if a.workload == "block":
+        return run_block(a, rank, world)
+    return run_stack(a, rank, world)
 
 
 if __name__ == "__main__":

@@ -99,6 +99,13 @@ void make_trellis_map(CUtensorMap *out, const void *base, int E, int IT, int OT,
 }
 
 int sm_count() {
+  {
+    int d0 = 0;
+    if (cudaGetDevice(&d0) != cudaSuccess) {  // planning without a device (B200)
+      cudaGetLastError();
+      return 148;
+    }
+  }
   DeviceState &s = dev_state();
   if (!s.sms) {
     int d = 0;

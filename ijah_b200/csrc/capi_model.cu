@@ -73,7 +73,7 @@ static void check_desc(const ne_fn_model_desc &d, int max_rows) {
   IJ_CHECK(d.heads >= 1 && d.kv_heads >= 1 && d.heads % d.kv_heads == 0, "bad head counts %d / %d", d.heads, d.kv_heads);
   IJ_CHECK(d.q_out == d.heads * d.head_dim && d.kv_out == d.kv_heads * d.head_dim, "q_out / kv_out must be heads * head_dim");
   IJ_CHECK(d.kv_positions >= 64 && d.kv_positions % 64 == 0, "kv_positions %d must be a positive multiple of 64", d.kv_positions);
-  IJ_CHECK(max_rows >= 1 && max_rows <= 64, "max_rows %d outside 1..64", max_rows);
+  IJ_CHECK(max_rows >= 1 && max_rows * std::max(1, d.ep_world) <= 64, "max_rows %d (x %d ranks) outside 1..64", max_rows, std::max(1, d.ep_world));
   IJ_CHECK(d.hidden % 256 == 0, "hidden %d must be a multiple of 256", d.hidden);
 }
 
@@ -174,11 +174,10 @@ cudaGraphExec_t Model::graph_for(int rows, bool with_head) {
 void Model::step(const int *tokens_host, int rows, int with_head, float *logits_host, int *next_host, double *gpu_ms) {
   IJ_CHECK(rows >= 1 && rows <= max_rows, "rows %d outside 1..%d", rows, max_rows);
   IJ_CHECK(tokens_host != nullptr, "null tokens");
-  cudaGraphExec_t ex = ep ? nullptr : graph_for(rows, with_head != 0);  // the expert-parallel step advances an epoch per block: eager
+  cudaGraphExec_t ex = graph_for(rows, with_head != 0);
   IJ_CUDA(cudaMemcpyAsync(tokens, tokens_host, (size_t)rows * 4, cudaMemcpyHostToDevice, stream));
   IJ_CUDA(cudaEventRecord(ev0, stream));
-  if (ex) IJ_CUDA(cudaGraphLaunch(ex, stream));
-  else record(rows, with_head != 0, stream);
+  IJ_CUDA(cudaGraphLaunch(ex, stream));
   IJ_CUDA(cudaEventRecord(ev1, stream));
   if (with_head && next_host) IJ_CUDA(cudaMemcpyAsync(next_host, next, (size_t)rows * 4, cudaMemcpyDeviceToHost, stream));
   if (with_head && logits_host) IJ_CUDA(cudaMemcpyAsync(logits_host, logits, (size_t)rows * d.vocab * 4, cudaMemcpyDeviceToHost, stream));
@@ -374,7 +373,7 @@ static Model *model_synthetic(const ne_fn_model_desc &din, uint64_t seed, int ma
       md.sh_up = synth_linear(*M, d.hidden, d.inter, d.k_shared, ls + 44);
       md.sh_down = synth_linear(*M, d.inter, d.hidden, d.k_shared, ls + 47);
     }
-    L.moe = std::make_unique<Moe>(md, max_rows);
+    L.moe = std::make_unique<Moe>(md, max_rows * std::max(1, d.ep_world));  // expert parallel: the block sees the rows of all ranks
   }
   fill_kv(*M, seed + 5);
   M->finish_setup();
@@ -446,6 +445,23 @@ NE_API int ne_fn_model_step_rows(ne_fn_model *m, const int *tokens_host, int row
     M->step(tokens_host, rows, head, logits_host, next_host, gpu_ms);
   });
 }
+NE_API int ne_fn_model_replay(ne_fn_model *m, int rows, int head, int steps, double *total_ms) {
+  return c_call([&] {
+    Model *M = reinterpret_cast<Model *>(m);
+    IJ_CHECK(M != nullptr && steps >= 1, "bad arguments");
+    IJ_CHECK(rows >= 1 && rows <= M->max_rows, "rows %d outside 1..%d", rows, M->max_rows);
+    cudaGraphExec_t ex = M->graph_for(rows, head != 0);
+    IJ_CUDA(cudaStreamSynchronize(M->stream));
+    IJ_CUDA(cudaEventRecord(M->ev0, M->stream));
+    for (int i = 0; i < steps; i++) IJ_CUDA(cudaGraphLaunch(ex, M->stream));
+    IJ_CUDA(cudaEventRecord(M->ev1, M->stream));
+    IJ_CUDA(cudaStreamSynchronize(M->stream));
+    float ms = 0;
+    IJ_CUDA(cudaEventElapsedTime(&ms, M->ev0, M->ev1));
+    if (total_ms) *total_ms = ms;
+    M->steps += steps;
+  });
+}
 NE_API int ne_fn_model_time(ne_fn_model *m, int T, int reps, double *gpu_ms_median, double *gpu_ms_min, double *wall_ms_median) {
   return c_call([&] {
     Model *M = reinterpret_cast<Model *>(m);
@@ -487,6 +503,7 @@ NE_API int ne_fn_model_set_ep(ne_fn_model *m, ne_ep *e) {
   return c_call([&] {
     Model *M = reinterpret_cast<Model *>(m);
     IJ_CHECK(M != nullptr, "null model");
+    IJ_CHECK(M->graphs.empty(), "set the exchange context before the first step (the captured steps hold the single-GPU blocks)");
     M->ep = reinterpret_cast<EpCtx *>(e);
   });
 }
@@ -533,7 +550,7 @@ NE_API int ne_fn_model_last_bytes(ne_fn_model *m, int rows, uint64_t *total, int
     for (ModelLayer &L : M->layers) {
       uint64_t t = 0;
       int n = 0;
-      IJ_CHECK(ne_moe_last_bytes(reinterpret_cast<ne_moe *>(L.moe.get()), rows, &t, nullptr, nullptr, &n) == 0, "%s", ne_last_error());
+      IJ_CHECK(ne_moe_last_bytes(reinterpret_cast<ne_moe *>(L.moe.get()), rows * std::max(1, M->d.ep_world), &t, nullptr, nullptr, &n) == 0, "%s", ne_last_error());
       b += t + lin(L.q) + lin(L.k) + lin(L.v) + lin(L.o) + 2ull * (uint64_t)M->d.kv_positions * M->d.kv_out * 2;
       nu += n;
     }

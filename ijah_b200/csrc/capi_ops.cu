@@ -24,6 +24,9 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   IJ_CHECK(d.router_dev != nullptr, "null router weights");
   IJ_CHECK(d.expert_count == 0 || (d.gate.trellis_dev && d.up.trellis_dev && d.down.trellis_dev), "null expert weights");
   has_shared = d.shared_gate_w_dev != nullptr && d.sh_gate.trellis_dev != nullptr;
+  // the router reads its rows (and the shared gate) with 16-byte loads; the trellis stacks are checked where their tensor
+  // maps are made
+  IJ_CHECK(((uintptr_t)d.router_dev & 15) == 0 && ((uintptr_t)d.shared_gate_w_dev & 15) == 0, "router / shared-gate weights must be 16-byte aligned");
   for (int r = 1; r <= max_rows; r++) {  // validates dims; scratch is sized for the largest k-split of any row count
     const MoeSplits &sp = splits(r);
     max_S_gu = std::max(max_S_gu, sp.S_gu);
@@ -119,6 +122,8 @@ void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, c
 
 MoeParams Moe::params(const float *x, int rows, float *y) {
   IJ_CHECK(rows >= 1 && rows <= max_rows, "rows %d outside 1..%d", rows, max_rows);
+  // rows are staged with 16-byte asynchronous copies and exchanged as float4: a misaligned view would fault on the device
+  IJ_CHECK(((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0, "activation rows (x, y) must be 16-byte aligned on the device");
   MoeParams p{};
   p.H = desc.hidden; p.I = desc.inter; p.E = desc.experts; p.topk = desc.top_k;
   p.Kx = desc.k_expert; p.Ks = desc.k_shared;
@@ -139,7 +144,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   p.h_mid = h_mid; p.inj = inj; p.h_out = h_out; p.HC = HC;
   p.sh_row0 = 0; p.sh_rows = rows; p.lg_row0 = 0;
   p.ldx = desc.hidden; p.ldr = 2 * desc.top_k;
-  p.ep = nullptr; p.ep_rows = 0; p.ep_epoch = 0;
+  p.ep = nullptr; p.ep_rows = 0;
   return p;
 }
 
@@ -214,6 +219,7 @@ void Moe::forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all,
   if (ld_x > 0) p.ldx = ld_x;
   if (ld_route > 0) p.ldr = ld_route;
   IJ_CHECK(p.ldx >= desc.hidden && p.ldr >= 2 * desc.top_k, "row strides %d / %d too small", p.ldx, p.ldr);
+  IJ_CHECK(p.ldx % 4 == 0, "the row stride of x (%d floats) must keep every row 16-byte aligned", p.ldx);
   IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= rows, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, rows);
   p.route = const_cast<uint32_t *>(route_all);
   p.sh_row0 = own_row0; p.sh_rows = own_rows; p.lg_row0 = own_row0;
@@ -235,22 +241,21 @@ void Moe::forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own,
   IJ_CHECK(rows >= 1 && rows <= c.host.rows_cap && all <= max_rows, "rows %d x %d ranks exceed the context (%d) or the object (%d)", rows, world,
            c.host.rows_cap, max_rows);
   const int W = c.host.W;
-  const uint32_t epoch = ++c.epoch;
   route_rows(x_own, rows, c.route_own, 0, st);
-  launch_ep_exchange(c, x_own, c.route_own, rows, epoch, status, st);
+  launch_ep_exchange(c, x_own, c.route_own, rows, status, st);
   const float *gathered = c.host.gather[c.host.rank];
   MoeParams p = params(gathered, all, y_own);
   p.ldx = W; p.ldr = W;
   p.route = reinterpret_cast<uint32_t *>(const_cast<float *>(gathered) + H);
   p.sh_row0 = c.host.rank * rows; p.sh_rows = rows; p.lg_row0 = p.sh_row0;
-  p.ep = c.dev; p.ep_rows = rows; p.ep_epoch = epoch;
+  p.ep = c.dev; p.ep_rows = rows;
   const MoeSplits &s = splits(all);
   launch_moe_prep(p, true, st);
   launch_moe_gateup(p, maps, s, false, status, st);
   launch_moe_mid(p, st);
   launch_moe_down(p, maps, s, status, st);
   launch_moe_combine(p, false, st);
-  launch_ep_sum(c, rows, epoch, y_own, status, st);
+  launch_ep_sum(c, rows, y_own, status, st);
   last_rows = all;
 }
 
@@ -285,6 +290,26 @@ NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows,
     const LinearPlan p = plan_linear(w->in, w->out, w->K, rows);
     void *scratch = device_scratch(p.scratch_bytes());
     launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, x_dev, y_dev, scratch, device_status_word(), (cudaStream_t)stream);
+  });
+}
+
+NE_API int ne_exl3_linear_plan(int n_in, int n_out, int K, int rows, int *info8, uint64_t *scratch_bytes) {
+  return c_call([&] {
+    const LinearPlan p = plan_linear(n_in, n_out, K, rows);
+    if (info8) {
+      const int v[8] = {p.S, p.kc, p.lay.stages, p.lay.aslots, p.grid, p.MT, (int)p.lay.total(), p.lay.stage_bytes};
+      memcpy(info8, v, sizeof v);
+    }
+    if (scratch_bytes) *scratch_bytes = p.scratch_bytes();
+  });
+}
+NE_API int ne_moe_plan(int hidden, int inter, int experts, int top_k, int k_expert, int k_shared, int rows, int *info8) {
+  return c_call([&] {
+    const MoeSplits s = plan_moe(hidden, inter, experts, top_k, k_expert, k_shared, rows, k_shared > 0);
+    if (info8) {
+      const int v[8] = {s.S_gu, s.kc_gu, s.S_d, s.kc_d, s.lay_gu.stages, s.lay_d.stages, s.grid, (int)std::max(s.lay_gu.total(), s.lay_d.total())};
+      memcpy(info8, v, sizeof v);
+    }
   });
 }
 
@@ -420,8 +445,10 @@ NE_API ne_ep *ne_ep_create(int rank, int world, int rows_cap, int hidden, int to
     IJ_CUDA(cudaMalloc(&c->local, c->bytes));
     IJ_CUDA(cudaMemset(c->local, 0, c->bytes));
     IJ_CUDA(cudaMalloc((void **)&c->route_own, (size_t)rows_cap * 2 * top_k * 4));
-    IJ_CUDA(cudaMalloc((void **)&h.counter, 16));
-    IJ_CUDA(cudaMemset(h.counter, 0, 16));
+    IJ_CUDA(cudaMalloc((void **)&h.counter, 64));  // counter, epoch, ticket: one word each, 16 bytes apart
+    IJ_CUDA(cudaMemset(h.counter, 0, 64));
+    h.epoch = reinterpret_cast<uint32_t *>(h.counter + 4);
+    h.ticket = h.counter + 8;
     IJ_CUDA(cudaMalloc((void **)&c->dev, sizeof(EpDev)));
     IJ_CUDA(cudaDeviceSynchronize());
     out = reinterpret_cast<ne_ep *>(c.release());
@@ -458,6 +485,19 @@ NE_API int ne_ep_connect(ne_ep *e, const void *handles64) {
     c->connected = true;
   });
 }
+NE_API int ne_ep_disconnect(ne_ep *e) {
+  return c_call([&] {
+    EpCtx *c = reinterpret_cast<EpCtx *>(e);
+    IJ_CHECK(c != nullptr, "null argument");
+    IJ_CUDA(cudaDeviceSynchronize());
+    for (int r = 0; r < c->host.world; r++)
+      if (c->peer[r]) { cudaIpcCloseMemHandle(c->peer[r]); c->peer[r] = nullptr; }
+    c->connected = false;
+  });
+}
+// Teardown order across ranks: every rank calls ne_ep_disconnect (closes its mappings of the peers' buffers), the ranks
+// synchronise on the host (a barrier), then each calls ne_ep_free: a buffer must not be freed while a peer still has it
+// mapped. ne_ep_free alone (it closes the mappings first) is enough only once every peer has disconnected or exited.
 NE_API void ne_ep_free(ne_ep *e) {
   EpCtx *c = reinterpret_cast<EpCtx *>(e);
   if (!c) return;

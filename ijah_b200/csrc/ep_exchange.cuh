@@ -25,6 +25,11 @@ struct EpDev {  // lives in device memory of the owning rank; pointers to every 
   uint32_t *gflag[EP_MAX_RANKS];    // rank d's [EP_MAX_RANKS] epochs of arrived rows per source
   uint32_t *pflag[EP_MAX_RANKS];    // rank d's [EP_MAX_RANKS] epochs of arrived partial outputs per source
   unsigned *counter;                // local: CTAs of the combine kernel that have finished
+  // The epoch of the block in flight lives in device memory, so that a block (and a whole decode step) is the same
+  // sequence of launches with the same arguments every time and can be replayed from a CUDA graph: the dispatch kernel
+  // works with *epoch + 1 and its last CTA stores that value; the combine and sum kernels of the block then read it.
+  uint32_t *epoch;                  // local
+  unsigned *ticket;                 // local: CTAs of the dispatch kernel that have read the epoch and sent their rows
 };
 
 struct EpCtx {
@@ -35,11 +40,10 @@ struct EpCtx {
   uint32_t *route_own = nullptr;  // [rows_cap][2 top_k] routes of this rank's rows (the router's output)
   size_t off_gather = 0, off_part = 0, off_flags = 0, bytes = 0;
   int top_k = 0;
-  uint32_t epoch = 0;
   bool connected = false;
 };
 
-void launch_ep_exchange(const EpCtx &c, const float *x_own, const uint32_t *route_own, int rows, uint32_t epoch, int *status, cudaStream_t st);
-void launch_ep_sum(const EpCtx &c, int rows, uint32_t epoch, float *y_own, int *status, cudaStream_t st);
+void launch_ep_exchange(const EpCtx &c, const float *x_own, const uint32_t *route_own, int rows, int *status, cudaStream_t st);
+void launch_ep_sum(const EpCtx &c, int rows, float *y_own, int *status, cudaStream_t st);
 
 }  // namespace ijah

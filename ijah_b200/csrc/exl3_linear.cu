@@ -7,26 +7,41 @@
 
 namespace ijah {
 
+// Shared memory a CTA may use when `ctas` CTAs share an SM.
+static size_t smem_budget(int ctas) { return (size_t)(228 / ctas - 2) * 1024; }
+constexpr int kMinStages = SG_KS >= 16 ? 2 : 3;
+
 StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm) {
   StreamLayout l;
   l.stage_bytes = SG_KS * SG_WARPS * 32 * Kmax;
   l.lda = kcmax * 16 + 8;
   l.arows = std::max(arows, 1);
-  const size_t budget = (size_t)(228 / ctas_per_sm - 2) * 1024;
+  const size_t budget = smem_budget(ctas_per_sm);
   const size_t base = l.ring_off() + (size_t)l.lda * 2;
   const size_t want_stages = SG_KS >= 16 ? 3 : 6;
   // at least three A slots: the producer issues the rows of unit u + 2 while the consumers may still be on unit u
   l.aslots = base + SG_MAX_ASLOTS * l.slot_bytes() + want_stages * (size_t)l.stage_bytes <= budget ? SG_MAX_ASLOTS : 3;
   const size_t fixed = base + l.aslots * l.slot_bytes();
-  IJ_CHECK(fixed + (SG_KS >= 16 ? 2 : 3) * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory", arows, kcmax);
+  IJ_CHECK(fixed + kMinStages * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory", arows, kcmax);
   l.stages = (int)std::min<size_t>(SG_MAX_STAGES, (budget - fixed) / l.stage_bytes);
   return l;
 }
 
-int kc_cap(int arows) {
-  // three A slots may take about 48 KB of the ~110 KB a CTA gets (with two CTAs per SM; less with more)
-  const int cap = ((16 * 1024 * 2 / SG_CTAS / std::max(arows, 1)) - 16) / 32 / SG_KS * SG_KS;
-  return std::max(SG_KS, std::min(cap, 256));
+// Largest k-tile count per unit (a multiple of SG_KS) whose three A slots of `arows` rows leave room for the smallest ring
+// of K = Kmax stages when `ctas` CTAs share an SM; 0 if not even SG_KS k-tiles fit.
+int kc_cap(int arows, int Kmax, int ctas) {
+  const long room = (long)smem_budget(ctas) - 4096 - (long)kMinStages * SG_KS * SG_WARPS * 32 * Kmax;
+  const long halfs_per_row = room / 3 / std::max(arows, 1) / 2;
+  const int cap = (int)((halfs_per_row - 8) / 16) / SG_KS * SG_KS;
+  return std::max(0, std::min(cap, 256));
+}
+
+// CTAs per SM for units of `arows` rows: the default, or one CTA per SM with all of its shared memory when the default
+// cannot hold even the smallest unit (wide row counts at K = 7, 8)
+int stream_ctas(int arows, int Kmax) {
+  if (kc_cap(arows, Kmax, SG_CTAS) >= SG_KS) return SG_CTAS;
+  IJ_CHECK(kc_cap(arows, Kmax, 1) >= SG_KS, "%d activation rows at K%d do not fit the shared memory of an SM", arows, Kmax);
+  return 1;
 }
 
 // Units are dealt round-robin to a persistent grid; cost of a candidate = rounds * (k-tiles per unit + a per-unit
@@ -50,9 +65,10 @@ LinearPlan plan_linear(int in, int out, int K, int rows) {
   p.IT = in / 16; p.OT = out / 16; p.NG = (p.OT + SG_WARPS - 1) / SG_WARPS;
   p.hi = had_size(in); p.ho = had_size(out);
   p.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
-  p.grid = SG_CTAS * sm_count();
-  choose_split(p.IT, p.NG, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
-  p.lay = make_layout(K, p.kc, rows, SG_CTAS);
+  const int ctas = stream_ctas(rows, K);
+  p.grid = ctas * sm_count();
+  choose_split(p.IT, p.NG, kc_cap(rows, K, ctas), p.grid, rows, &p.S, &p.kc);
+  p.lay = make_layout(K, p.kc, rows, ctas);
   p.grid = std::min(p.grid, p.NG * p.S);
   return p;
 }
@@ -190,9 +206,10 @@ MultiLinearPlan plan_linear_multi(int n, int in, const int *out, const int *K, i
     kmax = std::max(kmax, K[m]);
   }
   p.MT = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
-  p.grid = SG_CTAS * sm_count();
-  choose_split(p.IT, ng, kc_cap(rows), p.grid, rows, &p.S, &p.kc);
-  p.lay = make_layout(kmax, p.kc, rows, SG_CTAS);
+  const int ctas = stream_ctas(rows, kmax);
+  p.grid = ctas * sm_count();
+  choose_split(p.IT, ng, kc_cap(rows, kmax, ctas), p.grid, rows, &p.S, &p.kc);
+  p.lay = make_layout(kmax, p.kc, rows, ctas);
   p.grid = std::min(p.grid, ng * p.S);
   return p;
 }

@@ -124,8 +124,9 @@ void launch_dequant(const void *trellis, int in, int out, int K, __half *w, cuda
 
 // shared-memory carve-up for a stream_gemm launch: kcmax k-tiles of A for arows rows, ring sized to what is left
 StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm);
-// largest k-tile count per unit whose A slots leave room for the ring
-int kc_cap(int arows);
+// largest k-tile count per unit whose A slots leave room for the ring (0: does not fit), and the CTAs per SM to plan with
+int kc_cap(int arows, int Kmax, int ctas);
+int stream_ctas(int arows, int Kmax);
 // k-split choice for `cols` column groups of IT k-tiles on a persistent grid: returns S and kc (multiple of 4)
 void choose_split(int IT, int cols, int kcap, int grid, double rows_per_unit, int *S, int *kc);
 

@@ -356,11 +356,7 @@ void launch_moe_router(const MoeParams &p, bool build_plan, cudaStream_t st) {
   IJ_CHECK(p.P <= RT_PMAX, "router: %d (row, slot) pairs > %d", p.P, RT_PMAX);
   const int grid = (p.E + 1 + RT_WARPS - 1) / RT_WARPS;
   const size_t smem = std::max((size_t)std::min(p.rows, RT_RC) * p.H * 4, (size_t)16 * RT_EMAX + (size_t)RT_PMAX * 4 + 2048);  // tables, pair ids, candidate lists
-  static bool ready = false;
-  if (!ready) {
-    IJ_CUDA(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_RC * 4096 * 4));
-    ready = true;
-  }
+  IJ_CUDA(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_RC * 4096 * 4));  // per device: every launch
   launch_pdl(moe_router_kernel, dim3(grid), dim3(RT_THREADS), smem, st, p, build_plan ? 1 : 0);
 }
 
@@ -650,8 +646,9 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
     if (lane == 0 && atomicAdd(p.ep->counter, 1u) == gridDim.x * gridDim.y - 1) {
       *p.ep->counter = 0u;
       __threadfence_system();
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(p.ep->epoch);
       for (int d = 0; d < p.ep->world; d++)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ep->pflag[d] + p.ep->rank), "r"(p.ep_epoch) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ep->pflag[d] + p.ep->rank), "r"(epoch) : "memory");
     }
   }
 }
@@ -663,21 +660,22 @@ MoeSplits plan_moe(int H, int I, int E, int topk, int Kx, int Ks, int rows, bool
   IJ_CHECK(Kx >= 4 && Kx <= 8 && (!has_shared || (Ks >= 4 && Ks <= 8)), "bits per weight outside 4..8");
   MoeSplits s{};
   s.MT = 1;  // every unit has at most PLAN_ROWS = 8 rows (the plan cuts experts with more rows into several entries)
-  s.grid = SG_CTAS * sm_count();
+  const int kmax = std::max(Kx, has_shared ? Ks : 0);
+  const int ctas = stream_ctas(std::min(rows, PLAN_ROWS), kmax);
+  s.grid = ctas * sm_count();
   const int urows = std::min(rows, PLAN_ROWS);
   // expected number of distinct experts under uniform routing; any actual count works, this only tunes the k-split
   const double nu = E * (1.0 - std::pow(1.0 - (double)topk / E, rows));
   const double rpu = std::min((double)urows, std::max(1.0, rows * (double)topk / std::max(nu, 1.0)));
   const double nsh = has_shared ? (rows + PLAN_ROWS - 1) / PLAN_ROWS : 0;
-  const int kcap = kc_cap(urows);
+  const int kcap = kc_cap(urows, kmax, ctas);
   // at most 16 splits (bounds the partial-sum scratch)
   choose_split(H / 16, (int)std::lround((nu + nsh) * 2 * (I / 128)), kcap, s.grid, rpu, &s.S_gu, &s.kc_gu);
   if (s.S_gu > 16) { s.kc_gu = (H / 16 + 15) / 16; s.kc_gu = (s.kc_gu + SG_KS - 1) / SG_KS * SG_KS; s.S_gu = (H / 16 + s.kc_gu - 1) / s.kc_gu; }
   choose_split(I / 16, (int)std::lround((nu + nsh) * (H / 128)), kcap, s.grid, rpu, &s.S_d, &s.kc_d);
   if (s.S_d > 16) { s.kc_d = (I / 16 + 15) / 16; s.kc_d = (s.kc_d + SG_KS - 1) / SG_KS * SG_KS; s.S_d = (I / 16 + s.kc_d - 1) / s.kc_d; }
-  const int kmax = std::max(Kx, has_shared ? Ks : 0);
-  s.lay_gu = make_layout(kmax, s.kc_gu, urows, SG_CTAS);
-  s.lay_d = make_layout(kmax, s.kc_d, urows, SG_CTAS);
+  s.lay_gu = make_layout(kmax, s.kc_gu, urows, ctas);
+  s.lay_d = make_layout(kmax, s.kc_d, urows, ctas);
   return s;
 }
 

@@ -53,10 +53,9 @@ struct MoeParams {
   // for the rows it owns, so that the sum over ranks contains it once); single GPU: 0, rows
   int sh_row0, sh_rows;
   // expert parallel over peer memory (null = off): the combine writes each finished row into the part buffer of the rank that
-  // owns it and, when its last CTA is done, raises this rank's flag on every peer with ep_epoch
+  // owns it and, when its last CTA is done, raises this rank's flag on every peer with the block's epoch (*ep->epoch)
   const EpDev *ep;
   int ep_rows;         // rows per rank (the gathered rows are world * ep_rows)
-  uint32_t ep_epoch;
   int ldx, ldr;  // row strides of x (floats) and route (words): H and 2 topk unless rows and routes arrive packed side by side
   int lg_row0;  // logits[] holds rows [lg_row0, ..) (expert parallel with own-row routing: only the own rows were routed here)
 };

@@ -20,11 +20,8 @@ void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cu
 
 template <class P, int MT>
 static void launch_stream_mt(const P &prob, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
-  static bool ready = false;  // one flag per (problem, MT) instantiation: opt in to large dynamic shared memory once
-  if (!ready) {
-    IJ_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<P, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    ready = true;
-  }
+  // the attribute belongs to the current device's context: set it on every launch (cheap) rather than once per process
+  IJ_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<P, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
   launch_pdl(stream_gemm_kernel<P, MT>, dim3(grid), dim3(SG_THREADS), lay.total(), st, prob, lay, status);
 }
 

@@ -213,11 +213,7 @@ static size_t pg_smem_bytes(int kmax) { return 1024 + (size_t)PG_RING * PG_KS * 
 static void launch_pf_gemm(const PgGemm &g, int *status, cudaStream_t st) {
   IJ_CHECK(g.IT % PG_KS == 0 && g.OT % 16 == 0 && g.in % 64 == 0, "prefill GEMM needs in %% 64 == 0 and out %% 256 == 0 (in %d, out %d)", g.in, g.OT * 16);
   const size_t smem = pg_smem_bytes(std::max(g.Kx, g.Ks));
-  static bool ready = false;
-  if (!ready) {
-    IJ_CUDA(cudaFuncSetAttribute(pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    ready = true;
-  }
+  IJ_CUDA(cudaFuncSetAttribute(pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));  // per device: every launch
   pf_gemm_kernel<<<sm_count(), PG_THREADS, smem, st>>>(g, status);
   IJ_CUDA(cudaGetLastError());
 }

@@ -59,7 +59,7 @@ class MoeDescC(C.Structure):
 class ModelDescC(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("layers", "hidden", "inter", "experts", "top_k", "k_expert", "k_shared", "q_out", "kv_out",
                                        "heads", "kv_heads", "head_dim", "k_trunk", "k_trunk_alt", "alt_every", "vocab",
-                                       "kv_positions", "expert_first", "expert_count")]
+                                       "kv_positions", "expert_first", "expert_count", "ep_world")]
 
 
 class EngineError(RuntimeError):
@@ -97,6 +97,8 @@ SIGNATURES = {
     "ne_exl3_dequant": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_void_p]),
     "ne_exl3_linear": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_host": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p]),
+    "ne_exl3_linear_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_uint64)]),
+    "ne_moe_plan": (C.c_int, [C.c_int] * 7 + [C.POINTER(C.c_int)]),
     "ne_exl3_linear_multi": (C.c_int, [C.POINTER(Exl3WeightC), C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_void_p]),
     "ne_exl3_linear_prefill": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_exl3_linear_static": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
@@ -113,7 +115,7 @@ SIGNATURES = {
     "ne_ep_create": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "ne_ep_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ne_ep_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
-    "ne_ep_free": (None, [C.c_void_p]),
+    "ne_ep_free": (None, [C.c_void_p]), "ne_ep_disconnect": (C.c_int, [C.c_void_p]),
     "ne_moe_forward_ep_fused": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_prefill_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
@@ -130,6 +132,7 @@ SIGNATURES = {
     "ne_fn_model_step_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_double)]),
     "ne_fn_model_time": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "ne_fn_model_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ne_fn_model_replay": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "ne_fn_model_desc_of": (C.c_int, [C.c_void_p, C.POINTER(ModelDescC)]),
     "ne_fn_model_set_ep": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ne_fn_model_read": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.c_void_p, C.c_uint64]),
@@ -326,6 +329,12 @@ class FnModel:
                                                         nx.ctypes.data, C.byref(ms)), "ne_fn_model_step_rows")
         return nx, lg, ms.value
 
+    def replay(self, rows, steps, head=True):
+        """device time in ms of `steps` replays of the captured step (inputs and results stay on the device)"""
+        ms = C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_replay(self.ptr, rows, int(head), steps, C.byref(ms)), "ne_fn_model_replay")
+        return ms.value
+
     def time(self, reps=10):
         a, b, c = C.c_double(0), C.c_double(0), C.c_double(0)
         self.eng._ok(self.eng.lib.ne_fn_model_time(self.ptr, 0, reps, C.byref(a), C.byref(b), C.byref(c)), "ne_fn_model_time")
@@ -516,8 +525,13 @@ class EpExchange:
         assert len(handles) == self.world and all(len(h) == 64 for h in handles)
         self.eng._ok(self.eng.lib.ne_ep_connect(self.ptr, C.create_string_buffer(b"".join(handles), 64 * self.world)), "ne_ep_connect")
 
-    def free(self):
+    def free(self, barrier=None):
+        """close the peers' mappings, let `barrier` (a callable, e.g. lambda: dist.barrier(group)) make sure every rank has
+        done so, then free this rank's buffer: a buffer must not be freed while a peer still maps it"""
         if self.ptr:
+            self.eng.lib.ne_ep_disconnect(self.ptr)
+            if barrier is not None:
+                barrier()
             self.eng.lib.ne_ep_free(self.ptr)
             self.ptr = None
 

@@ -1,6 +1,6 @@
 """Expert-parallel MoE block over torch.distributed (one process per GPU; NCCL on GPUs, gloo in the CPU tests).
 
-The reference is single-device; this is the sharding BASELINE's north star asks for. Rank g holds experts
+The reference is single-device; expert parallelism is this library's addition. Rank g holds experts
 [g * E/N, (g+1) * E/N) of the layer (a MoeBlock created with expert_first / expert_count) and `rows` rows of its own.
 
     route      block.route_rows(x)                                     -> routes of the rank's own rows (decode widths)
@@ -71,8 +71,10 @@ class ExpertParallelMoe:
         oks = [None] * world
         dist.all_gather_object(oks, err is None, group=group)
         if not all(oks):  # one rank could not set up peer access: every rank falls back (returns None)
+            if x is None:
+                dist.barrier(group)  # the barrier the ranks that do hold a context run between disconnect and free
             if x is not None:
-                x.free()
+                x.free(barrier=lambda: dist.barrier(group))
             if err is not None:
                 import sys
                 print(f"[rank {rank}] peer-memory exchange unavailable: {err}", file=sys.stderr)

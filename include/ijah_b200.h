@@ -34,6 +34,13 @@ NE_API int ne_exl3_dequant(const ne_exl3_weight *w, void *w_f16_dev, void *strea
  * owned by the library (grown on demand). */
 NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 NE_API int ne_exl3_linear_host(const ne_exl3_weight *w, const float *x_host, int rows, float *y_host);
+/* The launch plan ne_exl3_linear would use (host arithmetic only, no device needed): info8 = k-splits S, k-tiles per unit,
+ * ring stages, A slots, grid, 8-row groups, dynamic shared memory bytes, bytes per ring stage; scratch_bytes = the scratch
+ * the call needs (what ne_exl3_linear_static compares with its capacity). -1 if the shape is not supported. */
+NE_API int ne_exl3_linear_plan(int n_in, int n_out, int K, int rows, int *info8, uint64_t *scratch_bytes);
+/* The same for one MoE block: info8 = gate/up splits, gate/up k-tiles per unit, down splits, down k-tiles per unit, ring
+ * stages (gate/up, down), grid, dynamic shared memory bytes. */
+NE_API int ne_moe_plan(int hidden, int inter, int experts, int top_k, int k_expert, int k_shared, int rows, int *info8);
 /* n (1..4) Linears applied to the SAME rows x (the q, k, v projections of a layer; replaces t6::record_multi,
  * kernels/trunk6/trunk6.h:78-79, for the case of one shared input): one chain of three launches whose stream kernel holds the units of all matrices, so small
  * matrices neither pay a launch chain each nor leave most of the GPU idle. All w[i].in must be equal; y_dev[i] receives
@@ -131,6 +138,7 @@ typedef struct ne_ep ne_ep;
 NE_API ne_ep *ne_ep_create(int rank, int world, int rows_cap, int hidden, int top_k);
 NE_API int ne_ep_handle(ne_ep *e, void *handle64);
 NE_API int ne_ep_connect(ne_ep *e, const void *handles64 /* world x 64 bytes, rank order */);
+NE_API int ne_ep_disconnect(ne_ep *e); /* closes this rank's mappings of the peers' buffers: call on every rank, barrier, then ne_ep_free */
 NE_API void ne_ep_free(ne_ep *e);
 NE_API int ne_moe_forward_ep_fused(ne_moe *m, ne_ep *e, const float *x_own_dev, int rows, float *y_own_dev, void *stream);
 /* Expert-parallel prefill: x_all holds the tokens of ALL ranks, [own_row0, own_row0 + own_rows) being the caller's. Every
@@ -161,6 +169,7 @@ typedef struct {
   int k_trunk, k_trunk_alt, alt_every; /* trunk bits per weight; every alt_every-th layer uses k_trunk_alt (0 = never) */
   int vocab, kv_positions;       /* kv_positions: cached positions the attention stand-in reads (multiple of 64) */
   int expert_first, expert_count;
+  int ep_world;                  /* ranks of an expert-parallel run (0 or 1 = single GPU): the MoE blocks are sized for the rows of all ranks */
 } ne_fn_model_desc;
 NE_API ne_fn_model *ne_fn_model_create_synthetic(const ne_fn_model_desc *d, uint64_t seed, int max_rows);
 NE_API ne_fn_model *ne_fn_model_create_rows(ne_pack *pack, int tmax, int max_rows); /* ne_fn_model_create for up to max_rows rows per step */
@@ -169,6 +178,9 @@ NE_API ne_fn_model *ne_fn_model_create_rows(ne_pack *pack, int tmax, int max_row
  * CUDA graph for this row count (captured on first use); host -> device copy of the tokens and device -> host copies of the
  * results are part of the call. */
 NE_API int ne_fn_model_step_rows(ne_fn_model *m, const int *tokens_host, int rows, int head, float *logits_host, int *next_host, double *gpu_ms);
+/* `steps` replays of the captured step for `rows` rows back to back on the model's stream, inputs and results staying on the
+ * device: total device time between two events in *total_ms. */
+NE_API int ne_fn_model_replay(ne_fn_model *m, int rows, int head, int steps, double *total_ms);
 NE_API int ne_fn_model_desc_of(ne_fn_model *m, ne_fn_model_desc *out);
 /* Expert parallel: the MoE blocks of every layer exchange rows over the given peer-memory context (ne_ep_*); NULL = off. */
 NE_API int ne_fn_model_set_ep(ne_fn_model *m, ne_ep *e);

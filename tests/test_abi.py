@@ -83,3 +83,22 @@ def test_errors_are_reported_not_raised_across_the_abi(eng, tmp_path):
 def test_missing_library_fails_loudly(tmp_path):
     with pytest.raises(E.EngineError):
         E.Engine(tmp_path / "libnope.so")
+
+
+def test_launch_plans_fit_shared_memory_for_every_row_count(eng):
+    # host arithmetic only: every row count 1..64 at every K plans to a layout that fits an SM (one or two CTAs), with at
+    # least two ring stages and three A slots; the MoE block of the benchmark dims likewise
+    info = (ctypes.c_int * 8)()
+    scratch = ctypes.c_uint64(0)
+    for n_in, n_out in ((2048, 4096), (2048, 512), (4096, 2048), (768, 2048), (96, 160), (320, 48)):
+        for K in (4, 5, 6, 7, 8):
+            for rows in range(1, 65):
+                assert eng.lib.ne_exl3_linear_plan(n_in, n_out, K, rows, info, ctypes.byref(scratch)) == 0, (n_in, n_out, K, rows, eng.last_error())
+                S, kc, stages, aslots, grid, mt, smem, stage_bytes = list(info)
+                assert stages >= 2 and aslots >= 3 and smem <= 226 * 1024 and kc % 16 == 0 and S * kc >= n_in // 16 and rows <= 8 * mt
+                assert grid <= 2 * 148 and (smem <= 113 * 1024 or grid <= 148), "a layout beyond half an SM runs one CTA per SM"
+                assert scratch.value >= rows * (4 * S * n_out + 2 * n_in)
+    for rows in range(1, 65):
+        assert eng.lib.ne_moe_plan(2048, 768, 512, 10, 5, 6, rows, info) == 0, eng.last_error()
+        assert info[4] >= 2 and info[5] >= 2 and info[7] <= 113 * 1024 and info[0] <= 16 and info[2] <= 16
+    assert eng.lib.ne_exl3_linear_plan(100, 128, 5, 1, info, None) == -1 and "multiples of 16" in eng.last_error()

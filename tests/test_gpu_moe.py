@@ -237,3 +237,30 @@ def test_router_ties_go_to_the_lowest_index(eng, mode):
     assert rel_max(yp, want["out"]) < 2e-4
     assert eng.lib.ne_device_wait_status() == 0
     blk.free()
+
+
+def test_misaligned_pointers_are_refused_on_the_host(eng):
+    # a view that starts 4 bytes into a row would make the 16-byte copies of the kernels fault on the device: the entry
+    # points check on the host and launch nothing
+    import ctypes as C
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(12)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=32)
+    blk = E.MoeBlock(eng, t, top_k=4, max_rows=4)
+    x = torch.zeros((4, 513), device="cuda")
+    y = torch.zeros((4, 512), device="cuda")
+    off = C.c_void_p(x.data_ptr() + 4)
+    assert eng.lib.ne_moe_forward(blk.ptr, off, 2, C.c_void_p(y.data_ptr()), None) == -1
+    assert "16-byte aligned" in eng.last_error()
+    assert eng.lib.ne_moe_forward(blk.ptr, C.c_void_p(x.data_ptr()), 2, C.c_void_p(y.data_ptr() + 8), None) == -1
+    assert eng.lib.ne_moe_route(blk.ptr, off, 2, None, 0, None) == -1
+    d = blk.desc
+    bad = E.MoeDescC.from_buffer_copy(bytes(d))
+    bad.router = d.router + 2
+    assert eng.lib.ne_moe_create(C.byref(bad), 4) is None and "16-byte aligned" in eng.last_error()
+    bad = E.MoeDescC.from_buffer_copy(bytes(d))
+    bad.gate.trellis = d.gate.trellis + 8
+    assert eng.lib.ne_moe_create(C.byref(bad), 4) is None and "16-byte aligned" in eng.last_error()
+    assert eng.lib.ne_device_wait_status() == 0
+    blk.free()
