@@ -37,6 +37,7 @@ got2 = par.forward(xs)
 err_d = max(err_d, float((got2 - want).abs().max() / want.abs().max()))
 # the same block with both exchange steps over NVLink peer memory (two layers share one context; repeated calls)
 xchg = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, 16, 512, 4)
+assert xchg is not None, "the peer-memory exchange must come up on a box whose GPUs see each other (else this test would only repeat the NCCL path)"
 par.use_exchange(xchg)
 for _ in range(3):
     got3 = par.forward(xs)
@@ -47,12 +48,30 @@ xp = torch.from_numpy(x_all[rank * 40:(rank + 1) * 40]).to(dev)
 wantp = full.prefill(torch.from_numpy(x_all).to(dev))[rank * 40:(rank + 1) * 40]
 gotp = par.forward(xp, prefill=True)
 err_p = float((gotp - wantp).abs().max() / wantp.abs().max())
+# the whole decoder stack, expert parallel, replayed from the library's CUDA graph: logits of this rank's rows against a
+# single-GPU model over the rows of both ranks (synthetic weights do not depend on which slice a rank holds)
+d = dict(layers=2, hidden=512, inter=256, experts=32, top_k=4, k_expert=5, k_shared=6, q_out=256, kv_out=128, heads=4, kv_heads=2,
+         head_dim=64, k_trunk=6, k_trunk_alt=8, alt_every=2, vocab=1024, kv_positions=64)
+xm = ep.ExpertParallelMoe.make_exchange(eng, dist.group.WORLD, 3, 512, 4)
+assert xm is not None
+mp = eng.fn_model(desc=dict(d, expert_first=rank * per, expert_count=per, ep_world=world), seed=3, max_rows=3)
+mp.set_ep(xm)
+mf = eng.fn_model(desc=dict(d, expert_first=0, expert_count=0, ep_world=1), seed=3, max_rows=3 * world)
+toks = (np.arange(3 * world, dtype=np.int32) * 37 + 11) % 1024
+_, lf, _ = mf.step_rows(toks, want_logits=True)
+err_m = 0.0
+for _ in range(3):  # the first call captures the step, the others replay it
+    nx, lp, _ = mp.step_rows(toks[rank * 3:(rank + 1) * 3], want_logits=True)
+    err_m = max(err_m, float(np.abs(lp - lf[rank * 3:(rank + 1) * 3]).max() / np.abs(lf).max()))
+assert np.array_equal(nx, lf[rank * 3:(rank + 1) * 3].argmax(1))
 torch.cuda.synchronize()
 status = eng.lib.ne_device_wait_status()
 dist.barrier()
+mp.free(); mf.free()
+xm.free(barrier=dist.barrier); xchg.free(barrier=dist.barrier)
 dist.destroy_process_group()
-assert err_d < 1e-5 and err_p < 1e-5 and status == 0, (err_d, err_p, status)
-print("EP_OK", rank, err_d, err_p)
+assert err_d < 1e-5 and err_p < 1e-5 and err_m < 1e-4 and status == 0, (err_d, err_p, err_m, status)
+print("EP_OK", rank, err_d, err_p, err_m)
 """
 
 
