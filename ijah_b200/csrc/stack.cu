@@ -71,6 +71,8 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
+constexpr int AT_QCAP = 64;  // query vectors staged at a time (fp16, scaled)
+
 template <int HD>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restrict__ q, const __half *__restrict__ kc, const __half *__restrict__ vc, int rows,
                                                            int heads, int kv_heads, int nsplit, float *__restrict__ part, float *__restrict__ ml) {
@@ -80,148 +82,211 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
   __half *Ks = reinterpret_cast<__half *>(at_smem);
   __half *Vs = Ks + AT_PB * LD;
   __half *Qs = Vs + AT_PB * LD;
-  __half *Ps = Qs + 16 * LD;
+  __half *Ps = Qs + AT_QCAP * LD;
   float *red = reinterpret_cast<float *>(Ps + 16 * LDP);  // [2][4][16]: per-warp max, per-warp sum
   const int split = blockIdx.x, kvh = blockIdx.y, G = heads / kv_heads, NQ = rows * G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qq = lane & 3;
-  // stage K and V of the block (static data: before the wait on the preceding kernel)
+  // K and V of the block: asynchronous 16-byte copies, all in flight at once (static data: before the wait on the
+  // preceding kernel, so the copies overlap its tail)
   {
     const size_t rstride = (size_t)kv_heads * HD;
     const __half *ksrc = kc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
     const __half *vsrc = vc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
+    const uint32_t Kd = smem_u32(Ks), Vd = smem_u32(Vs);
+#pragma unroll 4
     for (int i = threadIdx.x; i < AT_PB * (HD / 8); i += 128) {
       const int p = i / (HD / 8), c = i % (HD / 8);
-      *reinterpret_cast<uint4 *>(Ks + p * LD + c * 8) = *reinterpret_cast<const uint4 *>(ksrc + p * rstride + c * 8);
-      *reinterpret_cast<uint4 *>(Vs + p * LD + c * 8) = *reinterpret_cast<const uint4 *>(vsrc + p * rstride + c * 8);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(Kd + (uint32_t)((p * LD + c * 8) * 2)), "l"(ksrc + p * rstride + c * 8) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(Vd + (uint32_t)((p * LD + c * 8) * 2)), "l"(vsrc + p * rstride + c * 8) : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   }
   pdl_launch();
   pdl_wait();
   const float scale = rsqrtf((float)HD);
-  const uint32_t Qa = smem_u32(Qs), Ka = smem_u32(Ks), Va = smem_u32(Vs), Pa = smem_u32(Ps);
-  for (int qt = 0; qt * 16 < NQ; qt++) {
-    __syncthreads();  // previous tile's readers of Qs / Ps / red are done (first pass: K / V are in place)
-    for (int i = threadIdx.x; i < 16 * (HD / 4); i += 128) {
-      const int j = i / (HD / 4), c = i % (HD / 4), qi = qt * 16 + j;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (qi < NQ) v = *reinterpret_cast<const float4 *>(q + ((size_t)(qi / G) * heads + kvh * G + qi % G) * HD + c * 4);
-      __half2 *dst = reinterpret_cast<__half2 *>(Qs + j * LD + c * 4);
-      dst[0] = __floats2half2_rn(v.x * scale, v.y * scale);
-      dst[1] = __floats2half2_rn(v.z * scale, v.w * scale);
-    }
-    __syncthreads();
-    // ---- S = Q K^T for this warp's 16 positions
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  const uint32_t Qa0 = smem_u32(Qs), Ka = smem_u32(Ks), Va = smem_u32(Vs), Pa = smem_u32(Ps);
+  for (int qc = 0; qc < NQ; qc += AT_QCAP) {
+    __syncthreads();  // the previous chunk's readers of Qs are done
+    // the chunk's query vectors: fp32 -> scaled fp16, four independent 16-byte loads per thread per pass
+    for (int i0 = 0; i0 < AT_QCAP * (HD / 4); i0 += 128 * 4) {
+      float4 v[4];
 #pragma unroll
-    for (int kk = 0; kk < HD / 16; kk++) {
-      uint32_t a[4], b[4];
-      ldsm_x4(a, Qa + (uint32_t)(((lane & 15) * LD + kk * 16 + (lane >> 4) * 8) * 2));
-      const int m = lane >> 3;
-      ldsm_x4(b, Ka + (uint32_t)(((warp * 16 + (lane & 7) + (m >> 1) * 8) * LD + kk * 16 + (m & 1) * 8) * 2));
-      mma_16816(s[0], a, b[0], b[1]);
-      mma_16816(s[1], a, b[2], b[3]);
-    }
-    // ---- block max and sum per query row (rows g and g + 8 of the tile)
-    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])), mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * 128 + threadIdx.x, j = i / (HD / 4), c = i % (HD / 4), qi = qc + j;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (qi < NQ) v[u] = __ldcg(reinterpret_cast<const float4 *>(q + ((size_t)(qi / G) * heads + kvh * G + qi % G) * HD + c * 4));
+      }
 #pragma unroll
-    for (int o = 1; o <= 2; o <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
-    }
-    if (qq == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
-    __syncthreads();
-    float m0 = red[g], m1 = red[g + 8];
-#pragma unroll
-    for (int w = 1; w < 4; w++) { m0 = fmaxf(m0, red[w * 16 + g]); m1 = fmaxf(m1, red[w * 16 + g + 8]); }
-    float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < 2; nt++) {
-      const float p0 = __expf(s[nt][0] - m0), p1 = __expf(s[nt][1] - m0), p2 = __expf(s[nt][2] - m1), p3 = __expf(s[nt][3] - m1);
-      const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-      // the sums use the rounded values the tensor core will multiply with
-      l0 += __low2float(h01) + __high2float(h01);
-      l1 += __low2float(h23) + __high2float(h23);
-      *reinterpret_cast<__half2 *>(Ps + g * LDP + warp * 16 + nt * 8 + 2 * qq) = h01;
-      *reinterpret_cast<__half2 *>(Ps + (g + 8) * LDP + warp * 16 + nt * 8 + 2 * qq) = h23;
-    }
-#pragma unroll
-    for (int o = 1; o <= 2; o <<= 1) {
-      l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, o);
-      l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
-    }
-    if (qq == 0) { red[64 + warp * 16 + g] = l0; red[64 + warp * 16 + g + 8] = l1; }
-    __syncthreads();
-    // ---- O = P V for this warp's quarter of the head dimension
-    constexpr int NTW = HD / 4 / 8;  // n-tiles per warp
-    float o_acc[NTW][4];
-#pragma unroll
-    for (int n = 0; n < NTW; n++)
-#pragma unroll
-      for (int j = 0; j < 4; j++) o_acc[n][j] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < AT_PB / 16; ks++) {
-      uint32_t a[4];
-      ldsm_x4(a, Pa + (uint32_t)(((lane & 15) * LDP + ks * 16 + (lane >> 4) * 8) * 2));
-#pragma unroll
-      for (int n2 = 0; n2 < NTW / 2; n2++) {
-        uint32_t b[4];
-        const int m = lane >> 3, n0 = warp * (HD / 4) + n2 * 16;
-        ldsm_x4_trans(b, Va + (uint32_t)(((ks * 16 + (lane & 7) + (m & 1) * 8) * LD + n0 + (m >> 1) * 8) * 2));
-        mma_16816(o_acc[2 * n2], a, b[0], b[1]);
-        mma_16816(o_acc[2 * n2 + 1], a, b[2], b[3]);
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + u * 128 + threadIdx.x, j = i / (HD / 4), c = i % (HD / 4);
+        __half2 *dst = reinterpret_cast<__half2 *>(Qs + j * LD + c * 4);
+        dst[0] = __floats2half2_rn(v[u].x * scale, v[u].y * scale);
+        dst[1] = __floats2half2_rn(v[u].z * scale, v[u].w * scale);
       }
     }
-    // ---- partial results of the tile's live query vectors
-    const int q0 = qt * 16 + g, q1 = q0 + 8;
-    if (warp == 0 && qq == 0) {
-      float la = 0.f, lb = 0.f;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    for (int qt = 0; qt * 16 < min(AT_QCAP, NQ - qc); qt++) {
+      const uint32_t Qa = Qa0 + (uint32_t)(qt * 16 * LD * 2);
+      // ---- S = Q K^T for this warp's 16 positions
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-      for (int w = 0; w < 4; w++) { la += red[64 + w * 16 + g]; lb += red[64 + w * 16 + g + 8]; }
-      if (q0 < NQ) { ml[(((size_t)kvh * NQ + q0) * nsplit + split) * 2] = m0; ml[(((size_t)kvh * NQ + q0) * nsplit + split) * 2 + 1] = la; }
-      if (q1 < NQ) { ml[(((size_t)kvh * NQ + q1) * nsplit + split) * 2] = m1; ml[(((size_t)kvh * NQ + q1) * nsplit + split) * 2 + 1] = lb; }
-    }
+      for (int kk = 0; kk < HD / 16; kk++) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, Qa + (uint32_t)(((lane & 15) * LD + kk * 16 + (lane >> 4) * 8) * 2));
+        const int m = lane >> 3;
+        ldsm_x4(b, Ka + (uint32_t)(((warp * 16 + (lane & 7) + (m >> 1) * 8) * LD + kk * 16 + (m & 1) * 8) * 2));
+        mma_16816(s[0], a, b[0], b[1]);
+        mma_16816(s[1], a, b[2], b[3]);
+      }
+      // ---- block max and sum per query row (rows g and g + 8 of the tile)
+      float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])), mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
 #pragma unroll
-    for (int n = 0; n < NTW; n++) {
-      const int d = warp * (HD / 4) + n * 8 + 2 * qq;
-      if (q0 < NQ) *reinterpret_cast<float2 *>(part + (((size_t)kvh * NQ + q0) * nsplit + split) * HD + d) = make_float2(o_acc[n][0], o_acc[n][1]);
-      if (q1 < NQ) *reinterpret_cast<float2 *>(part + (((size_t)kvh * NQ + q1) * nsplit + split) * HD + d) = make_float2(o_acc[n][2], o_acc[n][3]);
+      for (int o = 1; o <= 2; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
+      }
+      __syncthreads();  // the previous tile's readers of red and Ps are done
+      if (qq == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
+      __syncthreads();
+      float m0 = red[g], m1 = red[g + 8];
+#pragma unroll
+      for (int w = 1; w < 4; w++) { m0 = fmaxf(m0, red[w * 16 + g]); m1 = fmaxf(m1, red[w * 16 + g + 8]); }
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++) {
+        const float p0 = __expf(s[nt][0] - m0), p1 = __expf(s[nt][1] - m0), p2 = __expf(s[nt][2] - m1), p3 = __expf(s[nt][3] - m1);
+        const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+        // the sums use the rounded values the tensor core will multiply with
+        l0 += __low2float(h01) + __high2float(h01);
+        l1 += __low2float(h23) + __high2float(h23);
+        *reinterpret_cast<__half2 *>(Ps + g * LDP + warp * 16 + nt * 8 + 2 * qq) = h01;
+        *reinterpret_cast<__half2 *>(Ps + (g + 8) * LDP + warp * 16 + nt * 8 + 2 * qq) = h23;
+      }
+#pragma unroll
+      for (int o = 1; o <= 2; o <<= 1) {
+        l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, o);
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
+      }
+      if (qq == 0) { red[64 + warp * 16 + g] = l0; red[64 + warp * 16 + g + 8] = l1; }
+      __syncthreads();
+      // ---- O = P V for this warp's quarter of the head dimension
+      constexpr int NTW = HD / 4 / 8;  // n-tiles per warp
+      float o_acc[NTW][4];
+#pragma unroll
+      for (int n = 0; n < NTW; n++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o_acc[n][j] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < AT_PB / 16; ks++) {
+        uint32_t a[4];
+        ldsm_x4(a, Pa + (uint32_t)(((lane & 15) * LDP + ks * 16 + (lane >> 4) * 8) * 2));
+#pragma unroll
+        for (int n2 = 0; n2 < NTW / 2; n2++) {
+          uint32_t b[4];
+          const int m = lane >> 3, n0 = warp * (HD / 4) + n2 * 16;
+          ldsm_x4_trans(b, Va + (uint32_t)(((ks * 16 + (lane & 7) + (m & 1) * 8) * LD + n0 + (m >> 1) * 8) * 2));
+          mma_16816(o_acc[2 * n2], a, b[0], b[1]);
+          mma_16816(o_acc[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+      // ---- partial results of the tile's live query vectors
+      const int q0 = qc + qt * 16 + g, q1 = q0 + 8;
+      if (warp == 0 && qq == 0) {
+        float la = 0.f, lb = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) { la += red[64 + w * 16 + g]; lb += red[64 + w * 16 + g + 8]; }
+        if (q0 < NQ) { ml[(((size_t)kvh * NQ + q0) * nsplit + split) * 2] = m0; ml[(((size_t)kvh * NQ + q0) * nsplit + split) * 2 + 1] = la; }
+        if (q1 < NQ) { ml[(((size_t)kvh * NQ + q1) * nsplit + split) * 2] = m1; ml[(((size_t)kvh * NQ + q1) * nsplit + split) * 2 + 1] = lb; }
+      }
+#pragma unroll
+      for (int n = 0; n < NTW; n++) {
+        const int d = warp * (HD / 4) + n * 8 + 2 * qq;
+        if (q0 < NQ) *reinterpret_cast<float2 *>(part + (((size_t)kvh * NQ + q0) * nsplit + split) * HD + d) = make_float2(o_acc[n][0], o_acc[n][1]);
+        if (q1 < NQ) *reinterpret_cast<float2 *>(part + (((size_t)kvh * NQ + q1) * nsplit + split) * HD + d) = make_float2(o_acc[n][2], o_acc[n][3]);
+      }
     }
   }
 }
 
-// merge: one CTA per query vector (row, head), one thread per dimension; also adds the row's own (k, v) as one more position
-__global__ void attn_merge_kernel(const float *__restrict__ q, const float *__restrict__ knew, const float *__restrict__ vnew, const float *__restrict__ part,
-                                  const float *__restrict__ ml, int rows, int heads, int kv_heads, int hd, int nsplit, float *__restrict__ out) {
-  __shared__ float red[8];
-  __shared__ float s_self;
+// merge: one CTA per query vector (row, head), 1024 threads. The block maxima and sums of all position blocks are loaded in
+// parallel (one per thread), reduced to the global maximum and the weights exp(m_s - M) in shared memory; then 1024 / hd
+// thread groups each sum a slice of the blocks for every dimension with independent loads (eight in flight) and the slices
+// are added through shared memory, so the kernel costs a few memory round trips instead of one per block. The row's own
+// (k, v) enters as one more position.
+constexpr int AT_MAXSPLIT = 1024;
+constexpr int AT_MT = 1024;  // merge threads
+__global__ void __launch_bounds__(AT_MT) attn_merge_kernel(const float *__restrict__ q, const float *__restrict__ knew, const float *__restrict__ vnew,
+                                                           const float *__restrict__ part, const float *__restrict__ ml, int rows, int heads, int kv_heads,
+                                                           int hd, int nsplit, float *__restrict__ out) {
+  __shared__ float red[32], red2[32];
+  __shared__ float wsh[AT_MAXSPLIT];
+  __shared__ float acc[AT_MT];
+  __shared__ float s_M, s_den, s_wself;
   const int r = blockIdx.x / heads, h = blockIdx.x % heads, G = heads / kv_heads, kvh = h / G, NQ = rows * G, qi = r * G + h % G;
-  const int d = threadIdx.x;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   pdl_launch();
   pdl_wait();
-  float dot = d < hd ? q[((size_t)r * heads + h) * hd + d] * knew[((size_t)r * kv_heads + kvh) * hd + d] : 0.f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
-  if ((d & 31) == 0) red[d >> 5] = dot;
-  __syncthreads();
-  if (d == 0) {
-    float t = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += red[i];
-    s_self = t * rsqrtf((float)hd);
-  }
-  __syncthreads();
   const float *mlq = ml + ((size_t)kvh * NQ + qi) * nsplit * 2;
-  float M = s_self;
-  for (int s = 0; s < nsplit; s++) M = fmaxf(M, mlq[2 * s]);
-  if (d >= hd) return;
-  const float wself = __expf(s_self - M);
-  float num = wself * vnew[((size_t)r * kv_heads + kvh) * hd + d], den = wself;
-  const float *pq = part + ((size_t)kvh * NQ + qi) * nsplit * hd + d;
-  for (int s = 0; s < nsplit; s++) {
-    const float w = __expf(mlq[2 * s] - M);
-    num += w * pq[(size_t)s * hd];
-    den += w * mlq[2 * s + 1];
+  // every thread's block statistics (threads beyond nsplit: neutral), and the dot product q . k_new
+  const float m_own = t < nsplit ? mlq[2 * t] : -INFINITY, l_own = t < nsplit ? mlq[2 * t + 1] : 0.f;
+  float m_loc = m_own;
+  float dot = t < hd ? q[((size_t)r * heads + h) * hd + t] * knew[((size_t)r * kv_heads + kvh) * hd + t] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    m_loc = fmaxf(m_loc, __shfl_xor_sync(0xFFFFFFFFu, m_loc, o));
+    dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
   }
-  out[((size_t)r * heads + h) * hd + d] = num / den;
+  if (lane == 0) { red[warp] = m_loc; red2[warp] = dot; }
+  __syncthreads();
+  if (warp == 0) {
+    float M = red[lane], dsum = red2[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+      dsum += __shfl_xor_sync(0xFFFFFFFFu, dsum, o);
+    }
+    if (lane == 0) {
+      const float s_self = dsum * rsqrtf((float)hd);
+      M = fmaxf(M, s_self);
+      s_M = M;
+      s_wself = __expf(s_self - M);
+    }
+  }
+  __syncthreads();
+  const float w_own = t < nsplit ? __expf(m_own - s_M) : 0.f;
+  if (t < nsplit) wsh[t] = w_own;
+  float den_loc = w_own * l_own;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) den_loc += __shfl_xor_sync(0xFFFFFFFFu, den_loc, o);
+  if (lane == 0) red[warp] = den_loc;
+  __syncthreads();
+  if (warp == 0) {
+    float den = red[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xFFFFFFFFu, den, o);
+    if (lane == 0) s_den = den + s_wself;
+  }
+  // thread (d, grp): dimension d over the blocks grp, grp + ngrp, ...
+  const int ngrp = AT_MT / hd, d = t % hd, grp = t / hd;
+  const float *pq = part + ((size_t)kvh * NQ + qi) * nsplit * hd + d;
+  float num = 0.f;
+  int s = grp;
+  for (; s + 7 * ngrp < nsplit; s += 8 * ngrp) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = __ldcg(pq + (size_t)(s + j * ngrp) * hd);
+#pragma unroll
+    for (int j = 0; j < 8; j++) num += wsh[s + j * ngrp] * v[j];
+  }
+  for (; s < nsplit; s += ngrp) num += wsh[s] * __ldcg(pq + (size_t)s * hd);
+  acc[t] = num;
+  __syncthreads();
+  if (t < hd) {
+    float tot = s_wself * vnew[((size_t)r * kv_heads + kvh) * hd + t];
+    for (int gI = 0; gI < ngrp; gI++) tot += acc[gI * hd + t];
+    out[((size_t)r * heads + h) * hd + t] = tot / s_den;
+  }
 }
 
 size_t attn_scratch_bytes(int rows, int heads, int hd, int T) {
@@ -232,14 +297,15 @@ size_t attn_scratch_bytes(int rows, int heads, int hd, int T) {
 template <int HD>
 static void launch_attn_partial(const float *q, const __half *kc, const __half *vc, int rows, int heads, int kv_heads, int nsplit, float *part, float *ml,
                                 cudaStream_t st) {
-  const size_t smem = (size_t)(2 * AT_PB * (HD + 8) + 16 * (HD + 8) + 16 * (AT_PB + 8)) * 2 + 128 * 4;
+  const size_t smem = (size_t)(2 * AT_PB * (HD + 8) + AT_QCAP * (HD + 8) + 16 * (AT_PB + 8)) * 2 + 128 * 4;
   IJ_CUDA(cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   launch_pdl(attn_partial_kernel<HD>, dim3(nsplit, kv_heads), dim3(128), smem, st, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml);
 }
 
 void launch_attn_standin(const float *q, const float *knew, const float *vnew, const __half *kc, const __half *vc, int rows, int heads, int kv_heads,
                          int hd, int T, float *out, void *scratch, cudaStream_t st) {
-  IJ_CHECK(T % AT_PB == 0 && T >= AT_PB, "attention stand-in: cache length %d must be a multiple of %d", T, AT_PB);
+  IJ_CHECK(T % AT_PB == 0 && T >= AT_PB && T / AT_PB <= AT_MAXSPLIT, "attention stand-in: cache length %d must be a multiple of %d, at most %d", T, AT_PB,
+           AT_PB * AT_MAXSPLIT);
   IJ_CHECK(heads % kv_heads == 0 && (hd == 64 || hd == 128 || hd == 256), "attention stand-in: heads %d / %d, head dim %d not supported", heads, kv_heads, hd);
   const int nsplit = T / AT_PB;
   float *part = (float *)scratch;
@@ -249,8 +315,8 @@ void launch_attn_standin(const float *q, const float *knew, const float *vnew, c
     case 128: launch_attn_partial<128>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
     default: launch_attn_partial<256>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
   }
-  launch_pdl(attn_merge_kernel, dim3(rows * heads), dim3((hd + 31) / 32 * 32), 0, st, q, knew, vnew, (const float *)part, (const float *)ml, rows, heads,
-             kv_heads, hd, nsplit, out);
+  launch_pdl(attn_merge_kernel, dim3(rows * heads), dim3(AT_MT), 0, st, q, knew, vnew, (const float *)part, (const float *)ml, rows, heads, kv_heads, hd,
+             nsplit, out);
 }
 
 // =============================================================================================== LM head
