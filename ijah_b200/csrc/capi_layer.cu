@@ -260,24 +260,84 @@ NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, 
   });
 }
 
-// Kernels are compiled into the library; the names below are the CUDA kernels that exist. The reference's Metal
-// kernel names (fn_moe_gateup_k5_r1, t6_simd, ...) are reported absent: their argument lists bind Metal buffers of
-// the reference's scratch layout, which this library does not reproduce.
+// Kernel-by-name entry (reference core/capi.mm:157-182, client tools/engine.py:392-420). The reference runs one Metal
+// pipeline with caller-chosen grid and positional buffer / inline-bytes arguments. The CUDA kernels of this library are
+// launched by planners that size grids, shared memory and scratch themselves, so what can be run by name are the operators:
+//   "exl3_linear"   args: trellis, suh, svh, x (f32 [rows][in]), y (f32 [rows][out]) buffers, then inline u32 {in, out, K, rows}
+//   "exl3_dequant"  args: trellis, w (f16 [in][out]) buffers, then inline u32 {in, out, K}
+// with buffer arguments given as (ne_buf, offset) exactly as in the reference, `reps` repetitions timed on the GPU and the
+// total returned in *gpu_ms; grid, threadgroup size, threadgroup memory, function constants and backend are accepted and
+// ignored. The reference's Metal kernel names (fn_moe_gateup_k5_r1, t6_simd, ...) are reported absent: their argument lists
+// bind the reference's Metal scratch layout (its per-row `uq` tables, split buffers and counters), which does not exist here.
+static const char *kOperators[] = {"exl3_linear", "exl3_dequant"};
 static const char *kKernels[] = {"stream_gemm_kernel", "moe_router_kernel", "moe_prep_kernel", "moe_mid_kernel", "moe_combine_kernel",
                                  "prep_rows_kernel", "linear_finish_kernel", "dequant_kernel", "pf_gemm_kernel", "pf_logits_kernel",
                                  "pf_route_kernel", "pf_prep_kernel", "pf_mid_kernel", "pf_finish_kernel"};
 NE_API int ne_kernel_exists(const char *fn) {
   if (!fn) return -1;
+  for (const char *k : kOperators)
+    if (strcmp(k, fn) == 0) return 1;
   for (const char *k : kKernels)
     if (strcmp(k, fn) == 0) return 1;
   return 0;
 }
-NE_API int ne_run_kernel(const char *fn, const ne_fconst *, int, const ne_arg *, int, const uint32_t[3], const uint32_t[3],
-                         uint32_t, int, const char *, double *) {
+
+static void *arg_device(const ne_arg &a, const char *what) {
+  IJ_CHECK(a.buf != nullptr, "%s must be a buffer argument", what);
+  const uint64_t base = ne_buf_gpu_address(a.buf);
+  IJ_CHECK(base != 0, "%s: %s", what, ne_last_error());
+  IJ_CHECK(a.offset <= ne_buf_size(a.buf), "%s: offset beyond the buffer", what);
+  return reinterpret_cast<void *>(base + a.offset);
+}
+static void arg_u32(const ne_arg &a, uint32_t *dst, int n, const char *what) {
+  IJ_CHECK(a.buf == nullptr && a.bytes != nullptr && a.nbytes == (uint32_t)n * 4, "%s must be %d inline u32 values", what, n);
+  memcpy(dst, a.bytes, (size_t)n * 4);
+}
+
+NE_API int ne_run_kernel(const char *fn, const ne_fconst *, int, const ne_arg *args, int nargs, const uint32_t[3], const uint32_t[3], uint32_t,
+                         int reps, const char *, double *gpu_ms) {
   return c_call([&] {
-    fail("ne_run_kernel(%s): kernels of the CUDA build are reached through their operator entry points (ne_exl3_linear, "
-         "ne_exl3_dequant, ne_moe_stage, ne_fn_layer_run_dispatch), not by name with positional Metal-style arguments",
-         fn ? fn : "(null)");
+    IJ_CHECK(fn != nullptr, "null kernel name");
+    IJ_CHECK(reps >= 1 && reps <= 100000, "reps %d outside 1..100000", reps);
+    const std::string name = fn;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    auto timed = [&](auto &&launch) {
+      IJ_CUDA(cudaEventCreate(&e0));
+      IJ_CUDA(cudaEventCreate(&e1));
+      launch();  // untimed first run: first-use set-up (scratch arena, attributes)
+      IJ_CUDA(cudaEventRecord(e0, 0));
+      for (int i = 0; i < reps; i++) launch();
+      IJ_CUDA(cudaEventRecord(e1, 0));
+      IJ_CUDA(cudaEventSynchronize(e1));
+      float ms = 0;
+      IJ_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      if (gpu_ms) *gpu_ms = ms;
+      check_status_word();
+    };
+    if (name == "exl3_linear") {
+      IJ_CHECK(args != nullptr && nargs == 6, "exl3_linear takes 6 arguments: trellis, suh, svh, x, y, {in, out, K, rows}");
+      uint32_t d[4];
+      arg_u32(args[5], d, 4, "argument 5");
+      ne_exl3_weight w{arg_device(args[0], "trellis"), arg_device(args[1], "suh"), arg_device(args[2], "svh"), (int)d[0], (int)d[1], (int)d[2]};
+      const float *x = (const float *)arg_device(args[3], "x");
+      float *y = (float *)arg_device(args[4], "y");
+      timed([&] { IJ_CHECK(ne_exl3_linear(&w, x, (int)d[3], y, nullptr) == 0, "%s", ne_last_error()); });
+    } else if (name == "exl3_dequant") {
+      IJ_CHECK(args != nullptr && nargs == 3, "exl3_dequant takes 3 arguments: trellis, w, {in, out, K}");
+      uint32_t d[3];
+      arg_u32(args[2], d, 3, "argument 2");
+      ne_exl3_weight w{arg_device(args[0], "trellis"), nullptr, nullptr, (int)d[0], (int)d[1], (int)d[2]};
+      void *out = arg_device(args[1], "w");
+      timed([&] { IJ_CHECK(ne_exl3_dequant(&w, out, nullptr) == 0, "%s", ne_last_error()); });
+    } else if (ne_kernel_exists(fn) == 1) {
+      fail("ne_run_kernel(%s): this CUDA kernel is launched by its operator's planner (grid, shared memory and scratch are the planner's); "
+           "run the operator by name instead: exl3_linear, exl3_dequant", fn);
+    } else {
+      fail("ne_run_kernel(%s): no such kernel in the CUDA build (the reference's Metal kernels bind its Metal scratch layout; operators "
+           "that can be run by name: exl3_linear, exl3_dequant)", fn);
+    }
   });
 }
 

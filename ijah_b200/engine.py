@@ -62,6 +62,10 @@ class ModelDescC(C.Structure):
                                        "kv_positions", "expert_first", "expert_count", "ep_world")]
 
 
+class ArgC(C.Structure):  # ne_arg: a buffer with a byte offset, or inline bytes
+    _fields_ = [("buf", C.c_void_p), ("offset", C.c_uint64), ("bytes", C.c_void_p), ("nbytes", C.c_uint32)]
+
+
 class EngineError(RuntimeError):
     pass
 
@@ -154,141 +158,176 @@ def load_library(path=None):
     return lib
 
 
-class Buf:
-    """An ne_buf handle. owned=False for pack-owned views (never freed)."""
+class _Owned:
+    """Base of the wrappers around an opaque C handle: remembers the engine, releases the handle once (explicitly with
+    free() / close(), or when used as a context manager) and refuses further use afterwards."""
+
+    _release = None  # name of the C function that releases the handle
+
+    def __init__(self, eng, ptr, what):
+        if not ptr:
+            raise EngineError(f"{what}: {eng.last_error()}")
+        self.eng, self.ptr = eng, ptr
+
+    def _live(self):
+        if not self.ptr:
+            raise EngineError(f"{type(self).__name__} used after it was released")
+        return self.ptr
+
+    def free(self):
+        ptr, self.ptr = self.ptr, None
+        if ptr and self._release:
+            getattr(self.eng.lib, self._release)(ptr)
+
+    close = free
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.free()
+
+
+def _flat_count(nbytes, dtype, shape):
+    return int(np.prod(shape)) if shape is not None else nbytes // np.dtype(dtype).itemsize
+
+
+class Buf(_Owned):
+    """A device buffer of the library (ne_buf): a managed allocation made by Engine.alloc, a device copy of pack rows, or
+    -- with owned=False -- the handle of a pack tensor, which the pack releases, never this object."""
 
     def __init__(self, eng, ptr, owned=True):
-        self.eng, self.ptr, self.owned = eng, ptr, owned
+        super().__init__(eng, ptr, "ne_buf")
+        self._release = "ne_free" if owned else None
+        self.owned = owned
 
     @property
     def size(self):
-        return self.eng.lib.ne_buf_size(self.ptr)
+        return int(self.eng.lib.ne_buf_size(self._live()))
 
     def contents(self):
-        return self.eng.lib.ne_buf_contents(self.ptr)
+        """address of the bytes as the CPU sees them"""
+        return self.eng.lib.ne_buf_contents(self._live())
 
     def gpu_address(self):
-        a = self.eng.lib.ne_buf_gpu_address(self.ptr)
-        if not a:
+        """address of the bytes as kernels see them (a pack tensor becomes resident on the device here)"""
+        addr = self.eng.lib.ne_buf_gpu_address(self._live())
+        if not addr:
             raise EngineError(self.eng.last_error())
-        return a
+        return addr
 
     def upload(self, arr, offset=0):
-        a = np.ascontiguousarray(arr)
-        self.eng._ok(self.eng.lib.ne_upload(self.ptr, offset, a.ctypes.data, a.nbytes), "ne_upload")
+        src = np.ascontiguousarray(arr)
+        self.eng._ok(self.eng.lib.ne_upload(self._live(), int(offset), src.ctypes.data, src.nbytes), "ne_upload")
 
     def download(self, dtype=np.float32, shape=None, offset=0):
-        dtype = np.dtype(dtype)
-        n = (self.size - offset) // dtype.itemsize if shape is None else int(np.prod(shape))
-        out = np.empty(n, dtype)
-        self.eng._ok(self.eng.lib.ne_download(self.ptr, offset, out.ctypes.data, out.nbytes), "ne_download")
-        return out.reshape(shape) if shape is not None else out
+        out = np.empty(_flat_count(self.size - offset, dtype, shape), dtype)
+        self.eng._ok(self.eng.lib.ne_download(self._live(), int(offset), out.ctypes.data, out.nbytes), "ne_download")
+        return out if shape is None else out.reshape(shape)
 
-    def free(self):
-        if self.ptr and self.owned:
-            self.eng.lib.ne_free(self.ptr)
-        self.ptr = None
+    def numpy(self, dtype=np.float32, shape=None, offset=0):
+        """the same bytes as a numpy array without a copy (managed memory: synchronise with the GPU before touching it)"""
+        n = _flat_count(self.size - offset, dtype, shape)
+        mem = (C.c_char * (n * np.dtype(dtype).itemsize)).from_address(self.contents() + offset)
+        out = np.frombuffer(mem, dtype, n)
+        return out if shape is None else out.reshape(shape)
 
 
 class TensorDesc:
+    """What ne_tensor_info reports about one pack tensor."""
+
     def __init__(self, eng, name, d):
-        self.name = name
-        self.dtype = DTYPES.get(d.dtype, str(d.dtype))
-        self.shape = tuple(d.shape[i] for i in range(d.ndim))
-        self.nbytes = d.nbytes
+        self.name, self.nbytes = name, int(d.nbytes)
+        self.dtype = DTYPES.get(d.dtype, f"dtype{d.dtype}")
+        self.shape = tuple(int(d.shape[i]) for i in range(d.ndim))
         self.file = d.file.decode() if d.file else None
-        self.file_offset = d.file_offset
+        self.file_offset = int(d.file_offset)
         self.host_ptr = d.host
         self.buf = Buf(eng, d.buf, owned=False) if d.buf else None
-        self.buf_offset = d.buf_offset
+        self.buf_offset = int(d.buf_offset)
 
     def host(self):
-        """numpy view of the read-only file mapping (valid while the pack is open)"""
-        dt = np.dtype(NP[self.dtype])
-        raw = (C.c_char * self.nbytes).from_address(self.host_ptr)
-        return np.frombuffer(raw, dt, self.nbytes // dt.itemsize).reshape(self.shape)
+        """the tensor's bytes in the read-only file mapping as a numpy array (bf16 as uint16); valid while the pack is open"""
+        elem = np.dtype(NP[self.dtype])
+        mem = (C.c_char * self.nbytes).from_address(self.host_ptr)
+        return np.frombuffer(mem, elem, self.nbytes // elem.itemsize).reshape(self.shape)
+
+    def __repr__(self):
+        return f"<{self.name}: {self.dtype} {list(self.shape)}>"
 
 
-class Pack:
+class Pack(_Owned):
+    """An open pack directory (safetensors shards, their index, config.json)."""
+
+    _release = "ne_pack_close"
+
     def __init__(self, eng, path):
-        self.eng = eng
         self.path = str(Path(path).expanduser())
-        self.ptr = eng.lib.ne_pack_open(self.path.encode())
-        if not self.ptr:
-            raise EngineError(f"ne_pack_open({self.path}): {eng.last_error()}")
+        super().__init__(eng, eng.lib.ne_pack_open(self.path.encode()), f"ne_pack_open({self.path})")
 
     def config(self):
-        return json.loads(self.eng.lib.ne_pack_config_json(self.ptr).decode())
+        return json.loads(self.eng.lib.ne_pack_config_json(self._live()).decode())
 
     def names(self):
-        n = self.eng.lib.ne_pack_num_tensors(self.ptr)
-        return [self.eng.lib.ne_pack_tensor_name(self.ptr, i).decode() for i in range(n)]
+        lib, ptr = self.eng.lib, self._live()
+        return [lib.ne_pack_tensor_name(ptr, i).decode() for i in range(lib.ne_pack_num_tensors(ptr))]
 
     def info(self, name):
-        d = TensorDescC()
-        if self.eng.lib.ne_tensor_info(self.ptr, name.encode(), C.byref(d)) != 0:
+        raw = TensorDescC()
+        if self.eng.lib.ne_tensor_info(self._live(), name.encode(), C.byref(raw)):
             raise KeyError(f"{name}: {self.eng.last_error()}")
-        return TensorDesc(self.eng, name, d)
+        return TensorDesc(self.eng, name, raw)
 
     def view_rows(self, name, row0, nrows):
-        off = C.c_uint64(0)
-        p = self.eng.lib.ne_pack_view_rows(self.ptr, name.encode(), row0, nrows, C.byref(off))
-        if not p:
-            raise EngineError(self.eng.last_error())
-        return Buf(self.eng, p), off.value
-
-    def close(self):
-        if self.ptr:
-            self.eng.lib.ne_pack_close(self.ptr)
-        self.ptr = None
+        """(Buf, offset): a device copy of rows [row0, row0 + nrows) of a tensor's first dimension, owned by the caller"""
+        offset = C.c_uint64(0)
+        ptr = self.eng.lib.ne_pack_view_rows(self._live(), name.encode(), row0, nrows, C.byref(offset))
+        return Buf(self.eng, ptr), int(offset.value)
 
 
-class FnLayer:
-    """The MoE block of one decoder layer behind the reference's layer entry points (f32 host I/O)."""
+class FnLayer(_Owned):
+    """The MoE block of one decoder layer behind the reference's layer entry points; every named buffer crosses the ABI as
+    float32 host memory."""
+
+    _release = "ne_fn_layer_free"
 
     def __init__(self, eng, pack, layer, rows=1):
-        self.eng = eng
-        self.ptr = eng.lib.ne_fn_layer_create_rows(pack.ptr, layer, rows)
-        if not self.ptr:
-            raise EngineError(f"ne_fn_layer_create_rows(L{layer}, {rows}): {eng.last_error()}")
+        super().__init__(eng, eng.lib.ne_fn_layer_create_rows(pack.ptr, layer, rows), f"ne_fn_layer_create_rows(layer {layer}, {rows} rows)")
         self.layer, self.rows = layer, rows
 
+    def _call(self, fn, *args):
+        self.eng._ok(getattr(self.eng.lib, fn)(self._live(), *args), fn)
+
     def step(self, h_in=None):
-        ms = C.c_double(0)
-        self.eng._ok(self.eng.lib.ne_fn_layer_step(self.ptr, None, None, C.byref(ms)), "step")
+        self._call("ne_fn_layer_step", None, None, C.byref(C.c_double(0)))  # always an error here: only the MoE block exists
 
     def run_stage(self, stage):
-        self.eng._ok(self.eng.lib.ne_fn_layer_run_stage(self.ptr, int(stage)), f"run_stage({stage})")
+        self._call("ne_fn_layer_run_stage", int(stage))
 
     def run_dispatch(self, stage):
-        self.eng._ok(self.eng.lib.ne_fn_layer_run_dispatch(self.ptr, int(stage)), f"run_dispatch({stage})")
+        self._call("ne_fn_layer_run_dispatch", int(stage))
 
     def size(self, name):
-        n = self.eng.lib.ne_fn_layer_read(self.ptr, name.encode(), None, 0)
-        if n < 0:
+        count = self.eng.lib.ne_fn_layer_read(self._live(), name.encode(), None, 0)
+        if count < 0:
             raise KeyError(f"{name}: {self.eng.last_error()}")
-        return n
+        return count
 
     def read(self, name):
-        n = self.size(name)
-        out = np.empty(n, np.float32)
-        if self.eng.lib.ne_fn_layer_read(self.ptr, name.encode(), out.ctypes.data, n) < 0:
+        out = np.empty(self.size(name), np.float32)
+        if self.eng.lib.ne_fn_layer_read(self._live(), name.encode(), out.ctypes.data, out.size) < 0:
             raise EngineError(self.eng.last_error())
         return out
 
     def write(self, name, arr):
-        a = np.ascontiguousarray(arr, np.float32).reshape(-1)
-        self.eng._ok(self.eng.lib.ne_fn_layer_write(self.ptr, name.encode(), a.ctypes.data, a.size), f"write({name})")
+        src = np.ascontiguousarray(arr, np.float32).ravel()
+        self._call("ne_fn_layer_write", name.encode(), src.ctypes.data, src.size)
 
     def time(self, reps1=8, reps2=40, flush_mb=0):
-        us, fl = C.c_double(0), C.c_double(0)
-        self.eng._ok(self.eng.lib.ne_fn_layer_time(self.ptr, reps1, reps2, flush_mb, C.byref(us), C.byref(fl)), "time")
-        return us.value, fl.value
-
-    def free(self):
-        if self.ptr:
-            self.eng.lib.ne_fn_layer_free(self.ptr)
-        self.ptr = None
+        """(microseconds per MoE block, microseconds of the cache flush between blocks), differential over two chain lengths"""
+        step_us, flush_us = C.c_double(0), C.c_double(0)
+        self._call("ne_fn_layer_time", reps1, reps2, flush_mb, C.byref(step_us), C.byref(flush_us))
+        return step_us.value, flush_us.value
 
 
 class FnModel:
@@ -364,40 +403,42 @@ class FnModel:
         return dict(total=t.value, distinct_experts_mean=n.value)
 
     def free(self):
-        if self.ptr:
-            self.eng.lib.ne_fn_model_free(self.ptr)
-        self.ptr = None
+        ptr, self.ptr = self.ptr, None
+        if ptr:
+            self.eng.lib.ne_fn_model_free(ptr)
 
 
 class Engine:
+    """The loaded library plus the factories of the handle wrappers above."""
+
     def __init__(self, lib=None):
         self.lib = load_library(lib)
 
     def last_error(self):
-        return self.lib.ne_last_error().decode()
+        msg = self.lib.ne_last_error()
+        return msg.decode() if msg else ""
 
     def _ok(self, rc, what):
-        if rc != 0:
+        if rc:
             raise EngineError(f"{what}: {self.last_error()}")
 
+    def abi_version(self):
+        return self.lib.ne_abi_version()
+
     def device(self):
-        d = DeviceInfo()
-        self._ok(self.lib.ne_device_query(C.byref(d)), "ne_device_query")
-        return dict(name=d.name.decode(), has_nax=d.has_nax, has_metal4=d.has_metal4,
-                    max_buffer_length=d.max_buffer_length, recommended_working_set=d.recommended_working_set,
-                    max_threadgroup_memory=d.max_threadgroup_memory, backend=d.backend.decode())
+        info = DeviceInfo()
+        self._ok(self.lib.ne_device_query(C.byref(info)), "ne_device_query")
+        text = {"name", "backend"}
+        return {f: (getattr(info, f).decode() if f in text else getattr(info, f)) for f, _ in DeviceInfo._fields_}
 
     def alloc(self, nbytes):
-        p = self.lib.ne_alloc(nbytes)
-        if not p:
-            raise EngineError(self.last_error())
-        return Buf(self, p)
+        return Buf(self, self.lib.ne_alloc(int(nbytes)))
 
     def from_numpy(self, arr):
-        a = np.ascontiguousarray(arr)
-        b = self.alloc(a.nbytes)
-        b.upload(a)
-        return b
+        src = np.ascontiguousarray(arr)
+        buf = self.alloc(max(src.nbytes, 1))
+        buf.upload(src)
+        return buf
 
     def pack_open(self, path):
         return Pack(self, path)
@@ -410,6 +451,28 @@ class Engine:
 
     def kernel_exists(self, name):
         return self.lib.ne_kernel_exists(name.encode()) == 1
+
+    def run_kernel(self, name, args, reps=1):
+        """Run an operator by name (ne_run_kernel: "exl3_linear", "exl3_dequant") `reps` times; returns the GPU milliseconds of
+        all repetitions. Each argument is a Buf, a (Buf, byte offset) pair, a TensorDesc of a pack tensor, or anything numpy
+        can turn into bytes (passed inline)."""
+        packed, keep = (ArgC * max(len(args), 1))(), []
+        for slot, a in zip(packed, args):
+            if isinstance(a, TensorDesc):
+                a = (a.buf, a.buf_offset)
+            if isinstance(a, Buf):
+                a = (a, 0)
+            if isinstance(a, tuple):
+                slot.buf, slot.offset = a[0].ptr, int(a[1])
+            else:
+                blob = np.ascontiguousarray(a).tobytes()
+                keep.append(C.create_string_buffer(blob, len(blob)))
+                slot.bytes, slot.nbytes = C.cast(keep[-1], C.c_void_p), len(blob)
+        ms = C.c_double(0)
+        three = (C.c_uint32 * 3)(1, 1, 1)
+        self._ok(self.lib.ne_run_kernel(name.encode(), None, 0, packed, len(args), three, three, 0, int(reps), None, C.byref(ms)),
+                 f"ne_run_kernel({name})")
+        return ms.value
 
 
 # ------------------------------------------------------------------ dimension-explicit operators (torch for memory)

@@ -11,8 +11,9 @@
  *    return after the work is done unless they take a stream).
  *  - A pack tensor's GPU view is a device copy made on first use (the reference maps the file without a copy); the
  *    copy is 256-byte aligned whatever the file offset is, so nothing like the reference's align-pack step is needed.
- *  - ne_run_kernel knows the CUDA kernels of this library by their own names (see ne_kernel_exists); the reference's
- *    Metal kernel names are reported as absent.
+ *  - ne_run_kernel runs this library's operators by name ("exl3_linear", "exl3_dequant": argument lists at its
+ *    declaration below); the reference's Metal kernel names are reported as absent, because their argument lists bind the
+ *    reference's Metal scratch layout.
  */
 #ifndef IJAH_ENGINE_H
 #define IJAH_ENGINE_H
@@ -85,7 +86,11 @@ NE_API ne_buf *ne_pack_view_rows(const ne_pack *p, const char *name, int64_t row
 /* kernels: reference include/engine.h:85-98 */
 typedef struct { uint32_t index; uint32_t type; uint32_t bits; } ne_fconst;
 typedef struct { ne_buf *buf; uint64_t offset; const void *bytes; uint32_t nbytes; } ne_arg;
-NE_API int ne_kernel_exists(const char *fn);
+NE_API int ne_kernel_exists(const char *fn); /* 1 for the operators below and for the names of this library's CUDA kernels */
+/* Operators that can be run by name, `reps` times, GPU milliseconds of all repetitions in *gpu_ms (fc, grid, tg, tg_mem and
+ * backend are accepted and ignored: the planners size the launches):
+ *   "exl3_linear"   args: trellis, suh, svh, x (f32 [rows][in]), y (f32 [rows][out]) as (buf, offset), then inline u32 {in, out, K, rows}
+ *   "exl3_dequant"  args: trellis, w (f16 [in][out]) as (buf, offset), then inline u32 {in, out, K} */
 NE_API int ne_run_kernel(const char *fn, const ne_fconst *fc, int nfc, const ne_arg *args, int nargs,
                          const uint32_t grid[3], const uint32_t tg[3], uint32_t tg_mem, int reps, const char *backend,
                          double *gpu_ms);

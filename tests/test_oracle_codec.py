@@ -1,9 +1,11 @@
 """The codec oracle against restatements of the reference's device readers (CPU only).
 
-Two readers exist in the reference: the K = 4..6 expert reader (kernels/ne_common.h:109-157: lane_load, lane_funnel,
-win_off, cw_at, dec8) and the any-K trunk reader (kernels/trunk6/trunk6.metal:91-127: t6_lane, t6_load, t6_dec). Both
-are restated below step by step in scalar Python with 32-bit wrap-around; the oracle's ring formula must give the same
-codeword for every slot of random tiles.
+Three readers exist in the reference: the K = 4..6 expert reader (kernels/ne_common.h:109-157: lane_load, lane_funnel,
+win_off, cw_at, dec8), the any-K trunk reader (kernels/trunk6/trunk6.metal:91-127: t6_lane, t6_load, t6_dec) and the
+prefill reader that feeds the matrix unit (kernels/prefill/pf_moe.metal:164-222: exl3_window, nax_wfrag, nax_quads,
+nax_wfrag_k). All three are restated below step by step in scalar Python with 32- / 64-bit wrap-around; the oracle's ring
+formula must give the same codeword for every slot of random tiles. The reference holds no known-answer vector for the
+codec, so three readers written independently of each other agreeing with one formula is the pin there is.
 """
 import numpy as np
 import pytest
@@ -70,6 +72,56 @@ def reader_trunk(words, K):
     return np.array(out, np.uint32)
 
 
+M64 = 0xFFFFFFFFFFFFFFFF
+
+
+def _exl3_window(words, end, nwords, full):
+    """pf_moe.metal exl3_window: the bits that end at ring bit `end`, right-aligned (64 bits, or 96 folded when `full`)"""
+    last = (end - 1) >> 5
+    prev = nwords - 1 if last == 0 else last - 1
+    s = (0 - end) & 31
+    bits = (((int(words[prev]) << 32) | int(words[last])) & M64) >> s
+    if full:
+        pp = nwords - 1 if prev == 0 else prev - 1
+        bits |= (((int(words[pp]) << 32) & M64) << (32 - s)) & M64
+    return bits
+
+
+def reader_prefill(words, K):
+    """pf_moe.metal nax_wfrag_k<N = 16K> for the 32 lanes: (slot, 16-bit window) pairs in the order the fragment holds them.
+    Lane l's fragment holds slots base + (0, 1, 8, 9, 4, 5, 12, 13), base = 128 (l >> 4) + 16 (l & 7) + 2 ((l >> 3) & 1)."""
+    N = 16 * K
+    W = N // 2
+    end_of = lambda b, j: ((2 * b + j + 1) * N) >> 4  # nax_end
+    out = []
+    for lane in range(32):
+        b = (lane >> 3) & 1
+        base = 128 * (lane >> 4) + 16 * (lane & 7) + 2 * b
+        if N == 64:  # nax_wfrag: K = 4, eight 4-bit steps per word
+            source0 = (lane & 16) + ((lane & 7) << 1)
+            cx, cy = int(words[source0]), int(words[source0 + 1])
+            previous = int(words[(source0 + 31) & 31])
+            slot = b * 2
+            w0, w1 = (previous << 32) | cx, (cx << 32) | cy
+            s0, s1 = 28 - slot * 4, 28 - (slot + 4) * 4
+            cws = [(w0 >> s0) & 0xFFFF, (w0 >> (s0 - 4)) & 0xFFFF, (w1 >> s0) & 0xFFFF, (w1 >> (s0 - 4)) & 0xFFFF,
+                   (w0 >> s1) & 0xFFFF, (w0 >> (s1 - 4)) & 0xFFFF, (w1 >> s1) & 0xFFFF, (w1 >> (s1 - 4)) & 0xFFFF]
+        else:
+            end = 8 * N * (lane >> 4) + N * (lane & 7) + (end_of(1, 5) - end_of(0, 5)) * b + end_of(0, 5)
+            sh = lambda j: (end_of(0, 5) - end_of(0, j)) + b * ((end_of(1, 5) - end_of(1, j)) - (end_of(0, 5) - end_of(0, j)))  # nax_sh
+            s0, s1, s4 = sh(0), sh(1), sh(4)
+            fit = end_of(0, 5) - end_of(0, 0) <= 16 and end_of(1, 5) - end_of(1, 0) <= 16  # nax_quads_fit
+            lo, hi = _exl3_window(words, end, W, not fit), _exl3_window(words, end + W, W, not fit)
+            if fit:
+                lo, hi = lo & M32, hi & M32
+            q = lambda v: [(v >> s0) & 0xFFFF, (v >> s1) & 0xFFFF, (v >> s4) & 0xFFFF, v & 0xFFFF]
+            p01, p23 = q(lo), q(hi)  # nax_quads: p0 = (s0, s1), p1 = (s4, 0) of lo; p2, p3 the same of hi
+            cws = [p01[0], p01[1], p23[0], p23[1], p01[2], p01[3], p23[2], p23[3]]
+        for off, cw in zip((0, 1, 8, 9, 4, 5, 12, 13), cws):
+            out.append((base + off, cw))
+    return out
+
+
 def dec_mcg_scalar(cw):
     """ne_common.h dec_mcg for one codeword, half-precision add via numpy float16"""
     cw &= 0x7FFF
@@ -91,6 +143,10 @@ def test_ring_formula_matches_both_device_readers(K):
         if K <= 6:
             a = reader_expert(words, K)
             assert np.array_equal(mine, a)
+        c = reader_prefill(words, K)
+        assert sorted(slot for slot, _ in c) == list(range(256)), "the 32 fragments cover every slot once"
+        for slot, cw in c:
+            assert (cw & 0x7FFF) == (int(mine[slot]) & 0x7FFF), (K, slot)
 
 
 def test_codebook_values_and_statistics():
