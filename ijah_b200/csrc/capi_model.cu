@@ -44,6 +44,7 @@ struct Model {
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::map<int, cudaGraphExec_t> graphs;  // key: rows * 2 + head
+  std::vector<int> graph_lru;             // keys, most recently used last; at most kMaxGraphs graphs are kept
   EpCtx *ep = nullptr;                    // expert-parallel exchange over peer memory (not owned); null = single GPU
   int launches_full = 0, launches_body = 0;
   uint64_t steps = 0;
@@ -145,10 +146,22 @@ int Model::record(int rows, bool with_head, cudaStream_t st) {
   return n;
 }
 
+// One captured step per (row count, head), as the reference keeps one recording per chunk length with the least recently
+// used one dropped beyond 32 (models/flash_next/prefill.mm:295-345).
+constexpr size_t kMaxGraphs = 32;
 cudaGraphExec_t Model::graph_for(int rows, bool with_head) {
   const int key = rows * 2 + (with_head ? 1 : 0);
   auto it = graphs.find(key);
+  graph_lru.erase(std::remove(graph_lru.begin(), graph_lru.end(), key), graph_lru.end());
+  graph_lru.push_back(key);
   if (it != graphs.end()) return it->second;
+  if (graphs.size() >= kMaxGraphs) {
+    IJ_CUDA(cudaStreamSynchronize(stream));
+    const int old = graph_lru.front();
+    graph_lru.erase(graph_lru.begin());
+    cudaGraphExecDestroy(graphs[old]);
+    graphs.erase(old);
+  }
   // a first eager run outside capture: opts the kernels in to their shared-memory sizes and surfaces launch errors early
   record(rows, with_head, stream);
   IJ_CUDA(cudaStreamSynchronize(stream));
@@ -443,6 +456,31 @@ NE_API int ne_fn_model_step_rows(ne_fn_model *m, const int *tokens_host, int row
     Model *M = reinterpret_cast<Model *>(m);
     IJ_CHECK(M != nullptr, "null model");
     M->step(tokens_host, rows, head, logits_host, next_host, gpu_ms);
+  });
+}
+// Prompt prefill (reference models/flash_next/model.h:231): the prompt goes through the stack in chunks of up to max_rows
+// rows, each chunk replayed from the graph of its length (captured on first use, least recently used dropped beyond 32);
+// the head runs on the last chunk only and the last token's logits / greedy token are returned. The attention stand-in
+// keeps no per-token state, so unlike the reference nothing is appended to a cache.
+NE_API int ne_fn_model_prefill(ne_fn_model *m, const int *prompt, int n, float *logits, int *next, double *ms) {
+  return c_call([&] {
+    Model *M = reinterpret_cast<Model *>(m);
+    IJ_CHECK(M != nullptr && prompt != nullptr && n >= 1, "bad arguments");
+    const auto t0 = std::chrono::steady_clock::now();
+    std::vector<int> nx(M->max_rows);
+    std::vector<float> lg;
+    for (int i = 0; i < n; i += M->max_rows) {
+      const int rows = std::min(M->max_rows, n - i);
+      const bool last = i + rows >= n;
+      if (last && logits) lg.resize((size_t)rows * M->d.vocab);
+      M->step(prompt + i, rows, last ? 1 : 0, last && logits ? lg.data() : nullptr, last ? nx.data() : nullptr, nullptr);
+      if (last) {
+        if (next) *next = nx[rows - 1];
+        if (logits) memcpy(logits, lg.data() + (size_t)(rows - 1) * M->d.vocab, (size_t)M->d.vocab * 4);
+      }
+    }
+    check_status_word();
+    if (ms) *ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
   });
 }
 NE_API int ne_fn_model_replay(ne_fn_model *m, int rows, int head, int steps, double *total_ms) {

@@ -136,6 +136,7 @@ SIGNATURES = {
     "ne_fn_model_step_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_double)]),
     "ne_fn_model_time": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "ne_fn_model_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ne_fn_model_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_double)]),
     "ne_fn_model_replay": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "ne_fn_model_desc_of": (C.c_int, [C.c_void_p, C.POINTER(ModelDescC)]),
     "ne_fn_model_set_ep": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -367,6 +368,15 @@ class FnModel:
         self.eng._ok(self.eng.lib.ne_fn_model_step_rows(self.ptr, t.ctypes.data, rows, int(head), lg.ctypes.data if want_logits else None,
                                                         nx.ctypes.data, C.byref(ms)), "ne_fn_model_step_rows")
         return nx, lg, ms.value
+
+    def prefill(self, prompt, want_logits=True):
+        """the prompt in chunks of up to max_rows rows: (greedy next token, logits of the last token or None, wall ms)"""
+        ids = np.ascontiguousarray(prompt, np.int32)
+        lg = np.empty(self.desc["vocab"], np.float32) if want_logits else None
+        nx, ms = C.c_int(-1), C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_prefill(self.ptr, ids.ctypes.data, len(ids), lg.ctypes.data if want_logits else None,
+                                                      C.byref(nx), C.byref(ms)), "ne_fn_model_prefill")
+        return nx.value, lg, ms.value
 
     def replay(self, rows, steps, head=True):
         """device time in ms of `steps` replays of the captured step (inputs and results stay on the device)"""

@@ -132,6 +132,9 @@ NE_API int ne_fn_model_step(ne_fn_model *m, int token, int head, float *logits, 
 /* model.h:217-218: GPU time of the full decode step: median / min over reps graph replays, wall time per synchronous step */
 NE_API int ne_fn_model_time(ne_fn_model *m, int T, int reps, double *gpu_ms_median, double *gpu_ms_min, double *wall_ms_median);
 NE_API int ne_fn_model_info(ne_fn_model *m, int *n_dispatch_full, int *n_dispatch_body, int *T); /* model.h:219 */
+/* model.h:231: the prompt in chunks (one captured step per chunk length, at most 32 kept, least recently used dropped: as the
+ * reference's chunked-prefill recordings, prefill.mm:295-345), the head on the last token: its logits f32 [vocab] / greedy token */
+NE_API int ne_fn_model_prefill(ne_fn_model *m, const int *prompt, int n, float *logits, int *next, double *ms);
 
 #ifdef __cplusplus
 }

@@ -108,6 +108,11 @@ def test_synthetic_stack_runs_and_is_deterministic(eng):
     # a row's logits do not depend on which other rows share the step (up to the summation order of the k-splits)
     n1, l1, _ = a.step_rows(tokens[3:4], want_logits=True)
     assert np.abs(l1[0] - la[3]).max() / np.abs(la[3]).max() < 1e-4
+    # prompt prefill: chunks of max_rows rows, the head on the last chunk; its last row equals that token's own step
+    prompt = (np.arange(37, dtype=np.int32) * 29 + 3) % 1024
+    nx, lg, ms = a.prefill(prompt)
+    _, l5, _ = a.step_rows(prompt[32:37], want_logits=True)  # the last chunk (37 = 16 + 16 + 5)
+    assert np.array_equal(lg, l5[4]) and nx == int(l5[4].argmax()) and ms > 0
     assert a.weight_bytes() > 0 and a.last_bytes(16)["total"] > 0
     assert eng.lib.ne_device_wait_status() == 0
     a.free()
