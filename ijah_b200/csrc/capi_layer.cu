@@ -1,5 +1,5 @@
-// C ABI, part 3: the layer object of the reference (models/flash_next/layer.h:226-268) restricted to its MoE block,
-// and the kernel-by-name entry points. Dims come from the pack's tensor shapes (the reference hard-codes 2560 / 640).
+// C ABI, part 3: the layer object of the reference (models/flash_next/layer.h:226-268) restricted to its MoE block and the
+// hyper-connection read in front of it, and the kernel-by-name entry points. Dims come from the pack's tensor shapes (the reference hard-codes 2560 / 640).
 #include <cstring>
 #include <memory>
 #include <string>
@@ -7,18 +7,21 @@
 
 #include "../../include/ijah_b200.h"
 #include "capi_internal.hpp"
+#include "hc_read.cuh"
 #include "moe_object.hpp"
 
 using namespace ijah;
 
 namespace ijah {
-constexpr int kHC = 4;  // hyper-connection streams (reference models/flash_next/layer.h:17-19)
+constexpr int kHC = HC_STREAMS;
 
 struct Layer {
   std::shared_ptr<Pack> pack;  // keeps the mapping alive past ne_pack_close (reference core/capi.mm:105-110)
   std::unique_ptr<Moe> moe;
   int rows = 1, H = 0, I = 0, E = 0, k = 0;
-  float *mlp_in = nullptr, *mlp_out = nullptr, *h_mid = nullptr, *h_out = nullptr, *inj = nullptr;
+  float *mlp_in = nullptr, *mlp_out = nullptr, *h_mid = nullptr, *h_out = nullptr, *inj = nullptr, *mlp_mix = nullptr;
+  bool has_hc = false;  // the pack holds this layer's mlp_hyper_connection tensors
+  HcWeights hc;
   std::vector<void *> owned;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   ~Layer() {
@@ -58,6 +61,40 @@ static ne_exl3_stack stack(Pack &p, const std::string &pre, int E, int in, int o
   w.svh_dev = p.device(pre + ".svh", &s);
   IJ_CHECK(s->dtype == NE_F16 && (int64_t)(s->nbytes / 2) == (int64_t)E * out, "%s.svh: want F16 [%d][%d]", pre.c_str(), E, out);
   return w;
+}
+
+// 8-bit affine Linear of the pack (reference models/flash_next/layer.mm:60-76): <pre>.weight U32 [rows][in / 4],
+// <pre>.scales / .biases BF16 [rows][in / group]
+static Q8Weight q8_weight(Pack &p, const std::string &pre) {
+  const TensorInfo *t = nullptr, *s = nullptr, *b = nullptr;
+  Q8Weight q;
+  q.w = static_cast<const uint8_t *>(p.device(pre + ".weight", &t));
+  IJ_CHECK(t->dtype == NE_U32 && t->ndim == 2, "%s.weight: want U32 [rows][in / 4]", pre.c_str());
+  q.rows = (int)t->shape[0];
+  q.in = (int)t->shape[1] * 4;
+  q.scales = static_cast<const uint16_t *>(p.device(pre + ".scales", &s));
+  q.biases = static_cast<const uint16_t *>(p.device(pre + ".biases", &b));
+  IJ_CHECK(s->dtype == NE_BF16 && b->dtype == NE_BF16 && s->ndim == 2 && s->shape[0] == q.rows && s->shape[1] > 0 && q.in % s->shape[1] == 0 &&
+               b->nbytes == s->nbytes, "%s.scales / .biases: want BF16 [rows][in / group]", pre.c_str());
+  q.group = q.in / (int)s->shape[1];
+  return q;
+}
+
+static bool load_hc(Pack &p, const std::string &pre, int H, HcWeights *out) {
+  if (!p.info(pre + ".hc_norm.weight")) return false;
+  const TensorInfo *t = nullptr;
+  HcWeights w;
+  w.H = H;
+  w.norm = static_cast<const uint16_t *>(p.device(pre + ".hc_norm.weight", &t));
+  IJ_CHECK(t->dtype == NE_BF16 && (int64_t)(t->nbytes / 2) == (int64_t)kHC * H, "%s.hc_norm.weight: want BF16 [%d]", pre.c_str(), kHC * H);
+  w.inject = static_cast<const uint16_t *>(p.device(pre + ".block_inject_weight.weight", &t));
+  IJ_CHECK(t->dtype == NE_BF16 && (int64_t)(t->nbytes / 2) == (int64_t)kHC * kHC * H, "%s.block_inject_weight.weight: want BF16 [%d][%d]", pre.c_str(), kHC, kHC * H);
+  w.down = q8_weight(p, pre + ".input_mix_weight_down");
+  w.up = q8_weight(p, pre + ".input_mix_weight_up");
+  w.LR = w.down.rows;
+  check_hc_weights(w);
+  *out = w;
+  return true;
 }
 
 static int config_top_k(const Pack &p) {
@@ -119,6 +156,8 @@ static Layer *make_layer(ne_pack *cp, int layer, int rows) {
   L->h_mid = al(R * kHC * H * 4);
   L->h_out = al(R * kHC * H * 4);
   L->inj = al(R * 2 * kHC * 4);
+  L->has_hc = load_hc(*pk, "language_model.model.layers." + std::to_string(layer) + ".mlp_hyper_connection", d.hidden, &L->hc);
+  if (L->has_hc) L->mlp_mix = al(R * L->hc.LR * 4);
   L->moe->h_mid = L->h_mid; L->moe->inj = L->inj; L->moe->h_out = L->h_out; L->moe->HC = kHC;
   IJ_CUDA(cudaEventCreate(&L->ev0));
   IJ_CUDA(cudaEventCreate(&L->ev1));
@@ -138,6 +177,7 @@ static Named named(Layer *L, const std::string &name) {
   if (name == "h_mid") return {L->h_mid, R * kHC * H, false};
   if (name == "h_out") return {L->h_out, R * kHC * H, false};
   if (name == "mlp_inj") return {L->inj, R * 2 * kHC, false};
+  if (name == "mlp_mix" && L->has_hc) return {L->mlp_mix, R * (size_t)L->hc.LR, false};
   if (name == "logits") return {m.logits, R * (E + 1), false};
   if (name == "route") return {(float *)m.route, R * 2 * k, true};
   if (name == "shared_gu") return {m.gush, R * 2 * I, false};
@@ -159,8 +199,8 @@ NE_API void ne_fn_layer_free(ne_fn_layer *l) { delete reinterpret_cast<Layer *>(
 
 NE_API int ne_fn_layer_step(ne_fn_layer *, const float *, float *, double *) {
   return c_call([&] {
-    fail("ne_fn_layer_step: only the MoE block of the layer is implemented (ne_fn_layer_run_stage(l, 5) or "
-         "ne_fn_layer_run_dispatch(l, 7|8|9)); attention / GDN / hyper-connection stages are not part of this library");
+    fail("ne_fn_layer_step: only the MLP half of the layer is implemented (ne_fn_layer_run_stage(l, 4 | 5) or "
+         "ne_fn_layer_run_dispatch(l, 5..9)); the attention / GDN stages are not part of this library");
   });
 }
 
@@ -168,8 +208,15 @@ NE_API int ne_fn_layer_run_stage(ne_fn_layer *l, int block) {
   return c_call([&] {
     Layer *L = reinterpret_cast<Layer *>(l);
     IJ_CHECK(L != nullptr, "null layer");
-    IJ_CHECK(block == 5, "sub-block %d is not implemented (only 5 = Moe: mlp_in, h_mid, mlp_inj -> logits ... h_out)", block);
-    L->moe->forward(L->mlp_in, L->rows, L->mlp_out, 0);
+    IJ_CHECK(block == 4 || block == 5, "sub-block %d is not implemented (4 = MlpHC: h_mid -> mlp_mix, mlp_inj, mlp_in; 5 = Moe: mlp_in, h_mid, "
+             "mlp_inj -> logits ... h_out)", block);
+    if (block == 4) {  // dispatches 5 and 6 (reference models/flash_next/layer.h:262-264)
+      IJ_CHECK(L->has_hc, "the pack holds no mlp_hyper_connection tensors for this layer");
+      launch_hc_pre(L->hc, L->h_mid, L->rows, L->mlp_mix, L->inj, 0);
+      launch_hc_mix(L->hc, L->h_mid, L->mlp_mix, L->inj, L->rows, L->mlp_in, 0);
+    } else {
+      L->moe->forward(L->mlp_in, L->rows, L->mlp_out, 0);
+    }
     IJ_CUDA(cudaStreamSynchronize(0));
     check_status_word();
   });
@@ -179,8 +226,14 @@ NE_API int ne_fn_layer_run_dispatch(ne_fn_layer *l, int stage) {
   return c_call([&] {
     Layer *L = reinterpret_cast<Layer *>(l);
     IJ_CHECK(L != nullptr, "null layer");
-    IJ_CHECK(stage >= 7 && stage <= 9, "dispatch %d is not implemented (7 moe_router, 8 moe_gateup, 9 moe_down)", stage);
-    L->moe->stage(stage, L->mlp_in, L->rows, L->mlp_out, 0);
+    IJ_CHECK(stage >= 5 && stage <= 9, "dispatch %d is not implemented (5 mlp_hc_pre, 6 mlp_hc_mix, 7 moe_router, 8 moe_gateup, 9 moe_down)", stage);
+    if (stage <= 6) {
+      IJ_CHECK(L->has_hc, "the pack holds no mlp_hyper_connection tensors for this layer");
+      if (stage == 5) launch_hc_pre(L->hc, L->h_mid, L->rows, L->mlp_mix, L->inj, 0);
+      else launch_hc_mix(L->hc, L->h_mid, L->mlp_mix, L->inj, L->rows, L->mlp_in, 0);
+    } else {
+      L->moe->stage(stage, L->mlp_in, L->rows, L->mlp_out, 0);
+    }
     IJ_CUDA(cudaStreamSynchronize(0));
     check_status_word();
   });
@@ -272,7 +325,7 @@ NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, 
 static const char *kOperators[] = {"exl3_linear", "exl3_dequant"};
 static const char *kKernels[] = {"stream_gemm_kernel", "moe_router_kernel", "moe_prep_kernel", "moe_mid_kernel", "moe_combine_kernel",
                                  "prep_rows_kernel", "linear_finish_kernel", "dequant_kernel", "pf_gemm_kernel", "pf_logits_kernel",
-                                 "pf_route_kernel", "pf_prep_kernel", "pf_mid_kernel", "pf_finish_kernel"};
+                                 "pf_route_kernel", "pf_prep_kernel", "pf_mid_kernel", "pf_finish_kernel", "hc_pre_kernel", "hc_mix_kernel"};
 NE_API int ne_kernel_exists(const char *fn) {
   if (!fn) return -1;
   for (const char *k : kOperators)

@@ -8,6 +8,9 @@ Tensor names and shapes are the ones the reference's layer loader reads (models/
   <pre>mlp.switch_mlp.{gate,up,down}_proj.{suh,svh}      F16  [E, in] / [E, out]
   <pre>mlp.shared_expert.{gate,up,down}_proj.{trellis,suh,svh}   (no leading E)
   <pre>self_attn.{q,k,v,o}_proj.{trellis,suh,svh}
+  <pre>mlp_hyper_connection.hc_norm.weight               BF16 [4H]          (layer.mm:81-94)
+  <pre>mlp_hyper_connection.block_inject_weight.weight   BF16 [4, 4H]
+  <pre>mlp_hyper_connection.input_mix_weight_{down,up}.{weight U32 [rows, in/4], scales BF16 [rows, in/G], biases}
 with <pre> = "language_model.model.layers.<L>.". Value distributions: trellis words uniform random (every bit pattern
 is a valid tail-biting ring), suh uniform +-1, svh = sign * |N(0,1)| * 0.02 (the format has no separate scale tensor),
 router / shared gate ~ N(0, 0.02) rounded to bf16.
@@ -49,6 +52,29 @@ def moe_layer(rng, layer=0, hidden=2048, inter=768, experts=512, k_expert=5, k_s
         t[f"{pre}shared_expert.{proj}_proj.trellis"] = ("U16", tr)
         t[f"{pre}shared_expert.{proj}_proj.suh"] = ("F16", su)
         t[f"{pre}shared_expert.{proj}_proj.svh"] = ("F16", sv)
+    return t
+
+
+def q8_linear(rng, rows, n_in, group=64, std=0.02):
+    """8-bit affine Linear in the MLX layout: (weight u32 [rows, in/4] = bytes little-endian, scales, biases bf16 bits
+    [rows, in/group]); w = scale * q + bias, roughly N(0, std)"""
+    q = np.clip(np.rint(rng.standard_normal((rows, n_in)) * 32 + 128), 0, 255).astype(np.uint8)
+    sc = (std / 32) * (1 + 0.1 * rng.standard_normal((rows, n_in // group)))
+    bi = -128 * sc + 0.1 * std * rng.standard_normal((rows, n_in // group))
+    return np.ascontiguousarray(q).view(np.uint32), f32_to_bf16_bits(sc), f32_to_bf16_bits(bi)
+
+
+def hc_block(rng, layer=0, which="mlp", hidden=2048, lr=320, group=64, streams=4):
+    """name -> (dtype, array) for one hyper-connection read (the reference's sizes: hidden 2560, lr 320, group 64)"""
+    pre = f"{PFX}{layer}.{which}_hyper_connection."
+    hcd = streams * hidden
+    t = {pre + "hc_norm.weight": ("BF16", f32_to_bf16_bits(1 + 0.1 * rng.standard_normal(hcd))),
+         pre + "block_inject_weight.weight": ("BF16", f32_to_bf16_bits(rng.standard_normal((streams, hcd)) * 0.02))}
+    for name, (rows, n_in) in (("input_mix_weight_down", (lr, hcd)), ("input_mix_weight_up", (hcd, lr))):
+        w, sc, bi = q8_linear(rng, rows, n_in, group, std=2.0 / np.sqrt(n_in))
+        t[pre + name + ".weight"] = ("U32", w)
+        t[pre + name + ".scales"] = ("BF16", sc)
+        t[pre + name + ".biases"] = ("BF16", bi)
     return t
 
 

@@ -222,3 +222,31 @@ def moe_block_emul(x, router_w, sgate_w, experts, shared, top_k=10, ids=None, w=
     out = y + sigmoid(sg_logit)[:, None].astype(np.float64) * sdown
     return dict(logits=np.concatenate([logits, sg_logit[:, None]], 1), ids=ids, weights=w, experts_gu=gu,
                 shared_gu=sgu, shared_down=sdown, routed=y.astype(np.float32), out=out.astype(np.float32))
+
+
+# ------------------------------------------------------------------ hyper-connection read (8-bit affine weights)
+def affine_dequant(wq_u32, scales_bf16, biases_bf16):
+    """MLX 8-bit affine (reference tools/opref.py:172-180): wq U32 [out, in/4] = codes little-endian within each word,
+    scales / biases bf16 bits [out, in/group]; w = q * scale + bias -> f32 [out, in]."""
+    q = np.ascontiguousarray(wq_u32).view(np.uint8).astype(np.float32)
+    out, n_in = q.shape
+    sc, bi = bf16_bits_to_f32(scales_bf16), bf16_bits_to_f32(biases_bf16)
+    ng = sc.shape[-1]
+    q = q.reshape(out, ng, n_in // ng)
+    return (q * sc[..., None] + bi[..., None]).reshape(out, n_in)
+
+
+def hc_read(h, norm_w, inject_w, down, up, streams=4, eps=1e-6):
+    """Hyper-connection read in f32 (reference tools/opref.py:221-236 with bf=False; models/flash_next/layer.mm:524-531):
+    h [rows, streams*H]; norm_w f32 [streams*H]; inject_w f32 [streams, streams*H]; down f32 [LR, streams*H]; up f32
+    [streams*H, LR] (dense, from affine_dequant). Returns dict normed, mix, block_in, inject_w."""
+    h = np.asarray(h, np.float32)
+    rows, hcd = h.shape
+    H = hcd // streams
+    x = h.reshape(rows, streams, H)
+    normed = (x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)).reshape(rows, hcd) * norm_w
+    mix = silu((normed @ down.T) / streams)
+    upv = mix @ up.T
+    m = sigmoid(upv).reshape(rows, streams, H) * normed.reshape(rows, streams, H)
+    return dict(normed=normed.astype(np.float32), mix=mix.astype(np.float32), block_in=np.mean(m, axis=-2).astype(np.float32),
+                inject_w=(2.0 * sigmoid((normed @ inject_w.T) / streams)).astype(np.float32))

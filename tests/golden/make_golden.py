@@ -30,6 +30,7 @@ from ijah_b200 import packgen  # noqa: E402
 SEED = 20261125
 DIMS = dict(hidden=256, inter=128, experts=32, k_expert=5, k_shared=6)
 TOPK = 4
+HC = dict(hidden=256, lr=128, group=64)  # hyper-connection read of layer 0 (the reference's sizes: 2560, 320, 64)
 TRUNK = [dict(layer=0, hidden=256, q_out=512, kv_out=64, K=6), dict(layer=1, hidden=256, q_out=512, kv_out=64, K=8)]
 
 
@@ -39,6 +40,16 @@ def small_pack_tensors():
     for tr in TRUNK:
         t.update(packgen.trunk_layer(rng, **tr))
     return t
+
+
+def hc_tensors():
+    """the mlp hyper-connection tensors of layer 0, from a random stream of their own (the MoE fixture's pack is unchanged)"""
+    return packgen.hc_block(np.random.default_rng(SEED + 2), layer=0, which="mlp", **HC)
+
+
+def hc_inputs():
+    rng = np.random.default_rng(SEED + 3)
+    return (rng.standard_normal((5, 4 * HC["hidden"])) * np.array([0.5, 1.0, 2.0, 4.0]).repeat(HC["hidden"])).astype(np.float32)
 
 
 def tensors_digest(t):
@@ -57,6 +68,7 @@ def inputs():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference repository (its tools/opref.py is imported unmodified)")
+    ap.add_argument("--which", default="all", choices=["all", "moe", "hc"], help="which fixture file to (re)write")
     a = ap.parse_args()
     tmp = Path(tempfile.mkdtemp(prefix="ijah_golden_"))
     try:
@@ -66,6 +78,8 @@ def main():
             "def _enc(*a, **k):\n    raise NotImplementedError('encoder-only name; not on the decode path')\n"
             "block_ldl = block_rms = refit_scales = sample_scale_tiles = _enc\n")
         tens = small_pack_tensors()
+        hct = hc_tensors()
+        tens.update(hct)
         pack = packgen.write_pack(tmp / "pack", tens, {"num_experts_per_tok": TOPK}, shards=3, misalign=2)
         os.environ["IJAH_REF_DIR"] = str(tmp / "ref")
         os.environ["IJAH_PACK"] = str(pack)
@@ -73,6 +87,21 @@ def main():
         import opref as O  # the reference's module
 
         P = O.PackNP()
+        if a.which in ("all", "hc"):
+            # the reference's hc_read with its two module constants (stream width D = 2560, HC = 4) set to the small pack's
+            O.D = HC["hidden"]
+            h = hc_inputs()
+            hc = dict(seed=np.int64(SEED), digest=np.array(tensors_digest(hct)), h=h)
+            for tag, bf in (("f32", False), ("bf16", True)):
+                r = O.hc_read(h, P, "language_model.model.layers.0.mlp_hyper_connection", bf=bf)
+                for k in ("normed", "mix", "block_in", "inject_w"):
+                    hc[f"{tag}_{k}"] = np.asarray(r[k], np.float32)
+            np.savez_compressed(HERE / "hc_small.npz", **hc)
+            print("wrote", HERE / "hc_small.npz", {k: np.shape(v) for k, v in hc.items()})
+            if a.which == "hc":
+                return
+        for k in hct:
+            del tens[k]
         x = inputs()
         out = dict(seed=np.int64(SEED), digest=np.array(tensors_digest(tens)), x=x, topk=np.int64(TOPK))
         pre = "language_model.model.layers.0.mlp"

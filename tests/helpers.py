@@ -26,6 +26,23 @@ def small_pack():
     return t, g
 
 
+def hc_small():
+    """(hyper-connection tensors of layer 0, their golden file) with the digest verified"""
+    g = np.load(GOLD / "hc_small.npz")
+    t = make_golden.hc_tensors()
+    assert make_golden.tensors_digest(t) == str(g["digest"]), "numpy random stream differs from the one that made the golden file"
+    return t, g
+
+
+def hc_oracle(tensors, h, layer=0, which="mlp"):
+    """oracle hyper-connection read over a packgen dict"""
+    pre = f"{PFX}{layer}.{which}_hyper_connection."
+    raw = lambda n: tensors[pre + n][1]  # noqa: E731
+    dn = O.affine_dequant(raw("input_mix_weight_down.weight"), raw("input_mix_weight_down.scales"), raw("input_mix_weight_down.biases"))
+    up = O.affine_dequant(raw("input_mix_weight_up.weight"), raw("input_mix_weight_up.scales"), raw("input_mix_weight_up.biases"))
+    return O.hc_read(h, O.bf16_bits_to_f32(raw("hc_norm.weight")), O.bf16_bits_to_f32(raw("block_inject_weight.weight")), dn, up)
+
+
 class MoeView:
     """Oracle-side view of one layer's MoE tensors in a packgen dict"""
 

@@ -3,7 +3,7 @@
 import numpy as np
 
 from oracle import opref_port as O
-from tests.helpers import MoeView, rel_max, small_pack, trunk_linear
+from tests.helpers import MoeView, hc_oracle, hc_small, rel_max, small_pack, trunk_linear
 
 
 def test_router_matches_reference():
@@ -69,3 +69,12 @@ def test_trunk_linears_match_reference():
             want = g[f"trunk_L{layer}_{proj}_y"]
             assert rel_max(O.exl3_linear_exact(xin, lin.trellis, lin.suh, lin.svh), want) < 1e-5
             assert rel_max(O.exl3_linear_emul(xin, lin.trellis, lin.suh, lin.svh), want) < 2e-3
+
+
+def test_hc_read_matches_reference():
+    # the reference's hc_read (f32 flow) on the small hyper-connection tensors; its bf16 flow differs by bf16 rounding only
+    t, g = hc_small()
+    r = hc_oracle(t, g["h"])
+    for k in ("normed", "mix", "block_in", "inject_w"):
+        assert rel_max(r[k], g["f32_" + k]) < 2e-6, k
+        assert rel_max(r[k], g["bf16_" + k]) < 2e-2, k
