@@ -42,10 +42,10 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   raw_sgu = (float *)al(Sg * R * 2 * I * 4);
   raw_d = (float *)al(Sd * P * H * 4);
   raw_sd = (float *)al(Sd * R * H * 4);
-  xh_gu = (__half *)al(P * 2 * H * 2);
-  xh_sgu = (__half *)al(R * 2 * H * 2);
-  xh_d = (__half *)al(P * I * 2);
-  xh_sd = (__half *)al(R * I * 2);
+  xh_gu = (__half *)al(P * 2 * H * 2 * A_HALFS_PER_INPUT);
+  xh_sgu = (__half *)al(R * 2 * H * 2 * A_HALFS_PER_INPUT);
+  xh_d = (__half *)al(P * I * 2 * A_HALFS_PER_INPUT);
+  xh_sd = (__half *)al(R * I * 2 * A_HALFS_PER_INPUT);
   gush = (float *)al(R * 2 * I * 4);
   sho = (float *)al(R * H * 4);
   counter = (unsigned *)al(16);

@@ -92,6 +92,13 @@ __device__ __forceinline__ uint32_t mcg_pair(uint32_t ca, uint32_t cb, const Mcg
   return *reinterpret_cast<const uint32_t *>(&r);
 }
 
+// one codeword -> the 32-bit word whose two fp16 halves add up to the weight (no add: see dec8_raw)
+__device__ __forceinline__ uint32_t mcg_raw(uint32_t cw, const McgConst &c) {
+  uint32_t r = cw * 0xCBAC1FEDu;
+  asm("lop3.b32 %0, %0, %1, %2, 0x6A;" : "+r"(r) : "r"(c.mask), "r"(c.flip));  // (a & b) ^ c
+  return r;
+}
+
 // The lane's 8 weights from its three window words: b[0] = (slot 0, slot 1), b[1] = (2, 3): column c;
 // b[2] = (4, 5), b[3] = (6, 7): column c + 8. `a` = Codec<K>::Lane::a (ignored for K = 4, 8).
 template <int K>
@@ -115,6 +122,46 @@ __device__ __forceinline__ void dec8(uint32_t w0, uint32_t w1, uint32_t w2, uint
     b[2] = mcg_pair(field15<4 * K, true>(x, y, 0u, mid), field15<5 * K, true>(x, y, 0u, mid), c);
     b[3] = mcg_pair(field15<6 * K, true>(x, y, 0u, mid), field15<7 * K, true>(x, y, 0u, mid), c);
   }
+}
+
+// The same 8 slots left as their summand pairs: r[t] = (lo, hi) with weight = lo + hi. A tensor-core product that takes
+// both halves as two k elements against a twice-repeated activation adds them in its fp32 accumulator, so the half add
+// and the pack of dec8 (12 instructions per tile) are not executed at all; the sum is then not rounded to fp16 first.
+template <int K>
+__device__ __forceinline__ void dec8_raw(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t a, const McgConst &c, uint32_t (&r)[8]) {
+  if constexpr (Codec<K>::UNIFORM) {
+    constexpr int A = Codec<K>::A0;
+    constexpr bool MID = K == 4;
+    const uint32_t mid = MID ? __byte_perm(w0, w1, 0x1076) : 0u;
+    r[0] = mcg_raw(field15<A + 0 * K, MID>(w0, w1, w2, mid), c);
+    r[1] = mcg_raw(field15<A + 1 * K, MID>(w0, w1, w2, mid), c);
+    r[2] = mcg_raw(field15<A + 2 * K, MID>(w0, w1, w2, mid), c);
+    r[3] = mcg_raw(field15<A + 3 * K, MID>(w0, w1, w2, mid), c);
+    r[4] = mcg_raw(field15<A + 4 * K, MID>(w0, w1, w2, mid), c);
+    r[5] = mcg_raw(field15<A + 5 * K, MID>(w0, w1, w2, mid), c);
+    r[6] = mcg_raw(field15<A + 6 * K, MID>(w0, w1, w2, mid), c);
+    r[7] = mcg_raw(field15<A + 7 * K, MID>(w0, w1, w2, mid), c);
+  } else {
+    const uint32_t x = __funnelshift_l(w1, w0, a), y = __funnelshift_l(w2, w1, a);
+    const uint32_t mid = __byte_perm(x, y, 0x1076);
+    r[0] = mcg_raw(field15<0 * K, true>(x, y, 0u, mid), c);
+    r[1] = mcg_raw(field15<1 * K, true>(x, y, 0u, mid), c);
+    r[2] = mcg_raw(field15<2 * K, true>(x, y, 0u, mid), c);
+    r[3] = mcg_raw(field15<3 * K, true>(x, y, 0u, mid), c);
+    r[4] = mcg_raw(field15<4 * K, true>(x, y, 0u, mid), c);
+    r[5] = mcg_raw(field15<5 * K, true>(x, y, 0u, mid), c);
+    r[6] = mcg_raw(field15<6 * K, true>(x, y, 0u, mid), c);
+    r[7] = mcg_raw(field15<7 * K, true>(x, y, 0u, mid), c);
+  }
+}
+
+// Layout of a prepared activation row (the B operand of the stream kernels) for that product: per k-tile of 16 inputs
+// 32 halfs = 16 (v, v) pairs in the order inputs 0, 2, .. 14, then 1, 3, .. 15, so that one ldmatrix.x4 of an 8-row group
+// yields the even-input and the odd-input fragments. A row of n inputs is 2 n halfs.
+constexpr int A_HALFS_PER_INPUT = 2;
+__device__ __forceinline__ void store_a(__half *row, int i, float v) {
+  const int w = (i >> 4) * 16 + (i & 1) * 8 + ((i & 15) >> 1);
+  reinterpret_cast<__half2 *>(row)[w] = __float2half2_rn(v);
 }
 
 // normalised Hadamard of size N (16..128) over a 128-element chunk held by a warp as (lane, lane+32, lane+64, lane+96);

@@ -14,13 +14,16 @@ constexpr int kMinStages = SG_KS >= 16 ? 2 : 3;
 StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm) {
   StreamLayout l;
   l.stage_bytes = SG_KS * SG_WARPS * 32 * Kmax;
-  l.lda = kcmax * 16 + 8;
+  l.lda = kcmax * 16 * A_HALFS_PER_INPUT + 8;
   l.arows = std::max(arows, 1);
   const size_t budget = smem_budget(ctas_per_sm);
   const size_t base = l.ring_off() + (size_t)l.lda * 2;
   const size_t want_stages = SG_KS >= 16 ? 3 : 6;
-  // at least three A slots: the producer issues the rows of unit u + 2 while the consumers may still be on unit u
-  l.aslots = base + SG_MAX_ASLOTS * l.slot_bytes() + want_stages * (size_t)l.stage_bytes <= budget ? SG_MAX_ASLOTS : 3;
+  // three A slots or more let the producer issue the rows of unit u + 2 while the consumers are still on unit u; the widest
+  // row counts only fit two (the producer then waits for the consumers to leave unit u - 1 before it sends unit u + 1)
+  l.aslots = base + SG_MAX_ASLOTS * l.slot_bytes() + want_stages * (size_t)l.stage_bytes <= budget ? SG_MAX_ASLOTS
+             : base + 3 * l.slot_bytes() + kMinStages * (size_t)l.stage_bytes <= budget             ? 3
+                                                                                                     : 2;
   const size_t fixed = base + l.aslots * l.slot_bytes();
   IJ_CHECK(fixed + kMinStages * (size_t)l.stage_bytes <= budget, "A operand of %d rows x %d k-tiles does not fit shared memory", arows, kcmax);
   l.stages = (int)std::min<size_t>(SG_MAX_STAGES, (budget - fixed) / l.stage_bytes);
@@ -28,12 +31,16 @@ StreamLayout make_layout(int Kmax, int kcmax, int arows, int ctas_per_sm) {
 }
 
 // Largest k-tile count per unit (a multiple of SG_KS) whose three A slots of `arows` rows leave room for the smallest ring
-// of K = Kmax stages when `ctas` CTAs share an SM; 0 if not even SG_KS k-tiles fit.
+// of K = Kmax stages when `ctas` CTAs share an SM (two slots with one CTA per SM, if three do not fit); 0 if not even
+// SG_KS k-tiles fit.
 int kc_cap(int arows, int Kmax, int ctas) {
   const long room = (long)smem_budget(ctas) - 4096 - (long)kMinStages * SG_KS * SG_WARPS * 32 * Kmax;
-  const long halfs_per_row = room / 3 / std::max(arows, 1) / 2;
-  const int cap = (int)((halfs_per_row - 8) / 16) / SG_KS * SG_KS;
-  return std::max(0, std::min(cap, 256));
+  auto cap = [&](int slots) {
+    const long halfs_per_row = room / slots / std::max(arows, 1) / 2;
+    return std::max(0, std::min((int)((halfs_per_row - 8) / (16 * A_HALFS_PER_INPUT)) / SG_KS * SG_KS, 256));
+  };
+  const int c3 = cap(3);
+  return c3 >= SG_KS || ctas > 1 ? c3 : cap(2);
 }
 
 // CTAs per SM for units of `arows` rows: the default, or one CTA per SM with all of its shared memory when the default
@@ -90,7 +97,7 @@ __global__ void __launch_bounds__(128) prep_rows_kernel(const float *__restrict_
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = chunk * 128 + lane + 32 * j;
-    if (i < n) xh[(size_t)r * n + i] = __float2half_rn(v[j]);
+    if (i < n) store_a(xh + (size_t)r * n * A_HALFS_PER_INPUT, i, v[j]);
   }
 }
 
@@ -157,7 +164,7 @@ __global__ void __launch_bounds__(128) prep_rows_multi_kernel(const float *__res
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = chunk * 128 + lane + 32 * j;
-    if (i < n) a.xh[m][(size_t)r * n + i] = __float2half_rn(v[j]);
+    if (i < n) store_a(a.xh[m] + (size_t)r * n * A_HALFS_PER_INPUT, i, v[j]);
   }
 }
 
@@ -225,7 +232,7 @@ void launch_linear_multi(const MultiLinearPlan &p, const MultiLinearArgs &a, con
     float *raw = (float *)cur;
     cur += (p.raw_floats(m) * 4 + 255) & ~(size_t)255;
     __half *xh = (__half *)cur;
-    cur += ((size_t)p.rows * p.in * 2 + 255) & ~(size_t)255;
+    cur += ((size_t)p.rows * p.in * A_HALFS_PER_INPUT * 2 + 255) & ~(size_t)255;
     make_trellis_map(&pr.maps[m], a.trellis[m], 1, p.IT, p.OT[m], p.K[m], SG_KS);
     pr.xh[m] = xh; pr.raw[m] = raw;
     pr.out[m] = p.out[m]; pr.K[m] = p.K[m]; pr.OT[m] = p.OT[m]; pr.NG[m] = p.NG[m];

@@ -18,7 +18,7 @@ struct LinearPlan {
   StreamLayout lay;
   int grid;
   size_t raw_floats() const { return (size_t)S * rows * out; }
-  size_t xh_halfs() const { return (size_t)rows * in; }
+  size_t xh_halfs() const { return (size_t)rows * in * A_HALFS_PER_INPUT; }
   size_t scratch_bytes() const { return raw_floats() * 4 + ((xh_halfs() * 2 + 255) & ~(size_t)255) + 256; }
 };
 
@@ -30,7 +30,7 @@ struct LinearProblem {
     int g, s, k0;
   };
   alignas(64) CUtensorMap map;  // over the trellis (make_trellis_map)
-  const __half *xh;  // [rows][in] prepared operand
+  const __half *xh;  // [rows][2 in] prepared operand (store_a layout)
   float *raw;
   int in, out, K, rows, IT, OT, NG, S, kc;
 
@@ -49,7 +49,7 @@ struct LinearProblem {
     return un;
   }
   __device__ int row_index(const Unit &, int i) const { return i; }
-  __device__ const __half *a_row(const Unit &un, int i) const { return xh + (size_t)i * in + un.k0 * 16; }
+  __device__ const __half *a_row(const Unit &un, int i) const { return xh + ((size_t)i * in + un.k0 * 16) * A_HALFS_PER_INPUT; }
   __device__ float *out_base(const Unit &un) const { return raw + (size_t)un.s * rows * out + un.g * 128; }
   __device__ int out_row_off(const Unit &, int row) const { return row * out; }
 };
@@ -65,7 +65,7 @@ struct MultiLinearPlan {
   size_t raw_floats(int m) const { return (size_t)S * rows * out[m]; }
   size_t scratch_bytes() const {
     size_t b = 256;
-    for (int m = 0; m < n; m++) b += ((raw_floats(m) * 4 + 255) & ~(size_t)255) + (((size_t)rows * in * 2 + 255) & ~(size_t)255);
+    for (int m = 0; m < n; m++) b += ((raw_floats(m) * 4 + 255) & ~(size_t)255) + (((size_t)rows * in * A_HALFS_PER_INPUT * 2 + 255) & ~(size_t)255);
     return b;
   }
 };
@@ -77,7 +77,7 @@ struct MultiLinearProblem {
     int g, s, k0, m;
   };
   alignas(64) CUtensorMap maps[ML_MAX];  // one per trellis
-  const __half *xh[ML_MAX];  // [rows][in] prepared operand per matrix (the scale vectors differ)
+  const __half *xh[ML_MAX];  // [rows][2 in] prepared operand per matrix (the scale vectors differ)
   float *raw[ML_MAX];
   int out[ML_MAX], K[ML_MAX], OT[ML_MAX], NG[ML_MAX], ubase[ML_MAX + 1];  // ubase[m]: first unit of matrix m
   int n, in, rows, IT, S, kc;
@@ -101,7 +101,7 @@ struct MultiLinearProblem {
     return un;
   }
   __device__ int row_index(const Unit &, int i) const { return i; }
-  __device__ const __half *a_row(const Unit &un, int i) const { return xh[un.m] + (size_t)i * in + un.k0 * 16; }
+  __device__ const __half *a_row(const Unit &un, int i) const { return xh[un.m] + ((size_t)i * in + un.k0 * 16) * A_HALFS_PER_INPUT; }
   __device__ float *out_base(const Unit &un) const { return raw[un.m] + (size_t)un.s * rows * out[un.m] + un.g * 128; }
   __device__ int out_row_off(const Unit &un, int row) const { return row * out[un.m]; }
 };

@@ -391,12 +391,12 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int bu
     if (e < 0 || e >= p.ecount) return;
     sg = p.gate.suh + (size_t)e * H;
     su = p.up.suh + (size_t)e * H;
-    dst = p.xh_gu + (size_t)job * 2 * H;
+    dst = p.xh_gu + (size_t)job * 2 * H * A_HALFS_PER_INPUT;
   } else {
     r = job - p.P;
     sg = p.sgt.suh;
     su = p.sup.suh;
-    dst = p.xh_sgu + (size_t)r * 2 * H;
+    dst = p.xh_sgu + (size_t)r * 2 * H * A_HALFS_PER_INPUT;
   }
   const int o = chunk * 128 + lane;
   float xv[4], v[4];
@@ -406,12 +406,12 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int bu
   for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(sg[o + 32 * j]);
   fwht_chunk(v, lane, 128, hs);
 #pragma unroll
-  for (int j = 0; j < 4; j++) dst[o + 32 * j] = __float2half_rn(v[j]);
+  for (int j = 0; j < 4; j++) store_a(dst, o + 32 * j, v[j]);
 #pragma unroll
   for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(su[o + 32 * j]);
   fwht_chunk(v, lane, 128, hs);
 #pragma unroll
-  for (int j = 0; j < 4; j++) dst[H + o + 32 * j] = __float2half_rn(v[j]);
+  for (int j = 0; j < 4; j++) store_a(dst + H * A_HALFS_PER_INPUT, o + 32 * j, v[j]);
 }
 
 // xh_d[pair][I] = fp16(H128(silu(g) * u * suh_down)), g = H128(sum_s raw gate) * svh_gate, u likewise
@@ -439,10 +439,10 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
     const int r = job / k, e = (int)p.route[(size_t)r * p.ldr + (job - r * k)] - p.e0;
     if (e < 0 || e >= p.ecount) return;
     svg = p.gate.svh + (size_t)e * I; svu = p.up.svh + (size_t)e * I; sud = p.down.suh + (size_t)e * I;
-    dst = p.xh_d + (size_t)job * I;
+    dst = p.xh_d + (size_t)job * I * A_HALFS_PER_INPUT;
   } else {
     svg = p.sgt.svh; svu = p.sup.svh; sud = p.sdn.suh;
-    dst = p.xh_sd + (size_t)(job - p.P) * I;
+    dst = p.xh_sd + (size_t)(job - p.P) * I * A_HALFS_PER_INPUT;
   }
   float gv[4], uv[4], hh[4], s_g[4], s_u[4], s_d[4];
 #pragma unroll
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
   }
   fwht_chunk(hh, lane, 128, hs);
 #pragma unroll
-  for (int j = 0; j < 4; j++) dst[o + 32 * j] = __float2half_rn(hh[j]);
+  for (int j = 0; j < 4; j++) store_a(dst, o + 32 * j, hh[j]);
 }
 
 // =============================================================================================== gate / up
@@ -514,7 +514,7 @@ struct MoeGateUpProblem {
     return un.shared ? p.sh_row0 + un.first + i : PlanView{p.plan, p.P}.pairs()[un.first + i];
   }
   __device__ const __half *a_row(const Unit &un, int idx) const {
-    return (un.shared ? p.xh_sgu : p.xh_gu) + ((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16;
+    return (un.shared ? p.xh_sgu : p.xh_gu) + (((size_t)idx * 2 + un.proj) * p.H + un.k0 * 16) * A_HALFS_PER_INPUT;
   }
   __device__ float *out_base(const Unit &un) const {
     return (un.shared ? p.raw_sgu + ((size_t)un.s * p.rows * 2 + un.proj) * p.I : p.raw_gu + ((size_t)un.s * p.P * 2 + un.proj) * p.I) + un.g * 128;
@@ -557,7 +557,7 @@ struct MoeDownProblem {
     return un.shared ? p.sh_row0 + un.first + i : PlanView{p.plan, p.P}.pairs()[un.first + i];
   }
   __device__ const __half *a_row(const Unit &un, int idx) const {
-    return (un.shared ? p.xh_sd : p.xh_d) + (size_t)idx * p.I + un.k0 * 16;
+    return (un.shared ? p.xh_sd : p.xh_d) + ((size_t)idx * p.I + un.k0 * 16) * A_HALFS_PER_INPUT;
   }
   __device__ float *out_base(const Unit &un) const {
     return (un.shared ? p.raw_sd + (size_t)un.s * p.rows * p.H : p.raw_d + (size_t)un.s * p.P * p.H) + un.g * 128;

@@ -30,10 +30,10 @@ struct MoeParams {
   float *logits;           // [rows][E + 1]
   uint32_t *route;         // [rows][2 topk]
   int *plan;               // see PlanView
-  __half *xh_gu;           // [P][2][H]  prepared gate | up operands per (row, slot) pair
-  __half *xh_sgu;          // [rows][2][H]  the shared expert's
-  __half *xh_d;            // [P][I]  prepared down operand per pair
-  __half *xh_sd;           // [rows][I]
+  __half *xh_gu;           // [P][2][2H]  prepared gate | up operands per (row, slot) pair (store_a layout)
+  __half *xh_sgu;          // [rows][2][2H]  the shared expert's
+  __half *xh_d;            // [P][2I]  prepared down operand per pair
+  __half *xh_sd;           // [rows][2I]
   float *raw_gu;           // [S_gu][P][2][I]
   float *raw_sgu;          // [S_gu][rows][2][I]
   float *raw_d;            // [S_d][P][H]

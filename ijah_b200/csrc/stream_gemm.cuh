@@ -71,7 +71,7 @@ struct UnitDesc {
 struct StreamLayout {  // dynamic shared memory carve-up (host computes, kernel mirrors)
   int stages;          // ring stages
   int stage_bytes;     // SG_KS * 8 * 32 * Kmax
-  int lda;             // A row stride in halfs (k elements + 8 pad: keeps ldmatrix rows on distinct banks)
+  int lda;             // A row stride in halfs (32 per k-tile + 8 pad: keeps ldmatrix rows on distinct banks)
   int arows;           // rows per A slot
   int aslots;          // A slots (units the producer may run ahead)
   __host__ __device__ size_t ring_off() const { return 512 + SG_MAX_ASLOTS * SG_DESC_BYTES; }
@@ -96,45 +96,36 @@ __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
 }
 
 // k-tile I of a stage for one output tile. The tensor core computes D^T = W'^T * X^T: the decoded tile is the A operand
-// (16 output columns x 16 k; the lane's 8 decoded weights are exactly its A fragment, in the order b0, b2, b1, b3), the
-// activations are the B operand (16 k x 8 rows), so 8 activation rows cost one mma.m16n8k16 per tile. MT = number of
-// 8-row groups (1, 2, 4, 8); a_row[p] is the ldmatrix address of row-group pair p for k-tile 0 of the stage, tile I
-// sits I * 32 bytes further in the A rows. acc[g] = D^T fragment of group g: (column gq, rows 2q, 2q+1), (column gq + 8, ..).
-template <int MT>
-struct RowPairs { static constexpr int N = MT == 1 ? 1 : MT / 2; };
-
-template <int OFF>
-__device__ __forceinline__ void ldsm2(uint32_t (&r)[2], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2+%3];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr), "n"(OFF));
-}
+// (16 output columns x 16 k), the activations are the B operand (16 k x 8 rows). Each decoded weight stays the pair of
+// fp16 summands (lo, hi) the codebook function yields (dec8_raw) and takes the place of TWO k elements of the A fragment,
+// against activation rows that hold every input twice (store_a): the accumulator adds lo * x + hi * x, which is
+// (lo + hi) * x without the half add, and the 16 inputs of the k-tile take two mma.m16n8k16 per 8 activation rows, the
+// even inputs (slots 0, 4, 2, 6 of the lane) and the odd ones (slots 1, 5, 3, 7). MT = number of 8-row groups (1, 2, 4, 8);
+// a_row[g] is the ldmatrix address of row group g for k-tile 0 of the stage, tile I sits I * 64 bytes further in the A rows.
+// acc[g] = D^T fragment of group g: (column gq, rows 2q, 2q+1), (column gq + 8, ..).
+constexpr uint32_t SG_A_TILE_BYTES = 16 * A_HALFS_PER_INPUT * 2;  // one k-tile of one prepared activation row
 
 template <int K, int MT, int I>
 __device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t la, const McgConst &mc,
-                                         const uint32_t (&a_row)[RowPairs<MT>::N], float (&acc)[MT][4]) {
-  uint32_t b[4];
+                                         const uint32_t (&a_row)[MT], float (&acc)[MT][4]) {
+  uint32_t r[8];
 #if SG_DBG == 2  // timing only: no decode, the raw words go to the tensor core
-  b[0] = w0; b[1] = w1; b[2] = w2; b[3] = w0 ^ la;
+  r[0] = w0; r[1] = w1; r[2] = w2; r[3] = w0 ^ la; r[4] = w1 ^ la; r[5] = w2 ^ la; r[6] = w0 + la; r[7] = w1 + la;
 #else
-  dec8<K>(w0, w1, w2, la, mc, b);
+  dec8_raw<K>(w0, w1, w2, la, mc, r);
 #endif
 #if SG_DBG == 1  // timing only: decode without the MMA
-  acc[0][0] = __uint_as_float(__float_as_uint(acc[0][0]) ^ b[0] ^ b[1]);
-  acc[0][1] = __uint_as_float(__float_as_uint(acc[0][1]) ^ b[2] ^ b[3]);
+  acc[0][0] = __uint_as_float(__float_as_uint(acc[0][0]) ^ r[0] ^ r[1] ^ r[2] ^ r[3]);
+  acc[0][1] = __uint_as_float(__float_as_uint(acc[0][1]) ^ r[4] ^ r[5] ^ r[6] ^ r[7]);
   (void)a_row;
 #else
-  const uint32_t wa[4] = {b[0], b[2], b[1], b[3]};
-  if constexpr (MT == 1) {
-    uint32_t x[2];
-    ldsm2<I * 32>(x, a_row[0]);
-    mma_16816(acc[0], wa, x[0], x[1]);
-  } else {
+  const uint32_t we[4] = {r[0], r[4], r[2], r[6]}, wo[4] = {r[1], r[5], r[3], r[7]};
 #pragma unroll
-    for (int p = 0; p < MT / 2; p++) {
-      uint32_t x[4];
-      ldsm4<I * 32>(x, a_row[p]);
-      mma_16816(acc[2 * p], wa, x[0], x[1]);
-      mma_16816(acc[2 * p + 1], wa, x[2], x[3]);
-    }
+  for (int g = 0; g < MT; g++) {
+    uint32_t x[4];
+    ldsm4<I * (int)SG_A_TILE_BYTES>(x, a_row[g]);
+    mma_16816(acc[g], we, x[0], x[1]);
+    mma_16816(acc[g], wo, x[2], x[3]);
   }
 #endif
 }
@@ -146,7 +137,7 @@ constexpr int SG_GROUPS = SG_KS / SG_HALF;
 template <int K, int MT, int B, int I, int N>
 struct TileLoop {
   static constexpr int KSTEP = SG_WARPS * Codec<K>::TILE_BYTES;
-  static constexpr int NP = RowPairs<MT>::N;
+  static constexpr int NP = MT;
   static __device__ __forceinline__ void load(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t (&w)[SG_HALF][3]) {
     w[I][0] = lds32<(B + I) * KSTEP>(p0);
     w[I][1] = lds32<(B + I) * KSTEP>(p1);
@@ -166,7 +157,7 @@ struct TileLoop {
 };
 template <int K, int MT, int B, int N>
 struct TileLoop<K, MT, B, N, N> {
-  static constexpr int NP = RowPairs<MT>::N;
+  static constexpr int NP = MT;
   static __device__ __forceinline__ void load(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_HALF][3]) {}
   static __device__ __forceinline__ void run(const uint32_t (&)[SG_HALF][3], uint32_t, const McgConst &, const uint32_t (&)[NP], float (&)[MT][4], int) {}
   static __device__ __forceinline__ void run_all(const uint32_t (&)[SG_HALF][3], uint32_t, const McgConst &, const uint32_t (&)[NP], float (&)[MT][4]) {}
@@ -175,7 +166,7 @@ struct TileLoop<K, MT, B, N, N> {
 // the SG_GROUPS groups of a stage, one after the other
 template <int K, int MT, int G, int NG>
 struct StageLoop {
-  static constexpr int NP = RowPairs<MT>::N;
+  static constexpr int NP = MT;
   static __device__ __forceinline__ void run_all(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t (&w)[SG_HALF][3], uint32_t la, const McgConst &mc,
                                                  const uint32_t (&a_row)[NP], float (&acc)[MT][4]) {
     TileLoop<K, MT, G * SG_HALF, 0, SG_HALF>::load(p0, p1, p2, w);
@@ -193,7 +184,7 @@ struct StageLoop {
 };
 template <int K, int MT, int NG>
 struct StageLoop<K, MT, NG, NG> {
-  static constexpr int NP = RowPairs<MT>::N;
+  static constexpr int NP = MT;
   static __device__ __forceinline__ void run_all(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_HALF][3], uint32_t, const McgConst &,
                                                  const uint32_t (&)[NP], float (&)[MT][4]) {}
   static __device__ __forceinline__ void run(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_HALF][3], uint32_t, const McgConst &,
@@ -238,15 +229,14 @@ __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, 
   for (int m = 0; m < MT; m++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[m][j] = 0.0f;
-  // ldmatrix row addresses: lanes 0-7 rows 0-7 (k 0-7), 8-15 rows 0-7 (k 8-15), 16-23 rows 8-15 (k 0-7), 24-31 rows 8-15
-  // (k 8-15); the .x2 form used for <= 8 rows takes the first 16 lanes' addresses. Dead rows read the zero row.
-  uint32_t a_row[RowPairs<MT>::N];
+  // ldmatrix.x4 row addresses of an 8-row group: lanes 8j .. 8j+7 give rows 0-7 at byte 16 j of the k-tile (the even
+  // inputs' low and high halves of the tile, then the odd inputs'). Dead rows read the zero row.
+  uint32_t a_row[MT];
   {
-    const int lrow = (lane & 7) + (lane >> 4) * 8;
-    const uint32_t lkof = (uint32_t)((lane >> 3) & 1) * 16u;
+    const uint32_t lkof = (uint32_t)(lane >> 3) * 16u;
 #pragma unroll
-    for (int m = 0; m < RowPairs<MT>::N; m++) {
-      const int r = m * 16 + lrow;
+    for (int m = 0; m < MT; m++) {
+      const int r = m * 8 + (lane & 7);
       a_row[m] = (r < d.nrows ? a_addr + (uint32_t)r * lda_bytes : z_addr) + lkof;
     }
   }
@@ -259,7 +249,7 @@ __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, 
     const uint32_t p0 = t0 + rc.stage * rc.stage_bytes, p1 = p0 + d1, p2 = p0 + d2;
     StageLoop<K, MT, 0, SG_GROUPS>::run_all(p0, p1, p2, w, L.a, mc, a_row, acc);
 #pragma unroll
-    for (int m = 0; m < RowPairs<MT>::N; m++) a_row[m] += SG_KS * 32u;  // the zero row is a full row too
+    for (int m = 0; m < MT; m++) a_row[m] += SG_KS * SG_A_TILE_BYTES;  // the zero row is a full row too
     __syncwarp();
     mbar_arrive_if(bar + SG_EMPTY_OFF, lane0);
     rc.advance();
@@ -394,7 +384,7 @@ __global__ void __launch_bounds__(SG_THREADS, SG_CTAS) stream_gemm_kernel(const 
       int *doff = reinterpret_cast<int *>(desc + (size_t)slot * SG_DESC_BYTES + SG_DESC_UNIT_BYTES);
       doff[lane] = lane < t.nrows ? prob.out_row_off(t, i0) : 0;
       doff[lane + 32] = lane + 32 < t.nrows ? prob.out_row_off(t, i1) : 0;
-      const uint32_t rowb = (uint32_t)t.kc * 32u;
+      const uint32_t rowb = (uint32_t)t.kc * SG_A_TILE_BYTES;
       __syncwarp();
       if (lane == 0) {
         *du = UnitDesc{prob.out_base(t), t.kc, t.ntiles, t.K, t.nrows};

@@ -46,7 +46,10 @@ def decode_inner(trellis):
     return out
 
 
-def linear_emul(trellis, suh, svh, x):
+def linear_emul(trellis, suh, svh, x, summands=True):
+    """the Linear in the device arithmetic; summands: each weight multiplied as its two float16 summands (the CUDA decode
+    kernels), False: as the rounded float16 value (the reference's kernels, the CUDA prefill kernels)"""
+    lib().exl3_emul_summands(int(bool(summands)))
     tr, su, sv = _u16(trellis), _u16(np.asarray(suh, np.float16)), _u16(np.asarray(svh, np.float16))
     x = np.ascontiguousarray(x, np.float32).reshape(-1, tr.shape[0] * 16)
     y = np.empty((x.shape[0], tr.shape[1] * 16), np.float32)
@@ -63,7 +66,7 @@ def router_logits(w_bf16, x):
 
 
 def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_gu=False, expert_range=None,
-                   shared_rows=None):
+                   shared_rows=None, summands=True):
     """The MoE block in the device arithmetic on a packgen-style tensor dict. Returns dict(logits [M, E+1], ids,
     weights, routed, shared_gu, shared_down, out[, experts_gu]). expert_range (e0, e1) keeps only the slots whose
     expert lies in [e0, e1); shared_rows (r0, n) adds the shared expert for rows [r0, r0 + n) only (the summand one
@@ -83,6 +86,7 @@ def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_g
     routed = np.zeros((M, H), np.float64)
     gu = np.zeros((M, top_k, 2, I), np.float32)
     L = lib()
+    L.exl3_emul_summands(int(bool(summands)))
     for r in range(M):
         for k in range(top_k):
             e = int(ids[r, k])
@@ -96,9 +100,9 @@ def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_g
     if pre + "shared_expert.gate_proj.trellis" in tensors:
         sg_logit = router_logits(g("shared_expert_gate.weight").reshape(1, H), x)[:, 0]
         sh = {p: tuple(g(f"shared_expert.{p}_proj.{s}") for s in ("trellis", "suh", "svh")) for p in ("gate", "up", "down")}
-        sgu = np.stack([linear_emul(*sh["gate"], x), linear_emul(*sh["up"], x)], 1)
+        sgu = np.stack([linear_emul(*sh["gate"], x, summands), linear_emul(*sh["up"], x, summands)], 1)
         act = (sgu[:, 0] / (1.0 + np.exp(-sgu[:, 0]))) * sgu[:, 1]
-        sdown = linear_emul(*sh["down"], act.astype(np.float32))
+        sdown = linear_emul(*sh["down"], act.astype(np.float32), summands)
         gate = (1.0 / (1.0 + np.exp(-sg_logit.astype(np.float64))))[:, None]
         if shared_rows is not None:
             keep = np.zeros((M, 1))

@@ -46,26 +46,29 @@ SLOT_ROW, SLOT_COL = _slot_positions()
 PERM = (SLOT_ROW * 16 + SLOT_COL).astype(np.int64)  # slot -> row-major position inside the 16x16 tile
 
 
-def mcg_value(cw):
-    """codewords (any int array; low 15 bits used) -> float16 values, exactly as the device decoder produces them"""
+def mcg_value(cw, rounded=True):
+    """codewords (any int array; low 15 bits used) -> float16 values, exactly as the device decoder produces them;
+    rounded=False: the exact float32 sum of the two float16 summands (what a product that takes both summands as
+    separate terms accumulates: the CUDA decode kernels)"""
     cw = (np.asarray(cw).astype(np.uint32)) & np.uint32(0x7FFF)
     r = ((cw * _MUL) & _MASK) ^ _XOR  # uint32 arithmetic wraps
     lo = (r & np.uint32(0xFFFF)).astype(np.uint16).view(np.float16)
     hi = (r >> np.uint32(16)).astype(np.uint16).view(np.float16)
     # the exact sum of two halfs with exponents this close fits a float32; one rounding to half = RN-even half add
-    return (lo.astype(np.float32) + hi.astype(np.float32)).astype(np.float16)
+    s = lo.astype(np.float32) + hi.astype(np.float32)
+    return s.astype(np.float16) if rounded else s
 
 
-_LUT = None
+_LUT = {}
 
 
-def lut(codebook="mcg", window=WINDOW):
-    """float16 [2^16]: value of every 16-bit window (the top bit is ignored, so the table repeats after 2^15)"""
-    global _LUT
+def lut(codebook="mcg", window=WINDOW, rounded=True):
+    """float16 [2^16]: value of every 16-bit window (the top bit is ignored, so the table repeats after 2^15);
+    rounded=False: float32, the unrounded sums"""
     assert codebook == "mcg" and window == WINDOW, (codebook, window)
-    if _LUT is None:
-        _LUT = mcg_value(np.arange(1 << 16, dtype=np.uint32))
-    return _LUT
+    if rounded not in _LUT:
+        _LUT[rounded] = mcg_value(np.arange(1 << 16, dtype=np.uint32), rounded)
+    return _LUT[rounded]
 
 
 def tile_codewords(trellis):
@@ -89,19 +92,20 @@ def tile_codewords(trellis):
     return out.reshape(*lead, 256)
 
 
-def decode_tiles(trellis):
-    """trellis u16 [..., 16K] -> float16 [..., 256] values in slot order"""
-    return lut()[tile_codewords(trellis)]
+def decode_tiles(trellis, rounded=True):
+    """trellis u16 [..., 16K] -> float16 [..., 256] values in slot order (rounded=False: float32 unrounded sums)"""
+    return lut(rounded=rounded)[tile_codewords(trellis)]
 
 
-def decode_inner(trellis, n=None, codebook="mcg", window=WINDOW):
-    """trellis u16 [in/16, out/16, 16K] -> W' float32 [in, out] (values are exact float16 numbers)"""
+def decode_inner(trellis, n=None, codebook="mcg", window=WINDOW, rounded=True):
+    """trellis u16 [in/16, out/16, 16K] -> W' float32 [in, out] (values are exact float16 numbers; rounded=False: the
+    unrounded sums of the two summands)"""
     assert codebook == "mcg" and int(window) == WINDOW, (codebook, window)
     tr = np.asarray(trellis)
     assert tr.ndim == 3 and (n is None or n == tr.shape[-1])
     it, ot = tr.shape[:2]
-    v = decode_tiles(tr)  # [it, ot, 256] slot order
-    tiles = np.empty((it, ot, 256), np.float16)
+    v = decode_tiles(tr, rounded)  # [it, ot, 256] slot order
+    tiles = np.empty((it, ot, 256), v.dtype)
     tiles[:, :, PERM] = v
     return tiles.reshape(it, ot, 16, 16).transpose(0, 2, 1, 3).reshape(it * 16, ot * 16).astype(np.float32)
 

@@ -43,8 +43,13 @@ static void parallel_for(int n, body_fn body, void *ctx) {
   for (int t = 0; t < T; t++) pthread_join(th[t], NULL);
 }
 
-static float g_lut[1 << 15];
+static float g_lut[1 << 15];      /* the weight as the format defines it: fp16(lo + hi) */
+static float g_lut_sum[1 << 15];  /* lo + hi unrounded: what a product accumulates that takes lo and hi as separate terms */
 static int g_lut_ready = 0;
+/* which of the two the *_emul functions multiply with: 1 = the CUDA decode kernels (summands), 0 = the reference's
+ * kernels and the CUDA prefill kernels (rounded value) */
+static int g_summands = 1;
+void exl3_emul_summands(int on) { g_summands = on ? 1 : 0; }
 
 static float half_bits_to_float(uint16_t h) {
   _Float16 f;
@@ -59,13 +64,14 @@ static void lut_init(void) {
   for (uint32_t cw = 0; cw < (1u << 15); cw++) {
     const uint32_t r = ((cw * 0xCBAC1FEDu) & 0x8FFF8FFFu) ^ 0x3B603B60u;
     /* the exact sum of the two halfs fits a float; one rounding to half = the half-precision add */
-    g_lut[cw] = round_to_half(half_bits_to_float((uint16_t)(r & 0xFFFF)) + half_bits_to_float((uint16_t)(r >> 16)));
+    g_lut_sum[cw] = half_bits_to_float((uint16_t)(r & 0xFFFF)) + half_bits_to_float((uint16_t)(r >> 16));
+    g_lut[cw] = round_to_half(g_lut_sum[cw]);
   }
   g_lut_ready = 1;
 }
 
 /* 256 values of one tile in slot order; words = 8K little-endian u32, ring read MSB-first, slot t ends at bit (t+1)K */
-static void decode_tile(const uint32_t *words, int K, float *v) {
+static void decode_tile(const uint32_t *words, int K, float *v, const float *lut) {
   const int TOT = 256 * K, NW = 8 * K;
   for (int t = 0; t < 256; t++) {
     int end = (t + 1) * K;               /* exclusive */
@@ -82,7 +88,7 @@ static void decode_tile(const uint32_t *words, int K, float *v) {
       bo = 0;
       wi = wi + 1 == NW ? 0 : wi + 1;
     }
-    v[t] = g_lut[cw & 0x7FFF];
+    v[t] = lut[cw & 0x7FFF];
   }
 }
 
@@ -130,7 +136,7 @@ typedef struct { const uint16_t *trellis; int IT, OT, K; float *out; } dec_ctx;
 static void dec_body(int tile, void *p) {
   dec_ctx *c = (dec_ctx *)p;
   float v[256];
-  decode_tile((const uint32_t *)(c->trellis + (size_t)tile * 16 * c->K), c->K, v);
+  decode_tile((const uint32_t *)(c->trellis + (size_t)tile * 16 * c->K), c->K, v, g_lut);
   const int tk = tile / c->OT, tn = tile % c->OT, n_out = c->OT * 16;
   for (int t = 0; t < 256; t++) c->out[(size_t)(tk * 16 + slot_row(t)) * n_out + tn * 16 + slot_col(t)] = v[t];
 }
@@ -165,7 +171,7 @@ static void gemm_body(int tn, void *p) {
     for (int r = 0; r < rows; r++)
       for (int c = 0; c < 16; c++) acc[r][c] = 0.0;
     for (int tk = 0; tk < IT; tk++) {
-      decode_tile((const uint32_t *)(trellis + ((size_t)tk * OT + tn) * 16 * K), K, v);
+      decode_tile((const uint32_t *)(trellis + ((size_t)tk * OT + tn) * 16 * K), K, v, g_summands ? g_lut_sum : g_lut);
       float w[16][16];
       for (int t = 0; t < 256; t++) w[slot_row(t)][slot_col(t)] = v[t];
       for (int r = 0; r < rows; r++) {

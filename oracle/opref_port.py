@@ -126,9 +126,11 @@ def exl3_linear_exact(x, trellis, suh, svh):
     return np.asarray(x, np.float64) @ W
 
 
-def exl3_linear_emul(x, trellis, suh, svh, inner=None):
-    """y_emul of tests/trunk6/check_kernels.py:93-99: device arithmetic, float64 after the float16 operand"""
-    inner = X.decode_inner(trellis).astype(np.float64) if inner is None else np.asarray(inner, np.float64)
+def exl3_linear_emul(x, trellis, suh, svh, inner=None, summands=True):
+    """y_emul of tests/trunk6/check_kernels.py:93-99: device arithmetic, float64 after the float16 operand. summands:
+    every weight enters the product as its two float16 summands (the CUDA decode kernels: no half add, hence no rounding
+    of the sum); False: as the rounded float16 value (the reference's kernels, the CUDA prefill kernels)"""
+    inner = X.decode_inner(trellis, rounded=not summands).astype(np.float64) if inner is None else np.asarray(inner, np.float64)
     raw = exl3_prep_emul(x, suh).astype(np.float64) @ inner
     m = raw.shape[-1]
     return had_blocks(raw, X.had_size(m)) * np.asarray(svh, np.float16).astype(np.float64)
@@ -147,6 +149,7 @@ class Exl3Linear:
         self.suh = np.asarray(suh, np.float16)
         self.svh = np.asarray(svh, np.float16)
         self._inner = None
+        self._inner_sum = None
         self._dense = None
 
     @property
@@ -154,6 +157,13 @@ class Exl3Linear:
         if self._inner is None:
             self._inner = X.decode_inner(self.trellis)
         return self._inner
+
+    @property
+    def inner_sum(self):
+        """W' with every value the unrounded sum of its two float16 summands"""
+        if self._inner_sum is None:
+            self._inner_sum = X.decode_inner(self.trellis, rounded=False)
+        return self._inner_sum
 
     @property
     def dense(self):
@@ -192,7 +202,7 @@ def moe_block_exact(x, router_w, sgate_w, experts, shared, top_k=10):
                 out=(routed + scale * sh).astype(np.float32))
 
 
-def moe_block_emul(x, router_w, sgate_w, experts, shared, top_k=10, ids=None, w=None):
+def moe_block_emul(x, router_w, sgate_w, experts, shared, top_k=10, ids=None, w=None, summands=True):
     """The block in the device arithmetic order (kernels/fn_moe.metal:304-343 gate/up, :370-445 down): float16
     prepared operands, raw inner products, H * svh, silu(g) * u * suh_down, H, float16, down, H * svh * w_k, slots
     summed in slot order, + sigmoid(shared logit) * shared. Returns dict with the intermediates the C ABI exposes."""
@@ -204,21 +214,22 @@ def moe_block_emul(x, router_w, sgate_w, experts, shared, top_k=10, ids=None, w=
         ids, w = route_device_order(logits, top_k)
     gu = np.zeros((M, top_k, 2, experts(0)[0].inner.shape[1]), np.float32)
     y = np.zeros((M, x.shape[1]), np.float64)
+    inner = (lambda l: l.inner_sum) if summands else (lambda l: l.inner)  # noqa: E731
     for r in range(M):
         for k in range(top_k):
             g, u, d = experts(int(ids[r, k]))
-            gr = exl3_prep_emul(x[r], g.suh).astype(np.float64) @ g.inner.astype(np.float64)
-            ur = exl3_prep_emul(x[r], u.suh).astype(np.float64) @ u.inner.astype(np.float64)
+            gr = exl3_prep_emul(x[r], g.suh).astype(np.float64) @ inner(g).astype(np.float64)
+            ur = exl3_prep_emul(x[r], u.suh).astype(np.float64) @ inner(u).astype(np.float64)
             gu[r, k, 0], gu[r, k, 1] = gr, ur
             gv = (had128(gr) * g.svh.astype(np.float64)).astype(np.float32)
             uv = (had128(ur) * u.svh.astype(np.float64)).astype(np.float32)
             mid = (gv / (1.0 + np.exp(-gv))) * uv
-            y[r] += np.float64(w[r, k]) * exl3_linear_emul(mid, None, d.suh, d.svh, inner=d.inner)
-    sgu = np.stack([exl3_linear_emul(x, None, shared[0].suh, shared[0].svh, inner=shared[0].inner),
-                    exl3_linear_emul(x, None, shared[1].suh, shared[1].svh, inner=shared[1].inner)], 1)
+            y[r] += np.float64(w[r, k]) * exl3_linear_emul(mid, None, d.suh, d.svh, inner=inner(d))
+    sgu = np.stack([exl3_linear_emul(x, None, shared[0].suh, shared[0].svh, inner=inner(shared[0])),
+                    exl3_linear_emul(x, None, shared[1].suh, shared[1].svh, inner=inner(shared[1]))], 1)
     sgu = sgu.astype(np.float32)
     act = silu(sgu[:, 0]) * sgu[:, 1]
-    sdown = exl3_linear_emul(act, None, shared[2].suh, shared[2].svh, inner=shared[2].inner).astype(np.float32)
+    sdown = exl3_linear_emul(act, None, shared[2].suh, shared[2].svh, inner=inner(shared[2])).astype(np.float32)
     out = y + sigmoid(sg_logit)[:, None].astype(np.float64) * sdown
     return dict(logits=np.concatenate([logits, sg_logit[:, None]], 1), ids=ids, weights=w, experts_gu=gu,
                 shared_gu=sgu, shared_down=sdown, routed=y.astype(np.float32), out=out.astype(np.float32))
