@@ -57,5 +57,8 @@ struct Pack {
 };
 
 std::shared_ptr<Pack> pack_from_c(ne_pack *p);
+struct Q8Weight;
+// 8-bit affine Linear `pre`.weight / .scales / .biases of a pack, resident on the device (capi_layer.cu)
+Q8Weight pack_q8(Pack &p, const std::string &pre);
 
 }  // namespace ijah

@@ -24,7 +24,31 @@ struct Layer {
   HcWeights hc;
   std::vector<void *> owned;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaStream_t stream = nullptr;       // all of the layer's launches (a capturable stream of its own)
+  cudaGraphExec_t block_graph = nullptr;  // the MoE block's six launches, captured on first use (the reference replays a
+                                          // recorded command buffer per step: core/recorder.h:45-99)
+  cudaGraphExec_t moe_graph() {
+    if (block_graph) return block_graph;
+    moe->forward(mlp_in, rows, mlp_out, stream);  // eager once: sets the kernels' attributes, surfaces launch errors
+    IJ_CUDA(cudaStreamSynchronize(stream));
+    cudaGraph_t g = nullptr;
+    IJ_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    try {
+      moe->forward(mlp_in, rows, mlp_out, stream);
+    } catch (...) {
+      cudaStreamEndCapture(stream, &g);
+      if (g) cudaGraphDestroy(g);
+      throw;
+    }
+    IJ_CUDA(cudaStreamEndCapture(stream, &g));
+    const cudaError_t rc = cudaGraphInstantiate(&block_graph, g, 0);
+    cudaGraphDestroy(g);
+    IJ_CHECK(rc == cudaSuccess, "cudaGraphInstantiate: %s", cudaGetErrorString(rc));
+    return block_graph;
+  }
   ~Layer() {
+    if (block_graph) cudaGraphExecDestroy(block_graph);
+    if (stream) cudaStreamDestroy(stream);
     for (void *p : owned) cudaFree(p);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -65,7 +89,7 @@ static ne_exl3_stack stack(Pack &p, const std::string &pre, int E, int in, int o
 
 // 8-bit affine Linear of the pack (reference models/flash_next/layer.mm:60-76): <pre>.weight U32 [rows][in / 4],
 // <pre>.scales / .biases BF16 [rows][in / group]
-static Q8Weight q8_weight(Pack &p, const std::string &pre) {
+Q8Weight pack_q8(Pack &p, const std::string &pre) {
   const TensorInfo *t = nullptr, *s = nullptr, *b = nullptr;
   Q8Weight q;
   q.w = static_cast<const uint8_t *>(p.device(pre + ".weight", &t));
@@ -89,8 +113,8 @@ static bool load_hc(Pack &p, const std::string &pre, int H, HcWeights *out) {
   IJ_CHECK(t->dtype == NE_BF16 && (int64_t)(t->nbytes / 2) == (int64_t)kHC * H, "%s.hc_norm.weight: want BF16 [%d]", pre.c_str(), kHC * H);
   w.inject = static_cast<const uint16_t *>(p.device(pre + ".block_inject_weight.weight", &t));
   IJ_CHECK(t->dtype == NE_BF16 && (int64_t)(t->nbytes / 2) == (int64_t)kHC * kHC * H, "%s.block_inject_weight.weight: want BF16 [%d][%d]", pre.c_str(), kHC, kHC * H);
-  w.down = q8_weight(p, pre + ".input_mix_weight_down");
-  w.up = q8_weight(p, pre + ".input_mix_weight_up");
+  w.down = pack_q8(p, pre + ".input_mix_weight_down");
+  w.up = pack_q8(p, pre + ".input_mix_weight_up");
   w.LR = w.down.rows;
   check_hc_weights(w);
   *out = w;
@@ -161,6 +185,7 @@ static Layer *make_layer(ne_pack *cp, int layer, int rows) {
   L->moe->h_mid = L->h_mid; L->moe->inj = L->inj; L->moe->h_out = L->h_out; L->moe->HC = kHC;
   IJ_CUDA(cudaEventCreate(&L->ev0));
   IJ_CUDA(cudaEventCreate(&L->ev1));
+  IJ_CUDA(cudaStreamCreateWithFlags(&L->stream, cudaStreamNonBlocking));
   return L.release();
 }
 
@@ -212,12 +237,12 @@ NE_API int ne_fn_layer_run_stage(ne_fn_layer *l, int block) {
              "mlp_inj -> logits ... h_out)", block);
     if (block == 4) {  // dispatches 5 and 6 (reference models/flash_next/layer.h:262-264)
       IJ_CHECK(L->has_hc, "the pack holds no mlp_hyper_connection tensors for this layer");
-      launch_hc_pre(L->hc, L->h_mid, L->rows, L->mlp_mix, L->inj, 0);
-      launch_hc_mix(L->hc, L->h_mid, L->mlp_mix, L->inj, L->rows, L->mlp_in, 0);
+      launch_hc_pre(L->hc, L->h_mid, L->rows, L->mlp_mix, L->inj, L->stream);
+      launch_hc_mix(L->hc, L->h_mid, L->mlp_mix, L->inj, L->rows, L->mlp_in, L->stream);
     } else {
-      L->moe->forward(L->mlp_in, L->rows, L->mlp_out, 0);
+      IJ_CUDA(cudaGraphLaunch(L->moe_graph(), L->stream));
     }
-    IJ_CUDA(cudaStreamSynchronize(0));
+    IJ_CUDA(cudaStreamSynchronize(L->stream));
     check_status_word();
   });
 }
@@ -229,12 +254,12 @@ NE_API int ne_fn_layer_run_dispatch(ne_fn_layer *l, int stage) {
     IJ_CHECK(stage >= 5 && stage <= 9, "dispatch %d is not implemented (5 mlp_hc_pre, 6 mlp_hc_mix, 7 moe_router, 8 moe_gateup, 9 moe_down)", stage);
     if (stage <= 6) {
       IJ_CHECK(L->has_hc, "the pack holds no mlp_hyper_connection tensors for this layer");
-      if (stage == 5) launch_hc_pre(L->hc, L->h_mid, L->rows, L->mlp_mix, L->inj, 0);
-      else launch_hc_mix(L->hc, L->h_mid, L->mlp_mix, L->inj, L->rows, L->mlp_in, 0);
+      if (stage == 5) launch_hc_pre(L->hc, L->h_mid, L->rows, L->mlp_mix, L->inj, L->stream);
+      else launch_hc_mix(L->hc, L->h_mid, L->mlp_mix, L->inj, L->rows, L->mlp_in, L->stream);
     } else {
-      L->moe->stage(stage, L->mlp_in, L->rows, L->mlp_out, 0);
+      L->moe->stage(stage, L->mlp_in, L->rows, L->mlp_out, L->stream);
     }
-    IJ_CUDA(cudaStreamSynchronize(0));
+    IJ_CUDA(cudaStreamSynchronize(L->stream));
     check_status_word();
   });
 }
@@ -250,7 +275,8 @@ NE_API int ne_fn_layer_write(ne_fn_layer *l, const char *name, const float *src,
     const Named t = named(L, name);
     IJ_CHECK(t.dev != nullptr, "unknown or read-only intermediate '%s'", name);
     IJ_CHECK(n >= 0 && (size_t)n <= t.n, "%s: n %d > size %zu", name, n, t.n);
-    IJ_CUDA(cudaMemcpy(t.dev, src, (size_t)n * 4, cudaMemcpyHostToDevice));
+    IJ_CUDA(cudaMemcpyAsync(t.dev, src, (size_t)n * 4, cudaMemcpyHostToDevice, L->stream));
+    IJ_CUDA(cudaStreamSynchronize(L->stream));
   });
 }
 
@@ -270,7 +296,8 @@ NE_API int ne_fn_layer_read(ne_fn_layer *l, const char *name, float *dst, int n)
       memcpy(dst, tmp.data(), (size_t)n * 4);
       return;
     }
-    IJ_CUDA(cudaMemcpy(dst, t.dev, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    IJ_CUDA(cudaMemcpyAsync(dst, t.dev, (size_t)n * 4, cudaMemcpyDeviceToHost, L->stream));
+    IJ_CUDA(cudaStreamSynchronize(L->stream));
   });
   return rc == 0 ? size : -1;
 }
@@ -286,15 +313,16 @@ NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, 
     void *fl = nullptr;
     const size_t fb = (size_t)std::max(flush_mb, 0) << 20;
     if (fb) IJ_CUDA(cudaMalloc(&fl, fb));
+    cudaGraphExec_t gx = L->moe_graph();
     auto chain = [&](int reps, bool layer, bool flush) {
       double best = 1e30;
       for (int it = 0; it < 5; it++) {
-        IJ_CUDA(cudaEventRecord(L->ev0, 0));
+        IJ_CUDA(cudaEventRecord(L->ev0, L->stream));
         for (int i = 0; i < reps; i++) {
-          if (layer) L->moe->forward(L->mlp_in, L->rows, L->mlp_out, 0);
-          if (flush) IJ_CUDA(cudaMemsetAsync(fl, i & 0xFF, fb, 0));
+          if (layer) IJ_CUDA(cudaGraphLaunch(gx, L->stream));
+          if (flush) IJ_CUDA(cudaMemsetAsync(fl, i & 0xFF, fb, L->stream));
         }
-        IJ_CUDA(cudaEventRecord(L->ev1, 0));
+        IJ_CUDA(cudaEventRecord(L->ev1, L->stream));
         IJ_CUDA(cudaEventSynchronize(L->ev1));
         float ms = 0;
         IJ_CUDA(cudaEventElapsedTime(&ms, L->ev0, L->ev1));
@@ -318,14 +346,17 @@ NE_API int ne_fn_layer_time(ne_fn_layer *l, int reps1, int reps2, int flush_mb, 
 // launched by planners that size grids, shared memory and scratch themselves, so what can be run by name are the operators:
 //   "exl3_linear"   args: trellis, suh, svh, x (f32 [rows][in]), y (f32 [rows][out]) buffers, then inline u32 {in, out, K, rows}
 //   "exl3_dequant"  args: trellis, w (f16 [in][out]) buffers, then inline u32 {in, out, K}
+//   "q8_linear"     args: weight, scales, biases, x (f32 [rows][in]), y (f32 [rows][out]) buffers, then inline u32 {in, out, group, rows}
+//                   (the reference's fn_lm_head: kernels/fn_model.metal:152-168, with the row count as an argument)
 // with buffer arguments given as (ne_buf, offset) exactly as in the reference, `reps` repetitions timed on the GPU and the
 // total returned in *gpu_ms; grid, threadgroup size, threadgroup memory, function constants and backend are accepted and
 // ignored. The reference's Metal kernel names (fn_moe_gateup_k5_r1, t6_simd, ...) are reported absent: their argument lists
 // bind the reference's Metal scratch layout (its per-row `uq` tables, split buffers and counters), which does not exist here.
-static const char *kOperators[] = {"exl3_linear", "exl3_dequant"};
+static const char *kOperators[] = {"exl3_linear", "exl3_dequant", "q8_linear"};
 static const char *kKernels[] = {"stream_gemm_kernel", "moe_router_kernel", "moe_prep_kernel", "moe_mid_kernel", "moe_combine_kernel",
                                  "prep_rows_kernel", "linear_finish_kernel", "dequant_kernel", "pf_gemm_kernel", "pf_logits_kernel",
-                                 "pf_route_kernel", "pf_prep_kernel", "pf_mid_kernel", "pf_finish_kernel", "hc_pre_kernel", "hc_mix_kernel"};
+                                 "pf_route_kernel", "pf_prep_kernel", "pf_mid_kernel", "pf_finish_kernel", "hc_pre_kernel", "hc_mix_kernel",
+                                 "q8_linear_kernel", "q8_embed_kernel"};
 NE_API int ne_kernel_exists(const char *fn) {
   if (!fn) return -1;
   for (const char *k : kOperators)
@@ -384,12 +415,20 @@ NE_API int ne_run_kernel(const char *fn, const ne_fconst *, int, const ne_arg *a
       ne_exl3_weight w{arg_device(args[0], "trellis"), nullptr, nullptr, (int)d[0], (int)d[1], (int)d[2]};
       void *out = arg_device(args[1], "w");
       timed([&] { IJ_CHECK(ne_exl3_dequant(&w, out, nullptr) == 0, "%s", ne_last_error()); });
+    } else if (name == "q8_linear") {
+      IJ_CHECK(args != nullptr && nargs == 6, "q8_linear takes 6 arguments: weight, scales, biases, x, y, {in, out, group, rows}");
+      uint32_t d[4];
+      arg_u32(args[5], d, 4, "argument 5");
+      ne_q8_weight w{arg_device(args[0], "weight"), arg_device(args[1], "scales"), arg_device(args[2], "biases"), (int)d[0], (int)d[1], (int)d[2]};
+      const float *x = (const float *)arg_device(args[3], "x");
+      float *y = (float *)arg_device(args[4], "y");
+      timed([&] { IJ_CHECK(ne_q8_linear(&w, x, (int)d[3], y, nullptr) == 0, "%s", ne_last_error()); });
     } else if (ne_kernel_exists(fn) == 1) {
       fail("ne_run_kernel(%s): this CUDA kernel is launched by its operator's planner (grid, shared memory and scratch are the planner's); "
-           "run the operator by name instead: exl3_linear, exl3_dequant", fn);
+           "run the operator by name instead: exl3_linear, exl3_dequant, q8_linear", fn);
     } else {
       fail("ne_run_kernel(%s): no such kernel in the CUDA build (the reference's Metal kernels bind its Metal scratch layout; operators "
-           "that can be run by name: exl3_linear, exl3_dequant)", fn);
+           "that can be run by name: exl3_linear, exl3_dequant, q8_linear)", fn);
     }
   });
 }

@@ -16,6 +16,7 @@
 #include "capi_internal.hpp"
 #include "exl3_linear.cuh"
 #include "moe_object.hpp"
+#include "q8_linear.cuh"
 #include "stack.cuh"
 
 using namespace ijah;
@@ -36,6 +37,7 @@ struct Model {
   int max_rows = 1;
   std::vector<ModelLayer> layers;
   const uint16_t *embed = nullptr, *head = nullptr, *final_norm = nullptr;
+  Q8Weight embed_q8, head_q8;  // 8-bit affine embedding / LM head (the reference's pack format); used when .w is set
   std::vector<void *> owned;
   int *tokens = nullptr, *next = nullptr;
   float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *o = nullptr, *y = nullptr, *logits = nullptr;
@@ -117,7 +119,9 @@ void Model::finish_setup() {
 int Model::record(int rows, bool with_head, cudaStream_t st) {
   const int H = d.hidden;
   int n = 0;
-  launch_embed(tokens, embed, d.vocab, H, rows, x, st); n++;
+  if (embed_q8.w) launch_q8_embed(embed_q8, tokens, rows, x, true, st);
+  else launch_embed(tokens, embed, d.vocab, H, rows, x, st);
+  n++;
   for (size_t l = 0; l < layers.size(); l++) {
     ModelLayer &L = layers[l];
     launch_rms_add(x, l == 0 ? nullptr : y, xn, L.norm1, rows, H, 1e-6f, st); n++;
@@ -139,7 +143,8 @@ int Model::record(int rows, bool with_head, cudaStream_t st) {
   launch_rms_add(x, y, xn, final_norm, rows, H, 1e-6f, st); n++;
   launches_body = n;
   if (with_head) {
-    launch_lm_head(xn, head, d.vocab, H, rows, logits, head_scratch, st); n += 2;
+    if (head_q8.w) { launch_q8_linear(head_q8, xn, rows, logits, st); n += (rows + 31) / 32; }
+    else { launch_lm_head(xn, head, d.vocab, H, rows, logits, head_scratch, st); n += 2; }
     launch_argmax(logits, d.vocab, rows, next, argmax_scratch, st); n += 2;
     launches_full = n;
   }
@@ -268,14 +273,26 @@ static Model *model_from_pack(ne_pack *cp, int tmax, int max_rows) {
            "config.json needs num_hidden_layers, num_attention_heads, num_key_value_heads and head_dim");
   const std::string mp = "language_model.model.";
   const TensorInfo *et = pk->info(mp + "embed_tokens.weight");
-  IJ_CHECK(et && et->dtype == NE_BF16 && et->ndim == 2, "%sembed_tokens.weight (BF16 [vocab][hidden]) missing", mp.c_str());
-  d.vocab = (int)et->shape[0];
-  d.hidden = (int)et->shape[1];
-  M->embed = (const uint16_t *)pk->device(mp + "embed_tokens.weight");
+  IJ_CHECK(et && et->ndim == 2, "%sembed_tokens.weight missing", mp.c_str());
+  if (pk->info(mp + "embed_tokens.scales")) {  // 8-bit affine table, as the reference's packs hold it (model.mm:229-230)
+    M->embed_q8 = pack_q8(*pk, mp + "embed_tokens");
+    d.vocab = M->embed_q8.rows;
+    d.hidden = M->embed_q8.in;
+  } else {
+    IJ_CHECK(et->dtype == NE_BF16, "%sembed_tokens.weight: want BF16 [vocab][hidden] or an 8-bit affine table with .scales / .biases", mp.c_str());
+    d.vocab = (int)et->shape[0];
+    d.hidden = (int)et->shape[1];
+    M->embed = (const uint16_t *)pk->device(mp + "embed_tokens.weight");
+  }
   const TensorInfo *ht = pk->info("language_model.lm_head.weight");
-  if (ht) {
+  if (ht && pk->info("language_model.lm_head.scales")) {  // 8-bit affine head (model.mm:231-232)
+    M->head_q8 = pack_q8(*pk, "language_model.lm_head");
+    IJ_CHECK(M->head_q8.rows == d.vocab && M->head_q8.in == d.hidden, "lm_head: want [%d][%d]", d.vocab, d.hidden);
+  } else if (ht) {
     IJ_CHECK(ht->dtype == NE_BF16 && ht->ndim == 2 && ht->shape[0] == d.vocab && ht->shape[1] == d.hidden, "lm_head.weight: want BF16 [%d][%d]", d.vocab, d.hidden);
     M->head = (const uint16_t *)pk->device("language_model.lm_head.weight");
+  } else if (M->embed_q8.w) {
+    M->head_q8 = M->embed_q8;  // tied
   } else {
     M->head = M->embed;  // tied
   }
@@ -569,7 +586,11 @@ NE_API uint64_t ne_fn_model_weight_bytes(ne_fn_model *m) {
   Model *M = reinterpret_cast<Model *>(m);
   if (!M) return 0;
   auto lin = [](const ne_exl3_weight &w) { return (uint64_t)w.in * w.out * w.K / 8 + 2ull * w.in + 2ull * w.out; };
-  uint64_t b = 2ull * M->d.vocab * M->d.hidden * (M->head == M->embed ? 1 : 2);
+  auto q8b = [](const Q8Weight &w) { return (uint64_t)w.rows * w.in + 4ull * w.rows * (w.in / w.group); };
+  uint64_t b = 0;
+  if (M->embed_q8.w) b += q8b(M->embed_q8); else b += 2ull * M->d.vocab * M->d.hidden;
+  if (M->head_q8.w) b += M->head_q8.w == M->embed_q8.w ? 0 : q8b(M->head_q8);
+  else if (M->head != M->embed) b += 2ull * M->d.vocab * M->d.hidden;
   for (const ModelLayer &L : M->layers) {
     b += lin(L.q) + lin(L.k) + lin(L.v) + lin(L.o) + 2ull * L.md.experts * L.md.hidden;
     b += 3ull * L.md.expert_count * ((uint64_t)L.md.hidden * L.md.inter * L.md.k_expert / 8 + 2ull * L.md.hidden + 2ull * L.md.inter);
@@ -583,7 +604,8 @@ NE_API int ne_fn_model_last_bytes(ne_fn_model *m, int rows, uint64_t *total, int
     Model *M = reinterpret_cast<Model *>(m);
     IJ_CHECK(M != nullptr, "null model");
     auto lin = [](const ne_exl3_weight &w) { return (uint64_t)w.in * w.out * w.K / 8 + 2ull * w.in + 2ull * w.out; };
-    uint64_t b = 2ull * M->d.vocab * M->d.hidden + (uint64_t)rows * M->d.hidden * 2;
+    uint64_t b = (M->head_q8.w ? (uint64_t)M->head_q8.rows * M->head_q8.in + 4ull * M->head_q8.rows * (M->head_q8.in / M->head_q8.group)
+                               : 2ull * M->d.vocab * M->d.hidden) + (uint64_t)rows * M->d.hidden * 2;
     long nu = 0;
     for (ModelLayer &L : M->layers) {
       uint64_t t = 0;

@@ -7,6 +7,7 @@
 #include "capi_internal.hpp"
 #include "fn_moe.cuh"
 #include "moe_object.hpp"
+#include "q8_linear.cuh"
 
 using namespace ijah;
 
@@ -290,6 +291,30 @@ NE_API int ne_exl3_linear(const ne_exl3_weight *w, const float *x_dev, int rows,
     const LinearPlan p = plan_linear(w->in, w->out, w->K, rows);
     void *scratch = device_scratch(p.scratch_bytes());
     launch_linear(p, w->trellis_dev, w->suh_dev, w->svh_dev, x_dev, y_dev, scratch, device_status_word(), (cudaStream_t)stream);
+  });
+}
+
+static Q8Weight q8_from_c(const ne_q8_weight *w) {
+  IJ_CHECK(w != nullptr, "null weight");
+  Q8Weight q;
+  q.w = static_cast<const uint8_t *>(w->weight_dev);
+  q.scales = static_cast<const uint16_t *>(w->scales_dev);
+  q.biases = static_cast<const uint16_t *>(w->biases_dev);
+  q.rows = w->out; q.in = w->in; q.group = w->group;
+  return q;
+}
+
+NE_API int ne_q8_linear(const ne_q8_weight *w, const float *x_dev, int rows, float *y_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(x_dev && y_dev, "null activation pointer");
+    launch_q8_linear(q8_from_c(w), x_dev, rows, y_dev, (cudaStream_t)stream);
+  });
+}
+
+NE_API int ne_q8_embed(const ne_q8_weight *w, const int *tokens_dev, int rows, float *x_dev, int round_bf16, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(tokens_dev && x_dev && rows >= 1, "bad arguments");
+    launch_q8_embed(q8_from_c(w), tokens_dev, rows, x_dev, round_bf16 != 0, (cudaStream_t)stream);
   });
 }
 

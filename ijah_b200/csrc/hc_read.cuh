@@ -10,16 +10,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "q8_linear.cuh"
+
 namespace ijah {
 
 constexpr int HC_STREAMS = 4;  // reference models/flash_next/layer.h:17-19
-
-struct Q8Weight {
-  const uint8_t *w = nullptr;        // [rows][in]
-  const uint16_t *scales = nullptr;  // bf16 [rows][in / group]
-  const uint16_t *biases = nullptr;
-  int rows = 0, in = 0, group = 64;
-};
 
 struct HcWeights {
   const uint16_t *norm = nullptr;    // bf16 [HC * H]

@@ -230,16 +230,19 @@ __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, 
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[m][j] = 0.0f;
   // ldmatrix.x4 row addresses of an 8-row group: lanes 8j .. 8j+7 give rows 0-7 at byte 16 j of the k-tile (the even
-  // inputs' low and high halves of the tile, then the odd inputs'). Dead rows read the zero row.
+  // inputs' low and high halves of the tile, then the odd inputs'). A dead row (its results are never stored) reads the
+  // unit's row 0 again: the same address as a live lane, i.e. a broadcast. (A separate zero row sat at the same offset
+  // modulo 128 bytes as row 0 and cost every ldmatrix a two-way bank conflict: 4 of 14 load wavefronts per tile.)
   uint32_t a_row[MT];
   {
     const uint32_t lkof = (uint32_t)(lane >> 3) * 16u;
 #pragma unroll
     for (int m = 0; m < MT; m++) {
       const int r = m * 8 + (lane & 7);
-      a_row[m] = (r < d.nrows ? a_addr + (uint32_t)r * lda_bytes : z_addr) + lkof;
+      a_row[m] = a_addr + (uint32_t)(r < d.nrows ? r : 0) * lda_bytes + lkof;
     }
   }
+  (void)z_addr;
   const typename Codec<K>::Lane L = Codec<K>::lane(lane);
   const uint32_t d1 = L.o1 - L.o0, d2 = L.o2 - L.o0, t0 = rc.tile0 + L.o0;
   uint32_t w[SG_HALF][3];

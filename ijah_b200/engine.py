@@ -45,6 +45,11 @@ class Exl3WeightC(C.Structure):
                 ("n_out", C.c_int), ("K", C.c_int)]
 
 
+class Q8WeightC(C.Structure):  # include/ijah_b200.h: ne_q8_weight
+    _fields_ = [("weight", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p), ("n_in", C.c_int), ("n_out", C.c_int),
+                ("group", C.c_int)]
+
+
 class Exl3StackC(C.Structure):
     _fields_ = [("trellis", C.c_void_p), ("suh", C.c_void_p), ("svh", C.c_void_p)]
 
@@ -100,6 +105,8 @@ SIGNATURES = {
     "ne_fn_layer_time": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "ne_exl3_dequant": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_void_p]),
     "ne_exl3_linear": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_q8_linear": (C.c_int, [C.POINTER(Q8WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_q8_embed": (C.c_int, [C.POINTER(Q8WeightC), C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "ne_exl3_linear_host": (C.c_int, [C.POINTER(Exl3WeightC), C.c_void_p, C.c_int, C.c_void_p]),
     "ne_exl3_linear_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_uint64)]),
     "ne_moe_plan": (C.c_int, [C.c_int] * 7 + [C.POINTER(C.c_int)]),
@@ -508,6 +515,35 @@ def to_device_u16(a, device="cuda"):
     if a.dtype == np.float16:
         return torch.from_numpy(a).to(device)
     return torch.from_numpy(a.view(np.int16)).to(device)
+
+
+class Q8Linear:
+    """One 8-bit affine Linear (MLX layout) on the device: y = x @ W^T through ne_q8_linear; embedding lookup through
+    ne_q8_embed. weight: uint32 [out, in / 4] (or uint8 [out, in]), scales / biases: bf16 bit patterns uint16 [out, in / group]"""
+
+    def __init__(self, eng, weight, scales, biases, device="cuda"):
+        torch = _torch()
+        self.eng = eng
+        w = np.ascontiguousarray(weight).view(np.uint8)
+        sc, bi = np.ascontiguousarray(scales, np.uint16), np.ascontiguousarray(biases, np.uint16)
+        self.n_out, self.n_in = w.shape
+        self.group = self.n_in // sc.shape[1]
+        self.t = (torch.from_numpy(w).to(device), to_device_u16(sc, device), to_device_u16(bi, device))
+        self.c = Q8WeightC(self.t[0].data_ptr(), self.t[1].data_ptr(), self.t[2].data_ptr(), self.n_in, self.n_out, self.group)
+
+    def __call__(self, x):
+        torch = _torch()
+        x = x.to(torch.float32).contiguous()
+        y = torch.empty((x.shape[0], self.n_out), dtype=torch.float32, device=x.device)
+        self.eng._ok(self.eng.lib.ne_q8_linear(C.byref(self.c), _dev(x), x.shape[0], _dev(y), _stream()), "ne_q8_linear")
+        return y
+
+    def embed(self, tokens, round_bf16=True):
+        torch = _torch()
+        t = tokens.to(torch.int32).contiguous()
+        x = torch.empty((t.shape[0], self.n_in), dtype=torch.float32, device=t.device)
+        self.eng._ok(self.eng.lib.ne_q8_embed(C.byref(self.c), _dev(t), t.shape[0], _dev(x), int(round_bf16), _stream()), "ne_q8_embed")
+        return x
 
 
 class Exl3Linear:

@@ -247,6 +247,17 @@ def affine_dequant(wq_u32, scales_bf16, biases_bf16):
     return (q * sc[..., None] + bi[..., None]).reshape(out, n_in)
 
 
+def q8_linear(x, wq_u32, scales_bf16, biases_bf16):
+    """x @ W^T for an 8-bit affine Linear in f32 (reference tools/opref.py:183-194 `linear_big` with bf=False)"""
+    return np.asarray(x, np.float32) @ affine_dequant(wq_u32, scales_bf16, biases_bf16).T
+
+
+def q8_embed(ids, wq_u32, scales_bf16, biases_bf16):
+    """rows `ids` of an 8-bit affine table, dequantised and rounded to bf16 (reference tools/opref.py:133-141 `linear_rows`)"""
+    ids = np.asarray(ids).reshape(-1)
+    return bf16_round(affine_dequant(np.asarray(wq_u32)[ids], np.asarray(scales_bf16)[ids], np.asarray(biases_bf16)[ids]))
+
+
 def hc_read(h, norm_w, inject_w, down, up, streams=4, eps=1e-6):
     """Hyper-connection read in f32 (reference tools/opref.py:221-236 with bf=False; models/flash_next/layer.mm:524-531):
     h [rows, streams*H]; norm_w f32 [streams*H]; inject_w f32 [streams, streams*H]; down f32 [LR, streams*H]; up f32

@@ -37,11 +37,14 @@ def attn_standin(q, knew, vnew, kc, vc, heads, kv_heads, hd):
     return out
 
 
-def stack_logits(tokens, embed_bf16, head_bf16, layers, heads, kv_heads, hd, top_k):
+def stack_logits(tokens, embed_bf16, head_bf16, layers, heads, kv_heads, hd, top_k, embed_q8=None, head_q8=None):
     """layers: list of dicts with q, k, v, o (opref_port.Exl3Linear), view (object with router, sgate, expert(e), shared as
-    tests/helpers.MoeView), kc, vc (float16 [T, kv_heads, hd]). Returns float64 logits [R, vocab]."""
-    emb = O.bf16_bits_to_f32(embed_bf16)
-    x = emb[np.asarray(tokens)].astype(np.float64)
+    tests/helpers.MoeView), kc, vc (float16 [T, kv_heads, hd]). embed_q8 / head_q8: (weight u32, scales, biases) of an
+    8-bit affine table instead of the bf16 one. Returns float64 logits [R, vocab]."""
+    if embed_q8 is not None:
+        x = O.q8_embed(tokens, *embed_q8).astype(np.float64)
+    else:
+        x = O.bf16_bits_to_f32(embed_bf16)[np.asarray(tokens)].astype(np.float64)
     y = None
     for L in layers:
         if y is not None:
@@ -54,6 +57,8 @@ def stack_logits(tokens, embed_bf16, head_bf16, layers, heads, kv_heads, hd, top
         vw = L["view"]
         y = O.moe_block_exact(xn.astype(np.float32), vw.router, vw.sgate, vw.expert, vw.shared, top_k)["out"].astype(np.float64)
     xn = rms(x + y)
+    if head_q8 is not None:  # the 8-bit head multiplies the f32 activations
+        return xn.astype(np.float32).astype(np.float64) @ O.affine_dequant(*head_q8).astype(np.float64).T
     xb = O.bf16_bits_to_f32(O.f32_to_bf16_bits(xn.astype(np.float32))).astype(np.float64)  # the head multiplies bf16 activations
     return xb @ O.bf16_bits_to_f32(head_bf16).astype(np.float64).T
 

@@ -52,6 +52,23 @@ def hc_inputs():
     return (rng.standard_normal((5, 4 * HC["hidden"])) * np.array([0.5, 1.0, 2.0, 4.0]).repeat(HC["hidden"])).astype(np.float32)
 
 
+Q8 = dict(vocab=1024, hidden=256, group=64)  # 8-bit affine LM head and token embedding (the reference's: 248320 x 2560, group 64 / 128)
+
+
+def q8_tensors():
+    rng = np.random.default_rng(SEED + 4)
+    t = {}
+    for name in ("language_model.lm_head", "language_model.model.embed_tokens"):
+        w, sc, bi = packgen.q8_linear(rng, Q8["vocab"], Q8["hidden"], Q8["group"])
+        t[name + ".weight"], t[name + ".scales"], t[name + ".biases"] = ("U32", w), ("BF16", sc), ("BF16", bi)
+    return t
+
+
+def q8_inputs():
+    rng = np.random.default_rng(SEED + 5)
+    return rng.standard_normal((6, Q8["hidden"])).astype(np.float32), rng.integers(0, Q8["vocab"], 9).astype(np.int32)
+
+
 def tensors_digest(t):
     h = hashlib.sha256()
     for name in sorted(t):
@@ -68,7 +85,7 @@ def inputs():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference repository (its tools/opref.py is imported unmodified)")
-    ap.add_argument("--which", default="all", choices=["all", "moe", "hc"], help="which fixture file to (re)write")
+    ap.add_argument("--which", default="all", choices=["all", "moe", "hc", "q8"], help="which fixture file to (re)write")
     a = ap.parse_args()
     tmp = Path(tempfile.mkdtemp(prefix="ijah_golden_"))
     try:
@@ -80,6 +97,8 @@ def main():
         tens = small_pack_tensors()
         hct = hc_tensors()
         tens.update(hct)
+        q8t = q8_tensors()
+        tens.update(q8t)
         pack = packgen.write_pack(tmp / "pack", tens, {"num_experts_per_tok": TOPK}, shards=3, misalign=2)
         os.environ["IJAH_REF_DIR"] = str(tmp / "ref")
         os.environ["IJAH_PACK"] = str(pack)
@@ -100,7 +119,16 @@ def main():
             print("wrote", HERE / "hc_small.npz", {k: np.shape(v) for k, v in hc.items()})
             if a.which == "hc":
                 return
-        for k in hct:
+        if a.which in ("all", "q8"):
+            x, ids = q8_inputs()
+            q8 = dict(seed=np.int64(SEED), digest=np.array(tensors_digest(q8t)), x=x, ids=ids)
+            q8["head_y"] = np.asarray(O.linear_big(x, P, "language_model.lm_head", bf=False), np.float32)
+            q8["embed_rows"] = np.asarray(P.linear_rows("language_model.model.embed_tokens", ids), np.float32)
+            np.savez_compressed(HERE / "q8_small.npz", **q8)
+            print("wrote", HERE / "q8_small.npz", {k: np.shape(v) for k, v in q8.items()})
+            if a.which == "q8":
+                return
+        for k in list(hct) + list(q8t):
             del tens[k]
         x = inputs()
         out = dict(seed=np.int64(SEED), digest=np.array(tensors_digest(tens)), x=x, topk=np.int64(TOPK))

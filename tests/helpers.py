@@ -34,6 +34,18 @@ def hc_small():
     return t, g
 
 
+def q8_small():
+    """(8-bit affine LM head + embedding tensors, their golden file) with the digest verified"""
+    g = np.load(GOLD / "q8_small.npz")
+    t = make_golden.q8_tensors()
+    assert make_golden.tensors_digest(t) == str(g["digest"]), "numpy random stream differs from the one that made the golden file"
+    return t, g
+
+
+def q8_parts(tensors, name):
+    return tuple(tensors[name + s][1] for s in (".weight", ".scales", ".biases"))
+
+
 def hc_oracle(tensors, h, layer=0, which="mlp"):
     """oracle hyper-connection read over a packgen dict"""
     pre = f"{PFX}{layer}.{which}_hyper_connection."

@@ -14,11 +14,16 @@ pytestmark = pytest.mark.gpu
 CFG = dict(layers=3, hidden=512, inter=256, experts=32, top_k=4, heads=4, kv_heads=2, head_dim=64, vocab=2048)
 
 
-def small_model_tensors(rng):
+def small_model_tensors(rng, fmt="bf16"):
     t = {}
     H, V = CFG["hidden"], CFG["vocab"]
-    t["language_model.model.embed_tokens.weight"] = ("BF16", packgen.f32_to_bf16_bits(rng.standard_normal((V, H))))
-    t["language_model.lm_head.weight"] = ("BF16", packgen.f32_to_bf16_bits(rng.standard_normal((V, H)) * 0.1))
+    if fmt == "q8":  # 8-bit affine embedding and head, the format of the reference's packs
+        for name, std in (("language_model.model.embed_tokens", 1.0), ("language_model.lm_head", 0.1)):
+            w, sc, bi = packgen.q8_linear(rng, V, H, 64, std=std)
+            t[name + ".weight"], t[name + ".scales"], t[name + ".biases"] = ("U32", w), ("BF16", sc), ("BF16", bi)
+    else:
+        t["language_model.model.embed_tokens.weight"] = ("BF16", packgen.f32_to_bf16_bits(rng.standard_normal((V, H))))
+        t["language_model.lm_head.weight"] = ("BF16", packgen.f32_to_bf16_bits(rng.standard_normal((V, H)) * 0.1))
     for l in range(CFG["layers"]):
         t.update(packgen.moe_layer(rng, layer=l, hidden=H, inter=CFG["inter"], experts=CFG["experts"]))
         t.update(packgen.trunk_layer(rng, layer=l, hidden=H, q_out=CFG["heads"] * CFG["head_dim"], kv_out=CFG["kv_heads"] * CFG["head_dim"],
@@ -54,9 +59,10 @@ def eng():
     return E.Engine()
 
 
-def test_stack_logits_match_the_operator_reference(eng, tmp_path):
+@pytest.mark.parametrize("fmt", ["bf16", "q8"])
+def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     rng = np.random.default_rng(2025)
-    t = small_model_tensors(rng)
+    t = small_model_tensors(rng, fmt)
     cfg = {"num_hidden_layers": CFG["layers"], "num_attention_heads": CFG["heads"], "num_key_value_heads": CFG["kv_heads"],
            "head_dim": CFG["head_dim"], "num_experts_per_tok": CFG["top_k"], "vocab_size": CFG["vocab"]}
     packgen.write_pack(tmp_path / "model", t, cfg, shards=4, misalign=2)
@@ -76,8 +82,10 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path):
                            view=FastView(t, l), kc=m.read("kv_k", l).reshape(kv), vc=m.read("kv_v", l).reshape(kv)))
         for n in ("q", "k", "v", "o"):
             layers[-1][n]._inner = CO.decode_inner(layers[-1][n].trellis)
+    q8 = (lambda n: tuple(t[n + s][1] for s in (".weight", ".scales", ".biases"))) if fmt == "q8" else (lambda n: None)
     want = S.stack_logits(tokens, t["language_model.model.embed_tokens.weight"][1], t["language_model.lm_head.weight"][1], layers,
-                          CFG["heads"], CFG["kv_heads"], CFG["head_dim"], CFG["top_k"])
+                          CFG["heads"], CFG["kv_heads"], CFG["head_dim"], CFG["top_k"], embed_q8=q8("language_model.model.embed_tokens"),
+                          head_q8=q8("language_model.lm_head"))
     kl = S.kl(want, logits)
     assert kl.max() < 1e-4, kl
     assert np.abs(logits - want).max() / np.abs(want).max() < 1e-2
@@ -89,7 +97,7 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path):
     lref = want[0] - want[0].max()
     assert abs(lp1 - (lref[n1] - np.log(np.exp(lref).sum()))) < 1e-2
     info = m.info()
-    assert info["launches_full"] == 1 + CFG["layers"] * 16 + 1 + 4 and info["T"] == 128
+    assert info["launches_full"] == 1 + CFG["layers"] * 16 + 1 + (3 if fmt == "q8" else 4) and info["T"] == 128
     a, b, c = m.time(reps=3)
     assert 0 < b <= a and c > 0
     m.free()

@@ -3,7 +3,7 @@
 import numpy as np
 
 from oracle import opref_port as O
-from tests.helpers import MoeView, hc_oracle, hc_small, rel_max, small_pack, trunk_linear
+from tests.helpers import MoeView, hc_oracle, hc_small, q8_parts, q8_small, rel_max, small_pack, trunk_linear
 
 
 def test_router_matches_reference():
@@ -78,3 +78,10 @@ def test_hc_read_matches_reference():
     for k in ("normed", "mix", "block_in", "inject_w"):
         assert rel_max(r[k], g["f32_" + k]) < 2e-6, k
         assert rel_max(r[k], g["bf16_" + k]) < 2e-2, k
+
+
+def test_q8_linear_and_embedding_match_reference():
+    # the reference's linear_big (f32 flow) and linear_rows (bf16 rows) on the small 8-bit affine head and embedding
+    t, g = q8_small()
+    assert rel_max(O.q8_linear(g["x"], *q8_parts(t, "language_model.lm_head")), g["head_y"]) < 2e-6
+    assert np.array_equal(O.q8_embed(g["ids"], *q8_parts(t, "language_model.model.embed_tokens")), g["embed_rows"])
