@@ -8,7 +8,7 @@ dimension 256), and the MoE block: 512 routed experts (top-10, intermediate 768,
 libijah_b200.so behind ne_fn_model_* and is replayed from a CUDA graph the library owns; weights are generated on the
 device by the library (about 75 GB resident on one GPU). value = rows / step time.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--verify M] [--impl reference] [--workload stack|block]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--verify M] [--impl reference] [--workload stack|block|q8head]
 
 N > 1 (under torchrun): expert parallel, weak scaling. Every rank holds experts/N experts of every layer and B x M rows of
 its own; per MoE block the ranks exchange rows and partial outputs over NVLink peer memory (the library's own kernels),
@@ -17,13 +17,15 @@ against a single-GPU step over all rows (`ep_check`).
 
 `e2e` is the same step through ne_fn_model_step_rows with the token ids in host memory and the sampled ids copied back.
 `roofline` is the dominant kernel (the gate/up stream GEMM of the MoE block) timed alone over layers with distinct weights.
-`--workload block` times the MoE block alone (the earlier headline; also what the ncu recipes under profiles/ run).
+`--workload block` times the MoE block alone (the earlier headline; also what the ncu recipes under profiles/ run);
+`--workload q8head` the 8-bit affine Linear at the reference's LM head size.
 
 --impl reference: the CPU restatement of the reference's operator path (oracle/, C with all host threads) on a bounded
 sample of the same workload; the reference's own code for this path is Metal / numpy-with-a-missing-module and cannot run
 on this box.
 """
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -50,6 +52,13 @@ def peaks():
     if p.exists():
         return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+# DRAM bytes (read + write) per algorithmic byte of the gate/up stream launch, from the ncu capture summarised in
+# profiles/stream_gemm_moe_decode.md (8 rows, one layer: 153.31 MB read + 4.21 MB written for 152.65 MB of compressed weights;
+# the writes are the k-split partial sums). The full-size launch processes the same units, only more of them, so the traffic
+# reported beside the roofline is this ratio times the launch's algorithmic bytes.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (153.31 + 4.21) / 152.65
 
 
 class ClockSampler:
@@ -422,7 +431,8 @@ def run_stack(a, rank, world):
         bf = block_figures(eng, rows, 8, a.steps, dev)
         roof = {"bound": "hbm", "kernel": "stream_gemm_kernel<MoeGateUpProblem> (gate/up of routed + shared experts)",
                 "achieved": bf["gateup_gbs"], "peak": peak, "unit": "GB/s", "frac": bf["gateup_frac"], "peak_source": which + " (stream copy)",
-                "traffic": None, "bytes_per_launch": bf["gateup_bytes"], "us_per_launch": bf["gateup_us"]}
+                "traffic": bf["gateup_bytes"] * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE, "traffic_source": "ncu capture of a one-layer case, scaled by bytes",
+                "bytes_per_launch": bf["gateup_bytes"], "us_per_launch": bf["gateup_us"]}
         if clocks and clocks.get("sm_mhz"):
             roof["kcycles_per_launch_at_median_mhz"] = bf["gateup_us"] * clocks["sm_mhz"] * 1e-3
         extra["block"] = {str(rows): bf}
@@ -480,9 +490,66 @@ def run_block(a, rank, world):
         "ms_per_step": bf["block_us"] * a.layers * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": block_config(a), "e2e": None, "gpu_launches": 6 * a.layers * a.steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "stream_gemm_kernel<MoeGateUpProblem> (gate/up of routed + shared experts)", "achieved": bf["gateup_gbs"],
-                     "peak": peak, "unit": "GB/s", "frac": bf["gateup_frac"], "peak_source": which + " (stream copy)", "traffic": None,
+                     "peak": peak, "unit": "GB/s", "frac": bf["gateup_frac"], "peak_source": which + " (stream copy)",
+                     "traffic": bf["gateup_bytes"] * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE, "traffic_source": "ncu capture of a one-layer case, scaled by bytes",
                      "bytes_per_launch": bf["gateup_bytes"], "us_per_launch": bf["gateup_us"]},
         "cpu_baseline": None, "extra": extra, "wait_status": eng.lib.ne_device_wait_status()}))
+
+
+# ---------------------------------------------------------------------------------------------- the 8-bit affine LM head alone
+def run_q8head(a, rank, world):
+    """ne_q8_linear at the reference's LM head size (248320 x 2560 bytes, group 64: 636 MB per launch, larger than L2) for
+    --rows activation rows: seeded random bytes / scales generated on the device, CUDA events around --steps launches."""
+    import torch
+    from ijah_b200 import engine as E
+    assert world == 1, "--workload q8head is a single-GPU measurement"
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    eng = E.Engine()
+    peak, which = peaks()
+    V, H = (int(v) for v in a.q8_dims.split("x"))
+    G = 64
+    g = torch.Generator(device=dev)
+    g.manual_seed(a.seed)
+    w = torch.randint(0, 256, (V, H), dtype=torch.uint8, device=dev, generator=g)
+    sc = (torch.randn((V, H // G), device=dev, generator=g) * 1e-4 + 6e-4).to(torch.bfloat16).view(torch.int16)
+    bi = (sc.view(torch.bfloat16).float() * -128).to(torch.bfloat16).view(torch.int16)
+    x = torch.randn((a.rows, H), device=dev, generator=g)
+    y = torch.empty((a.rows, V), device=dev)
+    c = E.Q8WeightC(w.data_ptr(), sc.data_ptr(), bi.data_ptr(), H, V, G)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        eng._ok(eng.lib.ne_q8_linear(ctypes.byref(c), x.data_ptr(), a.rows, y.data_ptr(), ctypes.c_void_p(st)), "ne_q8_linear")
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(a.warmup):
+        launch()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(a.steps):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    us = e0.elapsed_time(e1) * 1e3 / a.steps
+    # spot check against f32 arithmetic on 64 vocabulary rows
+    idx = torch.arange(0, V, V // 64, device=dev)[:64]
+    wd = w[idx].float().view(64, H // G, G) * sc.view(torch.bfloat16)[idx].float()[..., None] + bi.view(torch.bfloat16)[idx].float()[..., None]
+    want = x.double() @ wd.view(64, H).double().T
+    err = float((y[:, idx].double() - want).abs().max() / want.abs().max())
+    nbytes = V * H + 4 * V * (H // G) + a.rows * H * 4 + a.rows * V * 4
+    gbs = nbytes / (us * 1e-6) / 1e9
+    print(json.dumps({
+        "metric": "8-bit affine LM head tok/s", "value": a.rows / (us * 1e-6), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": us * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 weights, f16 hi+lo activations, f32 accumulate",
+        "data": "synthetic", "config": {"workload": f"ne_q8_linear {V} x {H}, group {G}, rows {a.rows}", "l2": "636 MB of weights per launch exceed L2"},
+        "e2e": None, "gpu_launches": a.steps * ((a.rows + 15) // 16), "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "q8_linear_kernel", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "peak_source": which + " (stream copy)", "traffic": None, "bytes_per_launch": nbytes, "us_per_launch": us},
+        "cpu_baseline": None, "extra": {"max_rel_err_vs_f64_on_64_rows": err}}))
 
 
 def main():
@@ -498,7 +565,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-extras", dest="extras", action="store_false", help="skip the extra block / prefill / other-row-count figures")
     ap.add_argument("--no-sustain", dest="sustain", action="store_false", help="skip the >= 2 s sustained replay")
-    ap.add_argument("--workload", default="stack", choices=["stack", "block"])
+    ap.add_argument("--workload", default="stack", choices=["stack", "block", "q8head"])
+    ap.add_argument("--q8-dims", default="248320x2560", help="--workload q8head: output rows x inputs (default: the reference's LM head)")
     ap.add_argument("--rows", type=int, default=4, help="--workload block: activation rows")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="--workload block: tokens of a prefill figure (0 = skip)")
     a = ap.parse_args()
@@ -511,6 +579,8 @@ def main():
         return run_reference(a, rank)
     if a.workload == "block":
         return run_block(a, rank, world)
+    if a.workload == "q8head":
+        return run_q8head(a, rank, world)
     return run_stack(a, rank, world)
 
 

@@ -143,7 +143,7 @@ int Model::record(int rows, bool with_head, cudaStream_t st) {
   launch_rms_add(x, y, xn, final_norm, rows, H, 1e-6f, st); n++;
   launches_body = n;
   if (with_head) {
-    if (head_q8.w) { launch_q8_linear(head_q8, xn, rows, logits, st); n += (rows + 31) / 32; }
+    if (head_q8.w) { launch_q8_linear(head_q8, xn, rows, logits, device_status_word(), st); n += (rows + 7) / 8; }
     else { launch_lm_head(xn, head, d.vocab, H, rows, logits, head_scratch, st); n += 2; }
     launch_argmax(logits, d.vocab, rows, next, argmax_scratch, st); n += 2;
     launches_full = n;

@@ -307,7 +307,7 @@ static Q8Weight q8_from_c(const ne_q8_weight *w) {
 NE_API int ne_q8_linear(const ne_q8_weight *w, const float *x_dev, int rows, float *y_dev, void *stream) {
   return c_call([&] {
     IJ_CHECK(x_dev && y_dev, "null activation pointer");
-    launch_q8_linear(q8_from_c(w), x_dev, rows, y_dev, (cudaStream_t)stream);
+    launch_q8_linear(q8_from_c(w), x_dev, rows, y_dev, device_status_word(), (cudaStream_t)stream);
   });
 }
 

@@ -16,8 +16,10 @@ struct Q8Weight {
 };
 
 void check_q8_weight(const Q8Weight &w);
-// y[r][o] = sum_i (scale[o][i / group] * q[o][i] + bias[o][i / group]) * x[r][i]   (x, y f32; rows 1..64; one launch, no scratch)
-void launch_q8_linear(const Q8Weight &w, const float *x, int rows, float *y, cudaStream_t st);
+// y[r][o] = sum_i (scale[o][i / group] * q[o][i] + bias[o][i / group]) * x[r][i]   (x, y f32; rows 1..64; one launch per 16 rows, no scratch;
+// groups of 64, 128 or 256)
+// `status`: the device word bounded waits report to (device_status_word())
+void launch_q8_linear(const Q8Weight &w, const float *x, int rows, float *y, int *status, cudaStream_t st);
 // x[r][:] = scale * q + bias of row tokens[r] (ids outside [0, rows) read row 0), optionally rounded to bf16 as the
 // reference's embedding is (kernels/fn_model.metal:14-40)
 void launch_q8_embed(const Q8Weight &w, const int *tokens, int rows, float *x, bool round_bf16, cudaStream_t st);

@@ -52,14 +52,15 @@ NE_API int ne_exl3_linear_multi(const ne_exl3_weight *w, int n, const float *x_d
 NE_API int ne_exl3_linear_prefill(const ne_exl3_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 /* One 8-bit affine Linear y = x @ W^T, W [out][in] = scale * q + bias per group (replaces the reference's q8 Linears:
  * loader models/flash_next/layer.mm:60-76, arithmetic kernels/ne_common.h:31-91, the LM head kernels/fn_model.metal:152-168;
- * MLX layout: weight bytes [out][in] (U32 [out][in/4] in the pack), scales / biases BF16 [out][in/group], group 32..256). */
+ * MLX layout: weight bytes [out][in] (U32 [out][in/4] in the pack), scales / biases BF16 [out][in/group]; ne_q8_linear takes
+ * groups of 64, 128 or 256 and a multiple of 64 inputs, ne_q8_embed any group from 32). */
 typedef struct {
   const void *weight_dev;
   const void *scales_dev;
   const void *biases_dev;
   int in, out, group;
 } ne_q8_weight;
-/* rows 1..64; x f32 [rows][in], y f32 [rows][out]; one kernel per 32 rows, no scratch. The activations enter the tensor
+/* rows 1..64; x f32 [rows][in], y f32 [rows][out]; one kernel per 16 rows, no scratch. The activations enter the tensor
  * core as fp16 hi + lo pairs, so the result agrees with f32 arithmetic to rounding. */
 NE_API int ne_q8_linear(const ne_q8_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 /* Embedding lookup of an 8-bit affine table (reference kernels/fn_model.metal:14-40): x[r] = dequantised row tokens[r],

@@ -31,9 +31,10 @@ def test_q8_head_and_embedding_match_reference_fixture(eng):
     assert np.array_equal(rows, g["embed_rows"])
 
 
-@pytest.mark.parametrize("n_out,n_in,group,rows", [(1000, 2560, 64, 1), (4100, 2560, 128, 8), (520, 2048, 64, 19), (136, 320, 32, 50)])
+@pytest.mark.parametrize("n_out,n_in,group,rows", [(1000, 2560, 64, 1), (4100, 2560, 128, 8), (520, 2048, 64, 19), (136, 320, 64, 50), (264, 5120, 256, 3), (300, 1024, 32, 7), (129, 10240, 64, 12)])
 def test_q8_linear_shapes(eng, n_out, n_in, group, rows):
-    # ragged output counts (not a multiple of 16 / 128), the reference's input widths and group sizes, more than 32 rows
+    # ragged output counts (not a multiple of 16 / 128), the reference's input widths and group sizes, more than 16 rows,
+    # more inputs than one staged chunk
     import torch
     from ijah_b200 import engine as E
     rng = np.random.default_rng(n_out + rows)
