@@ -221,72 +221,137 @@ static void launch_pf_gemm(const PgGemm &g, int *status, cudaStream_t st) {
 // (the routing, sorting, operand and finishing kernels follow)
 
 // =============================================================================================== router
-// logits[n][0 .. E) = x . W^T (bf16 W, fp32 multiply-add), 128 tokens x 128 experts per CTA, 8 x 8 outputs per thread, k in steps of
-// 16 through shared memory (k-major, so every operand read is a conflict-free float4) with the next step's global loads in
-// flight during the multiply. Reference: the router GEMM of the chunked prefill (kernels/prefill/pf_gemm.metal:159-186).
-// The shared expert's gate logit (column E) is a plain dot product in pf_route_kernel.
-constexpr int LG_T = 128, LG_K = 16;
+// logits[n][0 .. E) = x . W^T (bf16 W, f32 x) on tensor cores without giving up f32 accuracy: x is split into three bf16
+// terms (x = hi + mid + lo to 2^-24), each multiplied with the bf16 weights by mma.sync.m16n8k16 (products exact, f32
+// accumulate). 128 tokens x 128 experts per CTA, 8 warps of 32 x 64, k in steps of 32 through double-buffered shared
+// memory (rows padded to 80 bytes: conflict-free ldmatrix). Reference: the router GEMM of the chunked prefill
+// (kernels/prefill/pf_gemm.metal:159-186). The shared expert's gate logit (column E) is a plain dot product in
+// pf_route_kernel.
+constexpr int LG_T = 128, LG_K = 32, LG_LD = LG_K + 8;              // halfs per staged row
+constexpr int LG_PLANE = LG_T * LG_LD, LG_BUF = 4 * LG_PLANE;       // x hi, mid, lo, W
+constexpr int LG_SMEM = 2 * LG_BUF * 2;                             // bytes
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t bf16_rn_bits(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u + 0x7FFFu + ((u >> 16) & 1u)) >> 16;
+}
+// (a, b) -> packed bf16 pairs of the three terms
+__device__ __forceinline__ void split3(float a, float b, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
+  const uint32_t ah = bf16_rn_bits(a), bh = bf16_rn_bits(b);
+  const float a1 = a - __uint_as_float(ah << 16), b1 = b - __uint_as_float(bh << 16);
+  const uint32_t am = bf16_rn_bits(a1), bm = bf16_rn_bits(b1);
+  const float a2 = a1 - __uint_as_float(am << 16), b2 = b1 - __uint_as_float(bm << 16);
+  hi = ah | (bh << 16);
+  mid = am | (bm << 16);
+  lo = bf16_rn_bits(a2) | (bf16_rn_bits(b2) << 16);
+}
+
 __global__ void __launch_bounds__(256) pf_logits_kernel(const PfParams p) {
-  __shared__ __align__(16) float xs[2][LG_K][LG_T], ws[2][LG_K][LG_T];
-  const int tid = threadIdx.x, t0 = blockIdx.x * LG_T, c0 = blockIdx.y * LG_T, H = p.H;
-  const int tx = tid & 15, ty = tid >> 4;  // outputs: tokens {4 ty .. +3, 64 + 4 ty .. +3} x experts {4 tx .. +3, 64 + 4 tx .. +3}
-  // loads: x: thread -> (token tid >> 1, 8 k's of half tid & 1) as two float4; W: thread -> (expert tid >> 1, 8 k's) as one uint4
-  const int lr = tid >> 1, lh = tid & 1;
-  const float *xrow = p.x + (size_t)min(t0 + lr, p.n - 1) * H + lh * 8;
-  const uint16_t *wrow = p.router + (size_t)min(c0 + lr, p.E - 1) * H + lh * 8;
-  float4 xa = *reinterpret_cast<const float4 *>(xrow), xb = *reinterpret_cast<const float4 *>(xrow + 4);
-  uint4 wv = *reinterpret_cast<const uint4 *>(wrow);
-  float acc[8][8];
+  extern __shared__ __align__(16) unsigned char lg_smem[];
+  uint16_t *sm = reinterpret_cast<uint16_t *>(lg_smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, t0 = blockIdx.x * LG_T, c0 = blockIdx.y * LG_T, H = p.H;
+  const int wm = warp >> 1, wn = warp & 1;  // warp tile: tokens 32 wm .. +31, experts 64 wn .. +63
+  // loads. x: thread -> rows (tid >> 3) + 32 j, floats 4 (tid & 7) .. +3; W: rows (tid >> 2) + 64 j, 16-byte chunk tid & 3
+  const int xr = tid >> 3, xc = (tid & 7) * 4, wr = tid >> 2, wc = (tid & 3) * 8;
+  const float *xsrc[4];
+  const uint16_t *wsrc[2];
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int j = 0; j < 4; j++) xsrc[j] = p.x + (size_t)min(t0 + xr + 32 * j, p.n - 1) * H + xc;
 #pragma unroll
-    for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
-  auto stash = [&](int buf) {
-    float (*X)[LG_T] = xs[buf], (*W)[LG_T] = ws[buf];
-    const int kb = lh * 8;
-    X[kb + 0][lr] = xa.x; X[kb + 1][lr] = xa.y; X[kb + 2][lr] = xa.z; X[kb + 3][lr] = xa.w;
-    X[kb + 4][lr] = xb.x; X[kb + 5][lr] = xb.y; X[kb + 6][lr] = xb.z; X[kb + 7][lr] = xb.w;
-    W[kb + 0][lr] = __uint_as_float(wv.x << 16); W[kb + 1][lr] = __uint_as_float(wv.x & 0xFFFF0000u);
-    W[kb + 2][lr] = __uint_as_float(wv.y << 16); W[kb + 3][lr] = __uint_as_float(wv.y & 0xFFFF0000u);
-    W[kb + 4][lr] = __uint_as_float(wv.z << 16); W[kb + 5][lr] = __uint_as_float(wv.z & 0xFFFF0000u);
-    W[kb + 6][lr] = __uint_as_float(wv.w << 16); W[kb + 7][lr] = __uint_as_float(wv.w & 0xFFFF0000u);
+  for (int j = 0; j < 2; j++) wsrc[j] = p.router + (size_t)min(c0 + wr + 64 * j, p.E - 1) * H + wc;
+  float4 xv[4];
+  auto load_x = [&](int ks) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) xv[j] = *reinterpret_cast<const float4 *>(xsrc[j] + ks * LG_K);
   };
-  stash(0);
+  auto load_w = [&](int ks, int buf) {
+    const uint32_t dst = smem_u32(sm + buf * LG_BUF + 3 * LG_PLANE);
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(((wr + 64 * j) * LG_LD + wc) * 2)), "l"(wsrc[j] + ks * LG_K) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto stash_x = [&](int buf) {
+    uint16_t *b = sm + buf * LG_BUF;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      uint32_t h0, m0, l0, h1, m1, l1;
+      split3(xv[j].x, xv[j].y, h0, m0, l0);
+      split3(xv[j].z, xv[j].w, h1, m1, l1);
+      const int o = (xr + 32 * j) * LG_LD + xc;
+      *reinterpret_cast<uint2 *>(b + o) = make_uint2(h0, h1);
+      *reinterpret_cast<uint2 *>(b + LG_PLANE + o) = make_uint2(m0, m1);
+      *reinterpret_cast<uint2 *>(b + 2 * LG_PLANE + o) = make_uint2(l0, l1);
+    }
+  };
+  float acc[2][8][4];
+#pragma unroll
+  for (int i = 0; i < 2; i++)
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+      for (int q = 0; q < 4; q++) acc[i][j][q] = 0.0f;
+  load_x(0);
+  load_w(0, 0);
+  stash_x(0);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
+  // ldmatrix lane offsets (in halfs): A rows (lane & 15), k half (lane >> 4); B rows (lane & 7) + 8 ((lane >> 4) & 1), k half (lane >> 3) & 1
+  const int a_off = (32 * wm + (lane & 15)) * LG_LD + (lane >> 4) * 8;
+  const int b_off = (64 * wn + (lane & 7) + ((lane >> 4) & 1) * 8) * LG_LD + ((lane >> 3) & 1) * 8;
   const int nk = H / LG_K;
   for (int ks = 0; ks < nk; ks++) {
     const int buf = ks & 1;
     if (ks + 1 < nk) {
-      xa = *reinterpret_cast<const float4 *>(xrow + (ks + 1) * LG_K);
-      xb = *reinterpret_cast<const float4 *>(xrow + (ks + 1) * LG_K + 4);
-      wv = *reinterpret_cast<const uint4 *>(wrow + (ks + 1) * LG_K);
+      load_x(ks + 1);
+      load_w(ks + 1, buf ^ 1);  // that buffer was last read one step ago, before the barrier below
     }
+    const uint32_t base = smem_u32(sm + buf * LG_BUF);
 #pragma unroll
-    for (int k = 0; k < LG_K; k++) {
-      const float4 a0 = *reinterpret_cast<const float4 *>(&xs[buf][k][4 * ty]), a1 = *reinterpret_cast<const float4 *>(&xs[buf][k][64 + 4 * ty]);
-      const float4 b0 = *reinterpret_cast<const float4 *>(&ws[buf][k][4 * tx]), b1 = *reinterpret_cast<const float4 *>(&ws[buf][k][64 + 4 * tx]);
-      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    for (int kk = 0; kk < LG_K; kk += 16) {
+      uint32_t bfr[4][4];  // per pair of expert tiles: b0, b1 of tile 2 j, b0, b1 of tile 2 j + 1
 #pragma unroll
-      for (int i = 0; i < 8; i++)
+      for (int j = 0; j < 4; j++) ldmatrix_x4(bfr[j], base + (uint32_t)((3 * LG_PLANE + b_off + j * 16 * LG_LD + kk) * 2));
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] += a[i] * b[j];
+      for (int t = 0; t < 3; t++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+          uint32_t afr[4];
+          ldmatrix_x4(afr, base + (uint32_t)((t * LG_PLANE + a_off + i * 16 * LG_LD + kk) * 2));
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            mma_bf16_16816(acc[i][2 * j], afr, bfr[j][0], bfr[j][1]);
+            mma_bf16_16816(acc[i][2 * j + 1], afr, bfr[j][2], bfr[j][3]);
+          }
+        }
+      }
     }
-    if (ks + 1 < nk) stash(buf ^ 1);  // the other buffer was last read one step ago, before the barrier below
+    if (ks + 1 < nk) {
+      stash_x(buf ^ 1);
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
   }
+  const int g = lane >> 2, q = lane & 3;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const int t = t0 + (i < 4 ? 4 * ty + i : 64 + 4 * ty + i - 4);
-    if (t >= p.n) continue;
+  for (int i = 0; i < 2; i++)
 #pragma unroll
-    for (int jh = 0; jh < 2; jh++) {
-      const int c = c0 + jh * 64 + 4 * tx;
-      float *dst = p.logits + (size_t)t * (p.E + 1) + c;
-      if (c + 3 < p.E) { dst[0] = acc[i][jh * 4]; dst[1] = acc[i][jh * 4 + 1]; dst[2] = acc[i][jh * 4 + 2]; dst[3] = acc[i][jh * 4 + 3]; }
-      else for (int j = 0; j < 4; j++) if (c + j < p.E) dst[j] = acc[i][jh * 4 + j];
+    for (int hh = 0; hh < 2; hh++) {
+      const int t = t0 + 32 * wm + 16 * i + g + 8 * hh;
+      if (t >= p.n) continue;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int c = c0 + 64 * wn + 8 * j + 2 * q;
+        float *dst = p.logits + (size_t)t * (p.E + 1) + c;
+        if (c < p.E) dst[0] = acc[i][j][2 * hh];
+        if (c + 1 < p.E) dst[1] = acc[i][j][2 * hh + 1];
+      }
     }
-  }
 }
 
 // top-k on the logits (ties -> lowest index), weights = softmax over the k selected; one warp per token
@@ -737,7 +802,9 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   const int groups = p.pos_cap / 8;
   IJ_CUDA(cudaMemsetAsync(p.order, 0xFF, (size_t)p.pos_cap * 4, st));
   IJ_CUDA(cudaMemsetAsync(p.seid, 0xFF, (size_t)p.pos_cap * 4, st));
-  pf_logits_kernel<<<dim3((p.n + LG_T - 1) / LG_T, (p.E + LG_T - 1) / LG_T), 256, 0, st>>>(p);
+  IJ_CHECK(p.H % LG_K == 0, "prefill: hidden %d must be a multiple of %d", p.H, LG_K);
+  IJ_CUDA(cudaFuncSetAttribute(pf_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM));
+  pf_logits_kernel<<<dim3((p.n + LG_T - 1) / LG_T, (p.E + LG_T - 1) / LG_T), 256, LG_SMEM, st>>>(p);
   pf_route_kernel<<<(p.n + 7) / 8, 256, 0, st>>>(p);
   IJ_CHECK(p.e0 >= 0 && p.ecount >= 0 && p.e0 + p.ecount <= p.E, "prefill: bad expert slice");
   IJ_CHECK(p.sh_row0 >= 0 && p.sh_rows >= 0 && p.sh_row0 + p.sh_rows <= p.n, "prefill: shared rows [%d, %d) outside [0, %d)", p.sh_row0, p.sh_row0 + p.sh_rows, p.n);
