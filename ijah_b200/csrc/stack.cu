@@ -58,9 +58,10 @@ void launch_rms_add(float *x, const float *add, float *xn, const uint16_t *w_bf1
 
 // =============================================================================================== attention stand-in
 // partial: one CTA per (block of 64 cached positions, KV head). K and V of the block are staged once in shared memory
-// and used for every query vector of the head group (rows x heads / kv_heads of them), 16 at a time:
-//   S = Q K^T (warp w: positions 16 w .. 16 w + 15), block max and sum over the four warps, P = exp(S - max) as fp16,
-//   O = P V (warp w: a quarter of the head dimension).
+// and used for every query vector of the head group (rows x heads / kv_heads of them), 16 at a time; two groups of four
+// warps take alternate tiles of 16 query vectors (each group with its own P buffer, reductions and named barrier):
+//   S = Q K^T (warp w of the group: positions 16 w .. 16 w + 15), block max and sum over the four warps, P = exp(S - max)
+//   as fp16, O = P V (warp w: a quarter of the head dimension).
 // Per (query vector, block) it leaves max, sum and the unnormalised O; the merge kernel combines the blocks.
 constexpr int AT_PB = 64;  // positions per block
 
@@ -73,8 +74,9 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
 
 constexpr int AT_QCAP = 64;  // query vectors staged at a time (fp16, scaled)
 
+constexpr int AT_THREADS = 256;
 template <int HD>
-__global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restrict__ q, const __half *__restrict__ kc, const __half *__restrict__ vc, int rows,
+__global__ void __launch_bounds__(AT_THREADS) attn_partial_kernel(const float *__restrict__ q, const __half *__restrict__ kc, const __half *__restrict__ vc, int rows,
                                                            int heads, int kv_heads, int nsplit, float *__restrict__ part, float *__restrict__ ml) {
   constexpr int LD = HD + 8;          // padded row length in halfs (ldmatrix rows on distinct banks)
   constexpr int LDP = AT_PB + 8;
@@ -82,10 +84,12 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
   __half *Ks = reinterpret_cast<__half *>(at_smem);
   __half *Vs = Ks + AT_PB * LD;
   __half *Qs = Vs + AT_PB * LD;
-  __half *Ps = Qs + AT_QCAP * LD;
-  float *red = reinterpret_cast<float *>(Ps + 16 * LDP);  // [2][4][16]: per-warp max, per-warp sum
+  const int grp = threadIdx.x >> 7;  // warp group: tiles grp, grp + 2, ...
+  __half *Ps = Qs + AT_QCAP * LD + grp * 16 * LDP;
+  float *red = reinterpret_cast<float *>(Qs + AT_QCAP * LD + 2 * 16 * LDP) + grp * 128;  // [2][4][16]: per-warp max, per-warp sum
   const int split = blockIdx.x, kvh = blockIdx.y, G = heads / kv_heads, NQ = rows * G;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qq = lane & 3;
+  const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, g = lane >> 2, qq = lane & 3;
+  auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory"); };
   // K and V of the block: asynchronous 16-byte copies, all in flight at once (static data: before the wait on the
   // preceding kernel, so the copies overlap its tail)
   {
@@ -94,7 +98,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
     const __half *vsrc = vc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
     const uint32_t Kd = smem_u32(Ks), Vd = smem_u32(Vs);
 #pragma unroll 4
-    for (int i = threadIdx.x; i < AT_PB * (HD / 8); i += 128) {
+    for (int i = threadIdx.x; i < AT_PB * (HD / 8); i += AT_THREADS) {
       const int p = i / (HD / 8), c = i % (HD / 8);
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(Kd + (uint32_t)((p * LD + c * 8) * 2)), "l"(ksrc + p * rstride + c * 8) : "memory");
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(Vd + (uint32_t)((p * LD + c * 8) * 2)), "l"(vsrc + p * rstride + c * 8) : "memory");
@@ -108,17 +112,17 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
   for (int qc = 0; qc < NQ; qc += AT_QCAP) {
     __syncthreads();  // the previous chunk's readers of Qs are done
     // the chunk's query vectors: fp32 -> scaled fp16, four independent 16-byte loads per thread per pass
-    for (int i0 = 0; i0 < AT_QCAP * (HD / 4); i0 += 128 * 4) {
+    for (int i0 = 0; i0 < AT_QCAP * (HD / 4); i0 += AT_THREADS * 4) {
       float4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        const int i = i0 + u * 128 + threadIdx.x, j = i / (HD / 4), c = i % (HD / 4), qi = qc + j;
+        const int i = i0 + u * AT_THREADS + threadIdx.x, j = i / (HD / 4), c = i % (HD / 4), qi = qc + j;
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (qi < NQ) v[u] = __ldcg(reinterpret_cast<const float4 *>(q + ((size_t)(qi / G) * heads + kvh * G + qi % G) * HD + c * 4));
       }
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        const int i = i0 + u * 128 + threadIdx.x, j = i / (HD / 4), c = i % (HD / 4);
+        const int i = i0 + u * AT_THREADS + threadIdx.x, j = i / (HD / 4), c = i % (HD / 4);
         __half2 *dst = reinterpret_cast<__half2 *>(Qs + j * LD + c * 4);
         dst[0] = __floats2half2_rn(v[u].x * scale, v[u].y * scale);
         dst[1] = __floats2half2_rn(v[u].z * scale, v[u].w * scale);
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    for (int qt = 0; qt * 16 < min(AT_QCAP, NQ - qc); qt++) {
+    for (int qt = grp; qt * 16 < min(AT_QCAP, NQ - qc); qt += 2) {
       const uint32_t Qa = Qa0 + (uint32_t)(qt * 16 * LD * 2);
       // ---- S = Q K^T for this warp's 16 positions
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -146,9 +150,9 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
       }
-      __syncthreads();  // the previous tile's readers of red and Ps are done
+      group_sync();  // the group's previous tile: its readers of red and Ps are done
       if (qq == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
-      __syncthreads();
+      group_sync();
       float m0 = red[g], m1 = red[g + 8];
 #pragma unroll
       for (int w = 1; w < 4; w++) { m0 = fmaxf(m0, red[w * 16 + g]); m1 = fmaxf(m1, red[w * 16 + g + 8]); }
@@ -169,7 +173,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restri
         l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
       }
       if (qq == 0) { red[64 + warp * 16 + g] = l0; red[64 + warp * 16 + g + 8] = l1; }
-      __syncthreads();
+      group_sync();
       // ---- O = P V for this warp's quarter of the head dimension
       constexpr int NTW = HD / 4 / 8;  // n-tiles per warp
       float o_acc[NTW][4];
@@ -297,9 +301,9 @@ size_t attn_scratch_bytes(int rows, int heads, int hd, int T) {
 template <int HD>
 static void launch_attn_partial(const float *q, const __half *kc, const __half *vc, int rows, int heads, int kv_heads, int nsplit, float *part, float *ml,
                                 cudaStream_t st) {
-  const size_t smem = (size_t)(2 * AT_PB * (HD + 8) + AT_QCAP * (HD + 8) + 16 * (AT_PB + 8)) * 2 + 128 * 4;
+  const size_t smem = (size_t)(2 * AT_PB * (HD + 8) + AT_QCAP * (HD + 8) + 2 * 16 * (AT_PB + 8)) * 2 + 2 * 128 * 4;
   IJ_CUDA(cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  launch_pdl(attn_partial_kernel<HD>, dim3(nsplit, kv_heads), dim3(128), smem, st, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml);
+  launch_pdl(attn_partial_kernel<HD>, dim3(nsplit, kv_heads), dim3(AT_THREADS), smem, st, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml);
 }
 
 void launch_attn_standin(const float *q, const float *knew, const float *vnew, const __half *kc, const __half *vc, int rows, int heads, int kv_heads,

@@ -61,7 +61,8 @@ typedef struct {
   int in, out, group;
 } ne_q8_weight;
 /* rows 1..64; x f32 [rows][in], y f32 [rows][out]; one kernel per 16 rows, no scratch. The activations enter the tensor
- * core as fp16 hi + lo pairs, so the result agrees with f32 arithmetic to rounding. */
+ * core as fp16 hi + lo pairs, so the result agrees with f32 arithmetic to rounding for |x| < 65504 (the fp16 range; normed
+ * activations are far inside it). */
 NE_API int ne_q8_linear(const ne_q8_weight *w, const float *x_dev, int rows, float *y_dev, void *stream);
 /* Embedding lookup of an 8-bit affine table (reference kernels/fn_model.metal:14-40): x[r] = dequantised row tokens[r],
  * rounded to bf16 when round_bf16 != 0 (the reference's embedding is bf16-valued). tokens_dev: int32 [rows]. */
