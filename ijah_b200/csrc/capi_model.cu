@@ -500,6 +500,26 @@ NE_API int ne_fn_model_prefill(ne_fn_model *m, const int *prompt, int n, float *
     if (ms) *ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
   });
 }
+// Greedy verify of one speculative round (reference models/flash_next/mtp_loop.h:5-15): rows = [t1, d_1 .. d_D] (the last
+// emitted token and D drafted ones, R = D + 1 <= max_rows) go through ONE R-row step; row j's greedy token is the model's
+// choice after tokens[j], so the drafts are accepted while tokens[j + 1] equals it. *accepted = a (0..D), out[0 .. a] =
+// the accepted drafts followed by the correction (a < D) or bonus (a = D) token, as the reference emits them. Drafting
+// (the MTP head) and the cache roll-back of rejected rows are the caller's; the attention stand-in keeps no per-token state.
+NE_API int ne_fn_model_verify_greedy(ne_fn_model *m, const int *tokens, int rows, int *accepted, int *out, double *gpu_ms) {
+  return c_call([&] {
+    Model *M = reinterpret_cast<Model *>(m);
+    IJ_CHECK(M != nullptr && tokens != nullptr && accepted != nullptr && out != nullptr, "null argument");
+    IJ_CHECK(rows >= 1 && rows <= M->max_rows, "rows %d outside 1..%d", rows, M->max_rows);
+    std::vector<int> nx(rows);
+    M->step(tokens, rows, 1, nullptr, nx.data(), gpu_ms);
+    check_status_word();
+    int a = 0;
+    while (a < rows - 1 && tokens[a + 1] == nx[a]) a++;
+    for (int j = 0; j < a; j++) out[j] = tokens[j + 1];
+    out[a] = nx[a];
+    *accepted = a;
+  });
+}
 NE_API int ne_fn_model_replay(ne_fn_model *m, int rows, int head, int steps, double *total_ms) {
   return c_call([&] {
     Model *M = reinterpret_cast<Model *>(m);

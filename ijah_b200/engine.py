@@ -144,6 +144,7 @@ SIGNATURES = {
     "ne_fn_model_time": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "ne_fn_model_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "ne_fn_model_prefill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_double)]),
+    "ne_fn_model_verify_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_void_p, C.POINTER(C.c_double)]),
     "ne_fn_model_replay": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "ne_fn_model_desc_of": (C.c_int, [C.c_void_p, C.POINTER(ModelDescC)]),
     "ne_fn_model_set_ep": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -384,6 +385,15 @@ class FnModel:
         self.eng._ok(self.eng.lib.ne_fn_model_prefill(self.ptr, ids.ctypes.data, len(ids), lg.ctypes.data if want_logits else None,
                                                       C.byref(nx), C.byref(ms)), "ne_fn_model_prefill")
         return nx.value, lg, ms.value
+
+    def verify_greedy(self, tokens):
+        """one speculative round: tokens = [last emitted, drafts...]; returns (accepted count, emitted tokens, GPU ms)"""
+        ids = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty(len(ids), np.int32)
+        acc, ms = C.c_int(0), C.c_double(0)
+        self.eng._ok(self.eng.lib.ne_fn_model_verify_greedy(self.ptr, ids.ctypes.data, len(ids), C.byref(acc), out.ctypes.data, C.byref(ms)),
+                     "ne_fn_model_verify_greedy")
+        return acc.value, out[:acc.value + 1].copy(), ms.value
 
     def replay(self, rows, steps, head=True):
         """device time in ms of `steps` replays of the captured step (inputs and results stay on the device)"""

@@ -195,6 +195,11 @@ NE_API ne_fn_model *ne_fn_model_create_rows(ne_pack *pack, int tmax, int max_row
  * CUDA graph for this row count (captured on first use); host -> device copy of the tokens and device -> host copies of the
  * results are part of the call. */
 NE_API int ne_fn_model_step_rows(ne_fn_model *m, const int *tokens_host, int rows, int head, float *logits_host, int *next_host, double *gpu_ms);
+/* Greedy verify of one speculative round (the R = D + 1 row verify of the reference's MTP / DFlash loops,
+ * models/flash_next/mtp_loop.h:5-15): tokens = [t1, d_1 .. d_D] run as ONE step of `rows` rows; drafts are accepted while
+ * the model's greedy choice after tokens[j] equals tokens[j + 1]. *accepted = a, out[0 .. a] = the accepted drafts and the
+ * correction / bonus token (out holds `rows` ints). Drafting and cache roll-back stay with the caller. */
+NE_API int ne_fn_model_verify_greedy(ne_fn_model *m, const int *tokens, int rows, int *accepted, int *out, double *gpu_ms);
 /* `steps` replays of the captured step for `rows` rows back to back on the model's stream, inputs and results staying on the
  * device: total device time between two events in *total_ms. */
 NE_API int ne_fn_model_replay(ne_fn_model *m, int rows, int head, int steps, double *total_ms);

@@ -121,6 +121,21 @@ def test_synthetic_stack_runs_and_is_deterministic(eng):
     nx, lg, ms = a.prefill(prompt)
     _, l5, _ = a.step_rows(prompt[32:37], want_logits=True)  # the last chunk (37 = 16 + 16 + 5)
     assert np.array_equal(lg, l5[4]) and nx == int(l5[4].argmax()) and ms > 0
+    # one speculative round: drafts that are the model's own greedy continuations are all accepted (+ the bonus token),
+    # a wrong draft cuts the run there and is replaced by the model's choice
+    t1 = int(tokens[0])
+    chain = [t1]
+    for _ in range(3):
+        nj, _, _ = a.step_rows(np.array(chain, np.int32))
+        chain.append(int(nj[-1]))
+    # (the stand-in attention has no causal state: a row's output depends on its own token only, so chain[j + 1] is what
+    # the model picks after chain[j] in any batch)
+    acc, emitted, _ = a.verify_greedy(chain)
+    assert acc == 3 and list(emitted[:3]) == chain[1:] and len(emitted) == 4
+    bad = list(chain)
+    bad[2] = (bad[2] + 1) % 1024
+    acc, emitted, _ = a.verify_greedy(bad)
+    assert acc == 1 and list(emitted) == [chain[1], chain[2]]
     assert a.weight_bytes() > 0 and a.last_bytes(16)["total"] > 0
     assert eng.lib.ne_device_wait_status() == 0
     a.free()
