@@ -244,7 +244,6 @@ __global__ void __launch_bounds__(Q8S_THREADS, 1) q8_stream_kernel(const __grid_
   pdl_launch();
   if (warp == Q8S_CWARPS) {
     // ---------------------------------------------------------------- producer
-    if (lane == 0) tma_prefetch_descriptor(&P.map);
     const uint64_t pol = l2_evict_first_policy();
     uint32_t stage = 0, phase = 0;
     int sb = 0;
