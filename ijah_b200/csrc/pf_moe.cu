@@ -568,46 +568,62 @@ __device__ __forceinline__ __half *blocked_lane_ptr(__half *base, int pos, int c
   return base + (((size_t)(pos >> 3) * (in >> 3) + chunk * 16 + (lane >> 1)) << 6) + ((pos & 7) << 3) + ((lane & 1) << 2);
 }
 
-// gate / up operands: xh[pos] = fp16(H128(x[token(pos)] * suh[expert(pos)])), one warp per position (reference
-// kernels/prefill/pf_moe.metal:88-104); padding positions are written as zeros
+// gate / up operands: xh[pos] = fp16(H128(x[token(pos)] * suh[expert(pos)])), one warp per position, eight positions (one
+// row group of the blocked layout) per CTA (reference kernels/prefill/pf_moe.metal:88-104); padding positions are written
+// as zeros. In the blocked layout the eight rows of a group and one 128-input chunk form 2 KB of contiguous memory (16
+// core matrices of 8 rows x 16 bytes), of which a warp (one row) owns every eighth 16 bytes: the CTA therefore collects
+// four chunks of both operands in shared memory (16-byte slots XOR-swizzled by core matrix: conflict-free both ways)
+// and writes them out as whole 512-byte runs per warp instead of 16-byte pieces.
 __global__ void __launch_bounds__(256) pf_prep_kernel(const PfParams p, const int *order) {
+  __shared__ __align__(16) unsigned char tile[2][4][2048];  // [gate | up][chunk of the pass][core matrix 16][row 8][16 bytes]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pos = blockIdx.x * 8 + warp, H = p.H;
-  if (pos >= p.pos_cap) return;
+  const int pos = blockIdx.x * 8 + warp, H = p.H;  // pos_cap is a multiple of 8
   const int slot = pos < p.off[p.E + 1] ? order[pos] : -1;
-  if (slot < 0) {
-    for (int c = 0; c < H / 128; c++) {
-      *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_g, pos, c, lane, H)) = make_uint2(0u, 0u);
-      *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_u, pos, c, lane, H)) = make_uint2(0u, 0u);
-    }
-    return;
-  }
   const bool shared = slot >= p.S;
-  const int t = shared ? slot - p.S : slot / p.topk;
-  const int e = shared ? 0 : p.seid[pos] - p.e0;
+  const int t = slot < 0 ? 0 : shared ? slot - p.S : slot / p.topk;
+  const int e = (slot < 0 || shared) ? 0 : p.seid[pos] - p.e0;
   const __half *sg = shared ? p.sgt.suh : p.gate.suh + (size_t)e * H, *su = shared ? p.sup.suh : p.up.suh + (size_t)e * H;
   const float *xr = p.x + (size_t)t * H;
+  const int j = lane >> 1, hsel = lane & 1;
+  const uint32_t woff = (uint32_t)(j * 128 + ((warp ^ (j & 7)) * 16) + hsel * 8);  // this lane's 8 bytes of its row's share of a chunk
   for (int c0 = 0; c0 < H / 128; c0 += 4) {
     float4 xv[4];
     uint2 gs[4], us[4];
+    if (slot >= 0) {
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const int o = (min(c0 + i, H / 128 - 1)) * 128 + 4 * lane;
-      xv[i] = *reinterpret_cast<const float4 *>(xr + o);
-      gs[i] = *reinterpret_cast<const uint2 *>(sg + o);
-      us[i] = *reinterpret_cast<const uint2 *>(su + o);
+      for (int i = 0; i < 4; i++) {
+        const int o = (min(c0 + i, H / 128 - 1)) * 128 + 4 * lane;
+        xv[i] = *reinterpret_cast<const float4 *>(xr + o);
+        gs[i] = *reinterpret_cast<const uint2 *>(sg + o);
+        us[i] = *reinterpret_cast<const uint2 *>(su + o);
+      }
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      if (c0 + i < H / 128) {
+      uint2 go = make_uint2(0u, 0u), uo = make_uint2(0u, 0u);
+      if (slot >= 0 && c0 + i < H / 128) {  // uniform over the warp
         const float4 g4 = mul4(xv[i], gs[i]), u4 = mul4(xv[i], us[i]);
         float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
         fwht128_contig(g, lane, PF_HS);
         fwht128_contig(u, lane, PF_HS);
-        *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_g, pos, c0 + i, lane, H)) = pack4(g);
-        *reinterpret_cast<uint2 *>(blocked_lane_ptr(p.xh_u, pos, c0 + i, lane, H)) = pack4(u);
+        go = pack4(g);
+        uo = pack4(u);
+      }
+      *reinterpret_cast<uint2 *>(&tile[0][i][woff]) = go;
+      *reinterpret_cast<uint2 *>(&tile[1][i][woff]) = uo;
+    }
+    __syncthreads();
+    // 8 blocks of 2 KB (operand, chunk) = 1024 pieces of 16 bytes, four per thread; consecutive threads, consecutive bytes
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int idx = threadIdx.x + 256 * k, blk = idx >> 7, jj = (idx >> 3) & 15, r = idx & 7, op = blk >> 2, ci = blk & 3;
+      if (c0 + ci < H / 128) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(&tile[op][ci][jj * 128 + ((r ^ (jj & 7)) * 16)]);
+        __half *dst = (op ? p.xh_u : p.xh_g) + (((size_t)blockIdx.x * (H >> 3) + (c0 + ci) * 16 + jj) << 6) + (r << 3);
+        *reinterpret_cast<uint4 *>(dst) = v;
       }
     }
+    __syncthreads();
   }
 }
 
