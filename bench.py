@@ -365,10 +365,19 @@ def run_stack(a, rank, world):
     k_sus = max(a.steps, int(2000.0 / max(ms / a.steps, 1e-3)) + 1) if a.sustain else 0
     ms_sus = model.replay(rows, k_sus) if k_sus else None
     barrier()
+    # ---- strong scaling: the SAME total number of rows as one GPU's step (rows), split over the N ranks
+    ms_strong, rs = None, max(1, rows // N)
+    if N > 1 and a.extras and rs * N == rows:
+        model.step_rows(tokens[:rs])
+        barrier()
+        ms_strong = model.replay(rs, a.steps)
+        barrier()
+        model.step_rows(tokens)  # the byte accounting below reads the last step's routing: make that the headline step again
+        barrier()
     if N > 1:
-        tt = torch.tensor([ms, e2e_s, ms_sus or 0.0], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms, e2e_s, ms_sus or 0.0, ms_strong or 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_s, ms_sus = float(tt[0]), float(tt[1]), float(tt[2]) or None
+        ms, e2e_s, ms_sus, ms_strong = float(tt[0]), float(tt[1]), float(tt[2]) or None, float(tt[3]) or None
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / a.steps
     value = N * rows / (ms_per_step * 1e-3)
@@ -380,6 +389,10 @@ def run_stack(a, rank, world):
     extra = {"weights_gb_resident": wbytes / 1e9, "distinct_experts_per_layer": lb["distinct_experts_mean"],
              "step": {"bytes": lb["total"], "gbs": lb["total"] / (ms_per_step * 1e-3) / 1e9, "frac_of_hbm": lb["total"] / (ms_per_step * 1e-3) / 1e9 / peak},
              "graph": True, "exchange": "nvlink peer memory (own kernels)" if N > 1 else None}
+    if ms_strong:
+        extra["strong_scaling"] = {"total_rows": rs * N, "rows_per_rank": rs, "ms_per_step": ms_strong / a.steps,
+                                   "tok_per_s": rs * N * a.steps / (ms_strong * 1e-3),
+                                   "note": f"the same {rs * N} rows as the N = 1 line's step, split over {N} ranks (its value is the reference point)"}
     if ms_sus:
         extra["sustained"] = {"steps": k_sus, "seconds": ms_sus * 1e-3, "tok_per_s": N * rows * k_sus / (ms_sus * 1e-3)}
         if clocks and clocks.get("sm_mhz"):
