@@ -167,9 +167,16 @@ static Layer *make_layer(ne_pack *cp, int layer, int rows) {
     IJ_CHECK(ks == k2, "shared expert down uses a different K");
     IJ_CHECK(d.sh_gate.in == d.hidden && d.sh_gate.out == d.inter && d.sh_down.in == d.inter && d.sh_down.out == d.hidden, "shared expert shape mismatch");
     d.k_shared = ks;
-  } else {
-    IJ_CHECK(!pk->info(pre + "shared_expert.gate_proj.weight"),
-             "layer %d: the shared expert is 8-bit affine; only EXL3-coded shared experts are supported", layer);
+  } else if (pk->info(pre + "shared_expert_gate.weight") && pk->info(pre + "shared_expert.gate_proj.scales")) {
+    // the shared expert as three 8-bit affine Linears (packs whose trunk was not converted to EXL3)
+    d.shared_gate_w_dev = pk->device(pre + "shared_expert_gate.weight");
+    auto q8c = [&](const std::string &name) {
+      const Q8Weight q = pack_q8(*pk, pre + "shared_expert." + name);
+      return ne_q8_weight{q.w, q.scales, q.biases, q.in, q.rows, q.group};
+    };
+    d.sh_gate_q8 = q8c("gate_proj");
+    d.sh_up_q8 = q8c("up_proj");
+    d.sh_down_q8 = q8c("down_proj");
   }
   L->H = d.hidden; L->I = d.inter; L->E = d.experts; L->k = d.top_k;
   L->moe = std::make_unique<Moe>(d, rows);

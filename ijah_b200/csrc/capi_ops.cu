@@ -25,6 +25,12 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   IJ_CHECK(d.router_dev != nullptr, "null router weights");
   IJ_CHECK(d.expert_count == 0 || (d.gate.trellis_dev && d.up.trellis_dev && d.down.trellis_dev), "null expert weights");
   has_shared = d.shared_gate_w_dev != nullptr && d.sh_gate.trellis_dev != nullptr;
+  shared_q8 = d.shared_gate_w_dev != nullptr && !has_shared && d.sh_gate_q8.weight_dev != nullptr;
+  if (shared_q8) {
+    IJ_CHECK(d.sh_up_q8.weight_dev && d.sh_down_q8.weight_dev, "null 8-bit shared-expert weights");
+    IJ_CHECK(d.sh_gate_q8.in == d.hidden && d.sh_gate_q8.out == d.inter && d.sh_up_q8.in == d.hidden && d.sh_up_q8.out == d.inter &&
+                 d.sh_down_q8.in == d.inter && d.sh_down_q8.out == d.hidden, "8-bit shared expert shape mismatch");
+  }
   // the router reads its rows (and the shared gate) with 16-byte loads; the trellis stacks are checked where their tensor
   // maps are made
   IJ_CHECK(((uintptr_t)d.router_dev & 15) == 0 && ((uintptr_t)d.shared_gate_w_dev & 15) == 0, "router / shared-gate weights must be 16-byte aligned");
@@ -48,6 +54,7 @@ Moe::Moe(const ne_moe_desc &d, int max_rows_) : desc(d), max_rows(max_rows_) {
   xh_d = (__half *)al(P * I * 2 * A_HALFS_PER_INPUT);
   xh_sd = (__half *)al(R * I * 2 * A_HALFS_PER_INPUT);
   gush = (float *)al(R * 2 * I * 4);
+  if (shared_q8) { q8_g = (float *)al(R * I * 4); q8_u = (float *)al(R * I * 4); q8_act = (float *)al(R * I * 4); }
   sho = (float *)al(R * H * 4);
   counter = (unsigned *)al(16);
   x_stage = (float *)al(R * H * 4);
@@ -74,6 +81,7 @@ Moe::~Moe() {
 
 // Prefill: n tokens at once through the sorted / grouped path (pf_moe.cu). Scratch grows with the largest n seen.
 void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st) {
+  IJ_CHECK(!shared_q8, "an 8-bit affine shared expert runs in the decode-width single-GPU calls only (ne_moe_forward, ne_moe_stage)");
   IJ_CHECK(n >= 1 && n <= 65535, "prefill: %d tokens outside 1..65535", n);
   IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= n, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, n);
   const size_t H = desc.hidden, I = desc.inter, E = desc.experts, k = desc.top_k;
@@ -129,7 +137,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   p.H = desc.hidden; p.I = desc.inter; p.E = desc.experts; p.topk = desc.top_k;
   p.Kx = desc.k_expert; p.Ks = desc.k_shared;
   p.e0 = desc.expert_first; p.ecount = desc.expert_count;
-  p.rows = rows; p.P = rows * desc.top_k; p.has_shared = has_shared ? 1 : 0;
+  p.rows = rows; p.P = rows * desc.top_k; p.has_shared = has_shared ? 1 : 0; p.shared_pre = shared_q8 ? 1 : 0;
   p.router = (const uint16_t *)desc.router_dev;
   p.sgate = (const uint16_t *)desc.shared_gate_w_dev;
   auto stack = [](const ne_exl3_stack &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
@@ -162,7 +170,9 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
   switch (stage_no) {
     case 7: launch_moe_router(p, true, st); break;
     case 8: launch_moe_prep(p, false, st); launch_moe_gateup(p, maps, s, true, status, st); break;
-    case 9: launch_moe_mid(p, st); launch_moe_down(p, maps, s, status, st); launch_moe_combine(p, false, st); break;
+    case 9:
+      if (shared_q8) shared_q8_run(x, rows, st);
+      launch_moe_mid(p, st); launch_moe_down(p, maps, s, status, st); launch_moe_combine(p, false, st); break;
     // single kernels of stages 8 and 9 (for per-kernel timing; each needs the state the kernels before it leave)
     case 80: launch_moe_prep(p, false, st); break;
     case 81: launch_moe_gateup(p, maps, s, true, status, st); break;
@@ -174,9 +184,27 @@ void Moe::stage(int stage_no, const float *x, int rows, float *y, cudaStream_t s
   last_rows = rows;
 }
 
+static Q8Weight q8_of(const ne_q8_weight &w) {
+  Q8Weight q;
+  q.w = static_cast<const uint8_t *>(w.weight_dev);
+  q.scales = static_cast<const uint16_t *>(w.scales_dev);
+  q.biases = static_cast<const uint16_t *>(w.biases_dev);
+  q.rows = w.out; q.in = w.in; q.group = w.group;
+  return q;
+}
+
+// the 8-bit affine shared expert: four launches that depend on x only (they precede the router in the chain)
+void Moe::shared_q8_run(const float *x, int rows, cudaStream_t st) {
+  launch_q8_linear(q8_of(desc.sh_gate_q8), x, rows, q8_g, status, st);
+  launch_q8_linear(q8_of(desc.sh_up_q8), x, rows, q8_u, status, st);
+  launch_swiglu_rows(q8_g, q8_u, rows, desc.inter, gush, q8_act, st);
+  launch_q8_linear(q8_of(desc.sh_down_q8), q8_act, rows, sho, status, st);
+}
+
 void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
   const MoeParams p = params(x, rows, y);
   const MoeSplits &s = splits(rows);
+  if (shared_q8) shared_q8_run(x, rows, st);
   launch_moe_router(p, true, st);  // the finisher also builds the plan: final before the gate/up kernel can start
   launch_moe_prep(p, false, st);
   launch_moe_gateup(p, maps, s, true, status, st);
@@ -189,6 +217,7 @@ void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
 // Expert parallel: all ranks' rows come in; routing runs on all of them (replicated), the plan keeps only this object's
 // experts, and the shared expert is added for the caller's own rows only. y is this rank's summand of the block output.
 void Moe::forward_ep(const float *x, int rows, int own_row0, int own_rows, float *y, cudaStream_t st) {
+  IJ_CHECK(!shared_q8, "an 8-bit affine shared expert runs in the decode-width single-GPU calls only (ne_moe_forward, ne_moe_stage)");
   MoeParams p = params(x, rows, y);
   IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= rows, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, rows);
   p.sh_row0 = own_row0;
@@ -216,6 +245,7 @@ void Moe::route_rows(const float *x, int rows, uint32_t *route_out, int ld_route
 // gate logits of the own rows are the ones route_rows left in the object.
 void Moe::forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all, int ld_route, int rows, int own_row0, int own_rows, float *y,
                             cudaStream_t st) {
+  IJ_CHECK(!shared_q8, "an 8-bit affine shared expert runs in the decode-width single-GPU calls only (ne_moe_forward, ne_moe_stage)");
   MoeParams p = params(x, rows, y);
   if (ld_x > 0) p.ldx = ld_x;
   if (ld_route > 0) p.ldr = ld_route;
@@ -236,6 +266,7 @@ void Moe::forward_ep_routed(const float *x, int ld_x, const uint32_t *route_all,
 // The whole expert-parallel block over peer memory: route the own rows, exchange packed rows, compute this rank's experts
 // for all rows with the combine writing into the owners' memory, sum the partial rows that arrived here.
 void Moe::forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own, cudaStream_t st) {
+  IJ_CHECK(!shared_q8, "an 8-bit affine shared expert runs in the decode-width single-GPU calls only (ne_moe_forward, ne_moe_stage)");
   const int H = desc.hidden, k = desc.top_k, world = c.host.world, all = rows * world;
   IJ_CHECK(c.connected, "expert-parallel context is not connected");
   IJ_CHECK(c.host.H == H && c.top_k == k, "expert-parallel context was made for other dims");
@@ -261,6 +292,7 @@ void Moe::forward_ep_fused(EpCtx &c, const float *x_own, int rows, float *y_own,
 }
 
 void Moe::forward_routed(const float *x, const uint32_t *route_in, int rows, float *y, cudaStream_t st) {
+  IJ_CHECK(!shared_q8, "an 8-bit affine shared expert runs in the decode-width single-GPU calls only (ne_moe_forward, ne_moe_stage)");
   MoeParams p = params(x, rows, y);
   IJ_CUDA(cudaMemcpyAsync(route, route_in, (size_t)rows * 2 * desc.top_k * 4, cudaMemcpyDeviceToDevice, st));
   p.has_shared = 0;

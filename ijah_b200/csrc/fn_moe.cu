@@ -602,9 +602,14 @@ __global__ void __launch_bounds__(32 * (CB_MAXK + 1)) moe_combine_kernel(const M
       for (int j = 0; j < 4; j++) vals[warp][lane + 32 * j] = v[j] * sc[j] * wk;
     }
   } else if (warp == k) {
-    const bool on = !routed_only && p.has_shared && r >= p.sh_row0 && r < p.sh_row0 + p.sh_rows;
+    const bool on = !routed_only && (p.has_shared || p.shared_pre) && r >= p.sh_row0 && r < p.sh_row0 + p.sh_rows;
     if (lane == 0) used[k] = on ? 1 : 0;
-    if (on) {
+    if (on && p.shared_pre) {  // finished by other kernels (8-bit affine shared expert): only the sigmoid gate is applied here
+      const float lg = p.logits[(size_t)(r - p.lg_row0) * (p.E + 1) + p.E];
+      const float sg = 1.0f / (1.0f + expf(-lg));
+#pragma unroll
+      for (int j = 0; j < 4; j++) vals[k][lane + 32 * j] = sg * p.sho[(size_t)r * H + blk * 128 + lane + 32 * j];
+    } else if (on) {
       const float *const src[1] = {p.raw_sd + (size_t)r * H + blk * 128};
       float part[1][4], v[4];
       sum_splits<1>(src, (size_t)p.rows * H, p.S_d, lane, part);
@@ -707,6 +712,23 @@ void launch_moe_down(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s
   pr.IT = p.I / 16; pr.OT = p.H / 16; pr.NG = (pr.OT + SG_WARPS - 1) / SG_WARPS;
   pr.S = s.S_d; pr.kc = s.kc_d;
   launch_stream(pr, s.MT, s.lay_d, s.grid, status, st);
+}
+
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const float *__restrict__ g, const float *__restrict__ u, int rows, int I,
+                                                          float *__restrict__ gush, float *__restrict__ act) {
+  pdl_launch();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * I; i += gridDim.x * blockDim.x) {
+    const int r = i / I, c = i - r * I;
+    const float gv = g[i], uv = u[i];
+    gush[(size_t)r * 2 * I + c] = gv;
+    gush[(size_t)r * 2 * I + I + c] = uv;
+    act[i] = gv / (1.0f + expf(-gv)) * uv;
+  }
+}
+
+void launch_swiglu_rows(const float *g, const float *u, int rows, int I, float *gush, float *act, cudaStream_t st) {
+  launch_pdl(swiglu_rows_kernel, dim3((rows * I + 255) / 256), dim3(256), 0, st, g, u, rows, I, gush, act);
 }
 
 void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st) {

@@ -20,6 +20,7 @@ struct MoeParams {
   int rows;           // live rows of this run
   int P;              // rows * topk
   int has_shared;
+  int shared_pre;     // the shared expert's output is already in `sho` (8-bit affine shared expert: computed by other kernels)
   // weights
   const uint16_t *router;  // bf16 [E][H]
   const uint16_t *sgate;   // bf16 [H]
@@ -97,5 +98,7 @@ void launch_moe_mid(const MoeParams &p, cudaStream_t st);    // SwiGLU + down op
 void launch_moe_gateup(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s, bool plan_final, int *status, cudaStream_t st);
 void launch_moe_down(const MoeParams &p, const MoeMaps &maps, const MoeSplits &s, int *status, cudaStream_t st);
 void launch_moe_combine(const MoeParams &p, bool routed_only, cudaStream_t st);
+// gush[r] = (g | u), act[r] = silu(g) * u for the 8-bit shared expert's gate / up outputs g, u f32 [rows][I]
+void launch_swiglu_rows(const float *g, const float *u, int rows, int I, float *gush, float *act, cudaStream_t st);
 
 }  // namespace ijah

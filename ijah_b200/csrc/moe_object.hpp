@@ -15,6 +15,9 @@ struct Moe {
   ne_moe_desc desc;
   int max_rows;
   bool has_shared = false;
+  bool shared_q8 = false;  // the shared expert is three 8-bit affine Linears (decode-width single-GPU calls only)
+  float *q8_g = nullptr, *q8_u = nullptr, *q8_act = nullptr;
+  void shared_q8_run(const float *x, int rows, cudaStream_t st);  // sho = down(silu(gate x) * up x); gush = gate | up
   int last_rows = 1;
   std::vector<void *> owned;
   float *logits = nullptr, *raw_gu = nullptr, *raw_sgu = nullptr, *raw_d = nullptr, *raw_sd = nullptr, *gush = nullptr, *sho = nullptr;

@@ -58,7 +58,8 @@ class MoeDescC(C.Structure):
     _fields_ = [("hidden", C.c_int), ("inter", C.c_int), ("experts", C.c_int), ("top_k", C.c_int),
                 ("k_expert", C.c_int), ("k_shared", C.c_int), ("expert_first", C.c_int), ("expert_count", C.c_int),
                 ("router", C.c_void_p), ("shared_gate_w", C.c_void_p), ("gate", Exl3StackC), ("up", Exl3StackC),
-                ("down", Exl3StackC), ("sh_gate", Exl3WeightC), ("sh_up", Exl3WeightC), ("sh_down", Exl3WeightC)]
+                ("down", Exl3StackC), ("sh_gate", Exl3WeightC), ("sh_up", Exl3WeightC), ("sh_down", Exl3WeightC),
+                ("sh_gate_q8", Q8WeightC), ("sh_up_q8", Q8WeightC), ("sh_down_q8", Q8WeightC)]
 
 
 class ModelDescC(C.Structure):

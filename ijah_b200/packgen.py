@@ -38,6 +38,19 @@ def exl3_linear(rng, n_in, n_out, K, lead=()):
     return tr, suh.astype(np.float16), svh.astype(np.float16)
 
 
+def shared_expert_q8(rng, layer=0, hidden=2048, inter=768, group=64):
+    """name -> (dtype, array): the shared expert of one layer as three 8-bit affine Linears + its bf16 sigmoid gate (the
+    format of packs whose trunk was not converted to EXL3)"""
+    pre = f"{PFX}{layer}.mlp."
+    t = {pre + "shared_expert_gate.weight": ("BF16", f32_to_bf16_bits(rng.standard_normal((1, hidden)) * 0.02))}
+    for proj, (n_out, n_in) in (("gate", (inter, hidden)), ("up", (inter, hidden)), ("down", (hidden, inter))):
+        w, sc, bi = q8_linear(rng, n_out, n_in, group, std=1.0 / np.sqrt(n_in))
+        t[f"{pre}shared_expert.{proj}_proj.weight"] = ("U32", w)
+        t[f"{pre}shared_expert.{proj}_proj.scales"] = ("BF16", sc)
+        t[f"{pre}shared_expert.{proj}_proj.biases"] = ("BF16", bi)
+    return t
+
+
 def moe_layer(rng, layer=0, hidden=2048, inter=768, experts=512, k_expert=5, k_shared=6):
     """name -> (safetensors dtype, array) for the MoE block of one layer"""
     pre = f"{PFX}{layer}.mlp."

@@ -103,6 +103,10 @@ typedef struct {
   const void *shared_gate_w_dev;   /* BF16 [hidden]: the sigmoid gate of the shared expert; NULL = no shared expert */
   ne_exl3_stack gate, up, down;    /* routed experts, local slice */
   ne_exl3_weight sh_gate, sh_up, sh_down;
+  /* the shared expert as three 8-bit affine Linears instead (packs whose trunk was not converted to EXL3; reference loader
+   * models/flash_next/layer.mm:60-76): used when sh_gate.trellis_dev is NULL and sh_gate_q8.weight_dev is not. Decode-width
+   * single-GPU calls only (ne_moe_forward, ne_moe_stage); the prefill and expert-parallel entry points refuse such an object. */
+  ne_q8_weight sh_gate_q8, sh_up_q8, sh_down_q8;
 } ne_moe_desc;
 
 typedef struct ne_moe ne_moe;

@@ -258,6 +258,16 @@ def q8_embed(ids, wq_u32, scales_bf16, biases_bf16):
     return bf16_round(affine_dequant(np.asarray(wq_u32)[ids], np.asarray(scales_bf16)[ids], np.asarray(biases_bf16)[ids]))
 
 
+def shared_expert_q8(x, gate, up, down, sgate_w):
+    """the shared expert with 8-bit affine projections (reference tools/opref.py:438-446 with bf=False; each of gate, up,
+    down = (weight u32, scales, biases)): (gate_proj, up_proj, out, sigmoid scale [rows, 1])"""
+    x = np.asarray(x, np.float32)
+    g = q8_linear(x, *gate)
+    u = q8_linear(x, *up)
+    out = q8_linear(silu(g) * u, *down)
+    return g, u, out, sigmoid(linear(x, sgate_w)).reshape(-1, 1)
+
+
 def hc_read(h, norm_w, inject_w, down, up, streams=4, eps=1e-6):
     """Hyper-connection read in f32 (reference tools/opref.py:221-236 with bf=False; models/flash_next/layer.mm:524-531):
     h [rows, streams*H]; norm_w f32 [streams*H]; inject_w f32 [streams, streams*H]; down f32 [LR, streams*H]; up f32

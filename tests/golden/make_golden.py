@@ -64,6 +64,11 @@ def q8_tensors():
     return t
 
 
+def shared_q8_tensors():
+    """an 8-bit affine shared expert (layer 3 of the scratch pack: no EXL3 shared expert there to shadow it)"""
+    return packgen.shared_expert_q8(np.random.default_rng(SEED + 6), layer=3, hidden=DIMS["hidden"], inter=DIMS["inter"], group=64)
+
+
 def q8_inputs():
     rng = np.random.default_rng(SEED + 5)
     return rng.standard_normal((6, Q8["hidden"])).astype(np.float32), rng.integers(0, Q8["vocab"], 9).astype(np.int32)
@@ -98,6 +103,7 @@ def main():
         hct = hc_tensors()
         tens.update(hct)
         q8t = q8_tensors()
+        q8t.update(shared_q8_tensors())
         tens.update(q8t)
         pack = packgen.write_pack(tmp / "pack", tens, {"num_experts_per_tok": TOPK}, shards=3, misalign=2)
         os.environ["IJAH_REF_DIR"] = str(tmp / "ref")
@@ -124,6 +130,9 @@ def main():
             q8 = dict(seed=np.int64(SEED), digest=np.array(tensors_digest(q8t)), x=x, ids=ids)
             q8["head_y"] = np.asarray(O.linear_big(x, P, "language_model.lm_head", bf=False), np.float32)
             q8["embed_rows"] = np.asarray(P.linear_rows("language_model.model.embed_tokens", ids), np.float32)
+            sh = O.shared_expert(x, P, "language_model.model.layers.3.mlp", bf=False)  # x: [6, 256] = the small pack's hidden size
+            for k, v in sh.items():
+                q8["sh8_" + k] = np.asarray(v, np.float32)
             np.savez_compressed(HERE / "q8_small.npz", **q8)
             print("wrote", HERE / "q8_small.npz", {k: np.shape(v) for k, v in q8.items()})
             if a.which == "q8":

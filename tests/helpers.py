@@ -38,6 +38,7 @@ def q8_small():
     """(8-bit affine LM head + embedding tensors, their golden file) with the digest verified"""
     g = np.load(GOLD / "q8_small.npz")
     t = make_golden.q8_tensors()
+    t.update(make_golden.shared_q8_tensors())
     assert make_golden.tensors_digest(t) == str(g["digest"]), "numpy random stream differs from the one that made the golden file"
     return t, g
 

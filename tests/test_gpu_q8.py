@@ -5,7 +5,8 @@ import pytest
 
 from ijah_b200 import packgen
 from oracle import opref_port as O
-from tests.helpers import q8_parts, q8_small, rel_max
+from oracle import c_oracle as CO
+from tests.helpers import PFX, q8_parts, q8_small, rel_max, small_pack
 
 pytestmark = pytest.mark.gpu
 
@@ -60,3 +61,35 @@ def test_q8_linear_by_name_and_refusals(eng):
     assert rel_max(y, x @ O.affine_dequant(w, sc, bi).T) < 1e-5
     with pytest.raises(E.EngineError, match="group"):
         eng.run_kernel("q8_linear", bufs + [yb, np.array([512, 256, 48, 3], np.uint32)])
+
+
+def test_layer_with_q8_shared_expert(eng, tmp_path):
+    # a layer whose routed experts are EXL3 and whose shared expert is 8-bit affine (a pack whose trunk was not converted):
+    # the shared expert against the fixture of the reference's own shared_expert(), the block against routed + gate * shared
+    t, g = small_pack()
+    qt, qg = q8_small()
+    k = int(g["topk"])
+    pack = {n: v for n, v in t.items() if ".mlp.shared_expert" not in n}
+    for n, v in qt.items():
+        if ".layers.3.mlp." in n:
+            pack[n.replace(".layers.3.", ".layers.0.")] = v
+    packgen.write_pack(tmp_path / "pack", pack, {"num_experts_per_tok": k}, shards=3, misalign=2)
+    p = eng.pack_open(tmp_path / "pack")
+    x = qg["x"]
+    rows = x.shape[0]
+    L = eng.fn_layer(p, 0, rows=rows)
+    L.write("mlp_in", x)
+    L.run_stage(5)
+    y = L.read("mlp_out").reshape(rows, -1)
+    sgu = L.read("shared_gu").reshape(rows, 2, -1)
+    assert rel_max(sgu[:, 0], qg["sh8_shared_gate_proj"]) < 1e-5 and rel_max(sgu[:, 1], qg["sh8_shared_up_proj"]) < 1e-5
+    assert rel_max(L.read("shared_down").reshape(rows, -1), qg["sh8_shared_out"]) < 1e-5
+    routed = CO.moe_block_emul({n: v for n, v in t.items() if ".mlp.shared_expert" not in n}, x, top_k=k)
+    want = routed["routed"] + qg["sh8_shared_scale"] * qg["sh8_shared_out"]
+    assert rel_max(y, want) < 2e-4
+    y1 = y.copy()
+    for s in (7, 8, 9):
+        L.run_dispatch(s)
+    assert np.array_equal(L.read("mlp_out").reshape(rows, -1), y1)
+    L.free()
+    p.close()

@@ -85,3 +85,13 @@ def test_q8_linear_and_embedding_match_reference():
     t, g = q8_small()
     assert rel_max(O.q8_linear(g["x"], *q8_parts(t, "language_model.lm_head")), g["head_y"]) < 2e-6
     assert np.array_equal(O.q8_embed(g["ids"], *q8_parts(t, "language_model.model.embed_tokens")), g["embed_rows"])
+
+
+def test_q8_shared_expert_matches_reference():
+    t, g = q8_small()
+    pre = "language_model.model.layers.3.mlp."
+    gate, up, down = (q8_parts(t, pre + f"shared_expert.{p}_proj") for p in ("gate", "up", "down"))
+    gp, upj, out, scale = O.shared_expert_q8(g["x"], gate, up, down, O.bf16_bits_to_f32(t[pre + "shared_expert_gate.weight"][1]))
+    assert rel_max(gp, g["sh8_shared_gate_proj"]) < 2e-6 and rel_max(upj, g["sh8_shared_up_proj"]) < 2e-6
+    assert rel_max(out, g["sh8_shared_out"]) < 5e-6
+    assert rel_max(scale, g["sh8_shared_scale"]) < 2e-6
