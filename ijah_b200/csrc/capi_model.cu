@@ -25,6 +25,7 @@ namespace ijah {
 
 struct ModelLayer {
   ne_exl3_weight q{}, k{}, v{}, o{};
+  Q8Weight q8[4];  // q, k, v, o as 8-bit affine Linears instead (packs whose trunk was not converted to EXL3); used when q8[0].w is set
   ne_moe_desc md{};
   std::unique_ptr<Moe> moe;
   const uint16_t *norm1 = nullptr, *norm2 = nullptr;  // bf16 [H] or null (no learned scale)
@@ -100,6 +101,7 @@ void Model::finish_setup() {
   size_t lin = 0;
   for (int r = 1; r <= max_rows; r++) {  // the largest scratch any row count needs (the launch plans differ by row count)
     for (const ModelLayer &L : layers) {
+      if (L.q8[0].w) continue;  // the 8-bit affine kernels need no scratch
       const int outs[3] = {L.q.out, L.k.out, L.v.out}, Ks[3] = {L.q.K, L.k.K, L.v.K};
       lin = std::max(lin, plan_linear_multi(3, L.q.in, outs, Ks, r).scratch_bytes());
       lin = std::max(lin, plan_linear(L.o.in, L.o.out, L.o.K, r).scratch_bytes());
@@ -125,7 +127,12 @@ int Model::record(int rows, bool with_head, cudaStream_t st) {
   for (size_t l = 0; l < layers.size(); l++) {
     ModelLayer &L = layers[l];
     launch_rms_add(x, l == 0 ? nullptr : y, xn, L.norm1, rows, H, 1e-6f, st); n++;
-    {  // q, k, v in one launch chain
+    if (L.q8[0].w) {  // 8-bit affine projections: one stream kernel each
+      launch_q8_linear(L.q8[0], xn, rows, q, status, st);
+      launch_q8_linear(L.q8[1], xn, rows, k, status, st);
+      launch_q8_linear(L.q8[2], xn, rows, v, status, st);
+      for (int i = 0; i < 3; i++) n += q8_linear_launches(L.q8[i], rows);
+    } else {  // q, k, v in one launch chain
       const int outs[3] = {L.q.out, L.k.out, L.v.out}, Ks[3] = {L.q.K, L.k.K, L.v.K};
       const MultiLinearPlan p = plan_linear_multi(3, L.q.in, outs, Ks, rows);
       MultiLinearArgs a{};
@@ -135,15 +142,16 @@ int Model::record(int rows, bool with_head, cudaStream_t st) {
       launch_linear_multi(p, a, xn, lin_scratch, status, st); n += 3;
     }
     launch_attn_standin(q, k, v, L.kc, L.vc, rows, d.heads, d.kv_heads, d.head_dim, d.kv_positions, att, attn_scratch, st); n += 2;
-    launch_linear(plan_linear(L.o.in, L.o.out, L.o.K, rows), L.o.trellis_dev, L.o.suh_dev, L.o.svh_dev, att, o, lin_scratch, status, st); n += 3;
+    if (L.q8[0].w) { launch_q8_linear(L.q8[3], att, rows, o, status, st); n += q8_linear_launches(L.q8[3], rows); }
+    else { launch_linear(plan_linear(L.o.in, L.o.out, L.o.K, rows), L.o.trellis_dev, L.o.suh_dev, L.o.svh_dev, att, o, lin_scratch, status, st); n += 3; }
     launch_rms_add(x, o, xn, L.norm2, rows, H, 1e-6f, st); n++;
     if (ep) { L.moe->forward_ep_fused(*ep, xn, rows, y, st); n += 8; }
-    else { L.moe->forward(xn, rows, y, st); n += 6; }
+    else { L.moe->forward(xn, rows, y, st); n += 6 + L.moe->shared_q8_launches(rows); }
   }
   launch_rms_add(x, y, xn, final_norm, rows, H, 1e-6f, st); n++;
   launches_body = n;
   if (with_head) {
-    if (head_q8.w) { launch_q8_linear(head_q8, xn, rows, logits, device_status_word(), st); n += (rows + 7) / 8; }
+    if (head_q8.w) { launch_q8_linear(head_q8, xn, rows, logits, device_status_word(), st); n += q8_linear_launches(head_q8, rows); }
     else { launch_lm_head(xn, head, d.vocab, H, rows, logits, head_scratch, st); n += 2; }
     launch_argmax(logits, d.vocab, rows, next, argmax_scratch, st); n += 2;
     launches_full = n;
@@ -301,14 +309,26 @@ static Model *model_from_pack(ne_pack *cp, int tmax, int max_rows) {
   for (int l = 0; l < d.layers; l++) {
     ModelLayer &L = M->layers[l];
     const std::string pre = mp + "layers." + std::to_string(l) + ".";
-    L.q = pack_linear(*pk, pre + "self_attn.q_proj");
-    L.k = pack_linear(*pk, pre + "self_attn.k_proj");
-    L.v = pack_linear(*pk, pre + "self_attn.v_proj");
-    L.o = pack_linear(*pk, pre + "self_attn.o_proj");
-    IJ_CHECK(L.q.in == d.hidden && L.k.in == d.hidden && L.v.in == d.hidden && L.o.out == d.hidden && L.o.in == L.q.out && L.k.out == L.v.out,
-             "layer %d: attention projection shapes do not fit hidden %d", l, d.hidden);
-    if (l == 0) { d.q_out = L.q.out; d.kv_out = L.k.out; d.k_trunk = L.q.K; }
-    IJ_CHECK(L.q.out == d.q_out && L.k.out == d.kv_out, "layer %d: attention widths differ from layer 0", l);
+    int q_out = 0, kv_out = 0;
+    if (pk->info(pre + "self_attn.q_proj.scales")) {  // 8-bit affine projections
+      const char *names[4] = {"q_proj", "k_proj", "v_proj", "o_proj"};
+      for (int i = 0; i < 4; i++) L.q8[i] = pack_q8(*pk, pre + "self_attn." + names[i]);
+      IJ_CHECK(L.q8[0].in == d.hidden && L.q8[1].in == d.hidden && L.q8[2].in == d.hidden && L.q8[3].rows == d.hidden && L.q8[3].in == L.q8[0].rows &&
+                   L.q8[1].rows == L.q8[2].rows, "layer %d: attention projection shapes do not fit hidden %d", l, d.hidden);
+      q_out = L.q8[0].rows; kv_out = L.q8[1].rows;
+      if (l == 0) d.k_trunk = 8;
+    } else {
+      L.q = pack_linear(*pk, pre + "self_attn.q_proj");
+      L.k = pack_linear(*pk, pre + "self_attn.k_proj");
+      L.v = pack_linear(*pk, pre + "self_attn.v_proj");
+      L.o = pack_linear(*pk, pre + "self_attn.o_proj");
+      IJ_CHECK(L.q.in == d.hidden && L.k.in == d.hidden && L.v.in == d.hidden && L.o.out == d.hidden && L.o.in == L.q.out && L.k.out == L.v.out,
+               "layer %d: attention projection shapes do not fit hidden %d", l, d.hidden);
+      q_out = L.q.out; kv_out = L.k.out;
+      if (l == 0) d.k_trunk = L.q.K;
+    }
+    if (l == 0) { d.q_out = q_out; d.kv_out = kv_out; }
+    IJ_CHECK(q_out == d.q_out && kv_out == d.kv_out, "layer %d: attention widths differ from layer 0", l);
     if (pk->info(pre + "input_layernorm.weight")) L.norm1 = (const uint16_t *)pk->device(pre + "input_layernorm.weight");
     if (pk->info(pre + "post_attention_layernorm.weight")) L.norm2 = (const uint16_t *)pk->device(pre + "post_attention_layernorm.weight");
     ne_moe_desc &md = L.md;
@@ -331,6 +351,16 @@ static Model *model_from_pack(ne_pack *cp, int tmax, int max_rows) {
       md.sh_up = pack_linear(*pk, pre + "mlp.shared_expert.up_proj");
       md.sh_down = pack_linear(*pk, pre + "mlp.shared_expert.down_proj");
       md.k_shared = md.sh_gate.K;
+    } else if (pk->info(pre + "mlp.shared_expert_gate.weight") && pk->info(pre + "mlp.shared_expert.gate_proj.scales")) {
+      md.shared_gate_w_dev = pk->device(pre + "mlp.shared_expert_gate.weight");
+      auto q8c = [&](const char *name) {
+        const Q8Weight q = pack_q8(*pk, pre + "mlp.shared_expert." + name);
+        return ne_q8_weight{q.w, q.scales, q.biases, q.in, q.rows, q.group};
+      };
+      md.sh_gate_q8 = q8c("gate_proj");
+      md.sh_up_q8 = q8c("up_proj");
+      md.sh_down_q8 = q8c("down_proj");
+      md.k_shared = 8;
     }
     if (l == 0) { d.inter = md.inter; d.experts = md.experts; d.k_expert = md.k_expert; d.k_shared = md.k_shared; d.expert_count = md.experts; }
     L.moe = std::make_unique<Moe>(md, max_rows);
@@ -606,15 +636,19 @@ NE_API uint64_t ne_fn_model_weight_bytes(ne_fn_model *m) {
   Model *M = reinterpret_cast<Model *>(m);
   if (!M) return 0;
   auto lin = [](const ne_exl3_weight &w) { return (uint64_t)w.in * w.out * w.K / 8 + 2ull * w.in + 2ull * w.out; };
-  auto q8b = [](const Q8Weight &w) { return (uint64_t)w.rows * w.in + 4ull * w.rows * (w.in / w.group); };
+  auto q8b = [](const Q8Weight &w) { return q8_weight_bytes(w); };
+  auto q8c = [](const ne_q8_weight &w) { return (uint64_t)w.out * w.in + 4ull * w.out * (w.in / w.group); };
   uint64_t b = 0;
   if (M->embed_q8.w) b += q8b(M->embed_q8); else b += 2ull * M->d.vocab * M->d.hidden;
   if (M->head_q8.w) b += M->head_q8.w == M->embed_q8.w ? 0 : q8b(M->head_q8);
   else if (M->head != M->embed) b += 2ull * M->d.vocab * M->d.hidden;
   for (const ModelLayer &L : M->layers) {
-    b += lin(L.q) + lin(L.k) + lin(L.v) + lin(L.o) + 2ull * L.md.experts * L.md.hidden;
+    if (L.q8[0].w) for (const Q8Weight &w : L.q8) b += q8b(w);
+    else b += lin(L.q) + lin(L.k) + lin(L.v) + lin(L.o);
+    b += 2ull * L.md.experts * L.md.hidden;
     b += 3ull * L.md.expert_count * ((uint64_t)L.md.hidden * L.md.inter * L.md.k_expert / 8 + 2ull * L.md.hidden + 2ull * L.md.inter);
-    if (L.md.shared_gate_w_dev) b += lin(L.md.sh_gate) + lin(L.md.sh_up) + lin(L.md.sh_down) + 2ull * L.md.hidden;
+    if (L.md.shared_gate_w_dev && L.md.sh_gate_q8.weight_dev) b += q8c(L.md.sh_gate_q8) + q8c(L.md.sh_up_q8) + q8c(L.md.sh_down_q8) + 2ull * L.md.hidden;
+    else if (L.md.shared_gate_w_dev) b += lin(L.md.sh_gate) + lin(L.md.sh_up) + lin(L.md.sh_down) + 2ull * L.md.hidden;
   }
   return b;
 }
@@ -631,7 +665,9 @@ NE_API int ne_fn_model_last_bytes(ne_fn_model *m, int rows, uint64_t *total, int
       uint64_t t = 0;
       int n = 0;
       IJ_CHECK(ne_moe_last_bytes(reinterpret_cast<ne_moe *>(L.moe.get()), rows * std::max(1, M->d.ep_world), &t, nullptr, nullptr, &n) == 0, "%s", ne_last_error());
-      b += t + lin(L.q) + lin(L.k) + lin(L.v) + lin(L.o) + 2ull * (uint64_t)M->d.kv_positions * M->d.kv_out * 2;
+      if (L.q8[0].w) for (const Q8Weight &w : L.q8) b += q8_weight_bytes(w);
+      else b += lin(L.q) + lin(L.k) + lin(L.v) + lin(L.o);
+      b += t + 2ull * (uint64_t)M->d.kv_positions * M->d.kv_out * 2;
       nu += n;
     }
     if (total) *total = b;

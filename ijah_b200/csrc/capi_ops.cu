@@ -201,6 +201,12 @@ void Moe::shared_q8_run(const float *x, int rows, cudaStream_t st) {
   launch_q8_linear(q8_of(desc.sh_down_q8), q8_act, rows, sho, status, st);
 }
 
+int Moe::shared_q8_launches(int rows) const {
+  if (!shared_q8) return 0;
+  return q8_linear_launches(q8_of(desc.sh_gate_q8), rows) + q8_linear_launches(q8_of(desc.sh_up_q8), rows) + 1 +
+         q8_linear_launches(q8_of(desc.sh_down_q8), rows);
+}
+
 void Moe::forward(const float *x, int rows, float *y, cudaStream_t st) {
   const MoeParams p = params(x, rows, y);
   const MoeSplits &s = splits(rows);
@@ -622,7 +628,9 @@ NE_API int ne_moe_last_bytes(ne_moe *m, int rows, uint64_t *total, uint64_t *gat
     const uint64_t lin_x = H * I * o->desc.k_expert / 8, lin_s = H * I * o->desc.k_shared / 8;
     const uint64_t gu = (uint64_t)nu * 2 * (lin_x + 2 * H + 2 * I) + (o->has_shared ? 2 * (lin_s + 2 * H + 2 * I) : 0);
     const uint64_t dn = (uint64_t)nu * (lin_x + 2 * I + 2 * H) + (o->has_shared ? lin_s + 2 * I + 2 * H : 0);
-    const uint64_t rt = E * H * 2 + (o->has_shared ? H * 2 : 0);
+    uint64_t rt = E * H * 2 + (o->has_shared ? H * 2 : 0);
+    if (o->shared_q8)  // three 8-bit affine Linears and the gate vector
+      rt += q8_weight_bytes(q8_of(o->desc.sh_gate_q8)) + q8_weight_bytes(q8_of(o->desc.sh_up_q8)) + q8_weight_bytes(q8_of(o->desc.sh_down_q8)) + H * 2;
     if (gateup) *gateup = gu;
     if (down) *down = dn;
     if (total) *total = gu + dn + rt + 2ull * rows * H * 4;

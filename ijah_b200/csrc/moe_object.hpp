@@ -18,6 +18,7 @@ struct Moe {
   bool shared_q8 = false;  // the shared expert is three 8-bit affine Linears (decode-width single-GPU calls only)
   float *q8_g = nullptr, *q8_u = nullptr, *q8_act = nullptr;
   void shared_q8_run(const float *x, int rows, cudaStream_t st);  // sho = down(silu(gate x) * up x); gush = gate | up
+  int shared_q8_launches(int rows) const;                         // kernels shared_q8_run starts (0 without such an expert)
   int last_rows = 1;
   std::vector<void *> owned;
   float *logits = nullptr, *raw_gu = nullptr, *raw_sgu = nullptr, *raw_d = nullptr, *raw_sd = nullptr, *gush = nullptr, *sho = nullptr;

@@ -525,6 +525,8 @@ void launch_q8_linear(const Q8Weight &w, const float *x, int rows, float *y, int
   }
 }
 
+int q8_linear_launches(const Q8Weight &w, int rows) { return q8_streamable(w) ? (rows + 7) / 8 : (rows + 15) / 16; }
+
 void launch_q8_embed(const Q8Weight &w, const int *tokens, int rows, float *x, bool round_bf16, cudaStream_t st) {
   check_q8_weight(w);
   launch_pdl(q8_embed_kernel, dim3(rows), dim3(256), 0, st, w, tokens, x, round_bf16 ? 1 : 0);

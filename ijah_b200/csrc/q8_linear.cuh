@@ -20,6 +20,8 @@ void check_q8_weight(const Q8Weight &w);
 // groups of 64, 128 or 256)
 // `status`: the device word bounded waits report to (device_status_word())
 void launch_q8_linear(const Q8Weight &w, const float *x, int rows, float *y, int *status, cudaStream_t st);
+int q8_linear_launches(const Q8Weight &w, int rows);  // kernels launch_q8_linear starts for this weight and row count
+inline uint64_t q8_weight_bytes(const Q8Weight &w) { return (uint64_t)w.rows * w.in + 4ull * w.rows * (w.in / w.group); }
 // x[r][:] = scale * q + bias of row tokens[r] (ids outside [0, rows) read row 0), optionally rounded to bf16 as the
 // reference's embedding is (kernels/fn_model.metal:14-40)
 void launch_q8_embed(const Q8Weight &w, const int *tokens, int rows, float *x, bool round_bf16, cudaStream_t st);

@@ -103,6 +103,18 @@ def trunk_layer(rng, layer=0, hidden=2048, q_out=4096, kv_out=512, K=6):
     return t
 
 
+def trunk_layer_q8(rng, layer=0, hidden=2048, q_out=4096, kv_out=512, group=64):
+    """the attention projections of one layer as 8-bit affine Linears (packs whose trunk was not converted to EXL3)"""
+    pre = f"{PFX}{layer}.self_attn."
+    t = {}
+    for proj, (n_in, n_out) in (("q", (hidden, q_out)), ("k", (hidden, kv_out)), ("v", (hidden, kv_out)), ("o", (q_out, hidden))):
+        w, sc, bi = q8_linear(rng, n_out, n_in, group, std=1.0 / np.sqrt(n_in))
+        t[f"{pre}{proj}_proj.weight"] = ("U32", w)
+        t[f"{pre}{proj}_proj.scales"] = ("BF16", sc)
+        t[f"{pre}{proj}_proj.biases"] = ("BF16", bi)
+    return t
+
+
 def write_shard(path, tensors, misalign=0):
     """One safetensors file. `misalign` extra header bytes reproduce the real packs' odd data offsets (the reference
     needs Pack::aligned for those, core/pack.mm:254-268)."""

@@ -258,6 +258,14 @@ def q8_embed(ids, wq_u32, scales_bf16, biases_bf16):
     return bf16_round(affine_dequant(np.asarray(wq_u32)[ids], np.asarray(scales_bf16)[ids], np.asarray(biases_bf16)[ids]))
 
 
+class AffineLinear:
+    """An 8-bit affine Linear seen as the float32 matrix it stands for: .dense is [in, out] like Exl3Linear.dense, so
+    the float64 block and stack references take either kind of projection."""
+
+    def __init__(self, weight, scales, biases):
+        self.dense = np.ascontiguousarray(affine_dequant(weight, scales, biases).T)
+
+
 def shared_expert_q8(x, gate, up, down, sgate_w):
     """the shared expert with 8-bit affine projections (reference tools/opref.py:438-446 with bf=False; each of gate, up,
     down = (weight u32, scales, biases)): (gate_proj, up_proj, out, sigmoid scale [rows, 1])"""

@@ -17,7 +17,7 @@ CFG = dict(layers=3, hidden=512, inter=256, experts=32, top_k=4, heads=4, kv_hea
 def small_model_tensors(rng, fmt="bf16"):
     t = {}
     H, V = CFG["hidden"], CFG["vocab"]
-    if fmt == "q8":  # 8-bit affine embedding and head, the format of the reference's packs
+    if fmt in ("q8", "q8all"):  # 8-bit affine embedding and head, the format of the reference's packs
         for name, std in (("language_model.model.embed_tokens", 1.0), ("language_model.lm_head", 0.1)):
             w, sc, bi = packgen.q8_linear(rng, V, H, 64, std=std)
             t[name + ".weight"], t[name + ".scales"], t[name + ".biases"] = ("U32", w), ("BF16", sc), ("BF16", bi)
@@ -26,6 +26,13 @@ def small_model_tensors(rng, fmt="bf16"):
         t["language_model.lm_head.weight"] = ("BF16", packgen.f32_to_bf16_bits(rng.standard_normal((V, H)) * 0.1))
     for l in range(CFG["layers"]):
         t.update(packgen.moe_layer(rng, layer=l, hidden=H, inter=CFG["inter"], experts=CFG["experts"]))
+        if fmt == "q8all":  # a pack whose trunk stayed 8-bit affine: attention projections and the shared expert too
+            for name in [n for n in t if f"layers.{l}.mlp.shared_expert." in n]:
+                del t[name]
+            t.update(packgen.shared_expert_q8(rng, layer=l, hidden=H, inter=CFG["inter"], group=64 if l else 32))
+            t.update(packgen.trunk_layer_q8(rng, layer=l, hidden=H, q_out=CFG["heads"] * CFG["head_dim"],
+                                            kv_out=CFG["kv_heads"] * CFG["head_dim"], group=64 if l else 128))
+            continue
         t.update(packgen.trunk_layer(rng, layer=l, hidden=H, q_out=CFG["heads"] * CFG["head_dim"], kv_out=CFG["kv_heads"] * CFG["head_dim"],
                                      K=8 if l == 2 else 6))
     return t
@@ -51,6 +58,18 @@ class FastView(MoeView):
         return self._cache["s"]
 
 
+def affine(t, name):
+    return O.AffineLinear(*(t[name + s][1] for s in (".weight", ".scales", ".biases")))
+
+
+class AffineSharedView(FastView):
+    @property
+    def shared(self):
+        if "s" not in self._cache:
+            self._cache["s"] = tuple(affine(self.t, f"{self.pre}shared_expert.{p}_proj") for p in ("gate", "up", "down"))
+        return self._cache["s"]
+
+
 @pytest.fixture(scope="module")
 def eng():
     import torch
@@ -59,7 +78,7 @@ def eng():
     return E.Engine()
 
 
-@pytest.mark.parametrize("fmt", ["bf16", "q8"])
+@pytest.mark.parametrize("fmt", ["bf16", "q8", "q8all"])
 def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     rng = np.random.default_rng(2025)
     t = small_model_tensors(rng, fmt)
@@ -69,7 +88,7 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     p = eng.pack_open(tmp_path / "model")
     m = eng.fn_model(p, tmax=128, max_rows=8)
     p.close()  # the model keeps the pack alive
-    assert m.desc["layers"] == 3 and m.desc["kv_positions"] == 128 and m.desc["k_trunk"] == 6
+    assert m.desc["layers"] == 3 and m.desc["kv_positions"] == 128 and m.desc["k_trunk"] == (8 if fmt == "q8all" else 6)
     tokens = np.array([5, 77, 1999, 0, 1024], np.int32)
     nxt, logits, ms = m.step_rows(tokens, want_logits=True)
     assert eng.lib.ne_device_wait_status() == 0
@@ -78,11 +97,15 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     layers = []
     for l in range(CFG["layers"]):
         kv = (128, CFG["kv_heads"], CFG["head_dim"])
-        layers.append(dict(q=trunk_linear(t, l, "q"), k=trunk_linear(t, l, "k"), v=trunk_linear(t, l, "v"), o=trunk_linear(t, l, "o"),
-                           view=FastView(t, l), kc=m.read("kv_k", l).reshape(kv), vc=m.read("kv_v", l).reshape(kv)))
-        for n in ("q", "k", "v", "o"):
-            layers[-1][n]._inner = CO.decode_inner(layers[-1][n].trellis)
-    q8 = (lambda n: tuple(t[n + s][1] for s in (".weight", ".scales", ".biases"))) if fmt == "q8" else (lambda n: None)
+        if fmt == "q8all":
+            proj = {n: affine(t, f"{packgen.PFX}{l}.self_attn.{n}_proj") for n in ("q", "k", "v", "o")}
+        else:
+            proj = {n: trunk_linear(t, l, n) for n in ("q", "k", "v", "o")}
+            for n in proj:
+                proj[n]._inner = CO.decode_inner(proj[n].trellis)
+        layers.append(dict(**proj, view=(AffineSharedView if fmt == "q8all" else FastView)(t, l), kc=m.read("kv_k", l).reshape(kv),
+                           vc=m.read("kv_v", l).reshape(kv)))
+    q8 = (lambda n: tuple(t[n + s][1] for s in (".weight", ".scales", ".biases"))) if fmt != "bf16" else (lambda n: None)
     want = S.stack_logits(tokens, t["language_model.model.embed_tokens.weight"][1], t["language_model.lm_head.weight"][1], layers,
                           CFG["heads"], CFG["kv_heads"], CFG["head_dim"], CFG["top_k"], embed_q8=q8("language_model.model.embed_tokens"),
                           head_q8=q8("language_model.lm_head"))
@@ -97,7 +120,8 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     lref = want[0] - want[0].max()
     assert abs(lp1 - (lref[n1] - np.log(np.exp(lref).sum()))) < 1e-2
     info = m.info()
-    assert info["launches_full"] == 1 + CFG["layers"] * 16 + 1 + (3 if fmt == "q8" else 4) and info["T"] == 128
+    per_layer = 18 if fmt == "q8all" else 16  # four 8-bit Linears instead of two 3-kernel chains; + the shared expert's 4
+    assert info["launches_full"] == 1 + CFG["layers"] * per_layer + 1 + (4 if fmt == "bf16" else 3) and info["T"] == 128
     a, b, c = m.time(reps=3)
     assert 0 < b <= a and c > 0
     m.free()

@@ -95,3 +95,7 @@ def test_q8_shared_expert_matches_reference():
     assert rel_max(gp, g["sh8_shared_gate_proj"]) < 2e-6 and rel_max(upj, g["sh8_shared_up_proj"]) < 2e-6
     assert rel_max(out, g["sh8_shared_out"]) < 5e-6
     assert rel_max(scale, g["sh8_shared_scale"]) < 2e-6
+    # the dense view the float64 block / stack references multiply by gives the same shared expert
+    sh, sc = O.shared_expert(g["x"], O.AffineLinear(*gate), O.AffineLinear(*up), O.AffineLinear(*down),
+                             O.bf16_bits_to_f32(t[pre + "shared_expert_gate.weight"][1]))
+    assert rel_max(sh, g["sh8_shared_out"]) < 5e-6 and rel_max(sc.reshape(-1, 1), g["sh8_shared_scale"]) < 2e-6
