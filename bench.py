@@ -179,11 +179,17 @@ def cpu_numpy_row_seconds():
     return time.perf_counter() - t0
 
 
+def arithmetic(a):
+    if a.summand_product:
+        return "opt-in summand product: weights as their two f16 summands (sum unrounded), f16 activations, f32 accumulate"
+    return "weights decoded to f16 (the format's rounded values), f16 activations, f32 accumulate"
+
+
 def stack_config(a, rows):
     return {"workload": f"decoder stack decode step: {a.layers} layers (EXL3 trunk q/k/v/o K6/K8 + attention stand-in over 8192 cached positions + "
                         f"MoE block 512 experts top-10 K5 + shared K6), bf16 LM head 151936 x 2048; {a.batch} sequences x {a.verify} verify "
                         f"tokens = {rows} rows per GPU",
-            "arithmetic": "weights decoded to f16, f16 activations, f32 accumulate", "rows": rows, "layers": a.layers,
+            "arithmetic": arithmetic(a), "rows": rows, "layers": a.layers,
             "l2": "weights of a step (tens of GB) exceed L2", "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
 
 
@@ -214,7 +220,7 @@ def run_reference(a, rank):
 
 def block_config(a):
     return {"workload": f"MoE block decode: hidden 2048, 512 experts top-10, inter 768, K5 routed + K6 shared, rows {a.rows}",
-            "arithmetic": "weights decoded to f16, f16 activations, f32 accumulate", "rows": a.rows, "layers": a.layers,
+            "arithmetic": arithmetic(a), "rows": a.rows, "layers": a.layers,
             "l2": "weights of a step exceed L2 (distinct layers cycled)", "parallelism": "single GPU" if a.gpus == 1 else f"ep{a.gpus}"}
 
 
@@ -325,6 +331,8 @@ def run_stack(a, rank, world):
         dist.init_process_group("nccl", device_id=dev)
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE {world}"
     eng = E.Engine()
+    if a.summand_product:
+        eng.lib.ne_exl3_set_summand_product(1)
     N, rows = world, a.batch * a.verify
     assert rows * N <= 64, f"{rows} rows x {N} ranks: the decode-width MoE block takes at most 64 gathered rows"
     per = STACK["experts"] // N
@@ -460,10 +468,25 @@ def run_stack(a, rank, world):
             big = eng.fn_model(desc=dict(STACK, layers=a.layers, ep_world=1, expert_first=0, expert_count=0), seed=a.seed, max_rows=64)
             extra["stack_rows"] = {}
             for r in (4, 64):
-                big.step_rows(np.zeros(r, np.int32))
+                big.step_rows(np.random.default_rng(100).integers(0, STACK["vocab"], r).astype(np.int32))  # distinct rows, as in the headline
                 t = big.replay(r, 5) / 5
                 extra["stack_rows"][str(r)] = {"ms_per_step": t, "tok_per_s": r / t * 1e3}
             big.free()
+            # the opt-in summand product (every weight multiplied as its two fp16 summands, sum unrounded): same figures
+            if not a.summand_product:
+                eng.lib.ne_exl3_set_summand_product(1)
+                try:
+                    sbf = block_figures(eng, rows, 8, a.steps, dev)
+                    sm = eng.fn_model(desc=dict(STACK, layers=a.layers, ep_world=1, expert_first=0, expert_count=0), seed=a.seed, max_rows=rows)
+                    sm.step_rows(tokens)
+                    t = sm.replay(rows, 5) / 5
+                    sm.free()
+                    extra["summand_product"] = {"note": "ne_exl3_set_summand_product(1); off in every other figure of this line",
+                                                "rows": rows, "stack_ms_per_step": t, "stack_tok_per_s": rows / t * 1e3,
+                                                "block_us": sbf["block_us"], "gateup_us": sbf["gateup_us"], "gateup_frac": sbf["gateup_frac"],
+                                                "down_us": sbf["down_us"], "down_frac": sbf["down_frac"]}
+                finally:
+                    eng.lib.ne_exl3_set_summand_product(0)
         if a.cpu_seconds > 0:
             sec, cores, n = cpu_port_layer_seconds(rows, a.cpu_seconds)
             cpu = {"value": rows / (sec * a.layers), "unit": "tok/s", "cores": cores, "kind": "port",
@@ -493,6 +516,8 @@ def run_block(a, rank, world):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     eng = E.Engine()
+    if a.summand_product:
+        eng.lib.ne_exl3_set_summand_product(1)
     peak, which = peaks()
     sampler = ClockSampler(0)
     sampler.start()
@@ -563,6 +588,8 @@ def run_q8head(a, rank, world):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     eng = E.Engine()
+    if a.summand_product:
+        eng.lib.ne_exl3_set_summand_product(1)
     peak, which = peaks()
     V, H = (int(v) for v in a.q8_dims.split("x"))
     sampler = ClockSampler(0)
@@ -592,6 +619,8 @@ def main():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--summand-product", action="store_true",
+                    help="run everything under ne_exl3_set_summand_product(1) (opt-in arithmetic: weights as their two fp16 summands)")
     ap.add_argument("--no-extras", dest="extras", action="store_false", help="skip the extra block / prefill / other-row-count figures")
     ap.add_argument("--no-sustain", dest="sustain", action="store_false", help="skip the >= 2 s sustained replay")
     ap.add_argument("--workload", default="stack", choices=["stack", "block", "q8head"])

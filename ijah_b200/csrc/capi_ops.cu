@@ -137,7 +137,7 @@ MoeParams Moe::params(const float *x, int rows, float *y) {
   p.H = desc.hidden; p.I = desc.inter; p.E = desc.experts; p.topk = desc.top_k;
   p.Kx = desc.k_expert; p.Ks = desc.k_shared;
   p.e0 = desc.expert_first; p.ecount = desc.expert_count;
-  p.rows = rows; p.P = rows * desc.top_k; p.has_shared = has_shared ? 1 : 0; p.shared_pre = shared_q8 ? 1 : 0;
+  p.rows = rows; p.P = rows * desc.top_k; p.has_shared = has_shared ? 1 : 0; p.shared_pre = shared_q8 ? 1 : 0; p.dup = g_summand_product;
   p.router = (const uint16_t *)desc.router_dev;
   p.sgate = (const uint16_t *)desc.shared_gate_w_dev;
   auto stack = [](const ne_exl3_stack &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
@@ -616,6 +616,12 @@ NE_API int ne_moe_experts_gu(ne_moe *m, int rows, float *dst_host) {
     }
   });
 }
+NE_API int ne_exl3_set_summand_product(int on) {
+  const int was = g_summand_product;
+  if (on == 0 || on == 1) g_summand_product = on;
+  return was;
+}
+
 NE_API int ne_moe_last_bytes(ne_moe *m, int rows, uint64_t *total, uint64_t *gateup, uint64_t *down, int *distinct_experts) {
   return c_call([&] {
     Moe *o = reinterpret_cast<Moe *>(m);

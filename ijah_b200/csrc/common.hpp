@@ -27,6 +27,12 @@ struct Error : std::runtime_error {
   throw Error(buf);
 }
 
+// Product mode of the decode-width stream kernels (ne_exl3_set_summand_product): 0 = every weight enters the tensor
+// core as fp16(lo + hi), the value the format defines; 1 = as its two fp16 summands, whose sum the fp32 accumulator
+// forms unrounded. Read when a call is enqueued (or recorded into a graph), by the operand-prep kernels' launchers and
+// the stream kernel's launcher alike.
+inline int g_summand_product = 0;
+
 #define IJ_CHECK(cond, ...) \
   do {                      \
     if (!(cond)) ::ijah::fail(__VA_ARGS__); \

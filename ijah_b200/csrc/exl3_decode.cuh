@@ -156,12 +156,15 @@ __device__ __forceinline__ void dec8_raw(uint32_t w0, uint32_t w1, uint32_t w2, 
 }
 
 // Layout of a prepared activation row (the B operand of the stream kernels) for that product: per k-tile of 16 inputs
-// 32 halfs = 16 (v, v) pairs in the order inputs 0, 2, .. 14, then 1, 3, .. 15, so that one ldmatrix.x4 of an 8-row group
-// yields the even-input and the odd-input fragments. A row of n inputs is 2 n halfs.
+// 32 halfs = 16 pairs in the order inputs 0, 2, .. 14, then 1, 3, .. 15, so that one ldmatrix.x4 of an 8-row group
+// yields the even-input and the odd-input fragments. A row of n inputs is 2 n halfs. The pair is (v, 0) for the exact
+// product (the kernel feeds (w, w), w = fp16(lo + hi): the accumulator receives w * v) and (v, v) for the summand
+// product (the kernel feeds (lo, hi): lo * v + hi * v).
 constexpr int A_HALFS_PER_INPUT = 2;
-__device__ __forceinline__ void store_a(__half *row, int i, float v) {
+__device__ __forceinline__ void store_a(__half *row, int i, float v, int dup) {
   const int w = (i >> 4) * 16 + (i & 1) * 8 + ((i & 15) >> 1);
-  reinterpret_cast<__half2 *>(row)[w] = __float2half2_rn(v);
+  const __half h = __float2half_rn(v);
+  reinterpret_cast<__half2 *>(row)[w] = __halves2half2(h, dup ? h : __ushort_as_half((unsigned short)0));
 }
 
 // normalised Hadamard of size N (16..128) over a 128-element chunk held by a warp as (lane, lane+32, lane+64, lane+96);

@@ -83,7 +83,7 @@ LinearPlan plan_linear(int in, int out, int K, int rows) {
 }
 
 __global__ void __launch_bounds__(128) prep_rows_kernel(const float *__restrict__ x, const __half *__restrict__ suh,
-                                                        __half *__restrict__ xh, int rows, int n, int hn, float hscale) {
+                                                        __half *__restrict__ xh, int rows, int n, int hn, float hscale, int dup) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int chunk = blockIdx.x * 4 + warp, r = blockIdx.y;
   pdl_wait();
@@ -99,14 +99,14 @@ __global__ void __launch_bounds__(128) prep_rows_kernel(const float *__restrict_
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = chunk * 128 + lane + 32 * j;
-    if (i < n) store_a(xh + (size_t)r * n * A_HALFS_PER_INPUT, i, v[j]);
+    if (i < n) store_a(xh + (size_t)r * n * A_HALFS_PER_INPUT, i, v[j], dup);
   }
 }
 
 void launch_prep_rows(const float *x, const __half *suh, __half *xh, int rows, int n, cudaStream_t st) {
   const int hn = had_size(n);
   dim3 grid(((n + 127) / 128 + 3) / 4, rows);
-  launch_pdl(prep_rows_kernel, grid, dim3(128), 0, st, x, suh, xh, rows, n, hn, (float)(1.0 / sqrt((double)hn)));
+  launch_pdl(prep_rows_kernel, grid, dim3(128), 0, st, x, suh, xh, rows, n, hn, (float)(1.0 / sqrt((double)hn)), g_summand_product);
 }
 
 // y[r][c] = (H_ho(sum_s raw[s][r]))[c] * svh[c]; one warp per (row, 128-column chunk), splits summed in index order
@@ -148,6 +148,7 @@ struct MlPtrs {
   float *y[ML_MAX];
   int out[ML_MAX], ho[ML_MAX];
   float hs[ML_MAX];  // 1 / sqrt(ho), rounded once on the host like everywhere else
+  int dup;           // store_a's pair form: the product mode in force when the call was enqueued
 };
 
 __global__ void __launch_bounds__(128) prep_rows_multi_kernel(const float *__restrict__ x, const MlPtrs a, int rows, int n, int hn, float hscale) {
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(128) prep_rows_multi_kernel(const float *__res
 #pragma unroll
   for (int j = 0; j < 4; j++) {
     const int i = chunk * 128 + lane + 32 * j;
-    if (i < n) store_a(a.xh[m] + (size_t)r * n * A_HALFS_PER_INPUT, i, v[j]);
+    if (i < n) store_a(a.xh[m] + (size_t)r * n * A_HALFS_PER_INPUT, i, v[j], a.dup);
   }
 }
 
@@ -226,6 +227,7 @@ MultiLinearPlan plan_linear_multi(int n, int in, const int *out, const int *K, i
 void launch_linear_multi(const MultiLinearPlan &p, const MultiLinearArgs &a, const float *x, void *scratch, int *status, cudaStream_t st) {
   MultiLinearProblem pr{};
   MlPtrs q{};
+  q.dup = g_summand_product;
   char *cur = (char *)scratch;
   int maxout = 0;
   pr.n = p.n; pr.in = p.in; pr.rows = p.rows; pr.IT = p.IT; pr.S = p.S; pr.kc = p.kc;

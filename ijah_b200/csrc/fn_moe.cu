@@ -406,12 +406,12 @@ __global__ void __launch_bounds__(128) moe_prep_kernel(const MoeParams p, int bu
   for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(sg[o + 32 * j]);
   fwht_chunk(v, lane, 128, hs);
 #pragma unroll
-  for (int j = 0; j < 4; j++) store_a(dst, o + 32 * j, v[j]);
+  for (int j = 0; j < 4; j++) store_a(dst, o + 32 * j, v[j], p.dup);
 #pragma unroll
   for (int j = 0; j < 4; j++) v[j] = xv[j] * __half2float(su[o + 32 * j]);
   fwht_chunk(v, lane, 128, hs);
 #pragma unroll
-  for (int j = 0; j < 4; j++) store_a(dst + H * A_HALFS_PER_INPUT, o + 32 * j, v[j]);
+  for (int j = 0; j < 4; j++) store_a(dst + H * A_HALFS_PER_INPUT, o + 32 * j, v[j], p.dup);
 }
 
 // xh_d[pair][I] = fp16(H128(silu(g) * u * suh_down)), g = H128(sum_s raw gate) * svh_gate, u likewise
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(128) moe_mid_kernel(const MoeParams p) {
   }
   fwht_chunk(hh, lane, 128, hs);
 #pragma unroll
-  for (int j = 0; j < 4; j++) store_a(dst, o + 32 * j, hh[j]);
+  for (int j = 0; j < 4; j++) store_a(dst, o + 32 * j, hh[j], p.dup);
 }
 
 // =============================================================================================== gate / up

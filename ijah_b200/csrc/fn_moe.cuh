@@ -20,6 +20,7 @@ struct MoeParams {
   int rows;           // live rows of this run
   int P;              // rows * topk
   int has_shared;
+  int dup;            // store_a's pair form: the product mode in force when the call was enqueued
   int shared_pre;     // the shared expert's output is already in `sho` (8-bit affine shared expert: computed by other kernels)
   // weights
   const uint16_t *router;  // bf16 [E][H]

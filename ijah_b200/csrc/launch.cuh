@@ -18,11 +18,17 @@ void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cu
   IJ_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 
+template <class P, int MT, bool EX>
+static void launch_stream_ex(const P &prob, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
+  // the attribute belongs to the current device's context: set it on every launch (cheap) rather than once per process
+  IJ_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<P, MT, EX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+  launch_pdl(stream_gemm_kernel<P, MT, EX>, dim3(grid), dim3(SG_THREADS), lay.total(), st, prob, lay, status);
+}
+// the product mode in force (g_summand_product) picks the kernel; the prepared rows of the same call were written to match
 template <class P, int MT>
 static void launch_stream_mt(const P &prob, const StreamLayout &lay, int grid, int *status, cudaStream_t st) {
-  // the attribute belongs to the current device's context: set it on every launch (cheap) rather than once per process
-  IJ_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<P, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-  launch_pdl(stream_gemm_kernel<P, MT>, dim3(grid), dim3(SG_THREADS), lay.total(), st, prob, lay, status);
+  if (g_summand_product) launch_stream_ex<P, MT, false>(prob, lay, grid, status, st);
+  else launch_stream_ex<P, MT, true>(prob, lay, grid, status, st);
 }
 
 template <class P>

@@ -105,7 +105,7 @@ __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
 // acc[g] = D^T fragment of group g: (column gq, rows 2q, 2q+1), (column gq + 8, ..).
 constexpr uint32_t SG_A_TILE_BYTES = 16 * A_HALFS_PER_INPUT * 2;  // one k-tile of one prepared activation row
 
-template <int K, int MT, int I>
+template <int K, bool EX, int MT, int I>
 __device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t la, const McgConst &mc,
                                          const uint32_t (&a_row)[MT], float (&acc)[MT][4]) {
   uint32_t r[8];
@@ -114,6 +114,14 @@ __device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, 
 #else
   dec8_raw<K>(w0, w1, w2, la, mc, r);
 #endif
+  if constexpr (EX) {  // both halves = fp16(lo + hi), the format's weight; the activation rows then hold (v, 0) pairs
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+      const __half2 h = *reinterpret_cast<const __half2 *>(&r[t]);
+      const __half2 w = __hadd2(__low2half2(h), __high2half2(h));
+      r[t] = *reinterpret_cast<const uint32_t *>(&w);
+    }
+  }
 #if SG_DBG == 1  // timing only: decode without the MMA
   acc[0][0] = __uint_as_float(__float_as_uint(acc[0][0]) ^ r[0] ^ r[1] ^ r[2] ^ r[3]);
   acc[0][1] = __uint_as_float(__float_as_uint(acc[0][1]) ^ r[4] ^ r[5] ^ r[6] ^ r[7]);
@@ -134,7 +142,7 @@ __device__ __forceinline__ void tile_mma(uint32_t w0, uint32_t w1, uint32_t w2, 
 // warps of the SM cover the shared-memory latency at the start of each half.
 constexpr int SG_HALF = 4;
 constexpr int SG_GROUPS = SG_KS / SG_HALF;
-template <int K, int MT, int B, int I, int N>
+template <int K, bool EX, int MT, int B, int I, int N>
 struct TileLoop {
   static constexpr int KSTEP = SG_WARPS * Codec<K>::TILE_BYTES;
   static constexpr int NP = MT;
@@ -142,21 +150,21 @@ struct TileLoop {
     w[I][0] = lds32<(B + I) * KSTEP>(p0);
     w[I][1] = lds32<(B + I) * KSTEP>(p1);
     w[I][2] = lds32<(B + I) * KSTEP>(p2);
-    TileLoop<K, MT, B, I + 1, N>::load(p0, p1, p2, w);
+    TileLoop<K, EX, MT, B, I + 1, N>::load(p0, p1, p2, w);
   }
   static __device__ __forceinline__ void run(const uint32_t (&w)[SG_HALF][3], uint32_t la, const McgConst &mc, const uint32_t (&a_row)[NP],
                                              float (&acc)[MT][4], int n) {
-    if (B + I < n) tile_mma<K, MT, B + I>(w[I][0], w[I][1], w[I][2], la, mc, a_row, acc);
-    TileLoop<K, MT, B, I + 1, N>::run(w, la, mc, a_row, acc, n);
+    if (B + I < n) tile_mma<K, EX, MT, B + I>(w[I][0], w[I][1], w[I][2], la, mc, a_row, acc);
+    TileLoop<K, EX, MT, B, I + 1, N>::run(w, la, mc, a_row, acc, n);
   }
   static __device__ __forceinline__ void run_all(const uint32_t (&w)[SG_HALF][3], uint32_t la, const McgConst &mc, const uint32_t (&a_row)[NP],
                                                  float (&acc)[MT][4]) {  // straight-line: the tiles interleave freely
-    tile_mma<K, MT, B + I>(w[I][0], w[I][1], w[I][2], la, mc, a_row, acc);
-    TileLoop<K, MT, B, I + 1, N>::run_all(w, la, mc, a_row, acc);
+    tile_mma<K, EX, MT, B + I>(w[I][0], w[I][1], w[I][2], la, mc, a_row, acc);
+    TileLoop<K, EX, MT, B, I + 1, N>::run_all(w, la, mc, a_row, acc);
   }
 };
-template <int K, int MT, int B, int N>
-struct TileLoop<K, MT, B, N, N> {
+template <int K, bool EX, int MT, int B, int N>
+struct TileLoop<K, EX, MT, B, N, N> {
   static constexpr int NP = MT;
   static __device__ __forceinline__ void load(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_HALF][3]) {}
   static __device__ __forceinline__ void run(const uint32_t (&)[SG_HALF][3], uint32_t, const McgConst &, const uint32_t (&)[NP], float (&)[MT][4], int) {}
@@ -164,26 +172,26 @@ struct TileLoop<K, MT, B, N, N> {
 };
 
 // the SG_GROUPS groups of a stage, one after the other
-template <int K, int MT, int G, int NG>
+template <int K, bool EX, int MT, int G, int NG>
 struct StageLoop {
   static constexpr int NP = MT;
   static __device__ __forceinline__ void run_all(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t (&w)[SG_HALF][3], uint32_t la, const McgConst &mc,
                                                  const uint32_t (&a_row)[NP], float (&acc)[MT][4]) {
-    TileLoop<K, MT, G * SG_HALF, 0, SG_HALF>::load(p0, p1, p2, w);
-    TileLoop<K, MT, G * SG_HALF, 0, SG_HALF>::run_all(w, la, mc, a_row, acc);
-    StageLoop<K, MT, G + 1, NG>::run_all(p0, p1, p2, w, la, mc, a_row, acc);
+    TileLoop<K, EX, MT, G * SG_HALF, 0, SG_HALF>::load(p0, p1, p2, w);
+    TileLoop<K, EX, MT, G * SG_HALF, 0, SG_HALF>::run_all(w, la, mc, a_row, acc);
+    StageLoop<K, EX, MT, G + 1, NG>::run_all(p0, p1, p2, w, la, mc, a_row, acc);
   }
   static __device__ __forceinline__ void run(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t (&w)[SG_HALF][3], uint32_t la, const McgConst &mc,
                                              const uint32_t (&a_row)[NP], float (&acc)[MT][4], int n) {
     if (G * SG_HALF < n) {
-      TileLoop<K, MT, G * SG_HALF, 0, SG_HALF>::load(p0, p1, p2, w);
-      TileLoop<K, MT, G * SG_HALF, 0, SG_HALF>::run(w, la, mc, a_row, acc, n);
+      TileLoop<K, EX, MT, G * SG_HALF, 0, SG_HALF>::load(p0, p1, p2, w);
+      TileLoop<K, EX, MT, G * SG_HALF, 0, SG_HALF>::run(w, la, mc, a_row, acc, n);
     }
-    StageLoop<K, MT, G + 1, NG>::run(p0, p1, p2, w, la, mc, a_row, acc, n);
+    StageLoop<K, EX, MT, G + 1, NG>::run(p0, p1, p2, w, la, mc, a_row, acc, n);
   }
 };
-template <int K, int MT, int NG>
-struct StageLoop<K, MT, NG, NG> {
+template <int K, bool EX, int MT, int NG>
+struct StageLoop<K, EX, MT, NG, NG> {
   static constexpr int NP = MT;
   static __device__ __forceinline__ void run_all(uint32_t, uint32_t, uint32_t, uint32_t (&)[SG_HALF][3], uint32_t, const McgConst &,
                                                  const uint32_t (&)[NP], float (&)[MT][4]) {}
@@ -210,7 +218,7 @@ constexpr uint32_t SG_EMPTY_OFF = SG_MAX_STAGES * 8;
 // out[rowoff[row] + col]. Returns false if a bounded wait gave up. The steady-state loop (full stages of a live warp) is
 // straight-line code between one wait and one arrive; a short last stage and the warps without a tile (units narrower
 // than 8 tiles) take their own loops.
-template <int K, int MT>
+template <int K, bool EX, int MT>
 __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, bool live, int lane, const McgConst &mc, uint32_t a_addr,
                                              uint32_t lda_bytes, uint32_t z_addr, const int *rowoff, int col, int *status) {
   const uint32_t lane0 = lane == 0 ? 1u : 0u;
@@ -250,7 +258,7 @@ __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, 
     const uint32_t bar = rc.full + rc.stage * 8u;
     if (!mbar_wait_poll(bar, rc.phase)) { atomicExch(status, 2); return false; }
     const uint32_t p0 = t0 + rc.stage * rc.stage_bytes, p1 = p0 + d1, p2 = p0 + d2;
-    StageLoop<K, MT, 0, SG_GROUPS>::run_all(p0, p1, p2, w, L.a, mc, a_row, acc);
+    StageLoop<K, EX, MT, 0, SG_GROUPS>::run_all(p0, p1, p2, w, L.a, mc, a_row, acc);
 #pragma unroll
     for (int m = 0; m < MT; m++) a_row[m] += SG_KS * SG_A_TILE_BYTES;  // the zero row is a full row too
     __syncwarp();
@@ -261,7 +269,7 @@ __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, 
     const uint32_t bar = rc.full + rc.stage * 8u;
     if (!mbar_wait_poll(bar, rc.phase)) { atomicExch(status, 2); return false; }
     const uint32_t p0 = t0 + rc.stage * rc.stage_bytes, p1 = p0 + d1, p2 = p0 + d2;
-    StageLoop<K, MT, 0, SG_GROUPS>::run(p0, p1, p2, w, L.a, mc, a_row, acc, rem);
+    StageLoop<K, EX, MT, 0, SG_GROUPS>::run(p0, p1, p2, w, L.a, mc, a_row, acc, rem);
     __syncwarp();
     mbar_arrive_if(bar + SG_EMPTY_OFF, lane0);
     rc.advance();
@@ -287,25 +295,25 @@ __device__ __forceinline__ bool consume_unit(const UnitDesc &d, RingCursor &rc, 
 // per-unit dispatch on the unit's live rows: a launch compiled for up to 8 * MT rows runs a unit with fewer rows through the
 // narrowest path that holds them (one MMA per 8 rows), since most units of a wide launch are experts that only one or two
 // rows selected
-template <int K, int MT, int SUB>
+template <int K, bool EX, int MT, int SUB>
 __device__ __forceinline__ bool consume_rows(const UnitDesc &d, RingCursor &rc, bool live, int lane, const McgConst &mc, uint32_t a_addr,
                                              uint32_t lda_bytes, uint32_t z_addr, const int *rowoff, int col, int *status) {
   if constexpr (SUB < MT) {
-    if (d.nrows <= 8 * SUB) return consume_unit<K, SUB>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status);
-    return consume_rows<K, MT, SUB * 2>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status);
+    if (d.nrows <= 8 * SUB) return consume_unit<K, EX, SUB>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status);
+    return consume_rows<K, EX, MT, SUB * 2>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status);
   } else {
-    return consume_unit<K, MT>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status);
+    return consume_unit<K, EX, MT>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status);
   }
 }
 
-template <int MT>
+template <bool EX, int MT>
 __device__ __forceinline__ bool consume_any(const UnitDesc &d, RingCursor &rc, bool live, int warp, int lane, const McgConst &mc, uint32_t a_addr,
                                             uint32_t lda_bytes, uint32_t z_addr, const int *rowoff, int col, int *status) {
   const uint32_t ring0 = rc.tile0;  // address of stage 0; the warp's tile offset depends on the unit's K
 #define SG_CASE(KK)                                                                                              \
   case KK: {                                                                                                     \
     rc.tile0 = ring0 + (uint32_t)warp * Codec<KK>::TILE_BYTES;                                                   \
-    const bool ok = consume_rows<KK, MT, 1>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status); \
+    const bool ok = consume_rows<KK, EX, MT, 1>(d, rc, live, lane, mc, a_addr, lda_bytes, z_addr, rowoff, col, status); \
     rc.tile0 = ring0;                                                                                            \
     return ok;                                                                                                   \
   }
@@ -320,7 +328,7 @@ __device__ __forceinline__ bool consume_any(const UnitDesc &d, RingCursor &rc, b
 #undef SG_CASE
 }
 
-template <class P, int MT>
+template <class P, int MT, bool EX>
 __global__ void __launch_bounds__(SG_THREADS, SG_CTAS) stream_gemm_kernel(const __grid_constant__ P prob, const StreamLayout lay, int *status) {
   static_assert(sizeof(UnitDesc) <= SG_DESC_UNIT_BYTES, "unit descriptor too large for its shared-memory slot");
   extern __shared__ __align__(128) unsigned char smem[];
@@ -452,7 +460,7 @@ __global__ void __launch_bounds__(SG_THREADS, SG_CTAS) stream_gemm_kernel(const 
     if (!mbar_wait_a(afull_a + (uint32_t)slot * 8u, aphase, status, 4)) return;
     const UnitDesc d = *reinterpret_cast<const UnitDesc *>(desc + (size_t)slot * SG_DESC_BYTES);
     const int *rowoff = reinterpret_cast<const int *>(desc + (size_t)slot * SG_DESC_BYTES + SG_DESC_UNIT_BYTES);
-    if (!consume_any<MT>(d, rc, warp < d.ntiles, warp, lane, mc, a0_addr + (uint32_t)slot * slot_bytes, lda_bytes, z_addr, rowoff, col, status))
+    if (!consume_any<EX, MT>(d, rc, warp < d.ntiles, warp, lane, mc, a0_addr + (uint32_t)slot * slot_bytes, lda_bytes, z_addr, rowoff, col, status))
       return;
     // the stores above read the slot's row offsets: only now may it be refilled
     __syncwarp();

@@ -154,6 +154,7 @@ SIGNATURES = {
     "ne_fn_model_last_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
     "ne_copy_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
     "ne_device_wait_status": (C.c_int, []),
+    "ne_exl3_set_summand_product": (C.c_int, [C.c_int]),
 }
 
 

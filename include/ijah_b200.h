@@ -109,6 +109,18 @@ typedef struct {
   ne_q8_weight sh_gate_q8, sh_up_q8, sh_down_q8;
 } ne_moe_desc;
 
+/* Product mode of the decode-width kernels (ne_exl3_linear*, ne_moe_*, the layer and model objects; not the prefill
+ * kernels, which always multiply the rounded weights). No counterpart in the reference.
+ *   0 (default): every weight enters the tensor core as fp16(lo + hi), the value the EXL3 format defines
+ *                (reference kernels/ne_common.h:133-157); results differ from the reference's only by summation order.
+ *   1: every weight enters as its two fp16 summands lo, hi and the fp32 accumulator forms lo * x + hi * x; the sum is not
+ *      rounded to fp16 first (at most half an fp16 ulp per weight, about 2e-4 relative on an output), which saves one
+ *      instruction per weight in the decode loop. Opt-in.
+ * Returns the previous mode; any other argument only reads it. The mode is read when a call is enqueued: a CUDA graph
+ * (the layer and model objects record theirs on first use of a row count) keeps the mode it was recorded in, so set it
+ * before creating those objects. Not thread-safe against concurrent launches. */
+NE_API int ne_exl3_set_summand_product(int on);
+
 typedef struct ne_moe ne_moe;
 NE_API ne_moe *ne_moe_create(const ne_moe_desc *d, int max_rows); /* max_rows 1..64; allocates all scratch */
 NE_API void ne_moe_free(ne_moe *m);

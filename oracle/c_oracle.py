@@ -46,7 +46,7 @@ def decode_inner(trellis):
     return out
 
 
-def linear_emul(trellis, suh, svh, x, summands=True):
+def linear_emul(trellis, suh, svh, x, summands=False):
     """the Linear in the device arithmetic; summands: each weight multiplied as its two float16 summands (the CUDA decode
     kernels), False: as the rounded float16 value (the reference's kernels, the CUDA prefill kernels)"""
     lib().exl3_emul_summands(int(bool(summands)))
@@ -66,7 +66,7 @@ def router_logits(w_bf16, x):
 
 
 def moe_block_emul(tensors, x, top_k=10, layer=0, ids=None, weights=None, want_gu=False, expert_range=None,
-                   shared_rows=None, summands=True):
+                   shared_rows=None, summands=False):
     """The MoE block in the device arithmetic on a packgen-style tensor dict. Returns dict(logits [M, E+1], ids,
     weights, routed, shared_gu, shared_down, out[, experts_gu]). expert_range (e0, e1) keeps only the slots whose
     expert lies in [e0, e1); shared_rows (r0, n) adds the shared expert for rows [r0, r0 + n) only (the summand one

@@ -126,7 +126,7 @@ def exl3_linear_exact(x, trellis, suh, svh):
     return np.asarray(x, np.float64) @ W
 
 
-def exl3_linear_emul(x, trellis, suh, svh, inner=None, summands=True):
+def exl3_linear_emul(x, trellis, suh, svh, inner=None, summands=False):
     """y_emul of tests/trunk6/check_kernels.py:93-99: device arithmetic, float64 after the float16 operand. summands:
     every weight enters the product as its two float16 summands (the CUDA decode kernels: no half add, hence no rounding
     of the sum); False: as the rounded float16 value (the reference's kernels, the CUDA prefill kernels)"""
@@ -202,7 +202,7 @@ def moe_block_exact(x, router_w, sgate_w, experts, shared, top_k=10):
                 out=(routed + scale * sh).astype(np.float32))
 
 
-def moe_block_emul(x, router_w, sgate_w, experts, shared, top_k=10, ids=None, w=None, summands=True):
+def moe_block_emul(x, router_w, sgate_w, experts, shared, top_k=10, ids=None, w=None, summands=False):
     """The block in the device arithmetic order (kernels/fn_moe.metal:304-343 gate/up, :370-445 down): float16
     prepared operands, raw inner products, H * svh, silu(g) * u * suh_down, H, float16, down, H * svh * w_k, slots
     summed in slot order, + sigmoid(shared logit) * shared. Returns dict with the intermediates the C ABI exposes."""

@@ -188,13 +188,13 @@ def test_prefill_4096_tokens_zipf(eng):
     cold = np.argsort(pop.min(1))[:24]
     rnd = np.random.default_rng(5).choice(n, 16, replace=False)
     sample = np.unique(np.concatenate([hot, cold, rnd]))
-    want = CO.moe_block_emul(th, x[sample], top_k=TOPK, summands=False)  # prefill: rounded fp16 weights
+    want = CO.moe_block_emul(th, x[sample], top_k=TOPK)
     assert np.array_equal(want["ids"], want_ids[sample])
     assert rel_max(y[sample], want["out"]) < 2e-4
     ex = exact_block(FastView(th), x[sample[:4]], TOPK)
     assert rel_max(y[sample[:4]], ex["out"]) < 2e-3
     # the decode-width kernels give the same rows
     ref = blk.forward(xd[sample[:16]].contiguous()).cpu().numpy()
-    assert rel_max(y[sample[:16]], ref) < 1e-3  # decode: unrounded sums of the weights' two fp16 summands; prefill: rounded
+    assert rel_max(y[sample[:16]], ref) < 2e-4  # same weights, fp32 accumulation order differs
     assert np.array_equal(y, blk.prefill(xd).cpu().numpy()), "two runs must be bit-identical"
     blk.free()

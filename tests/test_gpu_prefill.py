@@ -27,7 +27,7 @@ def test_prefill_matches_oracle_small(eng):
     blk = E.MoeBlock(eng, t, top_k=4, max_rows=16)
     y = blk.prefill(torch.from_numpy(x).cuda()).cpu().numpy()
     assert eng.lib.ne_device_wait_status() == 0
-    want = CO.moe_block_emul(t, x, top_k=4, summands=False)  # the prefill kernels multiply the rounded fp16 weights
+    want = CO.moe_block_emul(t, x, top_k=4)
     assert rel_max(y, want["out"]) < 2e-4
     y2 = blk.prefill(torch.from_numpy(x).cuda()).cpu().numpy()
     assert np.array_equal(y, y2), "two runs must be bit-identical"
@@ -54,8 +54,7 @@ def test_prefill_equals_decode_path_with_skewed_routing(eng):
     y = blk.prefill(xd).cpu().numpy()
     assert eng.lib.ne_device_wait_status() == 0
     ref = np.concatenate([blk.forward(xd[i:i + 16]).cpu().numpy() for i in range(0, 300, 16)])
-    # decode multiplies every weight as its two fp16 summands, prefill as their rounded fp16 sum; accumulation order differs too
-    assert rel_max(y, ref) < 1e-3
+    assert rel_max(y, ref) < 2e-4  # fp32 accumulation order differs (tcgen05 vs mma.sync + k-splits)
     ids = np.concatenate([CO.moe_block_emul(t, x[i:i + 1], top_k=4)["ids"] for i in range(0, 300, 37)])
     assert ids.shape[1] == 4
 
@@ -72,9 +71,8 @@ def test_prefill_at_model_dims(eng):
     y = blk.prefill(xd).cpu().numpy()
     assert eng.lib.ne_device_wait_status() == 0
     ref = np.concatenate([blk.forward(xd[i:i + 16]).cpu().numpy() for i in range(0, 200, 16)])
-    # decode multiplies every weight as its two fp16 summands, prefill as their rounded fp16 sum; accumulation order differs too
-    assert rel_max(y, ref) < 1e-3
-    want = CO.moe_block_emul(t, x[:3], top_k=10, summands=False)
+    assert rel_max(y, ref) < 2e-4  # fp32 accumulation order differs (tcgen05 vs mma.sync + k-splits)
+    want = CO.moe_block_emul(t, x[:3], top_k=10)
     assert rel_max(y[:3], want["out"]) < 2e-4
 
 
@@ -90,10 +88,10 @@ def test_trunk_linear_prefill_matches_oracle_and_decode_path(eng, n_in, n_out, K
     xd = torch.from_numpy(x).cuda()
     y = lin.prefill(xd).cpu().numpy()
     assert eng.lib.ne_device_wait_status() == 0
-    want = np.concatenate([CO.linear_emul(tr, suh, svh, x[i:i + 64], summands=False) for i in range(0, rows, 64)])  # the oracle takes <= 64 rows
+    want = np.concatenate([CO.linear_emul(tr, suh, svh, x[i:i + 64]) for i in range(0, rows, 64)])  # the oracle takes <= 64 rows
     assert np.linalg.norm(y - want) / np.linalg.norm(want) < 5e-5
     ref = np.concatenate([lin(xd[i:i + 64]).cpu().numpy() for i in range(0, rows, 64)])
-    assert rel_max(y, ref) < 1e-3  # the decode path multiplies the unrounded sums of the weights' two fp16 summands
+    assert rel_max(y, ref) < 2e-4
     assert np.array_equal(y, lin.prefill(xd).cpu().numpy()), "two runs must be bit-identical"
 
 
@@ -122,7 +120,7 @@ def test_prefill_ep_summands_add_up_to_the_block(eng):
         part = blk.prefill_ep(x_all, 50 * r, 50).cpu().numpy()
         assert eng.lib.ne_device_wait_status() == 0
         for i in (0, 64, 128):
-            want = CO.moe_block_emul(t, x[i:i + 22], top_k=4, summands=False, expert_range=(16 * r, 16 * r + 16),
+            want = CO.moe_block_emul(t, x[i:i + 22], top_k=4, expert_range=(16 * r, 16 * r + 16),
                                      shared_rows=(max(50 * r - i, 0), max(min(50 * r + 50, i + 22) - max(50 * r, i), 0)))["out"]
             assert rel_max(part[i:i + 22], want) < 2e-4
         total += part
