@@ -319,6 +319,47 @@ def prefill_figure(eng, n_pf, dev):
             "frac_of_dense_f16_peak": flop / pms / 1e9 / tpeak, "routing": "Zipf(1.1) bias on the router logits"}
 
 
+def prefill_ep_figure(eng, dev, rank, world, n_total):
+    """Expert-parallel prefill of n_total tokens split evenly over the ranks (strong scaling against the single-GPU
+    `prefill` figure): the all-to-all form (ep.prefill_a2a) and the all-gather + reduce-scatter form, device-timed, max
+    over ranks. Every rank calls this."""
+    import torch
+    import torch.distributed as dist
+    from ijah_b200 import engine as E
+    from ijah_b200 import ep, synth
+    per, n = DIMS["experts"] // world, n_total // world
+    last = synth.moe_layer(1007, router_seed=84, device=dev, expert_first=rank * per, expert_count=per, **DIMS)
+    synth.zipf_router_bias(last)
+    blk = E.MoeBlock(eng, last, top_k=TOPK, max_rows=16, expert_first=rank * per, expert_count=per, device=dev)
+    par = ep.ExpertParallelMoe(blk, dist.group.WORLD)
+    gp = torch.Generator(device=dev).manual_seed(99 + rank)
+    xp = torch.randn((n, DIMS["hidden"]), device=dev, generator=gp).to(torch.float16).to(torch.float32)
+    xp[:, 0] = 1.0
+    yp = torch.empty_like(xp)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(5):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        tt = torch.tensor([t0.elapsed_time(t1) / 5], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt[0])
+
+    a2a = timed(lambda: par.prefill_a2a(xp, out=yp))
+    gat = timed(lambda: par.forward(xp, out=yp, prefill=True))
+    blk.free()
+    return {"tokens_total": n * world, "tokens_per_rank": n, "all_to_all_ms": a2a, "all_to_all_tok_per_s": n * world / a2a * 1e3,
+            "allgather_reduce_ms": gat, "routing": "Zipf(1.1) bias on the router logits",
+            "note": "the single-GPU time of the same token count is extra.prefill.ms of the N = 1 line"}
+
+
 # ---------------------------------------------------------------------------------------------- the stack (headline)
 def run_stack(a, rank, world):
     import torch
@@ -445,6 +486,10 @@ def run_stack(a, rank, world):
     if xchg is not None:
         xchg.free(barrier=lambda: dist.barrier())
     torch.cuda.empty_cache()
+    if N > 1 and a.extras:
+        pe = prefill_ep_figure(eng, dev, rank, N, 4096)
+        if rank == 0:
+            extra["prefill_ep"] = pe
 
     roof, cpu = None, None
     if N == 1 and rank == 0:

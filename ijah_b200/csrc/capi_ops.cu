@@ -80,20 +80,29 @@ Moe::~Moe() {
 }
 
 // Prefill: n tokens at once through the sorted / grouped path (pf_moe.cu). Scratch grows with the largest n seen.
-void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st) {
+// mode 0: route the n tokens here, run the slots of the experts this object holds and the shared expert of the own rows.
+// mode PF_HOME: route here, no routed expert at all (their slots are computed by the owners), shared expert of all n tokens.
+// mode PF_ROUTED: n (token, slot) pairs that were routed elsewhere: route_in [n][2] = (global expert id, weight bits), every
+//   id inside this object's slice; y[i] = weight_i * expert_i(x[i]), no shared expert.
+void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st, int mode, const uint32_t *route_in) {
   IJ_CHECK(!shared_q8, "an 8-bit affine shared expert runs in the decode-width single-GPU calls only (ne_moe_forward, ne_moe_stage)");
   IJ_CHECK(n >= 1 && n <= 65535, "prefill: %d tokens outside 1..65535", n);
   IJ_CHECK(own_row0 >= 0 && own_rows >= 0 && own_row0 + own_rows <= n, "own rows [%d, %d) outside [0, %d)", own_row0, own_row0 + own_rows, n);
-  const size_t H = desc.hidden, I = desc.inter, E = desc.experts, k = desc.top_k;
-  if (n > pf_tokens) {
+  IJ_CHECK((mode == PF_ROUTED) == (route_in != nullptr), "prefill: a route array goes with the routed mode only");
+  const size_t H = desc.hidden, I = desc.inter, E = desc.experts;
+  const size_t k = mode == PF_ROUTED ? 1 : desc.top_k;
+  const bool shared = has_shared && mode != PF_ROUTED;
+  if (n > pf_tokens || n * (int)k > pf_slots) {
     IJ_CUDA(cudaDeviceSynchronize());
     for (void *p : pf_owned) cudaFree(p);
     pf_owned.clear();
+    pf_tokens = std::max(pf_tokens, n);
+    pf_slots = std::max(pf_slots, n * (int)k);
     auto al = [&](size_t b) { void *p = nullptr; IJ_CUDA(cudaMalloc(&p, std::max<size_t>(b, 16))); pf_owned.push_back(p); return p; };
-    const size_t S = (size_t)n * k, cap = pf_pos_cap(n, (int)k, (int)E, has_shared);
-    const size_t passes = S / PF_NTOK + E + n / PF_NTOK + 2;
-    pf.logits = (float *)al((size_t)n * (E + 1) * 4);
-    pf.route = (uint32_t *)al((size_t)n * 2 * k * 4);
+    const size_t T = pf_tokens, S = pf_slots, cap = ((S + 8 * E + T + 15) / 8) * 8;  // >= pf_pos_cap of any call that fits
+    const size_t passes = S / PF_NTOK + E + T / PF_NTOK + 2;
+    pf.logits = (float *)al(T * (E + 1) * 4);
+    pf.route = (uint32_t *)al(T * 2 * desc.top_k * 4);
     pf.cnt = (int *)al(E * 4);
     pf.off = (int *)al((E + 2) * 4);
     pf.hist = (int *)al(((S + 255) / 256) * E * 4);
@@ -108,16 +117,16 @@ void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, c
     pf.items_gu = (PfItem *)al(passes * 2 * (I / PF_NCOL) * sizeof(PfItem));
     pf.items_d = (PfItem *)al(passes * (H / PF_NCOL) * sizeof(PfItem));
     pf.nitems = (int *)al(16);
-    pf.sho = (float *)al((size_t)n * H * 4);
-    pf.pos_cap = (int)cap;
-    pf_tokens = n;
+    pf.sho = (float *)al(T * H * 4);
   }
   PfParams p = pf;
-  p.H = (int)H; p.I = (int)I; p.E = (int)E; p.topk = (int)k; p.Kx = desc.k_expert; p.Ks = desc.k_shared; p.has_shared = has_shared ? 1 : 0;
+  p.H = (int)H; p.I = (int)I; p.E = (int)E; p.topk = (int)k; p.Kx = desc.k_expert; p.Ks = desc.k_shared; p.has_shared = shared ? 1 : 0;
   p.n = n; p.S = n * (int)k;
-  p.e0 = desc.expert_first; p.ecount = desc.expert_count;
-  p.sh_row0 = own_row0; p.sh_rows = own_rows;
-  p.pos_cap = (int)pf_pos_cap(n, (int)k, (int)E, has_shared);
+  p.e0 = desc.expert_first; p.ecount = mode == PF_HOME ? 0 : desc.expert_count;
+  p.sh_row0 = own_row0; p.sh_rows = shared ? own_rows : 0;
+  p.pos_cap = (int)pf_pos_cap(n, (int)k, (int)E, shared);
+  p.external_route = mode == PF_ROUTED ? 1 : 0;
+  if (mode == PF_ROUTED) p.route = const_cast<uint32_t *>(route_in);  // read only in this mode
   p.router = (const uint16_t *)desc.router_dev;
   p.sgate = (const uint16_t *)desc.shared_gate_w_dev;
   auto stack = [](const ne_exl3_stack &s) { return Exl3Stack{(const char *)s.trellis_dev, (const __half *)s.suh_dev, (const __half *)s.svh_dev}; };
@@ -125,7 +134,7 @@ void Moe::prefill(const float *x, int n, int own_row0, int own_rows, float *y, c
   p.gate = stack(desc.gate); p.up = stack(desc.up); p.down = stack(desc.down);
   p.sgt = single(desc.sh_gate); p.sup = single(desc.sh_up); p.sdn = single(desc.sh_down);
   p.x = x; p.y = y;
-  pf_last_n = n;
+  if (mode != PF_ROUTED) pf_last_n = n;
   launch_pf_moe(p, status, st);
 }
 
@@ -580,6 +589,40 @@ NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int o
   return c_call([&] {
     IJ_CHECK(m && x_all_dev && y_part_dev, "null argument");
     reinterpret_cast<Moe *>(m)->prefill(x_all_dev, n_all, own_row0, own_rows, y_part_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_moe_prefill_home(ne_moe *m, const float *x_dev, int n_tokens, float *y_shared_dev, uint32_t *route_out_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_dev && y_shared_dev && route_out_dev, "null argument");
+    Moe *o = reinterpret_cast<Moe *>(m);
+    o->prefill(x_dev, n_tokens, 0, n_tokens, y_shared_dev, (cudaStream_t)stream, Moe::PF_HOME);
+    IJ_CUDA(cudaMemcpyAsync(route_out_dev, o->pf.route, (size_t)n_tokens * 2 * o->desc.top_k * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  });
+}
+NE_API int ne_moe_prefill_routed(ne_moe *m, const float *x_pairs_dev, const uint32_t *route_pairs_dev, int n_pairs, float *y_pairs_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(m && x_pairs_dev && route_pairs_dev && y_pairs_dev, "null argument");
+    reinterpret_cast<Moe *>(m)->prefill(x_pairs_dev, n_pairs, 0, 0, y_pairs_dev, (cudaStream_t)stream, Moe::PF_ROUTED, route_pairs_dev);
+  });
+}
+NE_API int ne_ep_pairs_by_owner(const uint32_t *route_dev, int n_tokens, int top_k, int experts_per_rank, int world, int *send_token_dev,
+                                uint32_t *send_route_dev, int *pos_dev, long long *counts_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(route_dev && send_token_dev && send_route_dev && pos_dev && counts_dev, "null argument");
+    launch_pairs_by_owner(route_dev, n_tokens, top_k, experts_per_rank, world, send_token_dev, send_route_dev, pos_dev, counts_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_rows_gather(const float *src_dev, const int *index_dev, int n_out, int width, float *dst_dev, void *stream) {
+  return c_call([&] {
+    IJ_CHECK(src_dev && index_dev && dst_dev, "null argument");
+    launch_rows_gather(src_dev, index_dev, n_out, width, dst_dev, (cudaStream_t)stream);
+  });
+}
+NE_API int ne_slots_combine(const float *slots_dev, const int *pos_dev, const float *base_dev, float *y_dev, int n_tokens, int top_k, int width,
+                            void *stream) {
+  return c_call([&] {
+    IJ_CHECK(slots_dev && pos_dev && y_dev, "null argument");
+    launch_slots_combine(slots_dev, pos_dev, base_dev, y_dev, n_tokens, top_k, width, (cudaStream_t)stream);
   });
 }
 NE_API int ne_moe_buffer(ne_moe *m, const char *name, void **dev, uint64_t *nbytes) {

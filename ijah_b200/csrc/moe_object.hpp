@@ -36,9 +36,10 @@ struct Moe {
   MoeMaps maps{};  // tensor maps over the trellis stacks
   // prefill scratch, (re)allocated when a call brings more tokens than any before it
   PfParams pf{};
-  int pf_tokens = 0, pf_last_n = 0;
+  int pf_tokens = 0, pf_slots = 0, pf_last_n = 0;  // scratch capacity in tokens and in (token, slot) pairs
   std::vector<void *> pf_owned;
-  void prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st);
+  enum { PF_ALL = 0, PF_HOME = 1, PF_ROUTED = 2 };
+  void prefill(const float *x, int n, int own_row0, int own_rows, float *y, cudaStream_t st, int mode = PF_ALL, const uint32_t *route_in = nullptr);
 
   Moe(const ne_moe_desc &d, int max_rows);
   ~Moe();

@@ -678,7 +678,8 @@ __global__ void __launch_bounds__(256) pf_mid_kernel(const PfParams p) {
 // (reference pf_moe.metal:129-161)
 constexpr int PF_FQ = 512;
 __global__ void __launch_bounds__(32 * 17) pf_finish_kernel(const PfParams p) {
-  __shared__ __align__(16) float vals[17][PF_FQ];
+  extern __shared__ __align__(16) float vals_dyn[];  // [slots][PF_FQ]; the block has one warp per slot, at least 4 warps
+  float(*vals)[PF_FQ] = reinterpret_cast<float(*)[PF_FQ]>(vals_dyn);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q0 = blockIdx.x * PF_FQ, t = blockIdx.y, H = p.H, k = p.topk;
   const int nslots = k + (p.has_shared ? 1 : 0);
   const int nch = min(PF_FQ, H - q0) / 128;
@@ -718,7 +719,7 @@ __global__ void __launch_bounds__(32 * 17) pf_finish_kernel(const PfParams p) {
     for (int i = 0; i < 4; i++) *reinterpret_cast<float4 *>(&vals[warp][i * 128 + 4 * lane]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   }
   __syncthreads();
-  const int c = threadIdx.x * 4;
+  const int c = threadIdx.x * 4;  // 128 threads cover the quarter
   if (c >= nch * 128) return;
   float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (int s = 0; s < nslots; s++) {
@@ -819,9 +820,13 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   IJ_CUDA(cudaMemsetAsync(p.order, 0xFF, (size_t)p.pos_cap * 4, st));
   IJ_CUDA(cudaMemsetAsync(p.seid, 0xFF, (size_t)p.pos_cap * 4, st));
   IJ_CHECK(p.H % LG_K == 0, "prefill: hidden %d must be a multiple of %d", p.H, LG_K);
-  IJ_CUDA(cudaFuncSetAttribute(pf_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM));
-  pf_logits_kernel<<<dim3((p.n + LG_T - 1) / LG_T, (p.E + LG_T - 1) / LG_T), 256, LG_SMEM, st>>>(p);
-  pf_route_kernel<<<(p.n + 7) / 8, 256, 0, st>>>(p);
+  if (!p.external_route) {
+    IJ_CUDA(cudaFuncSetAttribute(pf_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM));
+    pf_logits_kernel<<<dim3((p.n + LG_T - 1) / LG_T, (p.E + LG_T - 1) / LG_T), 256, LG_SMEM, st>>>(p);
+    pf_route_kernel<<<(p.n + 7) / 8, 256, 0, st>>>(p);
+  } else {
+    IJ_CHECK(!p.has_shared, "prefill: caller-routed pairs carry no shared expert");
+  }
   IJ_CHECK(p.e0 >= 0 && p.ecount >= 0 && p.e0 + p.ecount <= p.E, "prefill: bad expert slice");
   IJ_CHECK(p.sh_row0 >= 0 && p.sh_rows >= 0 && p.sh_row0 + p.sh_rows <= p.n, "prefill: shared rows [%d, %d) outside [0, %d)", p.sh_row0, p.sh_row0 + p.sh_rows, p.n);
   const int nb = (p.S + PS_BLOCK - 1) / PS_BLOCK, nbs = p.has_shared ? (p.sh_rows + PS_BLOCK - 1) / PS_BLOCK : 0;
@@ -847,7 +852,103 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st) {
   d.out[0] = p.raw_d;
   d.ldo = p.H; d.in = p.I; d.IT = p.I / 16; d.OT = p.H / 16; d.Kx = p.Kx; d.Ks = g.Ks;
   launch_pf_gemm(d, status, st);
-  pf_finish_kernel<<<dim3((p.H + PF_FQ - 1) / PF_FQ, p.n), 32 * 17, 0, st>>>(p);
+  const int fslots = p.topk + (p.has_shared ? 1 : 0);  // one warp per slot; caller-routed pairs bring a single slot per row
+  pf_finish_kernel<<<dim3((p.H + PF_FQ - 1) / PF_FQ, p.n), 32 * std::max(fslots, 4), (size_t)fslots * PF_FQ * 4, st>>>(p);
+  IJ_CUDA(cudaGetLastError());
+}
+
+// =============================================================================================== all-to-all helpers
+// Stable counting sort of the n * k (token, slot) pairs of a route array by owner rank (= expert id / per): packed row `at`
+// of the dispatch buffer takes pair p, send_token[at] = its token, send_route[at] = (id, weight bits), pos[p] = at,
+// counts[d] = pairs going to rank d. One CTA; every thread owns a contiguous run of pairs, the ranks are placed one
+// after the other with a block-wide exclusive scan each (at most 16 ranks).
+__global__ void __launch_bounds__(1024) pairs_by_owner_kernel(const uint32_t *__restrict__ route, int n, int k, int per, int world,
+                                                              int *__restrict__ send_token, uint32_t *__restrict__ send_route,
+                                                              int *__restrict__ pos, long long *__restrict__ counts) {
+  __shared__ int wsum[32];
+  const int P = n * k, tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = (P + T - 1) / T, lo = min(P, tid * chunk), hi = min(P, lo + chunk);
+  int start = 0;
+  for (int d = 0; d < world; d++) {
+    int mine = 0;
+    for (int pr = lo; pr < hi; pr++) mine += (int)(route[(size_t)(pr / k) * 2 * k + pr % k] / (uint32_t)per) == d ? 1 : 0;
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += a;
+    }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int w = 0; w < T / 32; w++) {
+      before += w < warp ? wsum[w] : 0;
+      total += wsum[w];
+    }
+    int at = start + before + inc - mine;
+    for (int pr = lo; pr < hi; pr++) {
+      const size_t r = (size_t)(pr / k) * 2 * k + pr % k;
+      const uint32_t id = route[r];
+      if ((int)(id / (uint32_t)per) == d) {
+        send_token[at] = pr / k;
+        send_route[2 * at] = id;
+        send_route[2 * at + 1] = route[r + k];
+        pos[pr] = at;
+        at++;
+      }
+    }
+    if (tid == 0) counts[d] = total;
+    start += total;
+    __syncthreads();
+  }
+}
+void launch_pairs_by_owner(const uint32_t *route, int n, int k, int per, int world, int *send_token, uint32_t *send_route, int *pos,
+                           long long *counts, cudaStream_t st) {
+  IJ_CHECK(n >= 1 && k >= 1 && per >= 1 && world >= 1 && world <= 16, "pairs_by_owner: n %d k %d experts per rank %d ranks %d", n, k, per, world);
+  pairs_by_owner_kernel<<<1, 1024, 0, st>>>(route, n, k, per, world, send_token, send_route, pos, counts);
+  IJ_CUDA(cudaGetLastError());
+}
+
+// dst[i] = src[idx[i]] (rows of H floats, H a multiple of 4): packs the (token, slot) pairs of one destination rank after
+// the other for the dispatch all-to-all. One CTA per output row.
+__global__ void __launch_bounds__(256) rows_gather_kernel(const float4 *__restrict__ src, const int *__restrict__ idx, float4 *__restrict__ dst, int q) {
+  const size_t i = blockIdx.x, r = (size_t)idx[i];
+  for (int c = threadIdx.x; c < q; c += blockDim.x) dst[i * q + c] = __ldg(src + r * q + c);
+}
+void launch_rows_gather(const float *src, const int *idx, int n_out, int H, float *dst, cudaStream_t st) {
+  IJ_CHECK(H % 4 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0, "rows_gather: rows of a multiple of 4 floats, 16-byte aligned");
+  if (n_out <= 0) return;
+  rows_gather_kernel<<<n_out, 256, 0, st>>>(reinterpret_cast<const float4 *>(src), idx, reinterpret_cast<float4 *>(dst), H / 4);
+  IJ_CUDA(cudaGetLastError());
+}
+
+// y[t] = ((slot[pos[t][0]] + slot[pos[t][1]]) + .. + slot[pos[t][k-1]]) + base[t]: the combine of the all-to-all prefill on a
+// token's home rank. The slots are added in slot order and the shared expert's term last, as pf_finish_kernel does on one
+// GPU, so the result is bit-identical to it. pos < 0 skips a slot.
+__global__ void __launch_bounds__(256) slots_combine_kernel(const float4 *__restrict__ slot, const int *__restrict__ pos, const float4 *__restrict__ base,
+                                                            float4 *__restrict__ y, int k, int q) {
+  const size_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < q; c += blockDim.x) {
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < k; s++) {
+      const int ps = pos[t * k + s];
+      if (ps >= 0) {
+        const float4 v = __ldg(slot + (size_t)ps * q + c);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    if (base != nullptr) {
+      const float4 b = base[t * q + c];
+      acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+    }
+    y[t * q + c] = acc;
+  }
+}
+void launch_slots_combine(const float *slot, const int *pos, const float *base, float *y, int n, int k, int H, cudaStream_t st) {
+  IJ_CHECK(H % 4 == 0 && (((uintptr_t)slot | (uintptr_t)base | (uintptr_t)y) & 15) == 0, "slots_combine: rows of a multiple of 4 floats, 16-byte aligned");
+  IJ_CHECK(n >= 1 && k >= 1, "slots_combine: %d tokens, %d slots", n, k);
+  slots_combine_kernel<<<n, 256, 0, st>>>(reinterpret_cast<const float4 *>(slot), pos, reinterpret_cast<const float4 *>(base),
+                                          reinterpret_cast<float4 *>(y), k, H / 4);
   IJ_CUDA(cudaGetLastError());
 }
 

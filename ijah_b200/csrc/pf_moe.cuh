@@ -30,6 +30,7 @@ struct PfParams {
   int n;           // tokens
   int S;           // n * topk slots
   int pos_cap;     // capacity of the padded position space
+  int external_route;  // `route` was filled by the caller ([n][2 topk], read only): no router GEMM, no top-k
   // weights
   const uint16_t *router, *sgate;
   Exl3Stack gate, up, down, sgt, sup, sdn;
@@ -65,5 +66,11 @@ void launch_pf_moe(const PfParams &p, int *status, cudaStream_t st);
 size_t pf_linear_scratch_bytes(int in, int out, int n);
 void launch_pf_linear(const void *trellis, const void *suh, const void *svh, int in, int out, int K, const float *x, int n, float *y,
                       void *scratch, int *status, cudaStream_t st);
+
+// helpers of the all-to-all expert-parallel prefill: pack rows by index; add a token's returned slots in slot order
+void launch_pairs_by_owner(const uint32_t *route, int n, int k, int per, int world, int *send_token, uint32_t *send_route, int *pos,
+                           long long *counts, cudaStream_t st);
+void launch_rows_gather(const float *src, const int *idx, int n_out, int H, float *dst, cudaStream_t st);
+void launch_slots_combine(const float *slot, const int *pos, const float *base, float *y, int n, int k, int H, cudaStream_t st);
 
 }  // namespace ijah

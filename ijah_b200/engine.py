@@ -131,6 +131,11 @@ SIGNATURES = {
     "ne_moe_forward_ep_fused": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_prefill_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "ne_moe_forward_ep": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_moe_prefill_home": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ne_moe_prefill_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_ep_pairs_by_owner": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ne_rows_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "ne_slots_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "ne_moe_buffer": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
     "ne_moe_experts_gu": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "ne_moe_last_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
@@ -781,6 +786,57 @@ class MoeBlock:
         y = torch.empty((n, self.H), dtype=torch.float32, device=x_all.device) if out is None else out
         self.eng._ok(self.eng.lib.ne_moe_prefill_ep(self.ptr, _dev(x_all), n, own_row0, own_rows, _dev(y), _stream()),
                      "ne_moe_prefill_ep")
+        return y
+
+    # ---- the pieces of the all-to-all expert-parallel prefill (ijah_b200/ep.py puts the two exchanges between them)
+    def prefill_home(self, x):
+        """(y_shared [n, H], route int32 [n, 2k] = ids then f32 weight bits) of the rank's own tokens: routing and the
+        shared expert, no routed expert (ne_moe_prefill_home)"""
+        torch = _torch()
+        n = x.shape[0]
+        y = torch.empty((n, self.H), dtype=torch.float32, device=x.device)
+        route = torch.empty((n, 2 * self.k), dtype=torch.int32, device=x.device)
+        self.eng._ok(self.eng.lib.ne_moe_prefill_home(self.ptr, _dev(x), n, _dev(y), _dev(route), _stream()), "ne_moe_prefill_home")
+        return y, route
+
+    def prefill_routed(self, x_pairs, route_pairs):
+        """weight * expert(x) for (token, slot) pairs routed elsewhere; route_pairs int32 [n, 2] = (expert id, f32 weight
+        bits), every id one of this block's experts (ne_moe_prefill_routed)"""
+        torch = _torch()
+        n = x_pairs.shape[0]
+        y = torch.empty((n, self.H), dtype=torch.float32, device=x_pairs.device)
+        if n:
+            self.eng._ok(self.eng.lib.ne_moe_prefill_routed(self.ptr, _dev(x_pairs), _dev(route_pairs), n, _dev(y), _stream()),
+                         "ne_moe_prefill_routed")
+        return y
+
+    def pairs_by_owner(self, route, world):
+        """(send_token int32 [n k], send_route int32 [n k, 2], pos int32 [n, k], counts int64 [world]) of a route array:
+        its pairs in owner-rank order (ne_ep_pairs_by_owner)"""
+        torch = _torch()
+        n, k, dev = route.shape[0], self.k, route.device
+        tok = torch.empty(n * k, dtype=torch.int32, device=dev)
+        sr = torch.empty((n * k, 2), dtype=torch.int32, device=dev)
+        pos = torch.empty((n, k), dtype=torch.int32, device=dev)
+        counts = torch.empty(world, dtype=torch.int64, device=dev)
+        self.eng._ok(self.eng.lib.ne_ep_pairs_by_owner(_dev(route), n, k, self.E // world, world, _dev(tok), _dev(sr), _dev(pos), _dev(counts),
+                                                       _stream()), "ne_ep_pairs_by_owner")
+        return tok, sr, pos, counts
+
+    def gather_rows(self, src, index):
+        """src[index] for rows of float32 (ne_rows_gather); index int32 on the device"""
+        torch = _torch()
+        out = torch.empty((index.shape[0], src.shape[1]), dtype=torch.float32, device=src.device)
+        if index.shape[0]:
+            self.eng._ok(self.eng.lib.ne_rows_gather(_dev(src), _dev(index), index.shape[0], src.shape[1], _dev(out), _stream()), "ne_rows_gather")
+        return out
+
+    def combine_slots(self, slots, pos, base, out=None):
+        """y[t] = slots[pos[t, 0]] + .. + slots[pos[t, k-1]] + base[t], in that order (ne_slots_combine); pos int32 [n, k]"""
+        torch = _torch()
+        n, k = pos.shape
+        y = torch.empty((n, slots.shape[1]), dtype=torch.float32, device=slots.device) if out is None else out
+        self.eng._ok(self.eng.lib.ne_slots_combine(_dev(slots), _dev(pos), _dev(base), _dev(y), n, k, slots.shape[1], _stream()), "ne_slots_combine")
         return y
 
     def forward_ep(self, x_all, own_row0, own_rows, out=None):

@@ -12,6 +12,11 @@ The reference is single-device; expert parallelism is this library's addition. R
                (Blocks without route_rows, and the prefill path, route all rows on every rank: forward_ep / prefill_ep.)
     combine    reduce_scatter (sum) of y_part                          -> y [rows, H] of the rank's own rows
 
+The many-token prefill has a second form, prefill_a2a: a true all-to-all. Each token is routed on its home rank, every
+(token, slot) pair is sent to the one rank that owns its expert (all_to_all_single with the pair counts exchanged first),
+the owner runs its pairs through the grouped tensor-core GEMM, the per-pair outputs return by the mirrored all-to-all and
+the home rank adds a token's slots in slot order and the shared expert last: bit-identical to the single-GPU prefill.
+
 At decode widths the payload is tiny (rows * H * 4 bytes per rank each way), so both collectives are latency-bound and
 the win is the N-fold drop in weight bytes per GPU. The sum over ranks changes the order in which a row's slots are
 added (per-rank partial sums in slot order, then ranks in the collective's order); the result stays within the 2e-3
@@ -126,3 +131,24 @@ class ExpertParallelMoe:
         else:
             dist.reduce_scatter_tensor(y, y_part, group=self.group)
         return y
+
+    def prefill_a2a(self, x, out=None):
+        """x [n, H] float32, the rank's own tokens (any count per rank, zero excluded) -> y [n, H]. The block needs
+        prefill_home, pairs_by_owner, gather_rows, prefill_routed, combine_slots and k (engine.MoeBlock has them)."""
+        b, N, k = self.block, self.world, self.block.k
+        n, H = x.shape
+        x = x.contiguous()
+        y_sh, route = b.prefill_home(x)                      # routing + shared expert of the own tokens
+        tok, send_r, pos, counts = b.pairs_by_owner(route, N)  # pairs grouped by owner, (token, slot) order inside a group
+        got = torch.empty_like(counts)
+        dist.all_to_all_single(got, counts, group=self.group)
+        send_n, recv_n = counts.tolist(), got.tolist()       # the one host synchronisation of the call
+        send_x = b.gather_rows(x, tok)
+        recv_x = torch.empty((sum(recv_n), H), dtype=torch.float32, device=x.device)
+        recv_r = torch.empty((sum(recv_n), 2), dtype=torch.int32, device=x.device)
+        dist.all_to_all_single(recv_x, send_x, recv_n, send_n, group=self.group)
+        dist.all_to_all_single(recv_r, send_r, recv_n, send_n, group=self.group)
+        y_pairs = b.prefill_routed(recv_x, recv_r)           # this rank's experts on everybody's pairs
+        back = torch.empty((n * k, H), dtype=torch.float32, device=x.device)
+        dist.all_to_all_single(back, y_pairs, send_n, recv_n, group=self.group)
+        return b.combine_slots(back, pos, y_sh, out=out)     # slots in slot order, the shared term last

@@ -178,6 +178,27 @@ NE_API int ne_moe_forward_ep_fused(ne_moe *m, ne_ep *e, const float *x_own_dev, 
  * token is routed (same result on every rank), only the slots whose expert lies in this object's slice are sorted and
  * computed, the shared expert runs for the caller's own tokens only. y_part[n_all][hidden] is this rank's summand. */
 NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int own_row0, int own_rows, float *y_part_dev, void *stream);
+/* Expert-parallel prefill as an all-to-all (the dispatch / combine the path's multi-GPU form names): a token is routed on
+ * its home rank only, each (token, slot) pair travels to the one rank that owns its expert and its output travels back.
+ *   home:   ne_moe_prefill_home    routes n tokens (router GEMM + top-k) and runs their shared expert, no routed expert:
+ *                                  y_shared [n][hidden] = sigmoid(x . w_sg) * shared(x), route_out [n][2 * top_k] (ids, f32 weights)
+ *           ne_ep_pairs_by_owner   stable counting sort of the n * top_k pairs by owner rank (id / experts_per_rank): packed row
+ *                                  -> token (send_token) and (id, weight bits) (send_route), pair -> packed row (pos), pairs per
+ *                                  rank (counts, int64: the split sizes of the exchange)
+ *           ne_rows_gather         dst[i] = src[index[i]]: packs the pairs' activation rows in that order
+ *   owner:  ne_moe_prefill_routed  n_pairs received pairs, route_pairs [n_pairs][2] = (global expert id inside this object's
+ *                                  slice, f32 weight bits): y_pairs[i] = weight_i * expert_i(x_pairs[i]) through the grouped
+ *                                  tensor-core GEMM (counting sort by expert as in ne_moe_prefill, one slot per row)
+ *   home:   ne_slots_combine       y[t] = slot[pos[t][0]] + .. + slot[pos[t][top_k-1]] + base[t], slots in slot order, the
+ *                                  shared term last: bit-identical to ne_moe_prefill on one GPU holding all experts
+ * The two exchanges in between are the caller's (ijah_b200/ep.py: torch.distributed all_to_all_single over NCCL). */
+NE_API int ne_moe_prefill_home(ne_moe *m, const float *x_dev, int n_tokens, float *y_shared_dev, uint32_t *route_out_dev, void *stream);
+NE_API int ne_moe_prefill_routed(ne_moe *m, const float *x_pairs_dev, const uint32_t *route_pairs_dev, int n_pairs, float *y_pairs_dev, void *stream);
+NE_API int ne_ep_pairs_by_owner(const uint32_t *route_dev, int n_tokens, int top_k, int experts_per_rank, int world, int *send_token_dev,
+                                uint32_t *send_route_dev, int *pos_dev, long long *counts_dev, void *stream);
+NE_API int ne_rows_gather(const float *src_dev, const int *index_dev, int n_out, int width, float *dst_dev, void *stream);
+NE_API int ne_slots_combine(const float *slots_dev, const int *pos_dev, const float *base_dev, float *y_dev, int n_tokens, int top_k, int width,
+                            void *stream);
 /* Device pointer and size of a named intermediate of the last run: "logits" "route" "shared_gu" "shared_down"
  * "experts_gu_raw" (per k-split partial products [S][rows*top_k][2][inter]) "plan"; of the last ne_moe_prefill:
  * "prefill_route" [n][2*top_k] (ids, then f32 weights), "prefill_counts" [experts] slots per expert,

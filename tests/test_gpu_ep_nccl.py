@@ -48,6 +48,13 @@ xp = torch.from_numpy(x_all[rank * 40:(rank + 1) * 40]).to(dev)
 wantp = full.prefill(torch.from_numpy(x_all).to(dev))[rank * 40:(rank + 1) * 40]
 gotp = par.forward(xp, prefill=True)
 err_p = float((gotp - wantp).abs().max() / wantp.abs().max())
+# the same as an all-to-all (each pair computed once, by the owner of its expert; unequal token counts per rank): bit-identical
+n0 = 40 + 13 * rank
+lo = 0 if rank == 0 else 40
+xa = torch.from_numpy(x_all[lo:lo + n0]).to(dev)
+wanta = full.prefill(torch.from_numpy(x_all[lo:lo + n0]).to(dev))
+gota = par.prefill_a2a(xa)
+a2a_equal = bool(torch.equal(gota, wanta))
 # the whole decoder stack, expert parallel, replayed from the library's CUDA graph: logits of this rank's rows against a
 # single-GPU model over the rows of both ranks (synthetic weights do not depend on which slice a rank holds)
 d = dict(layers=2, hidden=512, inter=256, experts=32, top_k=4, k_expert=5, k_shared=6, q_out=256, kv_out=128, heads=4, kv_heads=2,
@@ -70,7 +77,7 @@ dist.barrier()
 mp.free(); mf.free()
 xm.free(barrier=dist.barrier); xchg.free(barrier=dist.barrier)
 dist.destroy_process_group()
-assert err_d < 1e-5 and err_p < 1e-5 and err_m < 1e-4 and status == 0, (err_d, err_p, err_m, status)
+assert err_d < 1e-5 and err_p < 1e-5 and err_m < 1e-4 and status == 0 and a2a_equal, (err_d, err_p, err_m, status, a2a_equal)
 print("EP_OK", rank, err_d, err_p, err_m)
 """
 

@@ -127,3 +127,43 @@ def test_prefill_ep_summands_add_up_to_the_block(eng):
     assert rel_max(total, full) < 1e-5
     with pytest.raises(E.EngineError):  # the single-GPU entry point refuses an object that holds a slice
         blk.prefill(x_all)
+
+
+def test_prefill_all_to_all_pieces_reproduce_the_block_bit_for_bit(eng):
+    # the all-to-all expert-parallel prefill with its three "ranks" as three objects on one GPU and the two exchanges done
+    # by indexing: routing + shared expert at home, every (token, slot) pair through the object that owns its expert, slots
+    # added in slot order
+    import torch
+    from ijah_b200 import engine as E
+    rng = np.random.default_rng(32)
+    t = packgen.moe_layer(rng, hidden=512, inter=256, experts=48)
+    k = 4
+    x = torch.from_numpy(rng.standard_normal((300, 512)).astype(np.float16).astype(np.float32)).cuda()
+    full = E.MoeBlock(eng, t, top_k=k, max_rows=8)
+    want = full.prefill(x)
+    ids_full = full.buffer("prefill_route", np.uint32).reshape(300, 2 * k)
+    blks = [E.MoeBlock(eng, t, top_k=k, max_rows=8, expert_first=16 * r, expert_count=16) for r in range(3)]
+    y_sh, route = blks[1].prefill_home(x)
+    assert np.array_equal(route.cpu().numpy().view(np.uint32), ids_full), "home routing = the block's own routing"
+    ids = route[:, :k].reshape(-1)
+    back = torch.zeros((300 * k, 512), device="cuda")
+    pos = torch.arange(300 * k, dtype=torch.int32, device="cuda")
+    for r in range(3):
+        mine = torch.nonzero((ids >= 16 * r) & (ids < 16 * r + 16)).reshape(-1)
+        xr = blks[r].gather_rows(x, (mine // k).to(torch.int32))
+        assert torch.equal(xr, x[mine // k])
+        rr = torch.stack((ids[mine], route[:, k:].reshape(-1)[mine]), 1).contiguous()
+        back[mine] = blks[r].prefill_routed(xr, rr)
+    assert eng.lib.ne_device_wait_status() == 0
+    got = blks[0].combine_slots(back, pos.view(300, k), y_sh)
+    assert torch.equal(got, want)
+    # the packing kernel: a stable counting sort of the pairs by owner rank
+    tok, sr, ps, counts = blks[0].pairs_by_owner(route, 3)
+    dest = ids // 16
+    perm = torch.argsort(dest, stable=True)
+    assert torch.equal(counts, torch.bincount(dest, minlength=3)) and torch.equal(tok, (perm // k).to(torch.int32))
+    assert torch.equal(sr[:, 0], ids[perm]) and torch.equal(sr[:, 1], route[:, k:].reshape(-1)[perm])
+    assert torch.equal(ps.reshape(-1)[perm], torch.arange(300 * k, dtype=torch.int32, device="cuda"))
+    # an object asked for a pair whose expert it does not hold contributes nothing for it
+    odd = torch.stack((torch.full((5,), 40, dtype=torch.int32, device="cuda"), route[:5, k]), 1).contiguous()
+    assert float(blks[0].prefill_routed(x[:5].contiguous(), odd).abs().max()) == 0.0
