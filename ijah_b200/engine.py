@@ -805,9 +805,10 @@ class MoeBlock:
         torch = _torch()
         n = x_pairs.shape[0]
         y = torch.empty((n, self.H), dtype=torch.float32, device=x_pairs.device)
-        if n:
-            self.eng._ok(self.eng.lib.ne_moe_prefill_routed(self.ptr, _dev(x_pairs), _dev(route_pairs), n, _dev(y), _stream()),
-                         "ne_moe_prefill_routed")
+        for i in range(0, n, 65535):  # one call takes at most 65535 rows
+            m = min(65535, n - i)
+            self.eng._ok(self.eng.lib.ne_moe_prefill_routed(self.ptr, _dev(x_pairs[i:i + m]), _dev(route_pairs[i:i + m]), m, _dev(y[i:i + m]),
+                                                            _stream()), "ne_moe_prefill_routed")
         return y
 
     def pairs_by_owner(self, route, world):
