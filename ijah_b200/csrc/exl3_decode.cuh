@@ -124,9 +124,9 @@ __device__ __forceinline__ void dec8(uint32_t w0, uint32_t w1, uint32_t w2, uint
   }
 }
 
-// The same 8 slots left as their summand pairs: r[t] = (lo, hi) with weight = lo + hi. A tensor-core product that takes
-// both halves as two k elements against a twice-repeated activation adds them in its fp32 accumulator, so the half add
-// and the pack of dec8 (12 instructions per tile) are not executed at all; the sum is then not rounded to fp16 first.
+// The same 8 slots left as their summand pairs: r[t] = (lo, hi) with weight = fp16(lo + hi). The stream kernels build the
+// tensor-core operand from these words directly (one half add per word for the exact weight, none for the opt-in summand
+// product), so the pack of dec8 (two weights per register) is not executed.
 template <int K>
 __device__ __forceinline__ void dec8_raw(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t a, const McgConst &c, uint32_t (&r)[8]) {
   if constexpr (Codec<K>::UNIFORM) {

@@ -96,13 +96,15 @@ __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
 }
 
 // k-tile I of a stage for one output tile. The tensor core computes D^T = W'^T * X^T: the decoded tile is the A operand
-// (16 output columns x 16 k), the activations are the B operand (16 k x 8 rows). Each decoded weight stays the pair of
+// (16 output columns x 16 k), the activations are the B operand (16 k x 8 rows). Each decoded weight arrives as the pair of
 // fp16 summands (lo, hi) the codebook function yields (dec8_raw) and takes the place of TWO k elements of the A fragment,
-// against activation rows that hold every input twice (store_a): the accumulator adds lo * x + hi * x, which is
-// (lo + hi) * x without the half add, and the 16 inputs of the k-tile take two mma.m16n8k16 per 8 activation rows, the
-// even inputs (slots 0, 4, 2, 6 of the lane) and the odd ones (slots 1, 5, 3, 7). MT = number of 8-row groups (1, 2, 4, 8);
-// a_row[g] is the ldmatrix address of row group g for k-tile 0 of the stage, tile I sits I * 64 bytes further in the A rows.
-// acc[g] = D^T fragment of group g: (column gq, rows 2q, 2q+1), (column gq + 8, ..).
+// against activation rows that hold two halfs per input (store_a), so the 16 inputs of the k-tile take two mma.m16n8k16
+// per 8 activation rows: the even inputs (slots 0, 4, 2, 6 of the lane) and the odd ones (slots 1, 5, 3, 7).
+//   EX (default): one half add turns (lo, hi) into (w, w), w = fp16(lo + hi), the weight as the format defines it; the
+//                 rows hold (v, 0) and the accumulator receives w * v.
+//   !EX (opt-in): (lo, hi) goes in as it is against (v, v): lo * v + hi * v, the sum of the summands unrounded.
+// MT = number of 8-row groups (1, 2, 4, 8); a_row[g] is the ldmatrix address of row group g for k-tile 0 of the stage,
+// tile I sits I * 64 bytes further in the A rows. acc[g] = D^T fragment of group g: (column gq, rows 2q, 2q+1), (column gq + 8, ..).
 constexpr uint32_t SG_A_TILE_BYTES = 16 * A_HALFS_PER_INPUT * 2;  // one k-tile of one prepared activation row
 
 template <int K, bool EX, int MT, int I>

@@ -48,7 +48,7 @@ def decode_inner(trellis):
 
 def linear_emul(trellis, suh, svh, x, summands=False):
     """the Linear in the device arithmetic; summands: each weight multiplied as its two float16 summands (the CUDA decode
-    kernels), False: as the rounded float16 value (the reference's kernels, the CUDA prefill kernels)"""
+    kernels' opt-in product mode), False: as the rounded float16 value (the reference's kernels, the CUDA kernels by default)"""
     lib().exl3_emul_summands(int(bool(summands)))
     tr, su, sv = _u16(trellis), _u16(np.asarray(suh, np.float16)), _u16(np.asarray(svh, np.float16))
     x = np.ascontiguousarray(x, np.float32).reshape(-1, tr.shape[0] * 16)

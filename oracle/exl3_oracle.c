@@ -46,9 +46,9 @@ static void parallel_for(int n, body_fn body, void *ctx) {
 static float g_lut[1 << 15];      /* the weight as the format defines it: fp16(lo + hi) */
 static float g_lut_sum[1 << 15];  /* lo + hi unrounded: what a product accumulates that takes lo and hi as separate terms */
 static int g_lut_ready = 0;
-/* which of the two the *_emul functions multiply with: 1 = the CUDA decode kernels (summands), 0 = the reference's
- * kernels and the CUDA prefill kernels (rounded value) */
-static int g_summands = 1;
+/* which of the two the *_emul functions multiply with: 0 = the rounded value (the reference's kernels and every CUDA
+ * kernel by default), 1 = the summands (the CUDA decode kernels' opt-in product mode) */
+static int g_summands = 0;
 void exl3_emul_summands(int on) { g_summands = on ? 1 : 0; }
 
 static float half_bits_to_float(uint16_t h) {

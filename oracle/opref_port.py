@@ -128,8 +128,8 @@ def exl3_linear_exact(x, trellis, suh, svh):
 
 def exl3_linear_emul(x, trellis, suh, svh, inner=None, summands=False):
     """y_emul of tests/trunk6/check_kernels.py:93-99: device arithmetic, float64 after the float16 operand. summands:
-    every weight enters the product as its two float16 summands (the CUDA decode kernels: no half add, hence no rounding
-    of the sum); False: as the rounded float16 value (the reference's kernels, the CUDA prefill kernels)"""
+    every weight enters the product as its two float16 summands (the CUDA decode kernels' opt-in mode: no half add, hence
+    no rounding of the sum); False: as the rounded float16 value (the reference's kernels, the CUDA kernels by default)"""
     inner = X.decode_inner(trellis, rounded=not summands).astype(np.float64) if inner is None else np.asarray(inner, np.float64)
     raw = exl3_prep_emul(x, suh).astype(np.float64) @ inner
     m = raw.shape[-1]
