@@ -354,9 +354,25 @@ def prefill_ep_figure(eng, dev, rank, world, n_total):
 
     a2a = timed(lambda: par.prefill_a2a(xp, out=yp))
     gat = timed(lambda: par.forward(xp, out=yp, prefill=True))
+    # one more all-to-all call with a device synchronisation after every stage: where the time goes on each rank
+    marks = [("start", time.perf_counter())]
+
+    def mark(name):
+        torch.cuda.synchronize()
+        marks.append((name, time.perf_counter()))
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    marks[0] = ("start", time.perf_counter())
+    par.prefill_a2a(xp, out=yp, mark=mark)
+    mine = {"pairs_received": par.last_pairs_received}
+    mine.update({nm: round((t - marks[i][1]) * 1e3, 3) for i, (nm, t) in enumerate(marks[1:])})
+    stages = [None] * world
+    dist.all_gather_object(stages, mine)
     blk.free()
     return {"tokens_total": n * world, "tokens_per_rank": n, "all_to_all_ms": a2a, "all_to_all_tok_per_s": n * world / a2a * 1e3,
             "allgather_reduce_ms": gat, "routing": "Zipf(1.1) bias on the router logits",
+            "all_to_all_stage_ms_per_rank": stages,
             "note": "the single-GPU time of the same token count is extra.prefill.ms of the N = 1 line"}
 
 

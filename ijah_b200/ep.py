@@ -132,23 +132,34 @@ class ExpertParallelMoe:
             dist.reduce_scatter_tensor(y, y_part, group=self.group)
         return y
 
-    def prefill_a2a(self, x, out=None):
+    def prefill_a2a(self, x, out=None, mark=None):
         """x [n, H] float32, the rank's own tokens (any count per rank, zero excluded) -> y [n, H]. The block needs
-        prefill_home, pairs_by_owner, gather_rows, prefill_routed, combine_slots and k (engine.MoeBlock has them)."""
+        prefill_home, pairs_by_owner, gather_rows, prefill_routed, combine_slots and k (engine.MoeBlock has them).
+        mark(name), if given, is called after each stage (a timing hook: bench.py synchronises in it)."""
         b, N, k = self.block, self.world, self.block.k
+        mark = mark or (lambda name: None)
         n, H = x.shape
         x = x.contiguous()
         y_sh, route = b.prefill_home(x)                      # routing + shared expert of the own tokens
+        mark("home")
         tok, send_r, pos, counts = b.pairs_by_owner(route, N)  # pairs grouped by owner, (token, slot) order inside a group
+        send_x = b.gather_rows(x, tok)
+        mark("pack")
         got = torch.empty_like(counts)
         dist.all_to_all_single(got, counts, group=self.group)
         send_n, recv_n = counts.tolist(), got.tolist()       # the one host synchronisation of the call
-        send_x = b.gather_rows(x, tok)
+        mark("counts")
         recv_x = torch.empty((sum(recv_n), H), dtype=torch.float32, device=x.device)
         recv_r = torch.empty((sum(recv_n), 2), dtype=torch.int32, device=x.device)
         dist.all_to_all_single(recv_x, send_x, recv_n, send_n, group=self.group)
         dist.all_to_all_single(recv_r, send_r, recv_n, send_n, group=self.group)
+        mark("dispatch")
         y_pairs = b.prefill_routed(recv_x, recv_r)           # this rank's experts on everybody's pairs
+        mark("owner")
         back = torch.empty((n * k, H), dtype=torch.float32, device=x.device)
         dist.all_to_all_single(back, y_pairs, send_n, recv_n, group=self.group)
-        return b.combine_slots(back, pos, y_sh, out=out)     # slots in slot order, the shared term last
+        mark("return")
+        y = b.combine_slots(back, pos, y_sh, out=out)        # slots in slot order, the shared term last
+        mark("combine")
+        self.last_pairs_received = sum(recv_n)
+        return y
