@@ -167,3 +167,14 @@ def test_prefill_all_to_all_pieces_reproduce_the_block_bit_for_bit(eng):
     # an object asked for a pair whose expert it does not hold contributes nothing for it
     odd = torch.stack((torch.full((5,), 40, dtype=torch.int32, device="cuda"), route[:5, k]), 1).contiguous()
     assert float(blks[0].prefill_routed(x[:5].contiguous(), odd).abs().max()) == 0.0
+    # more pairs than one call takes (65535): the wrapper cuts them into calls; rows do not depend on their neighbours
+    big = 70000
+    in0 = torch.nonzero((ids >= 0) & (ids < 16)).reshape(-1)          # pairs of the first object's experts
+    sel = in0[torch.arange(big, device="cuda") % in0.numel()]
+    xb = x[sel // k].contiguous()
+    rb = torch.stack((ids[sel], route[:, k:].reshape(-1)[sel]), 1).contiguous()
+    yb = blks[0].prefill_routed(xb, rb)
+    assert torch.equal(yb[:200], blks[0].prefill_routed(xb[:200].contiguous(), rb[:200].contiguous()))
+    assert torch.equal(yb[-200:], blks[0].prefill_routed(xb[-200:].contiguous(), rb[-200:].contiguous()))
+    assert torch.equal(yb[:in0.numel()], back[in0])
+    assert eng.lib.ne_device_wait_status() == 0
