@@ -57,13 +57,17 @@ void launch_rms_add(float *x, const float *add, float *xn, const uint16_t *w_bf1
 }
 
 // =============================================================================================== attention stand-in
-// partial: one CTA per (block of 64 cached positions, KV head). K and V of the block are staged once in shared memory
-// and used for every query vector of the head group (rows x heads / kv_heads of them), 16 at a time; two groups of four
-// warps take alternate tiles of 16 query vectors (each group with its own P buffer, reductions and named barrier):
-//   S = Q K^T (warp w of the group: positions 16 w .. 16 w + 15), block max and sum over the four warps, P = exp(S - max)
-//   as fp16, O = P V (warp w: a quarter of the head dimension).
-// Per (query vector, block) it leaves max, sum and the unnormalised O; the merge kernel combines the blocks.
-constexpr int AT_PB = 64;  // positions per block
+// partial: one CTA per (block of PB = 64, 128 or 256 cached positions, KV head). K and V of the block are staged once in
+// shared memory and used for every query vector of the head group (rows x heads / kv_heads of them), 16 at a time; two
+// groups of four warps take alternate tiles of 16 query vectors (each group with its own P buffer, reductions and named
+// barrier):
+//   S = Q K^T (warp w of the group: positions w PB/4 .. (w + 1) PB/4 - 1), block max and sum over the four warps,
+//   P = exp(S - max) as fp16, O = P V (warp w: a quarter of the head dimension).
+// Per (query vector, block) it leaves max, sum and the unnormalised O; the merge kernel combines the blocks. The launcher
+// takes the largest block that divides the cache length, fits shared memory and still fills the GPU: the partial results
+// (one [head dim + 2] float record per query vector and block) are as many bytes as the K / V cache itself at 64 positions
+// per block and 8 rows, a quarter of that at 256.
+constexpr int AT_PB_MIN = 64;  // smallest block: the cache length is a multiple of it
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -75,15 +79,17 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
 constexpr int AT_QCAP = 64;  // query vectors staged at a time (fp16, scaled)
 
 constexpr int AT_THREADS = 256;
-template <int HD>
+template <int HD, int PB>
 __global__ void __launch_bounds__(AT_THREADS) attn_partial_kernel(const float *__restrict__ q, const __half *__restrict__ kc, const __half *__restrict__ vc, int rows,
                                                            int heads, int kv_heads, int nsplit, float *__restrict__ part, float *__restrict__ ml) {
   constexpr int LD = HD + 8;          // padded row length in halfs (ldmatrix rows on distinct banks)
-  constexpr int LDP = AT_PB + 8;
+  constexpr int LDP = PB + 8;
+  constexpr int PW = PB / 4;   // positions per warp of a group
+  constexpr int PT = PW / 16;  // 16-position tiles per warp
   extern __shared__ __align__(16) unsigned char at_smem[];
   __half *Ks = reinterpret_cast<__half *>(at_smem);
-  __half *Vs = Ks + AT_PB * LD;
-  __half *Qs = Vs + AT_PB * LD;
+  __half *Vs = Ks + PB * LD;
+  __half *Qs = Vs + PB * LD;
   const int grp = threadIdx.x >> 7;  // warp group: tiles grp, grp + 2, ...
   __half *Ps = Qs + AT_QCAP * LD + grp * 16 * LDP;
   float *red = reinterpret_cast<float *>(Qs + AT_QCAP * LD + 2 * 16 * LDP) + grp * 128;  // [2][4][16]: per-warp max, per-warp sum
@@ -94,11 +100,11 @@ __global__ void __launch_bounds__(AT_THREADS) attn_partial_kernel(const float *_
   // preceding kernel, so the copies overlap its tail)
   {
     const size_t rstride = (size_t)kv_heads * HD;
-    const __half *ksrc = kc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
-    const __half *vsrc = vc + ((size_t)split * AT_PB) * rstride + (size_t)kvh * HD;
+    const __half *ksrc = kc + ((size_t)split * PB) * rstride + (size_t)kvh * HD;
+    const __half *vsrc = vc + ((size_t)split * PB) * rstride + (size_t)kvh * HD;
     const uint32_t Kd = smem_u32(Ks), Vd = smem_u32(Vs);
 #pragma unroll 4
-    for (int i = threadIdx.x; i < AT_PB * (HD / 8); i += AT_THREADS) {
+    for (int i = threadIdx.x; i < PB * (HD / 8); i += AT_THREADS) {
       const int p = i / (HD / 8), c = i % (HD / 8);
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(Kd + (uint32_t)((p * LD + c * 8) * 2)), "l"(ksrc + p * rstride + c * 8) : "memory");
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(Vd + (uint32_t)((p * LD + c * 8) * 2)), "l"(vsrc + p * rstride + c * 8) : "memory");
@@ -132,19 +138,32 @@ __global__ void __launch_bounds__(AT_THREADS) attn_partial_kernel(const float *_
     __syncthreads();
     for (int qt = grp; qt * 16 < min(AT_QCAP, NQ - qc); qt += 2) {
       const uint32_t Qa = Qa0 + (uint32_t)(qt * 16 * LD * 2);
-      // ---- S = Q K^T for this warp's 16 positions
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      // ---- S = Q K^T for this warp's PW positions
+      float s[PT][2][4];
+#pragma unroll
+      for (int pt = 0; pt < PT; pt++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) s[pt][0][j] = s[pt][1][j] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < HD / 16; kk++) {
-        uint32_t a[4], b[4];
+        uint32_t a[4];
         ldsm_x4(a, Qa + (uint32_t)(((lane & 15) * LD + kk * 16 + (lane >> 4) * 8) * 2));
         const int m = lane >> 3;
-        ldsm_x4(b, Ka + (uint32_t)(((warp * 16 + (lane & 7) + (m >> 1) * 8) * LD + kk * 16 + (m & 1) * 8) * 2));
-        mma_16816(s[0], a, b[0], b[1]);
-        mma_16816(s[1], a, b[2], b[3]);
+#pragma unroll
+        for (int pt = 0; pt < PT; pt++) {
+          uint32_t b[4];
+          ldsm_x4(b, Ka + (uint32_t)(((warp * PW + pt * 16 + (lane & 7) + (m >> 1) * 8) * LD + kk * 16 + (m & 1) * 8) * 2));
+          mma_16816(s[pt][0], a, b[0], b[1]);
+          mma_16816(s[pt][1], a, b[2], b[3]);
+        }
       }
       // ---- block max and sum per query row (rows g and g + 8 of the tile)
-      float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])), mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int pt = 0; pt < PT; pt++) {
+        mx0 = fmaxf(mx0, fmaxf(fmaxf(s[pt][0][0], s[pt][0][1]), fmaxf(s[pt][1][0], s[pt][1][1])));
+        mx1 = fmaxf(mx1, fmaxf(fmaxf(s[pt][0][2], s[pt][0][3]), fmaxf(s[pt][1][2], s[pt][1][3])));
+      }
 #pragma unroll
       for (int o = 1; o <= 2; o <<= 1) {
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
@@ -158,14 +177,17 @@ __global__ void __launch_bounds__(AT_THREADS) attn_partial_kernel(const float *_
       for (int w = 1; w < 4; w++) { m0 = fmaxf(m0, red[w * 16 + g]); m1 = fmaxf(m1, red[w * 16 + g + 8]); }
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-      for (int nt = 0; nt < 2; nt++) {
-        const float p0 = __expf(s[nt][0] - m0), p1 = __expf(s[nt][1] - m0), p2 = __expf(s[nt][2] - m1), p3 = __expf(s[nt][3] - m1);
-        const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-        // the sums use the rounded values the tensor core will multiply with
-        l0 += __low2float(h01) + __high2float(h01);
-        l1 += __low2float(h23) + __high2float(h23);
-        *reinterpret_cast<__half2 *>(Ps + g * LDP + warp * 16 + nt * 8 + 2 * qq) = h01;
-        *reinterpret_cast<__half2 *>(Ps + (g + 8) * LDP + warp * 16 + nt * 8 + 2 * qq) = h23;
+      for (int pt = 0; pt < PT; pt++) {
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          const float p0 = __expf(s[pt][nt][0] - m0), p1 = __expf(s[pt][nt][1] - m0), p2 = __expf(s[pt][nt][2] - m1), p3 = __expf(s[pt][nt][3] - m1);
+          const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+          // the sums use the rounded values the tensor core will multiply with
+          l0 += __low2float(h01) + __high2float(h01);
+          l1 += __low2float(h23) + __high2float(h23);
+          *reinterpret_cast<__half2 *>(Ps + g * LDP + warp * PW + pt * 16 + nt * 8 + 2 * qq) = h01;
+          *reinterpret_cast<__half2 *>(Ps + (g + 8) * LDP + warp * PW + pt * 16 + nt * 8 + 2 * qq) = h23;
+        }
       }
 #pragma unroll
       for (int o = 1; o <= 2; o <<= 1) {
@@ -182,7 +204,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_partial_kernel(const float *_
 #pragma unroll
         for (int j = 0; j < 4; j++) o_acc[n][j] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < AT_PB / 16; ks++) {
+      for (int ks = 0; ks < PB / 16; ks++) {
         uint32_t a[4];
         ldsm_x4(a, Pa + (uint32_t)(((lane & 15) * LDP + ks * 16 + (lane >> 4) * 8) * 2));
 #pragma unroll
@@ -294,30 +316,50 @@ __global__ void __launch_bounds__(AT_MT) attn_merge_kernel(const float *__restri
 }
 
 size_t attn_scratch_bytes(int rows, int heads, int hd, int T) {
-  const size_t nsplit = T / AT_PB;
+  const size_t nsplit = T / AT_PB_MIN;  // the smallest block = the most partial results
   return (size_t)rows * heads * nsplit * (hd + 2) * 4 + 256;
 }
 
-template <int HD>
+static size_t attn_smem_bytes(int hd, int pb) { return (size_t)(2 * pb * (hd + 8) + AT_QCAP * (hd + 8) + 2 * 16 * (pb + 8)) * 2 + 2 * 128 * 4; }
+
+// positions per block: the largest of 256, 128, 64 that divides the cache length, fits shared memory and leaves at least
+// 120 CTAs (most of the GPU's SMs) unless a smaller block does not either
+static int attn_block(int T, int hd, int kv_heads) {
+  for (int pb = 256; pb > AT_PB_MIN; pb >>= 1)
+    if (T % pb == 0 && attn_smem_bytes(hd, pb) <= 200 * 1024 && (T / pb) * kv_heads >= 120) return pb;
+  return AT_PB_MIN;
+}
+
+template <int HD, int PB>
 static void launch_attn_partial(const float *q, const __half *kc, const __half *vc, int rows, int heads, int kv_heads, int nsplit, float *part, float *ml,
                                 cudaStream_t st) {
-  const size_t smem = (size_t)(2 * AT_PB * (HD + 8) + AT_QCAP * (HD + 8) + 2 * 16 * (AT_PB + 8)) * 2 + 2 * 128 * 4;
-  IJ_CUDA(cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  launch_pdl(attn_partial_kernel<HD>, dim3(nsplit, kv_heads), dim3(AT_THREADS), smem, st, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml);
+  const size_t smem = attn_smem_bytes(HD, PB);
+  IJ_CUDA(cudaFuncSetAttribute(attn_partial_kernel<HD, PB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  launch_pdl(attn_partial_kernel<HD, PB>, dim3(nsplit, kv_heads), dim3(AT_THREADS), smem, st, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml);
+}
+template <int HD>
+static void launch_attn_partial_pb(int pb, const float *q, const __half *kc, const __half *vc, int rows, int heads, int kv_heads, int nsplit, float *part,
+                                   float *ml, cudaStream_t st) {
+  if constexpr (HD <= 128) {
+    if (pb == 256) return launch_attn_partial<HD, 256>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st);
+  }
+  if (pb == 128) return launch_attn_partial<HD, 128>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st);
+  IJ_CHECK(pb == 64, "attention stand-in: block of %d positions", pb);
+  launch_attn_partial<HD, 64>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st);
 }
 
 void launch_attn_standin(const float *q, const float *knew, const float *vnew, const __half *kc, const __half *vc, int rows, int heads, int kv_heads,
                          int hd, int T, float *out, void *scratch, cudaStream_t st) {
-  IJ_CHECK(T % AT_PB == 0 && T >= AT_PB && T / AT_PB <= AT_MAXSPLIT, "attention stand-in: cache length %d must be a multiple of %d, at most %d", T, AT_PB,
-           AT_PB * AT_MAXSPLIT);
+  IJ_CHECK(T % AT_PB_MIN == 0 && T >= AT_PB_MIN && T / AT_PB_MIN <= AT_MAXSPLIT, "attention stand-in: cache length %d must be a multiple of %d, at most %d",
+           T, AT_PB_MIN, AT_PB_MIN * AT_MAXSPLIT);
   IJ_CHECK(heads % kv_heads == 0 && (hd == 64 || hd == 128 || hd == 256), "attention stand-in: heads %d / %d, head dim %d not supported", heads, kv_heads, hd);
-  const int nsplit = T / AT_PB;
+  const int pb = attn_block(T, hd, kv_heads), nsplit = T / pb;
   float *part = (float *)scratch;
   float *ml = part + (size_t)rows * heads * nsplit * hd;
   switch (hd) {
-    case 64: launch_attn_partial<64>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
-    case 128: launch_attn_partial<128>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
-    default: launch_attn_partial<256>(q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
+    case 64: launch_attn_partial_pb<64>(pb, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
+    case 128: launch_attn_partial_pb<128>(pb, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
+    default: launch_attn_partial_pb<256>(pb, q, kc, vc, rows, heads, kv_heads, nsplit, part, ml, st); break;
   }
   launch_pdl(attn_merge_kernel, dim3(rows * heads), dim3(AT_MT), 0, st, q, knew, vnew, (const float *)part, (const float *)ml, rows, heads, kv_heads, hd,
              nsplit, out);

@@ -14,8 +14,9 @@ pytestmark = pytest.mark.gpu
 CFG = dict(layers=3, hidden=512, inter=256, experts=32, top_k=4, heads=4, kv_heads=2, head_dim=64, vocab=2048)
 
 
-def small_model_tensors(rng, fmt="bf16"):
+def small_model_tensors(rng, fmt="bf16", kv_heads=None):
     t = {}
+    kvh = kv_heads or CFG["kv_heads"]
     H, V = CFG["hidden"], CFG["vocab"]
     if fmt in ("q8", "q8all"):  # 8-bit affine embedding and head, the format of the reference's packs
         for name, std in (("language_model.model.embed_tokens", 1.0), ("language_model.lm_head", 0.1)):
@@ -31,9 +32,9 @@ def small_model_tensors(rng, fmt="bf16"):
                 del t[name]
             t.update(packgen.shared_expert_q8(rng, layer=l, hidden=H, inter=CFG["inter"], group=64 if l else 32))
             t.update(packgen.trunk_layer_q8(rng, layer=l, hidden=H, q_out=CFG["heads"] * CFG["head_dim"],
-                                            kv_out=CFG["kv_heads"] * CFG["head_dim"], group=64 if l else 128))
+                                            kv_out=kvh * CFG["head_dim"], group=64 if l else 128))
             continue
-        t.update(packgen.trunk_layer(rng, layer=l, hidden=H, q_out=CFG["heads"] * CFG["head_dim"], kv_out=CFG["kv_heads"] * CFG["head_dim"],
+        t.update(packgen.trunk_layer(rng, layer=l, hidden=H, q_out=CFG["heads"] * CFG["head_dim"], kv_out=kvh * CFG["head_dim"],
                                      K=8 if l == 2 else 6))
     return t
 
@@ -78,17 +79,18 @@ def eng():
     return E.Engine()
 
 
-@pytest.mark.parametrize("fmt", ["bf16", "q8", "q8all"])
-def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
+# (weight format, cached positions, KV heads): the long caches make the attention stand-in take its 128- and 256-position blocks
+@pytest.mark.parametrize("fmt,tmax,kvh", [("bf16", 128, 2), ("q8", 128, 2), ("q8all", 128, 2), ("bf16", 8192, 2), ("q8", 8192, 4)])
+def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt, tmax, kvh):
     rng = np.random.default_rng(2025)
-    t = small_model_tensors(rng, fmt)
-    cfg = {"num_hidden_layers": CFG["layers"], "num_attention_heads": CFG["heads"], "num_key_value_heads": CFG["kv_heads"],
+    t = small_model_tensors(rng, fmt, kvh)
+    cfg = {"num_hidden_layers": CFG["layers"], "num_attention_heads": CFG["heads"], "num_key_value_heads": kvh,
            "head_dim": CFG["head_dim"], "num_experts_per_tok": CFG["top_k"], "vocab_size": CFG["vocab"]}
     packgen.write_pack(tmp_path / "model", t, cfg, shards=4, misalign=2)
     p = eng.pack_open(tmp_path / "model")
-    m = eng.fn_model(p, tmax=128, max_rows=8)
+    m = eng.fn_model(p, tmax=tmax, max_rows=8)
     p.close()  # the model keeps the pack alive
-    assert m.desc["layers"] == 3 and m.desc["kv_positions"] == 128 and m.desc["k_trunk"] == (8 if fmt == "q8all" else 6)
+    assert m.desc["layers"] == 3 and m.desc["kv_positions"] == tmax and m.desc["k_trunk"] == (8 if fmt == "q8all" else 6)
     tokens = np.array([5, 77, 1999, 0, 1024], np.int32)
     nxt, logits, ms = m.step_rows(tokens, want_logits=True)
     assert eng.lib.ne_device_wait_status() == 0
@@ -96,7 +98,7 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     # CPU restatement of the same stack on the same weights and the KV cache the library generated
     layers = []
     for l in range(CFG["layers"]):
-        kv = (128, CFG["kv_heads"], CFG["head_dim"])
+        kv = (tmax, kvh, CFG["head_dim"])
         if fmt == "q8all":
             proj = {n: affine(t, f"{packgen.PFX}{l}.self_attn.{n}_proj") for n in ("q", "k", "v", "o")}
         else:
@@ -107,7 +109,7 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
                            vc=m.read("kv_v", l).reshape(kv)))
     q8 = (lambda n: tuple(t[n + s][1] for s in (".weight", ".scales", ".biases"))) if fmt != "bf16" else (lambda n: None)
     want = S.stack_logits(tokens, t["language_model.model.embed_tokens.weight"][1], t["language_model.lm_head.weight"][1], layers,
-                          CFG["heads"], CFG["kv_heads"], CFG["head_dim"], CFG["top_k"], embed_q8=q8("language_model.model.embed_tokens"),
+                          CFG["heads"], kvh, CFG["head_dim"], CFG["top_k"], embed_q8=q8("language_model.model.embed_tokens"),
                           head_q8=q8("language_model.lm_head"))
     kl = S.kl(want, logits)
     assert kl.max() < 1e-4, kl
@@ -121,7 +123,7 @@ def test_stack_logits_match_the_operator_reference(eng, tmp_path, fmt):
     assert abs(lp1 - (lref[n1] - np.log(np.exp(lref).sum()))) < 1e-2
     info = m.info()
     per_layer = 18 if fmt == "q8all" else 16  # four 8-bit Linears instead of two 3-kernel chains; + the shared expert's 4
-    assert info["launches_full"] == 1 + CFG["layers"] * per_layer + 1 + (4 if fmt == "bf16" else 3) and info["T"] == 128
+    assert info["launches_full"] == 1 + CFG["layers"] * per_layer + 1 + (4 if fmt == "bf16" else 3) and info["T"] == tmax
     a, b, c = m.time(reps=3)
     assert 0 < b <= a and c > 0
     m.free()
