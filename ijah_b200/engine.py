@@ -815,6 +815,8 @@ class MoeBlock:
         """(send_token int32 [n k], send_route int32 [n k, 2], pos int32 [n, k], counts int64 [world]) of a route array:
         its pairs in owner-rank order (ne_ep_pairs_by_owner)"""
         torch = _torch()
+        if self.E % world:
+            raise EngineError(f"pairs_by_owner: {self.E} experts do not split evenly over {world} ranks")
         n, k, dev = route.shape[0], self.k, route.device
         tok = torch.empty(n * k, dtype=torch.int32, device=dev)
         sr = torch.empty((n * k, 2), dtype=torch.int32, device=dev)

@@ -184,7 +184,8 @@ NE_API int ne_moe_prefill_ep(ne_moe *m, const float *x_all_dev, int n_all, int o
  *                                  y_shared [n][hidden] = sigmoid(x . w_sg) * shared(x), route_out [n][2 * top_k] (ids, f32 weights)
  *           ne_ep_pairs_by_owner   stable counting sort of the n * top_k pairs by owner rank (id / experts_per_rank): packed row
  *                                  -> token (send_token) and (id, weight bits) (send_route), pair -> packed row (pos), pairs per
- *                                  rank (counts, int64: the split sizes of the exchange)
+ *                                  rank (counts, int64: the split sizes of the exchange); experts_per_rank * world must
+ *                                  cover every expert id of the route array
  *           ne_rows_gather         dst[i] = src[index[i]]: packs the pairs' activation rows in that order
  *   owner:  ne_moe_prefill_routed  n_pairs received pairs, route_pairs [n_pairs][2] = (global expert id inside this object's
  *                                  slice, f32 weight bits): y_pairs[i] = weight_i * expert_i(x_pairs[i]) through the grouped
